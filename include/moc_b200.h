@@ -1,0 +1,196 @@
+/* moc_b200 -- C ABI of the B200 (sm_100a) Mixture-of-Chapters memory cross-attention kernels.
+ *
+ * Conventions
+ *   - every pointer named d_* or documented "device" is a CUDA device pointer owned by the caller;
+ *     the library allocates nothing unless a function says so;
+ *   - `stream` is a cudaStream_t passed as void*; every call only enqueues work on it;
+ *   - return value: MOC_OK or a negative MOC_ERR_* (moc_last_error() gives the text); nothing aborts;
+ *   - `status` is a device int32 the kernels raise (atomicMax) to a MOC_DEV_* code when a bounded device
+ *     wait gives up or a chapter id is out of range; the caller clears and reads it;
+ *   - tensors are row-major and contiguous unless a leading dimension is given;
+ *   - dtype codes: MOC_F32 = 0, MOC_BF16 = 1.
+ *
+ * Each entry point names the reference interface (file:line inside the Memory project) it stands in for.
+ */
+#ifndef MOC_B200_H_
+#define MOC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOC_OK 0
+#define MOC_ERR_INVALID (-1)
+#define MOC_ERR_CUDA (-2)
+#define MOC_ERR_UNSUPPORTED (-3)
+
+#define MOC_DEV_OK 0
+#define MOC_DEV_TIMEOUT 1
+#define MOC_DEV_BAD_INDEX 2
+
+#define MOC_F32 0
+#define MOC_BF16 1
+
+#define MOC_NORM_NONE 0
+#define MOC_NORM_RMS 1
+#define MOC_NORM_LAYERNORM 2
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* moc_last_error(void);
+/* ABI version of this library. */
+int moc_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Router.  Replaces ChapterRouter.forward / _compute_losses (memory_transformer/router.py:94-156,
+ * 197-260) and MemoryTransformer._prepend_shared_chapters (memory_transformer/model.py:356-391).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t batch;         /* B */
+  int32_t seq;           /* L */
+  int32_t hidden_dim;    /* d */
+  int32_t num_chapters;  /* C, shared prefix included */
+  int32_t top_k;         /* requested k; k' = min(k, C - num_shared) chapters are returned */
+  int32_t num_shared;    /* S, chapters [0,S) are always on and excluded from selection */
+  float routed_scale;    /* rho, multiplies the routed weights before the joint renormalisation */
+  int32_t h_dtype;       /* dtype of the hidden states */
+} moc_router_shape;
+
+/* Bytes of device scratch moc_router_fwd / moc_router_bwd need. */
+size_t moc_router_workspace_bytes(const moc_router_shape* s);
+
+/* Forward.  Outputs (device): pooled [B,d], logits [B,C], probs [B,C] (fp32);
+ * idx [B,k'] int64 and weights [B,k'] (sorted by weight descending, ties to the lower chapter id);
+ * comb_idx [B,S+k'] int32 and comb_w [B,S+k'] (shared prefix first);
+ * row_stats [B,4] = {logsumexp, masked mass, top-k mass, combined mass};
+ * chapter_stats [2,C] = {selection fraction f, mean squared probability};
+ * losses [4] = {load_balance, auxiliary, z_loss, entropy}, or NULL to skip them. */
+int moc_router_fwd(const moc_router_shape* s, const void* h, const float* w, const float* bias,
+                   float* pooled, float* logits, float* probs, int64_t* idx, float* weights,
+                   int32_t* comb_idx, float* comb_w, float* row_stats, float* chapter_stats, float* losses,
+                   void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* Backward of the above (autograd of router.py:94-156,197-260 and model.py:356-391).
+ * d_weights [B,k'] and d_comb_w [B,S+k'] are the incoming gradients of the two weight outputs (either
+ * may be NULL); d_losses [4] (device) the incoming gradients of the four loss scalars (NULL = none).
+ * Outputs: d_logits [B,C], d_w [C,d], d_bias [C], d_pooled [B,d]; d_h [B,L,d] in h_dtype receives
+ * d_pooled / L on every position (added to its contents when accumulate_dh != 0; NULL to skip). */
+int moc_router_bwd(const moc_router_shape* s, const float* w, const float* pooled, const float* probs,
+                   const int64_t* idx, const float* weights, const float* comb_w, const float* row_stats,
+                   const float* chapter_stats, const float* d_weights, const float* d_comb_w,
+                   const float* d_losses, float* d_logits, float* d_w, float* d_bias, float* d_pooled,
+                   void* d_h, int32_t accumulate_dh, void* workspace, size_t workspace_bytes,
+                   int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Chapter gather.  Replaces ChapteredMemoryBank.get_chapters_batched (memory_bank.py:244-293), the
+ * optional per-row normalisation (model.py:393-432) and the weight multiply (model.py:689-692).
+ * ---------------------------------------------------------------------------------------------- */
+/* out[b, s*T + r, :] = comb_w[b,s] * norm(bank[comb_idx[b,s]*T + r, :]).
+ * comb_w may be NULL (no scaling).  row_stats [B*K*T, 2] = {mean, 1/std or 1/rms} is written when
+ * norm_type != MOC_NORM_NONE (may be NULL otherwise). */
+int moc_gather_rows_fwd(const void* bank, int32_t bank_dtype, int64_t bank_rows, int32_t dim,
+                        int32_t tokens_per_chapter, const int32_t* comb_idx, const float* comb_w,
+                        int32_t batch, int32_t k_sel, int32_t norm_type, float eps, void* out,
+                        int32_t out_dtype, float* row_stats, int32_t* status, void* stream);
+
+/* Groups the B*K (batch, slot) pairs by chapter id, deterministically.
+ * uniq [<=n_pairs] ascending chapter ids, seg_offsets [n_pairs+1], seg_pairs [n_pairs] pair ids grouped by
+ * chapter and ascending inside a group, pair_to_uniq [n_pairs], num_unique [1].  One CTA; n_pairs <= 65536. */
+int moc_chapter_segments(const int32_t* comb_idx, int32_t n_pairs, int32_t num_chapters, int32_t* uniq,
+                         int32_t* seg_offsets, int32_t* seg_pairs, int32_t* pair_to_uniq,
+                         int32_t* num_unique, int32_t* status, void* stream);
+
+/* Backward of moc_gather_rows_fwd: the scatter-add that torch.gather's autograd performs densely
+ * (memory_bank.py:291) done only on touched rows.
+ * d_mem [B*K*T, dim] (fp32 or bf16) is the gradient of the scaled rows.
+ * d_comb_w [B,K] <- sum over the slot's rows of <d_mem, norm(bank row)>.
+ * bank_grad [num_unique*T, dim] fp32, compact: block u holds the gradient of chapter uniq[u]. */
+int moc_gather_rows_bwd(const void* d_mem, int32_t d_mem_dtype, const void* bank, int32_t bank_dtype,
+                        int64_t bank_rows, int32_t dim, int32_t tokens_per_chapter, const int32_t* comb_idx,
+                        const float* comb_w, int32_t batch, int32_t k_sel, int32_t norm_type, float eps,
+                        const float* row_stats, const int32_t* uniq, const int32_t* seg_offsets,
+                        const int32_t* seg_pairs, const int32_t* num_unique, float* d_comb_w,
+                        float* bank_grad, int32_t* status, void* stream);
+
+/* bank_dense[uniq[u]*T + r, :] += bank_grad[u*T + r, :]  (fp32). */
+int moc_scatter_bank_grad(const float* bank_grad, const int32_t* uniq, const int32_t* num_unique,
+                          int32_t max_unique, int32_t tokens_per_chapter, int32_t dim, float* bank_dense,
+                          int64_t bank_rows, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Dense projections.  Replaces the nn.Linear calls of MemoryCrossAttention._compute_qkv and
+ * _project_output (memory_attention.py:241-243, 456) and their autograd.
+ *   C[M,N] (+)= op(A)[M,K] * op(B)[K,N]
+ *   a_kmajor != 0: A is stored [M,K] (lda = row stride), else stored [K,M];
+ *   b_kmajor != 0: B is stored [N,K] (the nn.Linear weight layout), else stored [K,N].
+ * dtype MOC_F32: fp32 FMA kernel, any shape.  dtype MOC_BF16: tcgen05 kernel, bf16 operands, fp32
+ * accumulation in tensor memory, K % 8 == 0 and 16-byte aligned rows; c_dtype is the output type.
+ * row_scale (device, may be NULL): C row m is multiplied by row_scale[m / scale_block_rows].
+ * a_row_blocks (device int32, may be NULL; bf16, a_kmajor only): gather list -- rows
+ * [i*block, (i+1)*block) of op(A) are rows [a_row_blocks[i]*block, ...) of the stored A, block =
+ * a_block_rows (8..128, divides 128): this is the fused chapter gather + Wk/Wv projection, with the
+ * chapter rows fetched by TMA straight from the bank.
+ * accumulate != 0 adds into C (fp32 C only); split_k > 1 splits K over CTAs with fp32 atomics
+ * (fp32 C only, C must be pre-zeroed or accumulate set). */
+typedef struct {
+  int32_t dtype, c_dtype;
+  int32_t m, n, k;
+  int32_t a_kmajor, b_kmajor;
+  int64_t lda, ldb, ldc;
+  int32_t accumulate, split_k;
+  int32_t scale_block_rows;
+  int32_t a_block_rows;
+  int64_t a_stored_rows;   /* rows of the stored A when a gather list is used */
+} moc_gemm_desc;
+
+int moc_gemm(const moc_gemm_desc* g, const void* a, const void* b, void* c, const float* row_scale,
+             const int32_t* a_row_blocks, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Joint-softmax cross attention over the gathered chapters.  Replaces MemoryCrossAttention._attention
+ * (memory_attention.py:298-316) and its autograd.
+ *   q  [B, L, H*D]; kv [B, n_sel, 2*HK*D] = K heads then V heads per row; o [B, L, H*D];
+ *   lse [B, H, L] fp32 (natural log of the softmax denominator of the scaled scores).
+ * dtype MOC_F32: FMA kernels, D in {16,32,64,128}.  dtype MOC_BF16: tcgen05 kernels, D = 64.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t batch, seq, n_sel, num_heads, num_kv_heads, head_dim;
+  float scale;
+  int32_t dtype;
+} moc_attn_shape;
+
+int moc_attn_fwd(const moc_attn_shape* s, const void* q, const void* kv, void* o, float* lse,
+                 int32_t* status, void* stream);
+/* delta is scratch of 2*B*H*L floats.  d_q like q, d_kv like kv. */
+int moc_attn_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
+                 const void* d_o, void* d_q, void* d_kv, float* delta, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Per-token chapter-sparse attention: the contract of memory_cross_attn(q, k, v, block_indices,
+ * block_size, scale) (kernels-final/memory_cross_attn.py:1310-1366, 1387-1603, 1639-1652).
+ *   q [B,TQ,HQ,D], k/v [B,TK,H,D], block_indices [B,TQ,H,S] int32, o [B,TQ,HQ,D], lse [B,TQ,HQ].
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t batch, tq, tk, hq, h, head_dim, n_select, block_size;
+  float scale;
+  int32_t dtype;
+} moc_sparse_attn_shape;
+
+int moc_sparse_attn_fwd(const moc_sparse_attn_shape* s, const void* q, const void* k, const void* v,
+                        const int32_t* block_indices, void* o, float* lse, int32_t* status, void* stream);
+/* d_k / d_v are fp32 [B,TK,H,D] accumulators the call zeroes and fills (atomic adds). */
+int moc_sparse_attn_bwd(const moc_sparse_attn_shape* s, const void* q, const void* k, const void* v,
+                        const int32_t* block_indices, const void* o, const float* lse, const void* d_o,
+                        void* d_q, float* d_k, float* d_v, int32_t* status, void* stream);
+
+/* Element-wise helpers used by the host layer (device pointers, n elements). */
+int moc_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream);
+int moc_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOC_B200_H_ */

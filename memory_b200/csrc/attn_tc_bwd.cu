@@ -1,0 +1,470 @@
+// bf16 joint-softmax cross attention, backward, for sm_100a: two tcgen05 kernels, no atomics.
+//
+//  dQ kernel  (query stationary, CTA = 128 queries of one head): per 64-key tile
+//        S = Q K^T, dP = dO V^T            (SS MMAs into tensor memory)
+//        dS = exp2(S*c - lse*log2e) * (dP - delta) * scale   (one query row per thread)
+//        dQ += dS K                        (A = dS from tensor memory, B = K tile as MN-major operand)
+//  dKV kernel (key stationary, CTA = 128 keys of one KV head): per 64-query tile of every head of
+//  the KV group
+//        S^T = K Q^T, dP^T = V dO^T        (SS MMAs; one key row per thread afterwards)
+//        dV += P^T dO, dK += dS^T Q        (A = P^T / dS^T from tensor memory, written over the
+//                                           columns S^T / dP^T occupied; B = dO / Q tiles MN-major)
+// Recomputing S in both kernels costs 2 extra MMAs per tile pair against a fused 5-MMA backward
+// but keeps every accumulator private to one CTA: results are deterministic.
+#include "moc_common.cuh"
+
+namespace moc {
+namespace {
+
+constexpr int kD = 64;
+constexpr int kThreads = 192;
+constexpr int kStages = 3;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// delta[b,h,l] = <O, dO>; nlse2[b,h,l] = -lse * log2(e)
+__global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                const float* __restrict__ lse, float* __restrict__ delta,
+                                float* __restrict__ nlse2, int B, int L, int H) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long total = static_cast<long long>(B) * L * H;
+  if (w >= total) return;
+  const int h = static_cast<int>(w % H);
+  const long long bl = w / H;
+  const int l = static_cast<int>(bl % L);
+  const int b = static_cast<int>(bl / L);
+  const __nv_bfloat162* po = reinterpret_cast<const __nv_bfloat162*>(o + bl * H * kD + h * kD);
+  const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(d_o + bl * H * kD + h * kD);
+  const float2 a = __bfloat1622float2(po[lane]), g = __bfloat1622float2(pd[lane]);
+  float acc = warp_sum(a.x * g.x + a.y * g.y);
+  if (lane == 0) {
+    const long long idx = (static_cast<long long>(b) * H + h) * L + l;
+    delta[idx] = acc;
+    nlse2[idx] = -lse[idx] * kLog2e;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dQ
+// ------------------------------------------------------------------------------------------------
+constexpr int kQ = 128, kKeys = 64;
+constexpr int kQBytes = kQ * kD * 2;        // 16 KiB (Q and dO tiles)
+constexpr int kKvBytes = kKeys * kD * 2;    // 8 KiB
+constexpr int kDqSmem = 2 * kQBytes + kStages * 2 * kKvBytes + 1024;
+constexpr uint32_t kDqColS = 0, kDqColDP = 64, kDqColDQ = 128, kDqColDS = 192;   // 224 columns used
+
+struct DqParams {
+  __nv_bfloat16* d_q;
+  const float* delta;
+  const float* nlse2;
+  int L, n_sel, H, HK;
+  float scale, scale_log2;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                      const __grid_constant__ CUtensorMap tmap_kv, DqParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t q_bar, kv_full[kStages], kv_empty[kStages], sdp_full, sdp_free, ds_full, dq_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = base;
+  uint8_t* do_s = base + kQBytes;
+  uint8_t* kv_s = base + 2 * kQBytes;
+  const int q0 = blockIdx.x * kQ, h = blockIdx.y, b = blockIdx.z;
+  const int kh = h / (p.H / p.HK);
+  const int n_tiles = (p.n_sel + kKeys - 1) / kKeys;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&q_bar, 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(&sdp_full, 1);
+    mbar_init(&sdp_free, 128);
+    mbar_init(&ds_full, 128);
+    mbar_init(&dq_bar, 1);
+    fence_mbar_init();
+    prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_kv);
+  }
+  if (warp == 5) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); tc_fence_before(); }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&q_bar, 2 * kQBytes);
+      tma_load_2d(q_s, &tmap_q, &q_bar, h * kD, b * p.L + q0);
+      tma_load_2d(do_s, &tmap_do, &q_bar, h * kD, b * p.L + q0);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % kStages;
+        if (!mbar_wait(&kv_empty[s], ((j / kStages) & 1) ^ 1, &abort_flag, p.status)) break;
+        mbar_arrive_expect_tx(&kv_full[s], 2 * kKvBytes);
+        uint8_t* k_s = kv_s + s * 2 * kKvBytes;
+        const int row = b * p.n_sel + j * kKeys;
+        tma_load_2d(k_s, &tmap_kv, &kv_full[s], kh * kD, row);
+        tma_load_2d(k_s + kKvBytes, &tmap_kv, &kv_full[s], p.HK * kD + kh * kD, row);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_kk = umma_idesc_bf16(kQ, kKeys, 0, 0);   // S and dP: both operands K-major
+      const uint32_t idesc_dq = umma_idesc_bf16(kQ, kD, 0, 1);      // dQ: B = K tile, MN-major
+      const uint32_t q_addr = smem_u32(q_s), do_addr = smem_u32(do_s);
+      bool ok = mbar_wait(&q_bar, 0, &abort_flag, p.status);
+      for (int j = 0; j <= n_tiles && ok; ++j) {
+        if (j < n_tiles) {
+          const int s = j % kStages;
+          ok = mbar_wait(&kv_full[s], (j / kStages) & 1, &abort_flag, p.status);
+          if (ok && j > 0) ok = mbar_wait(&sdp_free, (j - 1) & 1, &abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(kv_s + s * 2 * kKvBytes), v_addr = k_addr + kKvBytes;
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk)
+            umma_ss(tmem + kDqColS, umma_desc_sw128(q_addr + kk * 32, 16, 1024),
+                    umma_desc_sw128(k_addr + kk * 32, 16, 1024), idesc_kk, kk > 0 ? 1u : 0u);
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk)
+            umma_ss(tmem + kDqColDP, umma_desc_sw128(do_addr + kk * 32, 16, 1024),
+                    umma_desc_sw128(v_addr + kk * 32, 16, 1024), idesc_kk, kk > 0 ? 1u : 0u);
+          tc_commit(&sdp_full);
+        }
+        if (j > 0) {
+          const int jp = j - 1, s = jp % kStages;
+          ok = mbar_wait(&ds_full, jp & 1, &abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(kv_s + s * 2 * kKvBytes);
+#pragma unroll
+          for (int kk = 0; kk < kKeys / 16; ++kk)
+            umma_ts(tmem + kDqColDQ, tmem + kDqColDS + kk * 8, umma_desc_sw128(k_addr + kk * 2048, 8192, 1024),
+                    idesc_dq, (jp > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(&kv_empty[s]);
+          tc_commit(&dq_bar);
+        }
+      }
+    }
+  } else {
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const int row = warp * 32 + lane;
+    const int l = q0 + row;
+    const long long sidx = (static_cast<long long>(b) * p.H + h) * p.L + (l < p.L ? l : 0);
+    const float nl = p.nlse2[sidx], dl = p.delta[sidx];
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = mbar_wait(&sdp_full, j & 1, &abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int valid = p.n_sel - j * kKeys;
+      uint32_t pk[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tmem + lane_sel + kDqColS + half * 32, rs);
+        tmem_ld32(tmem + lane_sel + kDqColDP + half * 32, rd);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float d0 = ex2(fmaf(__uint_as_float(rs[c]), p.scale_log2, nl)) * (__uint_as_float(rd[c]) - dl) * p.scale;
+          float d1 = ex2(fmaf(__uint_as_float(rs[c + 1]), p.scale_log2, nl)) * (__uint_as_float(rd[c + 1]) - dl) * p.scale;
+          if (half * 32 + c >= valid) d0 = 0.f;
+          if (half * 32 + c + 1 >= valid) d1 = 0.f;
+          pk[half * 16 + c / 2] = pack_bf16x2(d0, d1);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&sdp_free);          // S / dP may be overwritten by the next tile's MMAs
+      if (j > 0) {
+        ok = mbar_wait(&dq_bar, (j - 1) & 1, &abort_flag, p.status);   // previous dS consumed
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      tmem_st32(tmem + lane_sel + kDqColDS, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&ds_full);
+    }
+    if (ok) {
+      ok = mbar_wait(&dq_bar, (n_tiles - 1) & 1, &abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* dst = p.d_q + (static_cast<long long>(b) * p.L + l) * (p.H * kD) + h * kD;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_sel + kDqColDQ + half * 32, r);
+        tmem_wait_ld();
+        if (l < p.L) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * c + 0]), __uint_as_float(r[8 * c + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7]));
+            *reinterpret_cast<uint4*>(dst + half * 32 + c * 8) = v;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (abort_flag) { for (int i = 0; i < 200; ++i) __nanosleep(1000); }
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem, 256); }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dK / dV
+// ------------------------------------------------------------------------------------------------
+constexpr int kKeysB = 128, kQB = 64;
+constexpr int kKBytes = kKeysB * kD * 2;     // 16 KiB (K and V tiles, stationary)
+constexpr int kQTileBytes = kQB * kD * 2;    // 8 KiB (Q and dO tiles, streamed)
+constexpr int kStatBytes = kQB * 4;          // 256 B (nlse2 and delta rows, streamed)
+constexpr int kStageB = 2 * kQTileBytes;      // tile ring stride (keeps every tile 1024-byte aligned)
+constexpr int kStageTx = kStageB + 2 * kStatBytes;
+constexpr int kDkvSmem = 2 * kKBytes + kStages * kStageB + kStages * 2 * kStatBytes + 1024;
+constexpr uint32_t kColST = 0, kColDPT = 64, kColDV = 128, kColDK = 192;   // P^T / dS^T alias the first two
+
+struct DkvParams {
+  __nv_bfloat16* d_kv;
+  const float* delta;
+  const float* nlse2;
+  int L, n_sel, H, HK;
+  float scale, scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                       const __grid_constant__ CUtensorMap tmap_kv, DkvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t k_bar, q_full[kStages], q_empty[kStages], sdp_full, pt_full, acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* k_s = base;
+  uint8_t* v_s = base + kKBytes;
+  uint8_t* ring = base + 2 * kKBytes;
+  uint8_t* stats = ring + kStages * kStageB;
+  const int key0 = blockIdx.x * kKeysB, kh = blockIdx.y, b = blockIdx.z;
+  const int G = p.H / p.HK;
+  const int q_tiles = p.L / kQB;
+  const int n_iter = G * q_tiles;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&k_bar, 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+    mbar_init(&sdp_full, 1);
+    mbar_init(&pt_full, 128);
+    mbar_init(&acc_bar, 1);
+    fence_mbar_init();
+    prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_kv);
+  }
+  if (warp == 5) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); tc_fence_before(); }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&k_bar, 2 * kKBytes);
+      const int row = b * p.n_sel + key0;
+      tma_load_2d(k_s, &tmap_kv, &k_bar, kh * kD, row);
+      tma_load_2d(k_s + kKBytes / 2, &tmap_kv, &k_bar, kh * kD, row + 64);
+      tma_load_2d(v_s, &tmap_kv, &k_bar, p.HK * kD + kh * kD, row);
+      tma_load_2d(v_s + kKBytes / 2, &tmap_kv, &k_bar, p.HK * kD + kh * kD, row + 64);
+      for (int it = 0; it < n_iter; ++it) {
+        const int s = it % kStages;
+        if (!mbar_wait(&q_empty[s], ((it / kStages) & 1) ^ 1, &abort_flag, p.status)) break;
+        const int h = kh * G + it / q_tiles, l0 = (it % q_tiles) * kQB;
+        uint8_t* st = ring + s * kStageB;
+        mbar_arrive_expect_tx(&q_full[s], kStageTx);
+        tma_load_2d(st, &tmap_q, &q_full[s], h * kD, b * p.L + l0);
+        tma_load_2d(st + kQTileBytes, &tmap_do, &q_full[s], h * kD, b * p.L + l0);
+        const long long soff = (static_cast<long long>(b) * p.H + h) * p.L + l0;
+        bulk_load_1d(stats + s * 2 * kStatBytes, p.nlse2 + soff, kStatBytes, &q_full[s]);
+        bulk_load_1d(stats + s * 2 * kStatBytes + kStatBytes, p.delta + soff, kStatBytes, &q_full[s]);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc_bf16(kKeysB, kQB, 0, 0);   // S^T, dP^T
+      const uint32_t idesc_g = umma_idesc_bf16(kKeysB, kD, 0, 1);    // dV, dK: B = dO / Q tile, MN-major
+      const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+      bool ok = mbar_wait(&k_bar, 0, &abort_flag, p.status);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int s = it % kStages;
+        ok = mbar_wait(&q_full[s], (it / kStages) & 1, &abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(ring + s * kStageB), do_addr = q_addr + kQTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk)
+          umma_ss(tmem + kColST, umma_desc_sw128(k_addr + kk * 32, 16, 1024),
+                  umma_desc_sw128(q_addr + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk)
+          umma_ss(tmem + kColDPT, umma_desc_sw128(v_addr + kk * 32, 16, 1024),
+                  umma_desc_sw128(do_addr + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        tc_commit(&sdp_full);
+        ok = mbar_wait(&pt_full, it & 1, &abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kQB / 16; ++kk)
+          umma_ts(tmem + kColDV, tmem + kColST + kk * 8, umma_desc_sw128(do_addr + kk * 2048, 8192, 1024),
+                  idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kQB / 16; ++kk)
+          umma_ts(tmem + kColDK, tmem + kColDPT + kk * 8, umma_desc_sw128(q_addr + kk * 2048, 8192, 1024),
+                  idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&q_empty[s]);
+      }
+      tc_commit(&acc_bar);
+    }
+  } else {
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const int row = warp * 32 + lane;
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int s = it % kStages;
+      ok = mbar_wait(&sdp_full, it & 1, &abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const float* nl = reinterpret_cast<const float*>(stats + s * 2 * kStatBytes);
+      const float* dl = nl + kQB;
+      uint32_t pp[32], pd[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tmem + lane_sel + kColST + half * 32, rs);
+        tmem_ld32(tmem + lane_sel + kColDPT + half * 32, rd);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          const int qi = half * 32 + c;
+          const float p0 = ex2(fmaf(__uint_as_float(rs[c]), p.scale_log2, nl[qi]));
+          const float p1 = ex2(fmaf(__uint_as_float(rs[c + 1]), p.scale_log2, nl[qi + 1]));
+          const float d0 = p0 * (__uint_as_float(rd[c]) - dl[qi]) * p.scale;
+          const float d1 = p1 * (__uint_as_float(rd[c + 1]) - dl[qi + 1]) * p.scale;
+          pp[half * 16 + c / 2] = pack_bf16x2(p0, p1);
+          pd[half * 16 + c / 2] = pack_bf16x2(d0, d1);
+        }
+      }
+      // every fp32 value of this row has been read: overwrite the first 32 columns of each region
+      tmem_st32(tmem + lane_sel + kColST, pp);
+      tmem_st32(tmem + lane_sel + kColDPT, pd);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&pt_full);
+    }
+    if (ok) {
+      ok = mbar_wait(&acc_bar, 0, &abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const int key = key0 + row;
+      __nv_bfloat16* dst = p.d_kv + (static_cast<long long>(b) * p.n_sel + key) * (2 * p.HK * kD) + kh * kD;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {      // 0: dK, 1: dV
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32(tmem + lane_sel + (which ? kColDV : kColDK) + half * 32, r);
+          tmem_wait_ld();
+          if (key < p.n_sel) {
+            __nv_bfloat16* d2 = dst + (which ? p.HK * kD : 0) + half * 32;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * c + 0]), __uint_as_float(r[8 * c + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7]));
+              *reinterpret_cast<uint4*>(d2 + c * 8) = v;
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (abort_flag) { for (int i = 0; i < 200; ++i) __nanosleep(1000); }
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem, 256); }
+}
+
+}  // namespace
+
+int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
+                       const void* d_o, void* d_q, void* d_kv, float* scratch, int32_t* status,
+                       cudaStream_t stream) {
+  MOC_REQUIRE(s->head_dim == kD, "bf16 attention needs head_dim 64");
+  MOC_REQUIRE(s->seq % kQB == 0, "bf16 attention backward needs seq % 64 == 0");
+  MOC_REQUIRE(s->num_heads % s->num_kv_heads == 0, "num_heads must be a multiple of num_kv_heads");
+  const int B = s->batch, L = s->seq, H = s->num_heads, HK = s->num_kv_heads;
+  float* delta = scratch;
+  float* nlse2 = scratch + static_cast<long long>(B) * H * L;
+  {
+    const long long total = static_cast<long long>(B) * L * H;
+    const int blocks = static_cast<int>((total * 32 + 255) / 256);
+    bwd_prep_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(o),
+                                                static_cast<const __nv_bfloat16*>(d_o), lse, delta, nlse2, B, L, H);
+  }
+  CUtensorMap tq128, tdo128, tq64, tdo64, tkv;
+  const uint64_t qrows = static_cast<uint64_t>(B) * L, qcols = static_cast<uint64_t>(H) * kD;
+  const uint64_t kvrows = static_cast<uint64_t>(B) * s->n_sel, kvcols = static_cast<uint64_t>(2 * HK) * kD;
+  int rc;
+  if ((rc = make_tmap_bf16_2d(&tq128, q, qrows, qcols, qcols, kQ, kD)) != MOC_OK) return rc;
+  if ((rc = make_tmap_bf16_2d(&tdo128, d_o, qrows, qcols, qcols, kQ, kD)) != MOC_OK) return rc;
+  if ((rc = make_tmap_bf16_2d(&tq64, q, qrows, qcols, qcols, kQB, kD)) != MOC_OK) return rc;
+  if ((rc = make_tmap_bf16_2d(&tdo64, d_o, qrows, qcols, qcols, kQB, kD)) != MOC_OK) return rc;
+  if ((rc = make_tmap_bf16_2d(&tkv, kv, kvrows, kvcols, kvcols, 64, kD)) != MOC_OK) return rc;
+  MOC_CUDA_OK(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem));
+  MOC_CUDA_OK(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmem));
+  {
+    DqParams p;
+    p.d_q = static_cast<__nv_bfloat16*>(d_q); p.delta = delta; p.nlse2 = nlse2;
+    p.L = L; p.n_sel = s->n_sel; p.H = H; p.HK = HK;
+    p.scale = s->scale; p.scale_log2 = s->scale * kLog2e; p.status = status;
+    dim3 grid(ceil_div(L, kQ), H, B);
+    attn_bwd_dq_tc_kernel<<<grid, kThreads, kDqSmem, stream>>>(tq128, tdo128, tkv, p);
+  }
+  {
+    DkvParams p;
+    p.d_kv = static_cast<__nv_bfloat16*>(d_kv); p.delta = delta; p.nlse2 = nlse2;
+    p.L = L; p.n_sel = s->n_sel; p.H = H; p.HK = HK;
+    p.scale = s->scale; p.scale_log2 = s->scale * kLog2e; p.status = status;
+    dim3 grid(ceil_div(s->n_sel, kKeysB), HK, B);
+    attn_bwd_dkv_tc_kernel<<<grid, kThreads, kDkvSmem, stream>>>(tq64, tdo64, tkv, p);
+  }
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+}  // namespace moc

@@ -1,0 +1,275 @@
+// bf16 joint-softmax cross attention, forward, for sm_100a.
+//
+// One CTA = 128 queries of one (batch, head); it streams the (S+k) gathered chapters as tiles of
+// 64 keys:   S_j = Q K_j^T  (tcgen05.mma, operands in 128-byte-swizzled shared memory filled by TMA,
+// accumulator in tensor memory) -> online softmax by 128 threads that each own one query row
+// (tcgen05.ld, exp2 on the scaled scores, P written back to tensor memory as packed bf16) ->
+// O += P_j V_j (tcgen05.mma with A = P from tensor memory, B = the V tile as an MN-major operand).
+// S is double buffered in tensor memory so the next QK^T runs under the current softmax; two CTAs
+// share an SM (256 TMEM columns and ~81 KiB of shared memory each) so one CTA's exponentials
+// overlap the other's MMAs.  The running maximum is only raised (and O rescaled) when it grows by
+// more than 2^8, which keeps P within bf16 range while skipping almost every rescale.
+#include "moc_common.cuh"
+
+namespace moc {
+namespace {
+
+constexpr int kQ = 128;          // queries per CTA
+constexpr int kKeys = 64;        // keys per tile
+constexpr int kD = 64;           // head dim
+constexpr int kStages = 4;       // K/V ring depth
+constexpr int kThreads = 192;    // 4 softmax warps + TMA warp + MMA warp
+constexpr int kQBytes = kQ * kD * 2;
+constexpr int kTileBytes = kKeys * kD * 2;
+constexpr int kSmemBytes = kQBytes + kStages * 2 * kTileBytes + 1024;
+constexpr int kTmemCols = 256;
+constexpr uint32_t kColS = 0;      // two S buffers: columns [0,64) and [64,128)
+constexpr uint32_t kColO = 128;    // O accumulator: 64 columns
+constexpr uint32_t kColP = 192;    // P as packed bf16: 32 columns
+constexpr float kRescaleThreshold = 8.0f;
+
+struct FwdParams {
+  __nv_bfloat16* o;
+  float* lse;
+  int L, n_sel, H, HK;
+  float scale_log2;   // softmax scale * log2(e)
+  int* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
+                   FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t q_bar, kv_full[kStages], kv_empty[kStages], s_full[2], p_full, pv_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = base;
+  uint8_t* kv_s = base + kQBytes;
+
+  const int q0 = blockIdx.x * kQ;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kh = h / (p.H / p.HK);
+  const int n_tiles = (p.n_sel + kKeys - 1) / kKeys;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&q_bar, 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(&p_full, 128);
+    mbar_init(&pv_bar, 1);
+    fence_mbar_init();
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_kv);
+  }
+  if (warp == 5) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&q_bar, kQBytes);
+      tma_load_2d(q_s, &tmap_q, &q_bar, h * kD, b * p.L + q0);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (j / kStages) & 1;
+        if (!mbar_wait(&kv_empty[s], ph ^ 1, &abort_flag, p.status)) break;
+        mbar_arrive_expect_tx(&kv_full[s], 2 * kTileBytes);
+        uint8_t* k_s = kv_s + s * 2 * kTileBytes;
+        const int row = b * p.n_sel + j * kKeys;
+        tma_load_2d(k_s, &tmap_kv, &kv_full[s], kh * kD, row);
+        tma_load_2d(k_s + kTileBytes, &tmap_kv, &kv_full[s], p.HK * kD + kh * kD, row);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc_bf16(kQ, kKeys, 0, 0);
+      const uint32_t idesc_o = umma_idesc_bf16(kQ, kD, 0, 1);
+      const uint32_t q_addr = smem_u32(q_s);
+      bool ok = mbar_wait(&q_bar, 0, &abort_flag, p.status);
+      for (int j = 0; j <= n_tiles && ok; ++j) {
+        if (j < n_tiles) {
+          const int s = j % kStages;
+          ok = mbar_wait(&kv_full[s], (j / kStages) & 1, &abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(kv_s + s * 2 * kTileBytes);
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk)
+            umma_ss(tmem + kColS + (j & 1) * 64, umma_desc_sw128(q_addr + kk * 32, 16, 1024),
+                    umma_desc_sw128(k_addr + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          tc_commit(&s_full[j & 1]);
+        }
+        if (j > 0) {
+          const int jp = j - 1, s = jp % kStages;
+          ok = mbar_wait(&p_full, jp & 1, &abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t v_addr = smem_u32(kv_s + s * 2 * kTileBytes + kTileBytes);
+#pragma unroll
+          for (int kk = 0; kk < kKeys / 16; ++kk)
+            umma_ts(tmem + kColO, tmem + kColP + kk * 8, umma_desc_sw128(v_addr + kk * 2048, 8192, 1024),
+                    idesc_o, (jp > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(&kv_empty[s]);
+          tc_commit(&pv_bar);
+        }
+      }
+    }
+  } else {
+    // ---------------- softmax: thread <-> query row ----------------
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const int row = warp * 32 + lane;
+    float m_used = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, &abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t s_addr = tmem + lane_sel + kColS + (j & 1) * 64;
+      const int valid = p.n_sel - j * kKeys;   // keys of this tile that exist
+      uint32_t r[32];
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tmem_ld32(s_addr + half * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float v = __uint_as_float(r[c]);
+          tmax = fmaxf(tmax, (half * 32 + c < valid) ? v : -INFINITY);
+        }
+      }
+      const float m_new = fmaxf(m_used, tmax * p.scale_log2);
+      const bool need = (j == 0) || (m_new - m_used > kRescaleThreshold);
+      const bool any_need = __any_sync(0xffffffffu, need);
+      if (j > 0) {
+        ok = mbar_wait(&pv_bar, (j - 1) & 1, &abort_flag, p.status);   // O and P are free again
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (any_need) {
+          const float alpha = need ? ex2(m_used - m_new) : 1.f;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            tmem_ld32(tmem + lane_sel + kColO + half * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+            tmem_st32(tmem + lane_sel + kColO + half * 32, r);
+          }
+          l_sum *= alpha;
+        }
+      }
+      if (need) m_used = m_new;
+      uint32_t pk[32];
+      float psum = 0.f;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tmem_ld32(s_addr + half * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float e0 = ex2(fmaf(__uint_as_float(r[c]), p.scale_log2, -m_used));
+          float e1 = ex2(fmaf(__uint_as_float(r[c + 1]), p.scale_log2, -m_used));
+          if (half * 32 + c >= valid) e0 = 0.f;
+          if (half * 32 + c + 1 >= valid) e1 = 0.f;
+          psum += e0 + e1;
+          pk[half * 16 + c / 2] = pack_bf16x2(e0, e1);
+        }
+      }
+      l_sum += psum;
+      tmem_st32(tmem + lane_sel + kColP, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&p_full);
+    }
+    if (ok) {
+      ok = mbar_wait(&pv_bar, (n_tiles - 1) & 1, &abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = 1.f / l_sum;
+      const int l = q0 + row;
+      __nv_bfloat16* dst = p.o + (static_cast<long long>(b) * p.L + l) * (p.H * kD) + h * kD;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_sel + kColO + half * 32, r);
+        tmem_wait_ld();
+        if (l < p.L) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * c + 0]) * inv, __uint_as_float(r[8 * c + 1]) * inv);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * c + 2]) * inv, __uint_as_float(r[8 * c + 3]) * inv);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * c + 4]) * inv, __uint_as_float(r[8 * c + 5]) * inv);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * c + 6]) * inv, __uint_as_float(r[8 * c + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + half * 32 + c * 8) = v;
+          }
+        }
+      }
+      if (l < p.L)
+        p.lse[(static_cast<long long>(b) * p.H + h) * p.L + l] = (m_used + log2f(l_sum)) * 0.6931471805599453f;
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace
+
+int launch_attn_tc_fwd(const moc_attn_shape* s, const void* q, const void* kv, void* o, float* lse,
+                       int32_t* status, cudaStream_t stream) {
+  MOC_REQUIRE(s->head_dim == kD, "bf16 attention needs head_dim 64");
+  MOC_REQUIRE(s->num_heads % s->num_kv_heads == 0, "num_heads must be a multiple of num_kv_heads");
+  MOC_REQUIRE((reinterpret_cast<uintptr_t>(o) & 15) == 0, "output must be 16-byte aligned");
+  CUtensorMap tq, tkv;
+  int rc = make_tmap_bf16_2d(&tq, q, static_cast<uint64_t>(s->batch) * s->seq,
+                             static_cast<uint64_t>(s->num_heads) * kD, static_cast<uint64_t>(s->num_heads) * kD,
+                             kQ, kD);
+  if (rc != MOC_OK) return rc;
+  rc = make_tmap_bf16_2d(&tkv, kv, static_cast<uint64_t>(s->batch) * s->n_sel,
+                         static_cast<uint64_t>(2 * s->num_kv_heads) * kD,
+                         static_cast<uint64_t>(2 * s->num_kv_heads) * kD, kKeys, kD);
+  if (rc != MOC_OK) return rc;
+  MOC_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  FwdParams p;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.lse = lse;
+  p.L = s->seq; p.n_sel = s->n_sel; p.H = s->num_heads; p.HK = s->num_kv_heads;
+  p.scale_log2 = s->scale * 1.4426950408889634f;
+  p.status = status;
+  dim3 grid(ceil_div(s->seq, kQ), s->num_heads, s->batch);
+  attn_fwd_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tkv, p);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+}  // namespace moc

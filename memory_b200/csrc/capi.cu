@@ -1,0 +1,79 @@
+// extern "C" dispatch of the projection and attention entry points onto the fp32 (FMA) and bf16
+// (tcgen05) kernels.  There is no CPU path: a dtype / shape the kernels do not cover is an error.
+#include "moc_common.cuh"
+
+namespace moc {
+int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c, const float* row_scale,
+                   const int32_t* a_row_blocks, int32_t* status, cudaStream_t stream);
+int launch_sgemm(const moc_gemm_desc* g, const float* a, const float* b, float* c, const float* row_scale,
+                 cudaStream_t stream);
+int launch_delta(int dtype, const void* o, const void* d_o, float* delta, int B, int L, int H, int D,
+                 cudaStream_t stream);
+int launch_attn_f32_fwd(const moc_attn_shape* s, const float* q, const float* kv, float* o, float* lse,
+                        cudaStream_t stream);
+int launch_attn_f32_bwd(const moc_attn_shape* s, const float* q, const float* kv, const float* d_o,
+                        const float* lse, const float* delta, float* d_q, float* d_kv, cudaStream_t stream);
+int launch_attn_tc_fwd(const moc_attn_shape* s, const void* q, const void* kv, void* o, float* lse,
+                       int32_t* status, cudaStream_t stream);
+int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
+                       const void* d_o, void* d_q, void* d_kv, float* scratch, int32_t* status,
+                       cudaStream_t stream);
+}  // namespace moc
+
+using namespace moc;
+
+extern "C" int moc_gemm(const moc_gemm_desc* g, const void* a, const void* b, void* c, const float* row_scale,
+                        const int32_t* a_row_blocks, int32_t* status, void* stream_) {
+  MOC_REQUIRE(g && a && b && c && status, "NULL projection argument");
+  MOC_REQUIRE(g->m > 0 && g->n > 0 && g->k > 0, "empty projection");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (g->dtype == MOC_F32) {
+    MOC_REQUIRE(a_row_blocks == nullptr, "the fp32 projection takes gathered rows, not a gather list");
+    return launch_sgemm(g, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c),
+                        row_scale, stream);
+  }
+  if (g->dtype == MOC_BF16) return launch_gemm_tc(g, a, b, c, row_scale, a_row_blocks, status, stream);
+  set_last_error("dtype", "unknown dtype");
+  return MOC_ERR_INVALID;
+}
+
+static int check_attn(const moc_attn_shape* s) {
+  MOC_REQUIRE(s != nullptr, "shape is NULL");
+  MOC_REQUIRE(s->batch > 0 && s->seq > 0 && s->n_sel > 0, "empty attention problem");
+  MOC_REQUIRE(s->num_heads > 0 && s->num_kv_heads > 0 && s->num_heads % s->num_kv_heads == 0,
+              "num_heads must be a positive multiple of num_kv_heads");
+  return MOC_OK;
+}
+
+extern "C" int moc_attn_fwd(const moc_attn_shape* s, const void* q, const void* kv, void* o, float* lse,
+                            int32_t* status, void* stream_) {
+  int rc = check_attn(s);
+  if (rc != MOC_OK) return rc;
+  MOC_REQUIRE(q && kv && o && lse && status, "NULL attention buffer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (s->dtype == MOC_F32)
+    return launch_attn_f32_fwd(s, static_cast<const float*>(q), static_cast<const float*>(kv),
+                               static_cast<float*>(o), lse, stream);
+  if (s->dtype == MOC_BF16) return launch_attn_tc_fwd(s, q, kv, o, lse, status, stream);
+  set_last_error("dtype", "unknown dtype");
+  return MOC_ERR_INVALID;
+}
+
+extern "C" int moc_attn_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o,
+                            const float* lse, const void* d_o, void* d_q, void* d_kv, float* delta,
+                            int32_t* status, void* stream_) {
+  int rc = check_attn(s);
+  if (rc != MOC_OK) return rc;
+  MOC_REQUIRE(q && kv && o && lse && d_o && d_q && d_kv && delta && status, "NULL attention buffer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (s->dtype == MOC_F32) {
+    rc = launch_delta(MOC_F32, o, d_o, delta, s->batch, s->seq, s->num_heads, s->head_dim, stream);
+    if (rc != MOC_OK) return rc;
+    return launch_attn_f32_bwd(s, static_cast<const float*>(q), static_cast<const float*>(kv),
+                               static_cast<const float*>(d_o), lse, delta, static_cast<float*>(d_q),
+                               static_cast<float*>(d_kv), stream);
+  }
+  if (s->dtype == MOC_BF16) return launch_attn_tc_bwd(s, q, kv, o, lse, d_o, d_q, d_kv, delta, status, stream);
+  set_last_error("dtype", "unknown dtype");
+  return MOC_ERR_INVALID;
+}

@@ -1,0 +1,357 @@
+// Chapter gather (selected chapters -> per-batch memory rows), optional per-row normalisation and
+// router-weight scaling, and the backward that writes gradients only for touched chapters.
+// All kernels are HBM bound: one warp per 1-D row, vector accesses where alignment allows.
+#include <math.h>
+
+#include "moc_common.cuh"
+
+namespace moc {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ld(const T* p, long long i);
+template <> __device__ __forceinline__ float ld<float>(const float* p, long long i) { return p[i]; }
+template <> __device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p, long long i) {
+  return __bfloat162float(p[i]);
+}
+template <typename T> __device__ __forceinline__ void st(T* p, long long i, float v);
+template <> __device__ __forceinline__ void st<float>(float* p, long long i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void st<__nv_bfloat16>(__nv_bfloat16* p, long long i, float v) {
+  p[i] = __float2bfloat16(v);
+}
+
+// statistics of one bank row as the normalisation needs them: {mean, 1/sqrt(var or meansq + eps)}
+template <typename TB>
+__device__ __forceinline__ void row_norm_stats(const TB* row, int dim, int norm_type, float eps, int lane,
+                                               float& mean, float& rinv) {
+  mean = 0.f;
+  rinv = 1.f;
+  if (norm_type == MOC_NORM_NONE) return;
+  if (norm_type == MOC_NORM_LAYERNORM) {
+    float s = 0.f;
+    for (int c = lane; c < dim; c += 32) s += ld(row, c);
+    mean = warp_sum(s) / static_cast<float>(dim);
+  }
+  float s2 = 0.f;
+  for (int c = lane; c < dim; c += 32) {
+    const float v = ld(row, c) - mean;
+    s2 += v * v;
+  }
+  s2 = warp_sum(s2) / static_cast<float>(dim);
+  rinv = 1.f / sqrtf(s2 + eps);
+}
+
+template <typename TB, typename TO>
+__global__ void gather_rows_kernel(const TB* __restrict__ bank, long long bank_rows, int dim, int T,
+                                   const int* __restrict__ comb_idx, const float* __restrict__ comb_w,
+                                   long long n_rows, int norm_type, float eps, TO* __restrict__ out,
+                                   float* __restrict__ row_stats, int* __restrict__ status) {
+  const int lane = threadIdx.x & 31;
+  const long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  if (r >= n_rows) return;
+  const long long pair = r / T;
+  const int within = static_cast<int>(r - pair * T);
+  const long long chapter = comb_idx[pair];
+  const long long src = chapter * T + within;
+  TO* dst = out + r * dim;
+  if (chapter < 0 || src >= bank_rows) {
+    if (lane == 0) atomicMax(status, MOC_DEV_BAD_INDEX);
+    for (int c = lane; c < dim; c += 32) st(dst, c, 0.f);
+    return;
+  }
+  const TB* row = bank + src * dim;
+  float mean, rinv;
+  row_norm_stats(row, dim, norm_type, eps, lane, mean, rinv);
+  if (norm_type != MOC_NORM_NONE && row_stats != nullptr && lane == 0) {
+    row_stats[r * 2] = mean;
+    row_stats[r * 2 + 1] = rinv;
+  }
+  const float w = comb_w ? comb_w[pair] : 1.f;
+  for (int c = lane; c < dim; c += 32) st(dst, c, (ld(row, c) - mean) * rinv * w);
+}
+
+// Groups (batch, slot) pairs by chapter id.  Single CTA.
+__global__ void __launch_bounds__(1024)
+chapter_segments_kernel(const int* __restrict__ comb_idx, int n_pairs, int C, int* __restrict__ uniq,
+                        int* __restrict__ seg_offsets, int* __restrict__ seg_pairs,
+                        int* __restrict__ pair_to_uniq, int* __restrict__ num_unique, int* __restrict__ status) {
+  extern __shared__ int sh[];          // count[C], then start[C], urank[C]
+  int* count = sh;
+  int* start = sh + C;
+  int* urank = sh + 2 * C;
+  __shared__ int warp_tot[2][32];
+  for (int c = threadIdx.x; c < C; c += blockDim.x) count[c] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int c = comb_idx[i];
+    if (c < 0 || c >= C) atomicMax(status, MOC_DEV_BAD_INDEX);
+    else atomicAdd(&count[c], 1);
+  }
+  __syncthreads();
+  // exclusive scans of count[] and (count[] > 0), each thread owning a contiguous span
+  const int per = (C + blockDim.x - 1) / blockDim.x;
+  const int lo = threadIdx.x * per, hi = min(C, lo + per);
+  int s0 = 0, s1 = 0;
+  for (int c = lo; c < hi; ++c) { s0 += count[c]; s1 += (count[c] > 0); }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int i0 = s0, i1 = s1;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t0 = __shfl_up_sync(0xffffffffu, i0, o), t1 = __shfl_up_sync(0xffffffffu, i1, o);
+    if (lane >= o) { i0 += t0; i1 += t1; }
+  }
+  if (lane == 31) { warp_tot[0][warp] = i0; warp_tot[1][warp] = i1; }
+  __syncthreads();
+  if (warp == 0) {
+    int w0 = warp_tot[0][lane], w1 = warp_tot[1][lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t0 = __shfl_up_sync(0xffffffffu, w0, o), t1 = __shfl_up_sync(0xffffffffu, w1, o);
+      if (lane >= o) { w0 += t0; w1 += t1; }
+    }
+    warp_tot[0][lane] = w0; warp_tot[1][lane] = w1;   // inclusive
+  }
+  __syncthreads();
+  int e0 = i0 - s0 + (warp > 0 ? warp_tot[0][warp - 1] : 0);
+  int e1 = i1 - s1 + (warp > 0 ? warp_tot[1][warp - 1] : 0);
+  for (int c = lo; c < hi; ++c) {
+    start[c] = e0; urank[c] = e1;
+    if (count[c] > 0) { uniq[e1] = c; seg_offsets[e1] = e0; }
+    e0 += count[c]; e1 += (count[c] > 0);
+  }
+  __syncthreads();
+  const int U = warp_tot[1][31];
+  if (threadIdx.x == 0) { num_unique[0] = U; seg_offsets[U] = warp_tot[0][31]; }
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int c = comb_idx[i];
+    if (c < 0 || c >= C) { pair_to_uniq[i] = -1; continue; }
+    int pos = 0;
+    for (int j = 0; j < i; ++j) pos += (comb_idx[j] == c);
+    seg_pairs[start[c] + pos] = i;
+    pair_to_uniq[i] = urank[c];
+  }
+}
+
+// d_comb_w[pair] = sum over the pair's rows of <d_mem row, normalised bank row>; one CTA per pair
+template <typename TG, typename TB>
+__global__ void dcombw_kernel(const TG* __restrict__ d_mem, const TB* __restrict__ bank, long long bank_rows,
+                              int dim, int T, const int* __restrict__ comb_idx,
+                              const float* __restrict__ row_stats, int norm_type,
+                              float* __restrict__ d_comb_w) {
+  __shared__ float red[32];
+  const long long pair = blockIdx.x;
+  const long long chapter = comb_idx[pair];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float acc = 0.f;
+  if (chapter >= 0 && (chapter + 1) * T <= bank_rows) {
+    for (int r = warp; r < T; r += nw) {
+      const long long orow = pair * T + r;
+      const TB* row = bank + (chapter * T + r) * dim;
+      const TG* g = d_mem + orow * dim;
+      float mean = 0.f, rinv = 1.f;
+      if (norm_type != MOC_NORM_NONE) { mean = row_stats[orow * 2]; rinv = row_stats[orow * 2 + 1]; }
+      for (int c = lane; c < dim; c += 32) acc += ld(g, c) * (ld(row, c) - mean) * rinv;
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) red[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) d_comb_w[pair] = t;
+  }
+}
+
+// compact bank gradient: one warp per (unique chapter, row)
+template <typename TG, typename TB>
+__global__ void bank_grad_kernel(const TG* __restrict__ d_mem, const TB* __restrict__ bank, int dim, int T,
+                                 const float* __restrict__ comb_w, const float* __restrict__ row_stats,
+                                 int norm_type, const int* __restrict__ uniq,
+                                 const int* __restrict__ seg_offsets, const int* __restrict__ seg_pairs,
+                                 const int* __restrict__ num_unique, long long max_rows,
+                                 float* __restrict__ bank_grad) {
+  const int lane = threadIdx.x & 31;
+  const long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  if (r >= max_rows) return;
+  const int u = static_cast<int>(r / T);
+  if (u >= num_unique[0]) return;
+  const int within = static_cast<int>(r - static_cast<long long>(u) * T);
+  const int p0 = seg_offsets[u], p1 = seg_offsets[u + 1];
+  float* dst = bank_grad + r * dim;
+  if (norm_type == MOC_NORM_NONE) {
+    for (int c = lane; c < dim; c += 32) {
+      float acc = 0.f;
+      for (int q = p0; q < p1; ++q) {
+        const long long pair = seg_pairs[q];
+        acc = fmaf(comb_w ? comb_w[pair] : 1.f, ld(d_mem + (pair * T + within) * dim, c), acc);
+      }
+      dst[c] = acc;
+    }
+    return;
+  }
+  // normalised rows: g = sum_p w_p * d_mem_p is the gradient of y; push it through the row norm
+  const long long chapter = uniq[u];
+  const TB* row = bank + (chapter * T + within) * dim;
+  const long long first = static_cast<long long>(seg_pairs[p0]) * T + within;
+  const float mean = row_stats[first * 2], rinv = row_stats[first * 2 + 1];
+  float sg = 0.f, sgy = 0.f;
+  for (int c = lane; c < dim; c += 32) {
+    float acc = 0.f;
+    for (int q = p0; q < p1; ++q) {
+      const long long pair = seg_pairs[q];
+      acc = fmaf(comb_w ? comb_w[pair] : 1.f, ld(d_mem + (pair * T + within) * dim, c), acc);
+    }
+    dst[c] = acc;
+    sg += acc;
+    sgy += acc * (ld(row, c) - mean) * rinv;
+  }
+  sg = warp_sum(sg) / static_cast<float>(dim);
+  sgy = warp_sum(sgy) / static_cast<float>(dim);
+  if (norm_type == MOC_NORM_RMS) sg = 0.f;
+  __syncwarp();
+  for (int c = lane; c < dim; c += 32) {
+    const float y = (ld(row, c) - mean) * rinv;
+    dst[c] = rinv * (dst[c] - sg - y * sgy);
+  }
+}
+
+__global__ void scatter_bank_grad_kernel(const float* __restrict__ bank_grad, const int* __restrict__ uniq,
+                                         const int* __restrict__ num_unique, long long max_rows, int T, int dim,
+                                         float* __restrict__ dense, long long bank_rows) {
+  const int lane = threadIdx.x & 31;
+  const long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  if (r >= max_rows) return;
+  const int u = static_cast<int>(r / T);
+  if (u >= num_unique[0]) return;
+  const long long row = static_cast<long long>(uniq[u]) * T + (r - static_cast<long long>(u) * T);
+  if (row < 0 || row >= bank_rows) return;
+  for (int c = lane; c < dim; c += 32) dense[row * dim + c] += bank_grad[r * dim + c];
+}
+
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = __float2bfloat16(src[i]);
+}
+__global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = __bfloat162float(src[i]);
+}
+
+inline int grid_for(long long n, int per_block) {
+  long long g = (n + per_block - 1) / per_block;
+  const long long cap = 148LL * 32;
+  return static_cast<int>(g < cap ? (g > 0 ? g : 1) : cap);
+}
+
+}  // namespace
+}  // namespace moc
+
+using namespace moc;
+
+extern "C" int moc_gather_rows_fwd(const void* bank, int32_t bank_dtype, int64_t bank_rows, int32_t dim,
+                                   int32_t T, const int32_t* comb_idx, const float* comb_w, int32_t batch,
+                                   int32_t k_sel, int32_t norm_type, float eps, void* out, int32_t out_dtype,
+                                   float* row_stats, int32_t* status, void* stream_) {
+  MOC_REQUIRE(bank && comb_idx && out && status, "NULL gather buffer");
+  MOC_REQUIRE(dim > 0 && T > 0 && batch > 0 && k_sel > 0, "empty gather");
+  MOC_REQUIRE(norm_type >= 0 && norm_type <= 2, "bad norm_type");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long n_rows = static_cast<long long>(batch) * k_sel * T;
+  const int blocks = static_cast<int>((n_rows * 32 + 255) / 256);
+#define MOC_GATHER(TB, TO)                                                                                  \
+  gather_rows_kernel<TB, TO><<<blocks, 256, 0, stream>>>(static_cast<const TB*>(bank), bank_rows, dim, T,   \
+                                                         comb_idx, comb_w, n_rows, norm_type, eps,          \
+                                                         static_cast<TO*>(out), row_stats, status)
+  if (bank_dtype == MOC_F32 && out_dtype == MOC_F32) MOC_GATHER(float, float);
+  else if (bank_dtype == MOC_F32 && out_dtype == MOC_BF16) MOC_GATHER(float, __nv_bfloat16);
+  else if (bank_dtype == MOC_BF16 && out_dtype == MOC_BF16) MOC_GATHER(__nv_bfloat16, __nv_bfloat16);
+  else if (bank_dtype == MOC_BF16 && out_dtype == MOC_F32) MOC_GATHER(__nv_bfloat16, float);
+  else MOC_REQUIRE(false, "bad dtype");
+#undef MOC_GATHER
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+extern "C" int moc_chapter_segments(const int32_t* comb_idx, int32_t n_pairs, int32_t num_chapters,
+                                    int32_t* uniq, int32_t* seg_offsets, int32_t* seg_pairs,
+                                    int32_t* pair_to_uniq, int32_t* num_unique, int32_t* status, void* stream_) {
+  MOC_REQUIRE(comb_idx && uniq && seg_offsets && seg_pairs && pair_to_uniq && num_unique && status, "NULL buffer");
+  MOC_REQUIRE(n_pairs > 0 && n_pairs <= 65536, "n_pairs out of range");
+  MOC_REQUIRE(num_chapters > 0 && static_cast<size_t>(num_chapters) * 12 <= 200 * 1024, "num_chapters too large");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const size_t sm = static_cast<size_t>(num_chapters) * 12;
+  MOC_CUDA_OK(cudaFuncSetAttribute(chapter_segments_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
+  chapter_segments_kernel<<<1, 1024, sm, stream>>>(comb_idx, n_pairs, num_chapters, uniq, seg_offsets, seg_pairs,
+                                                   pair_to_uniq, num_unique, status);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+extern "C" int moc_gather_rows_bwd(const void* d_mem, int32_t d_mem_dtype, const void* bank, int32_t bank_dtype,
+                                   int64_t bank_rows, int32_t dim, int32_t T, const int32_t* comb_idx,
+                                   const float* comb_w, int32_t batch, int32_t k_sel, int32_t norm_type,
+                                   float eps, const float* row_stats, const int32_t* uniq,
+                                   const int32_t* seg_offsets, const int32_t* seg_pairs,
+                                   const int32_t* num_unique, float* d_comb_w, float* bank_grad,
+                                   int32_t* status, void* stream_) {
+  (void)eps; (void)status;
+  MOC_REQUIRE(d_mem && bank && comb_idx && uniq && seg_offsets && seg_pairs && num_unique, "NULL buffer");
+  MOC_REQUIRE(norm_type == MOC_NORM_NONE || row_stats != nullptr, "row_stats needed for normalised rows");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int n_pairs = batch * k_sel;
+  const long long max_rows = static_cast<long long>(n_pairs) * T;
+  const int blocks = static_cast<int>((max_rows * 32 + 255) / 256);
+#define MOC_GBWD(TG, TB)                                                                                      \
+  do {                                                                                                        \
+    if (d_comb_w != nullptr)                                                                                  \
+      dcombw_kernel<TG, TB><<<n_pairs, 256, 0, stream>>>(static_cast<const TG*>(d_mem),                       \
+                                                         static_cast<const TB*>(bank), bank_rows, dim, T,     \
+                                                         comb_idx, row_stats, norm_type, d_comb_w);           \
+    if (bank_grad != nullptr)                                                                                 \
+      bank_grad_kernel<TG, TB><<<blocks, 256, 0, stream>>>(static_cast<const TG*>(d_mem),                     \
+                                                           static_cast<const TB*>(bank), dim, T, comb_w,      \
+                                                           row_stats, norm_type, uniq, seg_offsets,           \
+                                                           seg_pairs, num_unique, max_rows, bank_grad);       \
+  } while (0)
+  if (d_mem_dtype == MOC_F32 && bank_dtype == MOC_F32) MOC_GBWD(float, float);
+  else if (d_mem_dtype == MOC_F32 && bank_dtype == MOC_BF16) MOC_GBWD(float, __nv_bfloat16);
+  else if (d_mem_dtype == MOC_BF16 && bank_dtype == MOC_F32) MOC_GBWD(__nv_bfloat16, float);
+  else if (d_mem_dtype == MOC_BF16 && bank_dtype == MOC_BF16) MOC_GBWD(__nv_bfloat16, __nv_bfloat16);
+  else MOC_REQUIRE(false, "bad dtype");
+#undef MOC_GBWD
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+extern "C" int moc_scatter_bank_grad(const float* bank_grad, const int32_t* uniq, const int32_t* num_unique,
+                                     int32_t max_unique, int32_t T, int32_t dim, float* bank_dense,
+                                     int64_t bank_rows, int32_t* status, void* stream_) {
+  (void)status;
+  MOC_REQUIRE(bank_grad && uniq && num_unique && bank_dense, "NULL buffer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long max_rows = static_cast<long long>(max_unique) * T;
+  const int blocks = static_cast<int>((max_rows * 32 + 255) / 256);
+  scatter_bank_grad_kernel<<<blocks, 256, 0, stream>>>(bank_grad, uniq, num_unique, max_rows, T, dim, bank_dense,
+                                                       bank_rows);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+extern "C" int moc_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream_) {
+  MOC_REQUIRE(src && dst && n >= 0, "bad cast arguments");
+  if (n == 0) return MOC_OK;
+  cast_f32_bf16_kernel<<<grid_for(n, 256 * 8), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      src, static_cast<__nv_bfloat16*>(dst), n);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+extern "C" int moc_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream_) {
+  MOC_REQUIRE(src && dst && n >= 0, "bad cast arguments");
+  if (n == 0) return MOC_OK;
+  cast_bf16_f32_kernel<<<grid_for(n, 256 * 8), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const __nv_bfloat16*>(src), dst, n);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}

@@ -1,0 +1,300 @@
+// bf16 tensor-core projection kernel for sm_100a: TMA -> shared memory (128-byte swizzle) ->
+// tcgen05.mma with the fp32 accumulator tile in tensor memory -> tcgen05.ld epilogue.
+//
+//   C[M,N] (+)= op(A)[M,K] * op(B)[K,N], 128 x 128 output tile per CTA, 64-wide K stages.
+//
+// Roles inside a CTA of 192 threads: warp 0 issues the TMA loads, warp 1 owns tensor memory and
+// issues the MMAs from one lane, warps 2-5 drain the accumulator (each warp may only touch the 32
+// TMEM lanes selected by warp_id % 4).  The A operand can be fetched through a row-block gather
+// list, which is how selected chapters are read straight out of the memory bank.
+#include "moc_common.cuh"
+
+namespace moc {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 128;
+constexpr int BK = 64;
+constexpr int kStages = 3;
+constexpr int kStageBytes = (BM * BK + BN * BK) * 2;   // 32 KiB
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 128;
+
+struct GemmTcParams {
+  int m, n, k;
+  int a_kmajor, b_kmajor;
+  void* c;
+  long long ldc;
+  int c_bf16;
+  int accumulate;
+  int atomic;
+  const float* row_scale;
+  int scale_block_rows;
+  const int* a_row_blocks;
+  int a_box_rows;          // rows per A box when A is K-major
+  int a_num_blocks;        // entries in the gather list
+  long long a_stored_rows;
+  int k_tiles_total;
+  int k_tiles_per_split;
+  int* status;
+};
+
+__device__ __forceinline__ void drain_after_abort() {
+  // give bulk copies already in flight time to land before the CTA's shared memory is released
+  for (int i = 0; i < 200; ++i) __nanosleep(1000);
+}
+
+__global__ void __launch_bounds__(kThreads)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               GemmTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * BM;
+  const int kt_begin = blockIdx.z * p.k_tiles_per_split;
+  int kt_count = p.k_tiles_total - kt_begin;
+  if (kt_count > p.k_tiles_per_split) kt_count = p.k_tiles_per_split;
+  if (kt_count < 0) kt_count = 0;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    fence_mbar_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kt = 0; kt < kt_count; ++kt) {
+        const int s = kt % kStages;
+        const uint32_t ph = (kt / kStages) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, p.status)) break;
+        mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+        uint8_t* a_s = tiles + s * kStageBytes;
+        uint8_t* b_s = a_s + BM * BK * 2;
+        const int k0 = (kt_begin + kt) * BK;
+        if (p.a_kmajor) {
+          const int nbox = BM / p.a_box_rows;
+          for (int i = 0; i < nbox; ++i) {
+            long long row;
+            if (p.a_row_blocks != nullptr) {
+              const int blk = m0 / p.a_box_rows + i;
+              row = (blk < p.a_num_blocks) ? static_cast<long long>(p.a_row_blocks[blk]) * p.a_box_rows
+                                           : p.a_stored_rows;
+              if (row < 0 || row > p.a_stored_rows) {
+                atomicMax(p.status, MOC_DEV_BAD_INDEX);
+                row = p.a_stored_rows;   // fully out of range: the copy zero-fills
+              }
+            } else {
+              row = m0 + i * p.a_box_rows;
+            }
+            tma_load_2d(a_s + i * p.a_box_rows * 128, &tmap_a, &full_bar[s], k0, static_cast<int>(row));
+          }
+        } else {
+          tma_load_2d(a_s, &tmap_a, &full_bar[s], m0, k0);
+          tma_load_2d(a_s + 8192, &tmap_a, &full_bar[s], m0 + 64, k0);
+        }
+        if (p.b_kmajor) {
+          tma_load_2d(b_s, &tmap_b, &full_bar[s], k0, n0);
+          tma_load_2d(b_s + 8192, &tmap_b, &full_bar[s], k0, n0 + 64);
+        } else {
+          tma_load_2d(b_s, &tmap_b, &full_bar[s], n0, k0);
+          tma_load_2d(b_s + 8192, &tmap_b, &full_bar[s], n0 + 64, k0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(BM, BN, p.a_kmajor ? 0 : 1, p.b_kmajor ? 0 : 1);
+      bool ok = true;
+      for (int kt = 0; kt < kt_count && ok; ++kt) {
+        const int s = kt % kStages;
+        const uint32_t ph = (kt / kStages) & 1;
+        ok = mbar_wait(&full_bar[s], ph, &abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(tiles + s * kStageBytes);
+        const uint32_t b_addr = a_addr + BM * BK * 2;
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; ++kk) {
+          const uint64_t ad = p.a_kmajor ? umma_desc_sw128(a_addr + kk * 32, 16, 1024)
+                                         : umma_desc_sw128(a_addr + kk * 2048, 8192, 1024);
+          const uint64_t bd = p.b_kmajor ? umma_desc_sw128(b_addr + kk * 32, 16, 1024)
+                                         : umma_desc_sw128(b_addr + kk * 2048, 8192, 1024);
+          umma_ss(tmem_acc, ad, bd, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&empty_bar[s]);
+      }
+      tc_commit(&acc_bar);
+    }
+  } else {
+    // epilogue: TMEM lanes [32*(warp%4), +32) <-> output rows
+    const int lane_group = (warp & 3) * 32;
+    const int row = m0 + lane_group + lane;
+    bool have_acc = false;
+    if (kt_count > 0) have_acc = mbar_wait(&acc_bar, 0, &abort_flag, p.status);
+    have_acc = __all_sync(0xffffffffu, have_acc);   // tcgen05.ld below is warp-collective
+    tc_fence_after();
+    float rs = 1.0f;
+    if (p.row_scale != nullptr && row < p.m) rs = p.row_scale[row / p.scale_block_rows];
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      if (have_acc) {
+        tmem_ld32(tmem_acc + (static_cast<uint32_t>(lane_group) << 16) + c * 32, r);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = 0u;
+      }
+      const int col0 = n0 + c * 32;
+      if (row >= p.m || col0 >= p.n || abort_flag) continue;
+      if (!have_acc && (p.atomic || p.accumulate)) continue;
+      if (p.c_bf16) {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+        const bool vec = ((p.ldc & 7) == 0) && (col0 + 32 <= p.n) &&
+                         ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
+        if (vec) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]) * rs, __uint_as_float(r[8 * j + 1]) * rs);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * rs, __uint_as_float(r[8 * j + 3]) * rs);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * rs, __uint_as_float(r[8 * j + 5]) * rs);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * rs, __uint_as_float(r[8 * j + 7]) * rs);
+            *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+          }
+        } else {
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.n) dst[j] = __float2bfloat16(__uint_as_float(r[j]) * rs);
+        }
+      } else {
+        float* dst = reinterpret_cast<float*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+        if (p.atomic) {
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.n) atomicAdd(dst + j, __uint_as_float(r[j]) * rs);
+        } else {
+          const bool vec = ((p.ldc & 3) == 0) && (col0 + 32 <= p.n) &&
+                           ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
+          if (vec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 v = make_float4(__uint_as_float(r[4 * j + 0]) * rs, __uint_as_float(r[4 * j + 1]) * rs,
+                                     __uint_as_float(r[4 * j + 2]) * rs, __uint_as_float(r[4 * j + 3]) * rs);
+              float4* d4 = reinterpret_cast<float4*>(dst + 4 * j);
+              if (p.accumulate) {
+                const float4 o = *d4;
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              }
+              *d4 = v;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.n) {
+                const float v = __uint_as_float(r[j]) * rs;
+                dst[j] = p.accumulate ? dst[j] + v : v;
+              }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (abort_flag) drain_after_abort();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, kTmemCols);
+  }
+}
+
+}  // namespace
+
+int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c, const float* row_scale,
+                   const int32_t* a_row_blocks, int32_t* status, cudaStream_t stream) {
+  MOC_REQUIRE(g->k % 8 == 0, "bf16 projection needs K % 8 == 0");
+  MOC_REQUIRE(g->lda % 8 == 0 && g->ldb % 8 == 0, "bf16 projection needs 16-byte aligned operand rows");
+  MOC_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(b) & 15) == 0,
+              "operands must be 16-byte aligned");
+  MOC_REQUIRE(g->c_dtype == MOC_BF16 || g->c_dtype == MOC_F32, "bad c_dtype");
+  const int split = g->split_k > 1 ? g->split_k : 1;
+  if (split > 1 || g->accumulate) MOC_REQUIRE(g->c_dtype == MOC_F32, "accumulate / split_k need an fp32 C");
+  int a_box_rows = 64;
+  int a_num_blocks = 0;
+  long long a_stored_rows = g->a_kmajor ? g->m : g->k;
+  if (a_row_blocks != nullptr) {
+    MOC_REQUIRE(g->a_kmajor, "the gather list needs a K-major A");
+    a_box_rows = g->a_block_rows;
+    MOC_REQUIRE(a_box_rows >= 8 && a_box_rows <= 128 && (128 % a_box_rows) == 0 && (a_box_rows % 8) == 0,
+                "a_block_rows must be a multiple of 8 that divides 128");
+    MOC_REQUIRE(g->m % a_box_rows == 0, "M must be a multiple of a_block_rows");
+    a_num_blocks = g->m / a_box_rows;
+    a_stored_rows = g->a_stored_rows;
+    MOC_REQUIRE(a_stored_rows > 0, "a_stored_rows missing");
+  }
+
+  const int smem_bytes = kStages * kStageBytes + 1024;
+  MOC_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+
+  CUtensorMap tmap_a, tmap_b;
+  int rc;
+  if (g->a_kmajor) {
+    rc = make_tmap_bf16_2d(&tmap_a, a, static_cast<uint64_t>(a_stored_rows), static_cast<uint64_t>(g->k),
+                           static_cast<uint64_t>(g->lda), static_cast<uint32_t>(a_box_rows), 64);
+  } else {
+    rc = make_tmap_bf16_2d(&tmap_a, a, static_cast<uint64_t>(g->k), static_cast<uint64_t>(g->m),
+                           static_cast<uint64_t>(g->lda), 64, 64);
+  }
+  if (rc != MOC_OK) return rc;
+  if (g->b_kmajor) {
+    rc = make_tmap_bf16_2d(&tmap_b, b, static_cast<uint64_t>(g->n), static_cast<uint64_t>(g->k),
+                           static_cast<uint64_t>(g->ldb), 64, 64);
+  } else {
+    rc = make_tmap_bf16_2d(&tmap_b, b, static_cast<uint64_t>(g->k), static_cast<uint64_t>(g->n),
+                           static_cast<uint64_t>(g->ldb), 64, 64);
+  }
+  if (rc != MOC_OK) return rc;
+
+  GemmTcParams p;
+  p.m = g->m; p.n = g->n; p.k = g->k;
+  p.a_kmajor = g->a_kmajor; p.b_kmajor = g->b_kmajor;
+  p.c = c; p.ldc = g->ldc; p.c_bf16 = (g->c_dtype == MOC_BF16);
+  p.accumulate = g->accumulate; p.atomic = split > 1;
+  p.row_scale = row_scale; p.scale_block_rows = g->scale_block_rows > 0 ? g->scale_block_rows : 1;
+  p.a_row_blocks = a_row_blocks; p.a_box_rows = a_box_rows; p.a_num_blocks = a_num_blocks;
+  p.a_stored_rows = a_stored_rows;
+  p.k_tiles_total = ceil_div(g->k, BK);
+  p.k_tiles_per_split = ceil_div(p.k_tiles_total, split);
+  p.status = status;
+
+  dim3 grid(ceil_div(g->n, BN), ceil_div(g->m, BM), split);
+  gemm_tc_kernel<<<grid, kThreads, smem_bytes, stream>>>(tmap_a, tmap_b, p);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+}  // namespace moc

@@ -1,0 +1,60 @@
+// Host-side utilities shared by the entry points: last-error text and TMA tensor-map creation.
+#include <string>
+
+#include "moc_common.cuh"
+
+namespace moc {
+
+static thread_local std::string g_last_error;
+
+void set_last_error(const char* what, const char* detail) {
+  g_last_error = std::string(what ? what : "") + ": " + (detail ? detail : "");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                      uint64_t row_stride_elems, uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) {
+    set_last_error("cuTensorMapEncodeTiled", "driver entry point not found");
+    return MOC_ERR_CUDA;
+  }
+  MOC_REQUIRE(box_cols * 2 == 128, "tile rows must be 128 bytes for the 128-byte swizzle");
+  MOC_REQUIRE(box_rows >= 1 && box_rows <= 256, "box rows out of range");
+  MOC_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "tensor base must be 16-byte aligned");
+  MOC_REQUIRE((row_stride_elems * 2) % 16 == 0, "row stride must be a multiple of 16 bytes");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_stride_elems * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled", "encode failed");
+    return MOC_ERR_CUDA;
+  }
+  return MOC_OK;
+}
+
+}  // namespace moc
+
+extern "C" const char* moc_last_error(void) { return moc::g_last_error.c_str(); }
+extern "C" int moc_abi_version(void) { return 1; }

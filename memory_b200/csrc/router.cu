@@ -1,0 +1,571 @@
+// Chapter router: fp32 mean-pool, router GEMV, softmax, prefix mask, exact top-k with the total
+// order (value descending, chapter id ascending), weight renormalisation, shared-chapter prefix,
+// load-balance / auxiliary / z losses and entropy -- and the backward of all of it.
+//
+// All kernels here are bandwidth or latency bound (the router is ~5e7 FLOPs); reductions are
+// done in a fixed order so results do not depend on scheduling.
+#include <math.h>
+
+#include "moc_common.cuh"
+
+namespace moc {
+namespace {
+
+constexpr int kPoolSplits = 32;       // sequence splits of the mean-pool
+constexpr int kSelectThreads = 1024;  // one CTA per batch row in the select / dlogits kernels
+constexpr int kLossChunk = 256;       // chapters per CTA in the loss kernels
+constexpr int kDpChunk = 128;         // chapters per CTA in the d_pooled kernel
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// ---- block reductions (fixed order) ----------------------------------------------------------
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  if (warp == 0) {
+    t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// ---- forward ---------------------------------------------------------------------------------
+// partial[b][split][c] = sum over the split's positions of h[b, t, c]
+template <typename T>
+__global__ void pool_partial_kernel(const T* __restrict__ h, float* __restrict__ partial, int L, int d) {
+  const int b = blockIdx.x, sp = blockIdx.y;
+  const int rows_per = (L + kPoolSplits - 1) / kPoolSplits;
+  const int t0 = sp * rows_per;
+  const int t1 = min(L, t0 + rows_per);
+  const T* base = h + (static_cast<long long>(b) * L) * d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float acc = 0.f;
+    for (int t = t0; t < t1; ++t) acc += to_f32(base[static_cast<long long>(t) * d + c]);
+    partial[(static_cast<long long>(b) * kPoolSplits + sp) * d + c] = acc;
+  }
+}
+__global__ void pool_finish_kernel(const float* __restrict__ partial, float* __restrict__ pooled, int L, int d,
+                                   int total) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int b = i / d, c = i - b * d;
+  float acc = 0.f;
+  for (int sp = 0; sp < kPoolSplits; ++sp) acc += partial[(static_cast<long long>(b) * kPoolSplits + sp) * d + c];
+  pooled[i] = acc / static_cast<float>(L);
+}
+
+// logits[b,c] = <pooled[b,:], w[c,:]> + bias[c]; one warp per chapter, 8 batch rows per pass
+__global__ void logits_kernel(const float* __restrict__ pooled, const float* __restrict__ w,
+                              const float* __restrict__ bias, float* __restrict__ logits, int B, int d, int C) {
+  extern __shared__ float sp[];   // [8][d]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * (blockDim.x >> 5) + warp;
+  for (int b0 = 0; b0 < B; b0 += 8) {
+    const int nb = min(8, B - b0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb * d; i += blockDim.x) sp[i] = pooled[static_cast<long long>(b0) * d + i];
+    __syncthreads();
+    if (c < C) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      const float* wr = w + static_cast<long long>(c) * d;
+      for (int k = lane; k < d; k += 32) {
+        const float wv = wr[k];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j < nb) acc[j] = fmaf(wv, sp[j * d + k], acc[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < nb) {
+          const float s = warp_sum(acc[j]);
+          if (lane == 0) logits[static_cast<long long>(b0 + j) * C + c] = s + (bias ? bias[c] : 0.f);
+        }
+      }
+    }
+  }
+}
+
+// One CTA per batch row: softmax, prefix mask + renormalise, exact top-k, weights, shared prefix.
+__global__ void __launch_bounds__(kSelectThreads)
+select_kernel(const float* __restrict__ logits, float* __restrict__ probs, long long* __restrict__ idx,
+              float* __restrict__ weights, int* __restrict__ comb_idx, float* __restrict__ comb_w,
+              float* __restrict__ row_stats, int C, int k_sel, int S, float rho) {
+  extern __shared__ float sm[];            // [C] masked probabilities, then selection scratch
+  float* pt = sm;                          // p~
+  uint32_t* sel_key = reinterpret_cast<uint32_t*>(sm + C);   // [k_sel]
+  int* sel_idx = reinterpret_cast<int*>(sel_key + k_sel);    // [k_sel]
+  __shared__ float red[33];
+  __shared__ int hist[256];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_krem, s_count, s_ties;
+
+  const int b = blockIdx.x;
+  const float* z = logits + static_cast<long long>(b) * C;
+  float* p = probs + static_cast<long long>(b) * C;
+
+  float m = -INFINITY;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) m = fmaxf(m, z[c]);
+  m = block_max(m, red);
+  float s = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float e = expf(z[c] - m);
+    pt[c] = e;
+    s += e;
+  }
+  const float denom = block_sum(s, red);
+  float ms = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float pv = pt[c] / denom;
+    p[c] = pv;
+    const float pm = (c < S) ? 0.f : pv;
+    pt[c] = pm;
+    ms += pm;
+  }
+  const float masked_mass = block_sum(ms, red);
+  if (S > 0) {
+    const float dn = fmaxf(masked_mass, 1e-12f);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) pt[c] = pt[c] / dn;
+  }
+  __syncthreads();
+
+  float topk_mass = 0.f, comb_mass = static_cast<float>(S);
+  if (k_sel > 0) {
+    // radix select on the fp32 bit pattern (non-negative values order like unsigned integers)
+    if (threadIdx.x == 0) { s_prefix = 0u; s_krem = k_sel; }
+    uint32_t mask = 0u;
+    for (int pass = 3; pass >= 0; --pass) {
+      for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+      __syncthreads();
+      const uint32_t prefix = s_prefix;
+      for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const uint32_t key = __float_as_uint(pt[c]);
+        if ((key & mask) == prefix) atomicAdd(&hist[(key >> (8 * pass)) & 255u], 1);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int rem = s_krem, bin = 255;
+        for (; bin > 0; --bin) {
+          if (hist[bin] >= rem) break;
+          rem -= hist[bin];
+        }
+        s_krem = rem;
+        s_prefix = prefix | (static_cast<uint32_t>(bin) << (8 * pass));
+        s_ties = hist[bin];
+      }
+      mask |= 0xFFu << (8 * pass);
+      __syncthreads();
+    }
+    const uint32_t thr = s_prefix;     // bit pattern of the k-th largest value
+    const int need_ties = s_krem;      // how many entries equal to it are selected
+    const int have_ties = s_ties;
+    if (threadIdx.x == 0) s_count = 0;
+    __syncthreads();
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      const uint32_t key = __float_as_uint(pt[c]);
+      if (key > thr || (key == thr && have_ties == need_ties)) {
+        const int pos = atomicAdd(&s_count, 1);
+        if (pos < k_sel) { sel_key[pos] = key; sel_idx[pos] = c; }
+      }
+    }
+    __syncthreads();
+    if (have_ties != need_ties && threadIdx.x == 0) {
+      int pos = s_count, taken = 0;            // more ties than slots: lowest chapter ids win
+      for (int c = 0; c < C && taken < need_ties; ++c) {
+        if (__float_as_uint(pt[c]) == thr) {
+          if (pos < k_sel) { sel_key[pos] = thr; sel_idx[pos] = c; }
+          ++pos; ++taken;
+        }
+      }
+    }
+    __syncthreads();
+    // rank sort of the k selected entries: value descending, chapter id ascending
+    long long* out_idx = idx + static_cast<long long>(b) * k_sel;
+    float* out_w = weights + static_cast<long long>(b) * k_sel;
+    for (int t = threadIdx.x; t < k_sel; t += blockDim.x) {
+      const uint32_t kt = sel_key[t];
+      const int it = sel_idx[t];
+      int rank = 0;
+      for (int j = 0; j < k_sel; ++j) {
+        const uint32_t kj = sel_key[j];
+        rank += (kj > kt) || (kj == kt && sel_idx[j] < it);
+      }
+      out_idx[rank] = it;
+      out_w[rank] = __uint_as_float(kt);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float sum = 0.f;
+      for (int j = 0; j < k_sel; ++j) sum += out_w[j];
+      topk_mass = sum;
+      const float dn = fmaxf(sum, 1e-12f);
+      float csum = static_cast<float>(S);
+      for (int j = 0; j < k_sel; ++j) {
+        const float wj = out_w[j] / dn;
+        out_w[j] = wj;
+        csum += wj * rho;
+      }
+      comb_mass = csum;
+      red[0] = topk_mass; red[1] = comb_mass;
+    }
+    __syncthreads();
+    topk_mass = red[0]; comb_mass = red[1];
+  }
+  // shared prefix + renormalised combined weights (only meaningful when S > 0; with S == 0 the
+  // combined lists are the routed lists unchanged)
+  const int kc = S + k_sel;
+  for (int j = threadIdx.x; j < kc; j += blockDim.x) {
+    int ci; float u;
+    if (j < S) { ci = j; u = 1.f; }
+    else { ci = static_cast<int>(idx[static_cast<long long>(b) * k_sel + (j - S)]);
+           u = weights[static_cast<long long>(b) * k_sel + (j - S)] * (S > 0 ? rho : 1.f); }
+    comb_idx[static_cast<long long>(b) * kc + j] = ci;
+    comb_w[static_cast<long long>(b) * kc + j] = (S > 0) ? u / fmaxf(comb_mass, 1e-12f) : u;
+  }
+  if (threadIdx.x == 0) {
+    float* rs = row_stats + static_cast<long long>(b) * 4;
+    rs[0] = m + logf(denom);
+    rs[1] = masked_mass;
+    rs[2] = topk_mass;
+    rs[3] = comb_mass;
+  }
+}
+
+// Per chapter chunk: f, mean p^2, and partial sums of the three chapter-separable loss terms.
+__global__ void loss_partial_kernel(const float* __restrict__ probs, const long long* __restrict__ idx,
+                                    float* __restrict__ chapter_stats, float* __restrict__ partial,
+                                    int B, int C, int k_sel) {
+  __shared__ int cnt[kLossChunk];
+  __shared__ float red[33];
+  const int c0 = blockIdx.x * kLossChunk;
+  for (int i = threadIdx.x; i < kLossChunk; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  const long long n_idx = static_cast<long long>(B) * k_sel;
+  for (long long i = threadIdx.x; i < n_idx; i += blockDim.x) {
+    const int c = static_cast<int>(idx[i]) - c0;
+    if (c >= 0 && c < kLossChunk) atomicAdd(&cnt[c], 1);
+  }
+  __syncthreads();
+  float lb = 0.f, aux = 0.f, ent = 0.f;
+  const int c = c0 + threadIdx.x;
+  if (threadIdx.x < kLossChunk && c < C) {
+    float ps = 0.f, p2 = 0.f, e = 0.f;
+    for (int b = 0; b < B; ++b) {
+      const float pv = probs[static_cast<long long>(b) * C + c];
+      ps += pv;
+      p2 += pv * pv;
+      e += pv * logf(fmaxf(pv, 1e-12f));
+    }
+    const float f = static_cast<float>(cnt[threadIdx.x]) / static_cast<float>(B);
+    const float P = ps / static_cast<float>(B);
+    const float q = p2 / static_cast<float>(B);
+    chapter_stats[c] = f;
+    chapter_stats[C + c] = q;
+    lb = f * P;
+    const float dv = q - 1.f / static_cast<float>(C);
+    aux = dv * dv;
+    ent = e;
+  }
+  lb = block_sum(lb, red);
+  aux = block_sum(aux, red);
+  ent = block_sum(ent, red);
+  if (threadIdx.x == 0) {
+    partial[blockIdx.x * 3 + 0] = lb;
+    partial[blockIdx.x * 3 + 1] = aux;
+    partial[blockIdx.x * 3 + 2] = ent;
+  }
+}
+__global__ void loss_finish_kernel(const float* __restrict__ partial, const float* __restrict__ row_stats,
+                                   float* __restrict__ losses, int nblk, int B, int C) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  float lb = 0.f, aux = 0.f, ent = 0.f, z = 0.f;
+  for (int i = 0; i < nblk; ++i) { lb += partial[i * 3]; aux += partial[i * 3 + 1]; ent += partial[i * 3 + 2]; }
+  for (int b = 0; b < B; ++b) { const float l = row_stats[b * 4]; z += l * l; }
+  losses[0] = static_cast<float>(C) * lb;
+  losses[1] = aux / static_cast<float>(C);
+  losses[2] = z / static_cast<float>(B);
+  losses[3] = -ent / static_cast<float>(B);
+}
+
+// ---- backward --------------------------------------------------------------------------------
+// One CTA per batch row: gradient of everything downstream of the logits.
+__global__ void __launch_bounds__(kSelectThreads)
+dlogits_kernel(const float* __restrict__ probs, const long long* __restrict__ idx,
+               const float* __restrict__ weights, const float* __restrict__ comb_w,
+               const float* __restrict__ row_stats, const float* __restrict__ chapter_stats,
+               const float* __restrict__ d_weights, const float* __restrict__ d_comb_w,
+               const float* __restrict__ d_losses, float* __restrict__ d_logits,
+               int B, int C, int k_sel, int S, float rho) {
+  extern __shared__ float dp[];   // [C]
+  __shared__ float red[33];
+  __shared__ float s_dv[1024];    // k_sel <= 1024
+  __shared__ float s_scal[2];
+  const int b = blockIdx.x;
+  const float* p = probs + static_cast<long long>(b) * C;
+  const float lse = row_stats[b * 4 + 0], s_mass = row_stats[b * 4 + 1];
+  const float v_mass = row_stats[b * 4 + 2], u_mass = row_stats[b * 4 + 3];
+  const float g_lb = d_losses ? d_losses[0] : 0.f, g_aux = d_losses ? d_losses[1] : 0.f;
+  const float g_z = d_losses ? d_losses[2] : 0.f, g_ent = d_losses ? d_losses[3] : 0.f;
+  const int kc = S + k_sel;
+
+  // (a)+(b): gradients of the k selected (unnormalised) masked probabilities v_j
+  if (threadIdx.x == 0) {
+    float dotu = 0.f;
+    if (d_comb_w != nullptr && S > 0)
+      for (int i = 0; i < kc; ++i) dotu += d_comb_w[static_cast<long long>(b) * kc + i] * comb_w[static_cast<long long>(b) * kc + i];
+    float dotw = 0.f;
+    for (int j = 0; j < k_sel; ++j) {
+      float dw = d_weights ? d_weights[static_cast<long long>(b) * k_sel + j] : 0.f;
+      if (d_comb_w != nullptr) {
+        const float dcu = d_comb_w[static_cast<long long>(b) * kc + S + j];
+        if (S > 0) dw += rho * ((u_mass >= 1e-12f) ? (dcu - dotu) / u_mass : dcu / 1e-12f);
+        else dw += dcu;
+      }
+      s_dv[j] = dw;
+      dotw += dw * weights[static_cast<long long>(b) * k_sel + j];
+    }
+    float A = 0.f;
+    for (int j = 0; j < k_sel; ++j) {
+      const float dv = (v_mass >= 1e-12f) ? (s_dv[j] - dotw) / v_mass : s_dv[j] / 1e-12f;
+      s_dv[j] = dv;
+      A += dv * (weights[static_cast<long long>(b) * k_sel + j] * fmaxf(v_mass, 1e-12f));   // v_j
+    }
+    s_scal[0] = A;
+  }
+  __syncthreads();
+  const float A = s_scal[0];
+  const bool renorm = (S > 0);
+  const float inv_s = renorm ? ((s_mass >= 1e-12f) ? 1.f / s_mass : 1e12f) : 1.f;
+  const float dense = (renorm && s_mass >= 1e-12f) ? -A * inv_s : 0.f;
+  const float invB = 1.f / static_cast<float>(B), invC = 1.f / static_cast<float>(C);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float pv = p[c];
+    float g = (c >= S) ? dense : 0.f;
+    g += g_lb * static_cast<float>(C) * chapter_stats[c] * invB;
+    g += g_aux * (2.f * invC) * (chapter_stats[C + c] - invC) * (2.f * pv * invB);
+    g += g_ent * (-invB) * (logf(fmaxf(pv, 1e-12f)) + (pv > 1e-12f ? 1.f : 0.f));
+    dp[c] = g;
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < k_sel; j += blockDim.x) {
+    const int c = static_cast<int>(idx[static_cast<long long>(b) * k_sel + j]);
+    dp[c] += s_dv[j] * inv_s;    // chapter ids in one row are distinct
+  }
+  __syncthreads();
+  float dot = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) dot += dp[c] * p[c];
+  dot = block_sum(dot, red);
+  const float zc = g_z * 2.f * lse * invB;
+  for (int c = threadIdx.x; c < C; c += blockDim.x)
+    d_logits[static_cast<long long>(b) * C + c] = p[c] * (dp[c] - dot + zc);
+}
+
+// d_w[c,:] = sum_b d_logits[b,c] * pooled[b,:]; d_bias[c] = sum_b d_logits[b,c]; one warp per chapter
+__global__ void dweight_kernel(const float* __restrict__ d_logits, const float* __restrict__ pooled,
+                               float* __restrict__ d_w, float* __restrict__ d_bias, int B, int d, int C) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (c >= C) return;
+  float bsum = 0.f;
+  for (int b = 0; b < B; ++b) bsum += d_logits[static_cast<long long>(b) * C + c];
+  if (lane == 0 && d_bias) d_bias[c] = bsum;
+  for (int k = lane; k < d; k += 32) {
+    float acc = 0.f;
+    for (int b = 0; b < B; ++b) acc = fmaf(d_logits[static_cast<long long>(b) * C + c], pooled[static_cast<long long>(b) * d + k], acc);
+    d_w[static_cast<long long>(c) * d + k] = acc;
+  }
+}
+
+// partial[chunk][b][k] = sum over the chunk's chapters of d_logits[b,c] * w[c,k]
+__global__ void dpooled_partial_kernel(const float* __restrict__ d_logits, const float* __restrict__ w,
+                                       float* __restrict__ partial, int B, int d, int C) {
+  __shared__ float dz[8][kDpChunk];
+  const int c0 = blockIdx.x * kDpChunk;
+  const int nc = min(kDpChunk, C - c0);
+  for (int b0 = 0; b0 < B; b0 += 8) {
+    const int nb = min(8, B - b0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb * kDpChunk; i += blockDim.x) {
+      const int j = i / kDpChunk, cc = i - j * kDpChunk;
+      dz[j][cc] = (cc < nc) ? d_logits[static_cast<long long>(b0 + j) * C + c0 + cc] : 0.f;
+    }
+    __syncthreads();
+    for (int k = threadIdx.x; k < d; k += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int cc = 0; cc < nc; ++cc) {
+        const float wv = w[static_cast<long long>(c0 + cc) * d + k];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = fmaf(dz[j][cc], wv, acc[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < nb) partial[(static_cast<long long>(blockIdx.x) * B + b0 + j) * d + k] = acc[j];
+    }
+  }
+}
+__global__ void dpooled_finish_kernel(const float* __restrict__ partial, float* __restrict__ d_pooled,
+                                      int nchunks, int total) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float acc = 0.f;
+  for (int ch = 0; ch < nchunks; ++ch) acc += partial[static_cast<long long>(ch) * total + i];
+  d_pooled[i] = acc;
+}
+template <typename T>
+__global__ void dh_broadcast_kernel(const float* __restrict__ d_pooled, T* __restrict__ d_h, int L, int d,
+                                    long long total, int accumulate) {
+  const float invL = 1.f / static_cast<float>(L);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / d;
+    const int c = static_cast<int>(i - row * d);
+    const int b = static_cast<int>(row / L);
+    float v = d_pooled[static_cast<long long>(b) * d + c] * invL;
+    if (accumulate) v += to_f32(d_h[i]);
+    if constexpr (sizeof(T) == 4) d_h[i] = v; else d_h[i] = __float2bfloat16(v);
+  }
+}
+
+inline int k_selected(const moc_router_shape* s) {
+  int k = s->top_k;
+  const int avail = s->num_chapters - s->num_shared;
+  if (k > avail) k = avail;
+  return k < 0 ? 0 : k;
+}
+inline size_t ws_bytes(const moc_router_shape* s) {
+  const size_t pool = static_cast<size_t>(s->batch) * kPoolSplits * s->hidden_dim;
+  const size_t dp = static_cast<size_t>(ceil_div(s->num_chapters, kDpChunk)) * s->batch * s->hidden_dim;
+  const size_t loss = static_cast<size_t>(ceil_div(s->num_chapters, kLossChunk)) * 3;
+  size_t n = pool > dp ? pool : dp;
+  n += loss;
+  return n * sizeof(float);
+}
+inline int check_shape(const moc_router_shape* s) {
+  MOC_REQUIRE(s != nullptr, "shape is NULL");
+  MOC_REQUIRE(s->batch > 0 && s->seq > 0 && s->hidden_dim > 0, "empty router input");
+  MOC_REQUIRE(s->num_chapters > 0, "num_chapters must be > 0");
+  MOC_REQUIRE(s->top_k > 0 && s->top_k <= s->num_chapters, "top_k must be in [1, num_chapters]");
+  MOC_REQUIRE(s->num_shared >= 0 && s->num_shared <= s->num_chapters, "exclude_prefix_chapters out of range");
+  MOC_REQUIRE(s->top_k <= 1024, "top_k above 1024 is not supported");
+  MOC_REQUIRE(s->h_dtype == MOC_F32 || s->h_dtype == MOC_BF16, "bad h_dtype");
+  MOC_REQUIRE((static_cast<size_t>(s->num_chapters) + 2 * 1024) * 4 <= 200 * 1024, "num_chapters too large");
+  return MOC_OK;
+}
+
+}  // namespace
+}  // namespace moc
+
+using namespace moc;
+
+extern "C" size_t moc_router_workspace_bytes(const moc_router_shape* s) { return s ? ws_bytes(s) : 0; }
+
+extern "C" int moc_router_fwd(const moc_router_shape* s, const void* h, const float* w, const float* bias,
+                              float* pooled, float* logits, float* probs, int64_t* idx, float* weights,
+                              int32_t* comb_idx, float* comb_w, float* row_stats, float* chapter_stats,
+                              float* losses, void* workspace, size_t workspace_bytes, int32_t* status,
+                              void* stream_) {
+  int rc = check_shape(s);
+  if (rc != MOC_OK) return rc;
+  MOC_REQUIRE(workspace_bytes >= ws_bytes(s), "router workspace too small");
+  MOC_REQUIRE(h && w && pooled && logits && probs && comb_idx && comb_w && row_stats, "NULL router buffer");
+  (void)status;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int B = s->batch, L = s->seq, d = s->hidden_dim, C = s->num_chapters, S = s->num_shared;
+  const int k_sel = k_selected(s);
+  MOC_REQUIRE(k_sel == 0 || (idx && weights), "NULL index / weight buffer");
+  float* ws = static_cast<float*>(workspace);
+  float* loss_partial = ws + (ws_bytes(s) / sizeof(float) - static_cast<size_t>(ceil_div(C, kLossChunk)) * 3);
+
+  dim3 pg(B, kPoolSplits);
+  if (s->h_dtype == MOC_F32)
+    pool_partial_kernel<float><<<pg, 256, 0, stream>>>(static_cast<const float*>(h), ws, L, d);
+  else
+    pool_partial_kernel<__nv_bfloat16><<<pg, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(h), ws, L, d);
+  pool_finish_kernel<<<ceil_div(B * d, 256), 256, 0, stream>>>(ws, pooled, L, d, B * d);
+  {
+    const int warps = 8;
+    const size_t sm = static_cast<size_t>(8) * d * sizeof(float);
+    MOC_CUDA_OK(cudaFuncSetAttribute(logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
+    logits_kernel<<<ceil_div(C, warps), warps * 32, sm, stream>>>(pooled, w, bias, logits, B, d, C);
+  }
+  {
+    const size_t sm = (static_cast<size_t>(C) + 2 * static_cast<size_t>(k_sel > 0 ? k_sel : 1)) * 4;
+    MOC_CUDA_OK(cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
+    select_kernel<<<B, kSelectThreads, sm, stream>>>(logits, probs, reinterpret_cast<long long*>(idx), weights,
+                                                     comb_idx, comb_w, row_stats, C, k_sel, S, s->routed_scale);
+  }
+  if (losses != nullptr) {
+    MOC_REQUIRE(chapter_stats != nullptr, "chapter_stats is NULL");
+    const int nblk = ceil_div(C, kLossChunk);
+    loss_partial_kernel<<<nblk, kLossChunk, 0, stream>>>(probs, reinterpret_cast<const long long*>(idx),
+                                                         chapter_stats, loss_partial, B, C, k_sel);
+    loss_finish_kernel<<<1, 32, 0, stream>>>(loss_partial, row_stats, losses, nblk, B, C);
+  }
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+extern "C" int moc_router_bwd(const moc_router_shape* s, const float* w, const float* pooled,
+                              const float* probs, const int64_t* idx, const float* weights,
+                              const float* comb_w, const float* row_stats, const float* chapter_stats,
+                              const float* d_weights, const float* d_comb_w, const float* d_losses,
+                              float* d_logits, float* d_w, float* d_bias, float* d_pooled, void* d_h,
+                              int32_t accumulate_dh, void* workspace, size_t workspace_bytes,
+                              int32_t* status, void* stream_) {
+  int rc = check_shape(s);
+  if (rc != MOC_OK) return rc;
+  MOC_REQUIRE(workspace_bytes >= ws_bytes(s), "router workspace too small");
+  MOC_REQUIRE(w && pooled && probs && comb_w && row_stats && d_logits && d_w && d_pooled, "NULL router buffer");
+  MOC_REQUIRE(d_losses == nullptr || chapter_stats != nullptr, "loss gradients need chapter_stats");
+  (void)status;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int B = s->batch, L = s->seq, d = s->hidden_dim, C = s->num_chapters, S = s->num_shared;
+  const int k_sel = k_selected(s);
+  float* ws = static_cast<float*>(workspace);
+  {
+    const size_t sm = static_cast<size_t>(C) * 4;
+    MOC_CUDA_OK(cudaFuncSetAttribute(dlogits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
+    dlogits_kernel<<<B, kSelectThreads, sm, stream>>>(probs, reinterpret_cast<const long long*>(idx), weights,
+                                                      comb_w, row_stats, chapter_stats, d_weights, d_comb_w,
+                                                      d_losses, d_logits, B, C, k_sel, S, s->routed_scale);
+  }
+  dweight_kernel<<<ceil_div(C, 8), 256, 0, stream>>>(d_logits, pooled, d_w, d_bias, B, d, C);
+  const int nchunks = ceil_div(C, kDpChunk);
+  dpooled_partial_kernel<<<nchunks, 256, 0, stream>>>(d_logits, w, ws, B, d, C);
+  dpooled_finish_kernel<<<ceil_div(B * d, 256), 256, 0, stream>>>(ws, d_pooled, nchunks, B * d);
+  if (d_h != nullptr) {
+    const long long total = static_cast<long long>(B) * L * d;
+    const int blocks = static_cast<int>(total / 256 / 4 + 1 < 148 * 16 ? total / 256 / 4 + 1 : 148 * 16);
+    if (s->h_dtype == MOC_F32)
+      dh_broadcast_kernel<float><<<blocks, 256, 0, stream>>>(d_pooled, static_cast<float*>(d_h), L, d, total, accumulate_dh);
+    else
+      dh_broadcast_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(d_pooled, static_cast<__nv_bfloat16*>(d_h), L, d, total, accumulate_dh);
+  }
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}

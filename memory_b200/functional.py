@@ -1,0 +1,219 @@
+"""Autograd bindings of the CUDA operators.
+
+Three differentiable pieces mirror the reference's sequence-level memory layer
+(memory_transformer/model.py:624-692 followed by memory_block.py:549-558):
+
+``route``             router forward/backward (router.py:94-156, 197-260; model.py:356-391)
+``gather_chapters``   chapter gather + optional row norm + weight scaling (memory_bank.py:244-293,
+                      model.py:393-432, 689-692), backward scatters only into touched chapters
+``cross_attention``   Q/K/V/O projections and joint-softmax attention over already gathered rows
+                      (memory_attention.py:209-261, 298-316, 452-478)
+
+``memory_layer`` chains them without materialising anything on the host.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import ops
+
+LOSS_KEYS = ("load_balance", "auxiliary", "z_loss", "entropy")
+
+
+class SparseBankGrad:
+    """Receives bank gradients as (chapter ids, [U*T, d] rows) instead of a dense tensor.
+
+    Attach one to a bank parameter with ``param.moc_sparse_grad = SparseBankGrad()``; backward
+    passes then append here and return no dense gradient for the bank.
+    """
+
+    def __init__(self):
+        self.entries = []   # list of (uniq int32 [n_pairs], num_unique int32 [1], rows fp32 [n_pairs*T, d], T)
+
+    def add(self, uniq, num_unique, rows, tokens_per_chapter):
+        self.entries.append((uniq, num_unique, rows, int(tokens_per_chapter)))
+
+    def clear(self):
+        self.entries.clear()
+
+    def to_dense(self, like: torch.Tensor) -> torch.Tensor:
+        dense = torch.zeros(like.shape, dtype=torch.float32, device=like.device)
+        for uniq, num_unique, rows, t in self.entries:
+            ops.scatter_bank_grad(rows, {"uniq": uniq, "num_unique": num_unique}, t, dense)
+        return dense
+
+
+# --------------------------------------------------------------------------------------------
+# router
+# --------------------------------------------------------------------------------------------
+class _Route(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, weight, bias, top_k, num_shared, routed_scale, with_losses):
+        r = ops.router_fwd(h, weight, bias, top_k, num_shared, routed_scale, with_losses)
+        ctx.cfg = (tuple(h.shape), h.dtype, int(top_k), int(num_shared), float(routed_scale), bias is not None)
+        ctx.saved = r
+        ctx.save_for_backward(weight)
+        ctx.mark_non_differentiable(r["idx"], r["comb_idx"])
+        losses = r["losses"] if with_losses else torch.zeros(4, dtype=torch.float32, device=h.device)
+        return r["idx"], r["weights"], r["comb_idx"], r["comb_w"], losses
+
+    @staticmethod
+    def backward(ctx, _g_idx, g_w, _g_cidx, g_cw, g_losses):
+        (weight,) = ctx.saved_tensors
+        h_shape, h_dtype, top_k, num_shared, routed_scale, has_bias = ctx.cfg
+        if g_w is not None:
+            g_w = g_w.float()
+        if g_cw is not None:
+            g_cw = g_cw.float()
+        if g_losses is not None:
+            g_losses = g_losses.float()
+        r = ops.router_bwd(h_shape, h_dtype, weight, ctx.saved, top_k, num_shared, routed_scale,
+                           g_w, g_cw, g_losses, want_dh=ctx.needs_input_grad[0])
+        d_w = r["d_w"].to(weight.dtype) if ctx.needs_input_grad[1] else None
+        d_b = r["d_bias"] if (has_bias and ctx.needs_input_grad[2]) else None
+        return r["d_h"], d_w, d_b, None, None, None, None
+
+
+def route(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, num_shared: int,
+          routed_scale: float = 1.0, with_losses: bool = True):
+    """Returns (idx int64 [B,k'], weights [B,k'], comb_idx int32 [B,S+k'], comb_w [B,S+k'], losses dict)."""
+    idx, w, cidx, cw, lv = _Route.apply(h, weight, bias, int(top_k), int(num_shared), float(routed_scale),
+                                        bool(with_losses))
+    losses = {k: lv[i] for i, k in enumerate(LOSS_KEYS)} if with_losses else {}
+    return idx, w, cidx, cw, losses
+
+
+# --------------------------------------------------------------------------------------------
+# gather
+# --------------------------------------------------------------------------------------------
+def _bank_backward(sink, d_mem, bank, t, comb_idx, comb_w, norm, eps, stats, num_chapters, want_dw, want_bank):
+    seg = ops.chapter_segments(comb_idx, num_chapters)
+    d_cw, rows = ops.gather_rows_bwd(d_mem, bank, t, comb_idx, comb_w, norm, eps, stats, seg,
+                                     want_dw=want_dw, want_bank=want_bank)
+    d_bank = None
+    if want_bank:
+        if sink is not None:
+            sink.add(seg["uniq"], seg["num_unique"], rows, t)
+        else:
+            d_bank = torch.zeros(bank.shape, dtype=torch.float32, device=bank.device)
+            ops.scatter_bank_grad(rows, seg, t, d_bank)
+            d_bank = d_bank.to(bank.dtype)
+    return d_cw, d_bank
+
+
+class _GatherChapters(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, bank, comb_idx, comb_w, tokens_per_chapter, norm_type, eps, out_dtype, sink):
+        out, stats = ops.gather_rows_fwd(bank, tokens_per_chapter, comb_idx, comb_w, norm_type, eps, out_dtype)
+        ctx.cfg = (int(tokens_per_chapter), norm_type, float(eps), bank.shape[0] // int(tokens_per_chapter))
+        ctx.sink = sink
+        ctx.save_for_backward(bank, comb_idx, comb_w, stats)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        bank, comb_idx, comb_w, stats = ctx.saved_tensors
+        t, norm, eps, num_chapters = ctx.cfg
+        g2 = g.reshape(-1, g.shape[-1])
+        d_cw, d_bank = _bank_backward(ctx.sink, g2, bank, t, comb_idx, comb_w, norm, eps, stats, num_chapters,
+                                      want_dw=comb_w is not None and ctx.needs_input_grad[2],
+                                      want_bank=ctx.needs_input_grad[0])
+        return d_bank, None, d_cw, None, None, None, None, None
+
+
+def gather_chapters(bank: torch.Tensor, comb_idx: torch.Tensor, comb_w: Optional[torch.Tensor],
+                    tokens_per_chapter: int, norm_type: Optional[str] = None, eps: float = 1e-5,
+                    out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """[B, K*T, d] rows of the selected chapters, normalised and scaled by ``comb_w``."""
+    sink = getattr(bank, "moc_sparse_grad", None)
+    return _GatherChapters.apply(bank, comb_idx.to(torch.int32), comb_w, int(tokens_per_chapter), norm_type,
+                                 float(eps), out_dtype or bank.dtype, sink)
+
+
+# --------------------------------------------------------------------------------------------
+# cross attention over gathered rows
+# --------------------------------------------------------------------------------------------
+class _CrossAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, memory, wq, wk, wv, wo, num_heads, num_kv_heads, compute_dtype):
+        b, l, d = h.shape
+        cd = compute_dtype
+        n_sel = memory.shape[-2]
+        mem_shared = memory.dim() == 2
+        h2 = ops.cast(h.reshape(b * l, d), cd)
+        m2 = ops.cast(memory.reshape(-1, memory.shape[-1]), cd)
+        wq_c, wo_c = ops.cast(wq, cd), ops.cast(wo, cd)
+        wkv_c = ops.cast(torch.cat([wk, wv], dim=0), cd)
+        q = ops.gemm(h2, wq_c)                                   # [B*L, H*D]
+        kv = ops.gemm(m2, wkv_c)                                 # [(B*)n_sel, 2*HK*D]
+        if mem_shared:
+            kv = kv.unsqueeze(0).expand(b, -1, -1).contiguous()
+        head_dim = d // num_heads
+        scale = head_dim ** -0.5
+        o, lse = ops.attn_fwd(q.view(b, l, -1), kv.view(b, n_sel, -1), num_heads, num_kv_heads, scale)
+        out = ops.gemm(o.view(b * l, -1), wo_c)
+        ctx.cfg = (num_heads, num_kv_heads, scale, cd, mem_shared, h.dtype, memory.dtype)
+        ctx.save_for_backward(h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse)
+        ctx.w_dtypes = (wq.dtype, wk.dtype, wv.dtype, wo.dtype)
+        return out.view(b, l, -1).to(h.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse = ctx.saved_tensors
+        num_heads, num_kv_heads, scale, cd, mem_shared, h_dtype, mem_dtype = ctx.cfg
+        b, l, _ = o.shape
+        d = h2.shape[1]
+        g2 = ops.cast(g.reshape(b * l, -1).contiguous(), cd)
+        f32 = torch.float32
+        split = 1 if cd == torch.float32 else max(1, min(16, (b * l) // 2048))
+        d_o = ops.gemm(g2, wo_c, b_kmajor=False)                                      # [B*L, H*D]
+        d_wo = ops.gemm(g2, o.view(b * l, -1), a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split)
+        d_q, d_kv = ops.attn_bwd(q.view(b, l, -1), kv, o, lse, d_o.view(b, l, -1), num_heads, num_kv_heads, scale)
+        d_q2 = d_q.view(b * l, -1)
+        d_h = ops.gemm(d_q2, wq_c, b_kmajor=False)
+        d_wq = ops.gemm(d_q2, h2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split)
+        d_kv2 = d_kv.view(-1, d_kv.shape[-1])
+        if mem_shared:
+            d_kv2 = d_kv.float().sum(dim=0).to(cd)
+        rows = d_kv2.shape[0]
+        split_kv = 1 if cd == torch.float32 else max(1, min(16, rows // 2048))
+        d_mem = ops.gemm(d_kv2, wkv_c, b_kmajor=False, out_dtype=f32 if cd == f32 else cd)
+        d_wkv = ops.gemm(d_kv2, m2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split_kv)
+        dkv_dim = wkv_c.shape[0] // 2
+        wdt = ctx.w_dtypes
+        d_mem = d_mem.view(-1, d_mem.shape[-1]) if mem_shared else d_mem.view(b, -1, d_mem.shape[-1])
+        return (d_h.view(b, l, d).to(h_dtype), d_mem.to(mem_dtype), d_wq.to(wdt[0]), d_wkv[:dkv_dim].to(wdt[1]),
+                d_wkv[dkv_dim:].to(wdt[2]), d_wo.to(wdt[3]), None, None, None)
+
+
+def cross_attention(h: torch.Tensor, memory: torch.Tensor, wq, wk, wv, wo, num_heads: int,
+                    num_kv_heads: Optional[int] = None, compute_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """softmax(Q K^T / sqrt(D)) V over the given memory rows, with the four projections."""
+    return _CrossAttention.apply(h, memory, wq, wk, wv, wo, int(num_heads), int(num_kv_heads or num_heads),
+                                 compute_dtype or h.dtype)
+
+
+# --------------------------------------------------------------------------------------------
+# the fused layer
+# --------------------------------------------------------------------------------------------
+def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tensor,
+                 router_weight: torch.Tensor, router_bias: Optional[torch.Tensor],
+                 wq, wk, wv, wo, *, num_heads: int, num_kv_heads: Optional[int], tokens_per_chapter: int,
+                 top_k: int, num_shared_chapters: int = 1, routed_scaling_factor: float = 2.5,
+                 norm_type: Optional[str] = None, norm_eps: float = 1e-5, with_losses: bool = True,
+                 compute_dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, Dict[str, torch.Tensor], Dict]:
+    """Sequence-level Mixture-of-Chapters memory layer on the GPU.
+
+    Returns (out [B,L,d], router losses, info) with info = indices / weights of the routing.
+    """
+    cd = compute_dtype or h_attn.dtype
+    idx, w, cidx, cw, losses = route(h_router, router_weight, router_bias, top_k, num_shared_chapters,
+                                     routed_scaling_factor, with_losses)
+    k_sel = idx.shape[1]
+    # the reference only normalises when both a shared and a routed slice exist (model.py:413-418)
+    norm = norm_type if (num_shared_chapters > 0 and k_sel > 0) else None
+    memory = gather_chapters(bank, cidx, cw, tokens_per_chapter, norm, norm_eps, out_dtype=cd)
+    out = cross_attention(h_attn, memory, wq, wk, wv, wo, num_heads, num_kv_heads, cd)
+    return out, losses, {"indices": idx, "weights": w, "combined_indices": cidx, "combined_weights": cw}

@@ -1,0 +1,79 @@
+"""``MemoryCrossAttention`` with the reference's constructor, parameters and forward contract
+(memory_transformer/memory_attention.py:60-146, 320-478), computed by the CUDA kernels."""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import functional as F_moc
+
+
+class MemoryCrossAttention(nn.Module):
+    """Cross attention from hidden states to memory rows that were already gathered and weighted.
+
+    ``forward(hidden_states, memory)`` takes memory of shape (N, d) or (B, N, d) and returns
+    ``(output (B, L, d), None)``.  Low-rank and reduced-dimension projection variants of the
+    reference are not part of this path and are rejected.  ``use_flash_attention`` and
+    ``gradient_checkpointing`` are accepted for signature compatibility; the kernels never
+    materialise the score matrix, so neither changes what is computed.
+    """
+
+    def __init__(self, hidden_dim: int, num_heads: int, num_kv_heads: Optional[int] = None,
+                 memory_dim: Optional[int] = None, use_low_rank_projections: bool = False,
+                 projection_rank: Optional[int] = None, reduced_dim_mode: bool = False,
+                 reduced_dim: Optional[int] = None, wo_init_zero: bool = True, dropout: float = 0.0,
+                 use_flash_attention: bool = True, gradient_checkpointing: bool = False,
+                 compute_dtype: Optional[torch.dtype] = None):
+        super().__init__()
+        if use_low_rank_projections or reduced_dim_mode:
+            raise NotImplementedError("low-rank / reduced-dim projections are outside the accelerated path")
+        if dropout != 0.0:
+            raise NotImplementedError("attention dropout is not supported by the fused kernels")
+        self.hidden_dim = hidden_dim
+        self.memory_dim = memory_dim if memory_dim is not None else hidden_dim
+        self.num_heads = num_heads
+        self.num_kv_heads = num_heads if num_kv_heads is None else num_kv_heads
+        if self.num_heads <= 0:
+            raise ValueError(f"num_heads must be > 0, got {self.num_heads}")
+        if hidden_dim % num_heads != 0:
+            raise ValueError(f"hidden_dim ({hidden_dim}) must be divisible by num_heads ({num_heads})")
+        if self.num_kv_heads <= 0:
+            raise ValueError(f"num_kv_heads must be > 0, got {self.num_kv_heads}")
+        if self.num_heads % self.num_kv_heads != 0:
+            raise ValueError(
+                f"num_heads ({self.num_heads}) must be divisible by num_kv_heads ({self.num_kv_heads})")
+        self.head_dim = hidden_dim // num_heads
+        self.kv_hidden_dim = self.num_kv_heads * self.head_dim
+        self.num_kv_groups = self.num_heads // self.num_kv_heads
+        self.scale = self.head_dim ** -0.5
+        self.dropout = dropout
+        self.use_flash_attention = use_flash_attention
+        self.gradient_checkpointing = gradient_checkpointing
+        self.reduced_dim_mode = False
+        self.use_low_rank_projections = False
+        self.compute_dtype = compute_dtype
+        self.q_proj = nn.Linear(self.hidden_dim, self.hidden_dim, bias=False)
+        self.k_proj = nn.Linear(self.memory_dim, self.kv_hidden_dim, bias=False)
+        self.v_proj = nn.Linear(self.memory_dim, self.kv_hidden_dim, bias=False)
+        self.o_proj = nn.Linear(self.hidden_dim, self.hidden_dim, bias=False)
+        if wo_init_zero:
+            nn.init.zeros_(self.o_proj.weight)
+
+    def forward(self, hidden_states: torch.Tensor, memory: Optional[torch.Tensor] = None,
+                token_routing_state: Optional[Dict[str, Any]] = None,
+                token_routing_kernel_version: str = "v2", return_attn_weights: bool = False
+                ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        if token_routing_state is not None:
+            if return_attn_weights:
+                raise ValueError("return_attn_weights=True is not supported for token_routing_state path.")
+            raise NotImplementedError("token-level routing is not wired into this module yet")
+        if memory is None:
+            raise ValueError("memory must be provided when token_routing_state is None.")
+        if return_attn_weights:
+            raise NotImplementedError("attention weights are never materialised by the fused kernels")
+        out = F_moc.cross_attention(hidden_states, memory, self.q_proj.weight, self.k_proj.weight,
+                                    self.v_proj.weight, self.o_proj.weight, self.num_heads, self.num_kv_heads,
+                                    self.compute_dtype or hidden_states.dtype)
+        return out, None

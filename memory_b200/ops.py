@@ -1,0 +1,281 @@
+"""Tensor-level wrappers of the C-ABI entry points: allocate outputs, pass raw pointers.
+
+Every function requires CUDA tensors; nothing here computes on the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib as L
+
+
+def _contig(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    return None if t is None else (t if t.is_contiguous() else t.contiguous())
+
+
+# --------------------------------------------------------------------------------------------
+# router
+# --------------------------------------------------------------------------------------------
+def _router_shape(h: torch.Tensor, num_chapters: int, top_k: int, num_shared: int, routed_scale: float):
+    b, l, d = h.shape
+    return L.RouterShape(b, l, d, num_chapters, top_k, num_shared, float(routed_scale), L.dtype_code(h.dtype))
+
+
+def router_selected_k(num_chapters: int, top_k: int, num_shared: int) -> int:
+    return max(0, min(int(top_k), int(num_chapters) - int(num_shared)))
+
+
+def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top_k: int,
+               num_shared: int, routed_scale: float, with_losses: bool) -> Dict[str, torch.Tensor]:
+    L.require_cuda(h, weight, bias)
+    if h.dim() != 3:
+        raise ValueError(f"hidden_states must be 3D (B, T, D), got shape {tuple(h.shape)}")
+    h = _contig(h)
+    weight = _contig(weight.float())
+    bias = _contig(bias.float()) if bias is not None else None
+    b, l, d = h.shape
+    c = weight.shape[0]
+    k = router_selected_k(c, top_k, num_shared)
+    dev = h.device
+    s = _router_shape(h, c, top_k, num_shared, routed_scale)
+    f32 = dict(dtype=torch.float32, device=dev)
+    out = {
+        "pooled": torch.empty(b, d, **f32), "logits": torch.empty(b, c, **f32), "probs": torch.empty(b, c, **f32),
+        "idx": torch.empty(b, k, dtype=torch.int64, device=dev), "weights": torch.empty(b, k, **f32),
+        "comb_idx": torch.empty(b, num_shared + k, dtype=torch.int32, device=dev),
+        "comb_w": torch.empty(b, num_shared + k, **f32),
+        "row_stats": torch.empty(b, 4, **f32), "chapter_stats": torch.empty(2, c, **f32),
+        "losses": torch.empty(4, **f32) if with_losses else None,
+    }
+    lib = L.lib()
+    ws_bytes = lib.moc_router_workspace_bytes(C.byref(s))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    rc = lib.moc_router_fwd(C.byref(s), L.ptr(h), L.ptr(weight), L.ptr(bias), L.ptr(out["pooled"]),
+                            L.ptr(out["logits"]), L.ptr(out["probs"]), L.ptr(out["idx"]), L.ptr(out["weights"]),
+                            L.ptr(out["comb_idx"]), L.ptr(out["comb_w"]), L.ptr(out["row_stats"]),
+                            L.ptr(out["chapter_stats"]), L.ptr(out["losses"]), L.ptr(ws), ws_bytes,
+                            L.ptr(L.status_word(dev)), L.stream_ptr(dev))
+    L.check(rc, "moc_router_fwd")
+    return out
+
+
+def router_bwd(h_shape, h_dtype, weight: torch.Tensor, saved: Dict[str, torch.Tensor], top_k: int,
+               num_shared: int, routed_scale: float, d_weights: Optional[torch.Tensor],
+               d_comb_w: Optional[torch.Tensor], d_losses: Optional[torch.Tensor],
+               want_dh: bool) -> Dict[str, torch.Tensor]:
+    b, l, d = h_shape
+    c = weight.shape[0]
+    dev = weight.device
+    s = L.RouterShape(b, l, d, c, top_k, num_shared, float(routed_scale), L.dtype_code(h_dtype))
+    f32 = dict(dtype=torch.float32, device=dev)
+    weight = _contig(weight.float())
+    out = {"d_logits": torch.empty(b, c, **f32), "d_w": torch.empty(c, d, **f32), "d_bias": torch.empty(c, **f32),
+           "d_pooled": torch.empty(b, d, **f32),
+           "d_h": torch.empty(b, l, d, dtype=h_dtype, device=dev) if want_dh else None}
+    lib = L.lib()
+    ws_bytes = lib.moc_router_workspace_bytes(C.byref(s))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    rc = lib.moc_router_bwd(C.byref(s), L.ptr(weight), L.ptr(saved["pooled"]), L.ptr(saved["probs"]),
+                            L.ptr(saved["idx"]), L.ptr(saved["weights"]), L.ptr(saved["comb_w"]),
+                            L.ptr(saved["row_stats"]), L.ptr(saved["chapter_stats"]),
+                            L.ptr(_contig(d_weights)), L.ptr(_contig(d_comb_w)), L.ptr(_contig(d_losses)),
+                            L.ptr(out["d_logits"]), L.ptr(out["d_w"]), L.ptr(out["d_bias"]), L.ptr(out["d_pooled"]),
+                            L.ptr(out["d_h"]), 0, L.ptr(ws), ws_bytes, L.ptr(L.status_word(dev)), L.stream_ptr(dev))
+    L.check(rc, "moc_router_bwd")
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# gather
+# --------------------------------------------------------------------------------------------
+def gather_rows_fwd(bank: torch.Tensor, tokens_per_chapter: int, comb_idx: torch.Tensor,
+                    comb_w: Optional[torch.Tensor], norm_type: Optional[str], eps: float,
+                    out_dtype: torch.dtype) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    L.require_cuda(bank, comb_idx, comb_w)
+    bank = _contig(bank)
+    comb_idx = _contig(comb_idx.to(torch.int32))
+    b, k = comb_idx.shape
+    n_rows, d = bank.shape
+    t = int(tokens_per_chapter)
+    out = torch.empty(b, k * t, d, dtype=out_dtype, device=bank.device)
+    code = L.NORM_CODES[norm_type]
+    stats = torch.empty(b * k * t, 2, dtype=torch.float32, device=bank.device) if code != 0 else None
+    rc = L.lib().moc_gather_rows_fwd(L.ptr(bank), L.dtype_code(bank.dtype), n_rows, d, t, L.ptr(comb_idx),
+                                     L.ptr(_contig(comb_w)), b, k, code, float(eps), L.ptr(out),
+                                     L.dtype_code(out_dtype), L.ptr(stats), L.ptr(L.status_word(bank.device)),
+                                     L.stream_ptr(bank.device))
+    L.check(rc, "moc_gather_rows_fwd")
+    return out, stats
+
+
+def chapter_segments(comb_idx: torch.Tensor, num_chapters: int) -> Dict[str, torch.Tensor]:
+    comb_idx = _contig(comb_idx.to(torch.int32))
+    n = comb_idx.numel()
+    dev = comb_idx.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    seg = {"uniq": torch.empty(n, **i32), "seg_offsets": torch.empty(n + 1, **i32),
+           "seg_pairs": torch.empty(n, **i32), "pair_to_uniq": torch.empty(n, **i32),
+           "num_unique": torch.empty(1, **i32)}
+    rc = L.lib().moc_chapter_segments(L.ptr(comb_idx), n, int(num_chapters), L.ptr(seg["uniq"]),
+                                      L.ptr(seg["seg_offsets"]), L.ptr(seg["seg_pairs"]),
+                                      L.ptr(seg["pair_to_uniq"]), L.ptr(seg["num_unique"]),
+                                      L.ptr(L.status_word(dev)), L.stream_ptr(dev))
+    L.check(rc, "moc_chapter_segments")
+    return seg
+
+
+def gather_rows_bwd(d_mem: torch.Tensor, bank: torch.Tensor, tokens_per_chapter: int, comb_idx: torch.Tensor,
+                    comb_w: Optional[torch.Tensor], norm_type: Optional[str], eps: float,
+                    row_stats: Optional[torch.Tensor], seg: Dict[str, torch.Tensor],
+                    want_dw: bool = True, want_bank: bool = True) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+    bank = _contig(bank)
+    d_mem = _contig(d_mem)
+    comb_idx = _contig(comb_idx.to(torch.int32))
+    b, k = comb_idx.shape
+    n_rows, d = bank.shape
+    t = int(tokens_per_chapter)
+    dev = bank.device
+    d_comb_w = torch.empty(b, k, dtype=torch.float32, device=dev) if want_dw else None
+    bank_grad = torch.empty(b * k * t, d, dtype=torch.float32, device=dev) if want_bank else None
+    rc = L.lib().moc_gather_rows_bwd(L.ptr(d_mem), L.dtype_code(d_mem.dtype), L.ptr(bank), L.dtype_code(bank.dtype),
+                                     n_rows, d, t, L.ptr(comb_idx), L.ptr(_contig(comb_w)), b, k,
+                                     L.NORM_CODES[norm_type], float(eps), L.ptr(row_stats), L.ptr(seg["uniq"]),
+                                     L.ptr(seg["seg_offsets"]), L.ptr(seg["seg_pairs"]), L.ptr(seg["num_unique"]),
+                                     L.ptr(d_comb_w), L.ptr(bank_grad), L.ptr(L.status_word(dev)), L.stream_ptr(dev))
+    L.check(rc, "moc_gather_rows_bwd")
+    return d_comb_w, bank_grad
+
+
+def scatter_bank_grad(bank_grad: torch.Tensor, seg: Dict[str, torch.Tensor], tokens_per_chapter: int,
+                      dense: torch.Tensor) -> None:
+    """dense[uniq[u]*T + r] += bank_grad[u*T + r] for the chapters listed in ``seg``."""
+    n_rows, d = dense.shape
+    rc = L.lib().moc_scatter_bank_grad(L.ptr(bank_grad), L.ptr(seg["uniq"]), L.ptr(seg["num_unique"]),
+                                       seg["uniq"].numel(), int(tokens_per_chapter), d, L.ptr(dense), n_rows,
+                                       L.ptr(L.status_word(dense.device)), L.stream_ptr(dense.device))
+    L.check(rc, "moc_scatter_bank_grad")
+
+
+# --------------------------------------------------------------------------------------------
+# projections
+# --------------------------------------------------------------------------------------------
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_kmajor: bool = True, b_kmajor: bool = True,
+         out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, accumulate: bool = False,
+         split_k: int = 1, row_scale: Optional[torch.Tensor] = None, scale_block_rows: int = 1,
+         a_row_blocks: Optional[torch.Tensor] = None, a_block_rows: int = 0, m: Optional[int] = None) -> torch.Tensor:
+    """C[M,N] (+)= op(A) op(B).  a_kmajor: A stored [M,K] else [K,M]; b_kmajor: B stored [N,K] else [K,N]."""
+    L.require_cuda(a, b)
+    if a.dtype != b.dtype:
+        raise TypeError("projection operands must share a dtype")
+    a, b = _contig(a), _contig(b)
+    if a_row_blocks is not None:
+        mm, kk = int(m), a.shape[1]
+    elif a_kmajor:
+        mm, kk = a.shape
+    else:
+        kk, mm = a.shape
+    if b_kmajor:
+        nn, kb = b.shape
+    else:
+        kb, nn = b.shape
+    if kk != kb:
+        raise ValueError(f"inner dimensions differ: {kk} vs {kb}")
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else a.dtype
+    if out is None:
+        out = (torch.zeros if (split_k > 1 and not accumulate) else torch.empty)(mm, nn, dtype=out_dtype, device=a.device)
+    g = L.GemmDesc(L.dtype_code(a.dtype), L.dtype_code(out_dtype), mm, nn, kk, int(a_kmajor), int(b_kmajor),
+                   a.stride(0), b.stride(0), out.stride(0), int(accumulate), int(split_k), int(scale_block_rows),
+                   int(a_block_rows), a.shape[0])
+    rc = L.lib().moc_gemm(C.byref(g), L.ptr(a), L.ptr(b), L.ptr(out), L.ptr(_contig(row_scale)),
+                          L.ptr(_contig(a_row_blocks)), L.ptr(L.status_word(a.device)), L.stream_ptr(a.device))
+    L.check(rc, "moc_gemm")
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------------
+def _attn_shape(q: torch.Tensor, kv: torch.Tensor, num_heads: int, num_kv_heads: int, scale: float):
+    b, l, hd = q.shape
+    n_sel = kv.shape[1]
+    d = hd // num_heads
+    if kv.shape[2] != 2 * num_kv_heads * d:
+        raise ValueError("kv must be [B, n_sel, 2 * num_kv_heads * head_dim]")
+    return L.AttnShape(b, l, n_sel, num_heads, num_kv_heads, d, float(scale), L.dtype_code(q.dtype))
+
+
+def attn_fwd(q: torch.Tensor, kv: torch.Tensor, num_heads: int, num_kv_heads: int,
+             scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    L.require_cuda(q, kv)
+    q, kv = _contig(q), _contig(kv)
+    s = _attn_shape(q, kv, num_heads, num_kv_heads, scale)
+    o = torch.empty_like(q)
+    lse = torch.empty(s.batch, num_heads, s.seq, dtype=torch.float32, device=q.device)
+    rc = L.lib().moc_attn_fwd(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse),
+                              L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))
+    L.check(rc, "moc_attn_fwd")
+    return o, lse
+
+
+def attn_bwd(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tensor, d_o: torch.Tensor,
+             num_heads: int, num_kv_heads: int, scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    q, kv, o, d_o = _contig(q), _contig(kv), _contig(o), _contig(d_o)
+    s = _attn_shape(q, kv, num_heads, num_kv_heads, scale)
+    d_q = torch.empty_like(q)
+    d_kv = torch.empty_like(kv)
+    scratch = torch.empty(2, s.batch, num_heads, s.seq, dtype=torch.float32, device=q.device)
+    rc = L.lib().moc_attn_bwd(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse), L.ptr(d_o), L.ptr(d_q),
+                              L.ptr(d_kv), L.ptr(scratch), L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))
+    L.check(rc, "moc_attn_bwd")
+    return d_q, d_kv
+
+
+def sparse_attn_fwd(q, k, v, block_indices, block_size: int, scale: float):
+    L.require_cuda(q, k, v, block_indices)
+    b, tq, hq, d = q.shape
+    _, tk, h, _ = k.shape
+    s = L.SparseAttnShape(b, tq, tk, hq, h, d, block_indices.shape[-1], int(block_size), float(scale),
+                          L.dtype_code(q.dtype))
+    o = torch.empty(b, tq, hq, v.shape[-1], dtype=v.dtype, device=q.device)
+    lse = torch.empty(b, tq, hq, dtype=torch.float32, device=q.device)
+    rc = L.lib().moc_sparse_attn_fwd(C.byref(s), L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(block_indices), L.ptr(o),
+                                     L.ptr(lse), L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))
+    L.check(rc, "moc_sparse_attn_fwd")
+    return o, lse
+
+
+def sparse_attn_bwd(q, k, v, block_indices, o, lse, d_o, block_size: int, scale: float):
+    b, tq, hq, d = q.shape
+    _, tk, h, _ = k.shape
+    s = L.SparseAttnShape(b, tq, tk, hq, h, d, block_indices.shape[-1], int(block_size), float(scale),
+                          L.dtype_code(q.dtype))
+    d_q = torch.empty_like(q)
+    d_k = torch.empty(k.shape, dtype=torch.float32, device=q.device)
+    d_v = torch.empty(v.shape, dtype=torch.float32, device=q.device)
+    rc = L.lib().moc_sparse_attn_bwd(C.byref(s), L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(block_indices), L.ptr(o),
+                                     L.ptr(lse), L.ptr(_contig(d_o)), L.ptr(d_q), L.ptr(d_k), L.ptr(d_v),
+                                     L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))
+    L.check(rc, "moc_sparse_attn_bwd")
+    return d_q, d_k, d_v
+
+
+def cast(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """fp32 <-> bf16 conversion on the device (identity when the dtype already matches)."""
+    if t.dtype == dtype:
+        return t
+    L.require_cuda(t)
+    t = _contig(t)
+    out = torch.empty(t.shape, dtype=dtype, device=t.device)
+    lib = L.lib()
+    if t.dtype == torch.float32 and dtype == torch.bfloat16:
+        rc = lib.moc_cast_f32_to_bf16(L.ptr(t), L.ptr(out), t.numel(), L.stream_ptr(t.device))
+    elif t.dtype == torch.bfloat16 and dtype == torch.float32:
+        rc = lib.moc_cast_bf16_to_f32(L.ptr(t), L.ptr(out), t.numel(), L.stream_ptr(t.device))
+    else:
+        raise TypeError(f"unsupported cast {t.dtype} -> {dtype}")
+    L.check(rc, "moc_cast")
+    return out
