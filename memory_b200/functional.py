@@ -152,7 +152,8 @@ class _CrossAttention(torch.autograd.Function):
             kv = kv.unsqueeze(0).expand(b, -1, -1).contiguous()
         head_dim = d // num_heads
         scale = head_dim ** -0.5
-        o, lse = ops.attn_fwd(q.view(b, l, -1), kv.view(b, n_sel, -1), num_heads, num_kv_heads, scale)
+        kv = kv.view(b, n_sel, -1)
+        o, lse = ops.attn_fwd(q.view(b, l, -1), kv, num_heads, num_kv_heads, scale)
         out = ops.gemm(o.view(b * l, -1), wo_c)
         ctx.cfg = (num_heads, num_kv_heads, scale, cd, mem_shared, h.dtype, memory.dtype)
         ctx.save_for_backward(h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse)
