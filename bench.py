@@ -1,0 +1,448 @@
+#!/usr/bin/env python
+"""Benchmark of the Mixture-of-Chapters memory cross-attention layer (forward + backward).
+
+    python bench.py --gpus N --steps K --warmup W          # CUDA path (this repository)
+    python bench.py --impl reference --steps K --warmup W  # CPU restatement of the reference, host cores
+
+One "step" is one forward+backward pass of one memory layer over one batch of synthetic hidden states
+at the paper shape (B=8 per GPU, L=1024, d=768, 12x64 heads, 4,097 chapters of 64 rows, top-64 routed
+plus one shared chapter, routed scale 2.5, bf16 activations, fp32 router), including router losses,
+projection / router gradients and the gradient of the touched bank rows.  Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PAPER = dict(batch=8, seq=1024, hidden_dim=768, num_heads=12, num_kv_heads=12, num_chapters=4097,
+             tokens_per_chapter=64, top_k=64, num_shared_chapters=1, routed_scaling_factor=2.5)
+METRIC = "memory-xattn fwd+bwd tokens/sec/GPU at L=1024,k=64; % of bf16 TC roofline"
+N_INPUT_SETS = 4       # distinct hidden-state batches rotated between steps
+
+
+def layer_flops(cfg) -> float:
+    """Matmul FLOPs of one forward pass with the reference's accounting (scripts/estimate_flops.py:
+    353-357, 385-417); fwd+bwd = 3x this (estimate_flops.py:805)."""
+    b, l, d = cfg["batch"], cfg["seq"], cfg["hidden_dim"]
+    dkv = cfg["num_kv_heads"] * (d // cfg["num_heads"])
+    n_sel = (cfg["top_k"] + cfg["num_shared_chapters"]) * cfg["tokens_per_chapter"]
+    return (2.0 * b * l * d * d * 2 + 2.0 * b * n_sel * d * dkv * 2 + 4.0 * b * l * n_sel * d
+            + 2.0 * b * d * cfg["num_chapters"])
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(tflops=float(p["bf16_tflops"]), tflops_sustained=float(p["bf16_tflops_sustained"]),
+                    hbm_gbs=float(p["hbm_gbs"]), source="measured")
+    return dict(tflops=1590.0, tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = os.path.join("/tmp", f"moc_clocks_{os.getpid()}.csv")
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_params(cfg, device, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    d = cfg["hidden_dim"]
+    dkv = cfg["num_kv_heads"] * (d // cfg["num_heads"])
+    rows = cfg["num_chapters"] * cfg["tokens_per_chapter"]
+
+    def normal(shape, std):
+        return (torch.randn(shape, generator=g) * std).to(device)
+
+    return dict(bank=normal((rows, d), 0.02), router_w=normal((cfg["num_chapters"], d), 0.02),
+                router_b=torch.zeros(cfg["num_chapters"], device=device), wq=normal((d, d), 0.02),
+                wk=normal((dkv, d), 0.02), wv=normal((dkv, d), 0.02), wo=normal((d, d), 0.02))
+
+
+def make_hidden(cfg, n_sets, seed, dtype):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    shape = (cfg["batch"], cfg["seq"], cfg["hidden_dim"])
+    return [torch.randn(shape, generator=g).to(dtype) for _ in range(n_sets)], \
+           [torch.randn(shape, generator=g).to(dtype) for _ in range(n_sets)]
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference, timed on the host cores
+# ----------------------------------------------------------------------------------------------
+def cpu_reference_step_time(cfg, sample_batch, steps, warmup, threads=None):
+    from oracle import moc_oracle as O
+    if threads:
+        torch.set_num_threads(threads)
+    small = dict(cfg, batch=sample_batch)
+    params = make_params(small, "cpu")
+    hs, gs = make_hidden(small, 1, 1234, torch.float32)
+    shape = O.LayerShape(cfg["hidden_dim"], cfg["num_heads"], cfg["num_kv_heads"], cfg["num_chapters"],
+                         cfg["tokens_per_chapter"], cfg["top_k"], cfg["num_shared_chapters"],
+                         cfg["routed_scaling_factor"])
+    tensors = dict(params, h_router=hs[0])
+    tensors["h_attn"] = tensors["h_router"]
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.memory_layer_fwd_bwd(shape, tensors, gs[0], 0.01, 0.001, autocast_bf16=False)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    return sum(times) / len(times), torch.get_num_threads()
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = dict(PAPER)
+    sample_b = args.cpu_sample_batch
+    step_s, cores = cpu_reference_step_time(cfg, sample_b, args.steps, max(1, min(args.warmup, 1)))
+    tokens = sample_b * cfg["seq"]
+    value = tokens / step_s
+    sample = (f"{sample_b} of {cfg['batch']} sequences per step (same L, bank, top-k), fp32 eager restatement "
+              f"of the reference, {args.steps} timed steps")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, 1),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, n_gpus):
+    return {"workload": "paper-shape single memory layer fwd+bwd (BASELINE configs[1])",
+            "batch_per_gpu": cfg["batch"], "global_batch": cfg["batch"] * n_gpus, "seq_len": cfg["seq"],
+            "hidden_dim": cfg["hidden_dim"], "heads": f"{cfg['num_heads']}x{cfg['hidden_dim'] // cfg['num_heads']}",
+            "bank_rows": cfg["num_chapters"] * cfg["tokens_per_chapter"], "chapters": cfg["num_chapters"],
+            "tokens_per_chapter": cfg["tokens_per_chapter"], "top_k": cfg["top_k"],
+            "shared_chapters": cfg["num_shared_chapters"], "routed_scale": cfg["routed_scaling_factor"],
+            "row_norm": "off", "parallelism": f"dp{n_gpus} (batch sharded, bank replicated)",
+            "l2_policy": f"inputs larger than L2: {N_INPUT_SETS} rotating hidden-state batches, "
+                         "per-step working set > 400 MB against a 126 MB L2"}
+
+
+# ----------------------------------------------------------------------------------------------
+# CUDA arm
+# ----------------------------------------------------------------------------------------------
+class LayerRunner:
+    def __init__(self, cfg, device, world=1, group=None):
+        import memory_b200 as M
+        self.M = M
+        self.cfg = cfg
+        self.device = device
+        self.world = world
+        p = make_params(cfg, device)
+        self.params = {k: v.requires_grad_(True) for k, v in p.items()}
+        self.sink = M.SparseBankGrad()
+        self.params["bank"].moc_sparse_grad = self.sink
+        self.reducer = None
+        if world > 1:
+            from memory_b200.distributed import GradReducer
+            self.reducer = GradReducer(cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["hidden_dim"], device,
+                                       group=group)
+
+    def step(self, h, d_out):
+        P, cfg = self.params, self.cfg
+        for v in P.values():
+            v.grad = None
+        self.sink.clear()
+        h.grad = None
+        out, losses, _ = self.M.memory_layer(
+            h, h, P["bank"], P["router_w"], P["router_b"], P["wq"], P["wk"], P["wv"], P["wo"],
+            num_heads=cfg["num_heads"], num_kv_heads=cfg["num_kv_heads"],
+            tokens_per_chapter=cfg["tokens_per_chapter"], top_k=cfg["top_k"],
+            num_shared_chapters=cfg["num_shared_chapters"], routed_scaling_factor=cfg["routed_scaling_factor"],
+            compute_dtype=torch.bfloat16)
+        loss = (out.float() * d_out.float()).sum() + 0.01 * losses["load_balance"] + 0.001 * losses["z_loss"]
+        loss.backward()
+        if self.reducer is not None:
+            dense = [P[k].grad for k in ("router_w", "router_b", "wq", "wk", "wv", "wo")]
+            self.reducer.reduce(dense, self.sink)
+        return loss
+
+
+def time_op_breakdown(runner, hs, gs, steps):
+    """Per-call CUDA-event timing (separate pass, after the headline timing)."""
+    from memory_b200 import ops
+    ops.TIMER = {}
+    for i in range(steps):
+        runner.step(hs[i % len(hs)], gs[i % len(gs)])
+    torch.cuda.synchronize()
+    table = {k: sum(a.elapsed_time(b) for a, b in v) / steps for k, v in ops.TIMER.items()}
+    ops.TIMER = None
+    return table
+
+
+def time_dominant_kernels(cfg, device, iters=10):
+    """The three attention kernels timed alone (CUDA events on the launching stream), inputs > L2:
+    Q/KV/dO/O for B=8 are ~150 MB and are rotated over two copies."""
+    from memory_b200 import ops
+    b, l, d = cfg["batch"], cfg["seq"], cfg["hidden_dim"]
+    h, hk = cfg["num_heads"], cfg["num_kv_heads"]
+    dh = d // h
+    n_sel = (cfg["top_k"] + cfg["num_shared_chapters"]) * cfg["tokens_per_chapter"]
+    sets = []
+    for s in range(2):
+        q = (torch.randn(b, l, d, device=device) * 1.0).bfloat16()
+        kv = (torch.randn(b, n_sel, 2 * hk * dh, device=device) * 0.3).bfloat16()
+        g = torch.randn(b, l, d, device=device).bfloat16()
+        o, lse = ops.attn_fwd(q, kv, h, hk, dh ** -0.5)
+        sets.append((q, kv, g, o, lse))
+    bufs = (torch.empty_like(sets[0][0]), torch.empty_like(sets[0][1]),
+            torch.empty(2, b, h, l, dtype=torch.float32, device=device))
+    res = {}
+
+    def timeit(fn):
+        for i in range(3):
+            fn(sets[i % 2])
+        torch.cuda.synchronize()
+        evs = []
+        for i in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(sets[i % 2]); e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in evs) / iters
+
+    res["attn_fwd"] = timeit(lambda s: ops.attn_fwd(s[0], s[1], h, hk, dh ** -0.5))
+    for s in sets:
+        ops.attn_bwd(s[0], s[1], s[3], s[4], s[2], h, hk, dh ** -0.5, parts=1, buffers=bufs)
+    res["attn_bwd_dq"] = timeit(lambda s: ops.attn_bwd(s[0], s[1], s[3], s[4], s[2], h, hk, dh ** -0.5, parts=2, buffers=bufs))
+    res["attn_bwd_dkv"] = timeit(lambda s: ops.attn_bwd(s[0], s[1], s[3], s[4], s[2], h, hk, dh ** -0.5, parts=4, buffers=bufs))
+    return res
+
+
+def run_cuda_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the operators have no CPU path")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    from memory_b200 import _lib as L, ops
+    from memory_b200.build import build
+    build()
+    L.lib()
+
+    cfg = dict(PAPER)
+    runner = LayerRunner(cfg, device, world)
+    hs_cpu, gs_cpu = make_hidden(cfg, N_INPUT_SETS, 1234 + rank, torch.bfloat16)
+    hs = [t.to(device).requires_grad_(True) for t in hs_cpu]
+    gs = [t.to(device) for t in gs_cpu]
+    tokens_per_step = cfg["batch"] * cfg["seq"] * world
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- headline: inputs resident in HBM ----
+    for i in range(args.warmup):
+        runner.step(hs[i % N_INPUT_SETS], gs[i % N_INPUT_SETS])
+    barrier()
+    L.check_device_status(device)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches0 = ops.LAUNCHES
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        runner.step(hs[i % N_INPUT_SETS], gs[i % N_INPUT_SETS])
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = ops.LAUNCHES - launches0
+    clocks = sampler.stop() if sampler else None
+    L.check_device_status(device)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = tokens_per_step / (ms_per_step * 1e-3)
+
+    # ---- end to end: hidden states come from pinned host memory every step, loss read back ----
+    pinned = [t.pin_memory() for t in hs_cpu]
+    copy_stream = torch.cuda.Stream(device)
+    stage = [torch.empty_like(hs[0]).requires_grad_(True) for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def prefetch(i):
+        slot = i % 2
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[slot])
+            with torch.no_grad():
+                stage[slot].copy_(pinned[i % N_INPUT_SETS], non_blocking=True)
+            ready[slot].record(copy_stream)
+
+    def e2e_loop(n):
+        cur = torch.cuda.current_stream(device)
+        for s in range(2):
+            consumed[s].record(cur)
+        prefetch(0)
+        for i in range(n):
+            if i + 1 < n:
+                prefetch(i + 1)
+            cur.wait_event(ready[i % 2])
+            loss = runner.step(stage[i % 2], gs[i % N_INPUT_SETS])
+            consumed[i % 2].record(cur)
+            loss_host.copy_(loss.detach(), non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_loop(max(3, args.warmup))
+    barrier()
+    e0.record()
+    e2e_loop(args.steps)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = tokens_per_step / (e2e_ms / args.steps * 1e-3)
+    h2d = hs[0].numel() * hs[0].element_size()
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # ---- rank 0 only: per-kernel timing, roofline, CPU baseline ----
+    peaks = measured_peaks()
+    f_fwd = layer_flops(cfg)
+    f_step = 3.0 * f_fwd
+    kern = time_dominant_kernels(cfg, device)
+    breakdown = time_op_breakdown(runner, hs, gs, max(3, min(args.steps, 10)))
+    b, l, d = cfg["batch"], cfg["seq"], cfg["hidden_dim"]
+    n_sel = (cfg["top_k"] + cfg["num_shared_chapters"]) * cfg["tokens_per_chapter"]
+    attn_unit = 2.0 * b * l * n_sel * d          # one [L x n_sel x D] GEMM over all heads and batch items
+    # algorithmic share of each attention kernel: fwd = QK^T + PV; bwd (2x fwd) = dP, dQ | dK, dV
+    alg = {"attn_fwd": 2 * attn_unit, "attn_bwd_dq": 2 * attn_unit, "attn_bwd_dkv": 2 * attn_unit}
+    executed = {"attn_fwd": 2 * attn_unit, "attn_bwd_dq": 3 * attn_unit, "attn_bwd_dkv": 4 * attn_unit}
+    dom = max(kern, key=kern.get)
+    achieved = alg[dom] / (kern[dom] * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["tflops"], "traffic": None, "peak_source": peaks["source"] + " (burst, kernel timed alone)",
+                "executed_tflops": executed[dom] / (kern[dom] * 1e-3) / 1e12,
+                "kernel_ms": {k: round(v, 4) for k, v in kern.items()},
+                "layer": {"algorithmic_flops_per_step": f_step, "achieved": f_step / (ms_per_step * 1e-3) / 1e12,
+                          "peak": peaks["tflops_sustained"], "frac": f_step / (ms_per_step * 1e-3) / 1e12 / peaks["tflops_sustained"],
+                          "peak_source": peaks["source"] + " (sustained, whole step)"},
+                "op_ms_per_step": {k: round(v, 4) for k, v in sorted(breakdown.items(), key=lambda kv: -kv[1])}}
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        step_s, cores = cpu_reference_step_time(cfg, args.cpu_sample_batch, 2, 1)
+        cpu_baseline = {"value": args.cpu_sample_batch * cfg["seq"] / step_s, "unit": "tokens/s", "cores": cores,
+                        "kind": "port",
+                        "sample": f"{args.cpu_sample_batch} of {cfg['batch']} sequences per step (same L, bank, top-k), "
+                                  "fp32 eager restatement of the reference, 1 warm-up + 2 timed steps"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(cfg, world),
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d * world,
+                "d2h_bytes_per_step": 4 * world, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu_baseline,
+        "pct_of_bf16_tc_roofline": 100.0 * roofline["layer"]["frac"],
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--cpu-sample-batch", type=int, default=2)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "cuda":
+        args.warmup = 3
+    if args.impl == "reference":
+        if args.steps > 3:
+            args.steps = 3          # each CPU step is seconds long; keep the arm within minutes
+        run_reference_arm(args)
+    else:
+        run_cuda_arm(args)
+
+
+if __name__ == "__main__":
+    main()

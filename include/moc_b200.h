@@ -168,6 +168,13 @@ int moc_attn_fwd(const moc_attn_shape* s, const void* q, const void* kv, void* o
 int moc_attn_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
                  const void* d_o, void* d_q, void* d_kv, float* delta, int32_t* status, void* stream);
 
+/* Measurement aid for the bf16 backward, same arguments as moc_attn_bwd: runs only the kernels selected by
+ * `parts` (1 = delta / log-sum-exp preparation, 2 = dQ kernel, 4 = dK/dV kernel), so each can be timed
+ * alone.  moc_attn_bwd is parts = 7.  No counterpart in the reference. */
+int moc_attn_bwd_parts(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
+                       const void* d_o, void* d_q, void* d_kv, float* delta, int32_t parts, int32_t* status,
+                       void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Per-token chapter-sparse attention: the contract of memory_cross_attn(q, k, v, block_indices,
  * block_size, scale) (kernels-final/memory_cross_attn.py:1310-1366, 1387-1603, 1639-1652).

@@ -61,6 +61,7 @@ _PROTOTYPES = {
     "moc_gemm": (C.c_int, [C.POINTER(GemmDesc), P, P, P, P, P, P, P]),
     "moc_attn_fwd": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P]),
     "moc_attn_bwd": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P, P, P, P, P]),
+    "moc_attn_bwd_parts": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P, P, P, C.c_int32, P, P]),
     "moc_sparse_attn_fwd": (C.c_int, [C.POINTER(SparseAttnShape), P, P, P, P, P, P, P, P]),
     "moc_sparse_attn_bwd": (C.c_int, [C.POINTER(SparseAttnShape), P, P, P, P, P, P, P, P, P, P, P, P]),
     "moc_cast_f32_to_bf16": (C.c_int, [P, P, C.c_int64, P]),

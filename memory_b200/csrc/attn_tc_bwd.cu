@@ -423,14 +423,14 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
 int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
                        const void* d_o, void* d_q, void* d_kv, float* scratch, int32_t* status,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, int parts) {
   MOC_REQUIRE(s->head_dim == kD, "bf16 attention needs head_dim 64");
   MOC_REQUIRE(s->seq % kQB == 0, "bf16 attention backward needs seq % 64 == 0");
   MOC_REQUIRE(s->num_heads % s->num_kv_heads == 0, "num_heads must be a multiple of num_kv_heads");
   const int B = s->batch, L = s->seq, H = s->num_heads, HK = s->num_kv_heads;
   float* delta = scratch;
   float* nlse2 = scratch + static_cast<long long>(B) * H * L;
-  {
+  if (parts & 1) {
     const long long total = static_cast<long long>(B) * L * H;
     const int blocks = static_cast<int>((total * 32 + 255) / 256);
     bwd_prep_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(o),
@@ -447,7 +447,7 @@ int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, c
   if ((rc = make_tmap_bf16_2d(&tkv, kv, kvrows, kvcols, kvcols, 64, kD)) != MOC_OK) return rc;
   MOC_CUDA_OK(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem));
   MOC_CUDA_OK(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmem));
-  {
+  if (parts & 2) {
     DqParams p;
     p.d_q = static_cast<__nv_bfloat16*>(d_q); p.delta = delta; p.nlse2 = nlse2;
     p.L = L; p.n_sel = s->n_sel; p.H = H; p.HK = HK;
@@ -455,7 +455,7 @@ int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, c
     dim3 grid(ceil_div(L, kQ), H, B);
     attn_bwd_dq_tc_kernel<<<grid, kThreads, kDqSmem, stream>>>(tq128, tdo128, tkv, p);
   }
-  {
+  if (parts & 4) {
     DkvParams p;
     p.d_kv = static_cast<__nv_bfloat16*>(d_kv); p.delta = delta; p.nlse2 = nlse2;
     p.L = L; p.n_sel = s->n_sel; p.H = H; p.HK = HK;

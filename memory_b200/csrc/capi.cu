@@ -17,7 +17,7 @@ int launch_attn_tc_fwd(const moc_attn_shape* s, const void* q, const void* kv, v
                        int32_t* status, cudaStream_t stream);
 int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
                        const void* d_o, void* d_q, void* d_kv, float* scratch, int32_t* status,
-                       cudaStream_t stream);
+                       cudaStream_t stream, int parts);
 }  // namespace moc
 
 using namespace moc;
@@ -59,6 +59,17 @@ extern "C" int moc_attn_fwd(const moc_attn_shape* s, const void* q, const void* 
   return MOC_ERR_INVALID;
 }
 
+extern "C" int moc_attn_bwd_parts(const moc_attn_shape* s, const void* q, const void* kv, const void* o,
+                                  const float* lse, const void* d_o, void* d_q, void* d_kv, float* delta,
+                                  int32_t parts, int32_t* status, void* stream_) {
+  int rc = check_attn(s);
+  if (rc != MOC_OK) return rc;
+  MOC_REQUIRE(q && kv && o && lse && d_o && d_q && d_kv && delta && status, "NULL attention buffer");
+  MOC_REQUIRE(s->dtype == MOC_BF16, "per-kernel launches exist for the bf16 kernels only");
+  return launch_attn_tc_bwd(s, q, kv, o, lse, d_o, d_q, d_kv, delta, status, static_cast<cudaStream_t>(stream_),
+                            parts);
+}
+
 extern "C" int moc_attn_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o,
                             const float* lse, const void* d_o, void* d_q, void* d_kv, float* delta,
                             int32_t* status, void* stream_) {
@@ -73,7 +84,7 @@ extern "C" int moc_attn_bwd(const moc_attn_shape* s, const void* q, const void* 
                                static_cast<const float*>(d_o), lse, delta, static_cast<float*>(d_q),
                                static_cast<float*>(d_kv), stream);
   }
-  if (s->dtype == MOC_BF16) return launch_attn_tc_bwd(s, q, kv, o, lse, d_o, d_q, d_kv, delta, status, stream);
+  if (s->dtype == MOC_BF16) return launch_attn_tc_bwd(s, q, kv, o, lse, d_o, d_q, d_kv, delta, status, stream, 7);
   set_last_error("dtype", "unknown dtype");
   return MOC_ERR_INVALID;
 }

@@ -1,0 +1,111 @@
+"""Data-parallel gradient reduction for the memory layer: batch sharded, bank replicated.
+
+The reference trains with DDP, which all-reduces the dense 262,208 x 768 fp32 bank gradient every
+step because ``torch.gather``'s backward materialises it (memory_bank.py:291).  Here only the chapters
+some rank touched travel:
+
+1. every rank marks its touched chapters in a ``[C]`` count vector; all-reduce(SUM);
+2. all ranks derive the same ascending union list ``U`` from it;
+3. each rank scatters its compact ``[U_local*T, d]`` rows into a zeroed ``[|U|*T, d]`` buffer;
+4. one all-reduce of that buffer (fp32, or bf16 on request), divided by the world size like DDP;
+5. the result is handed back as a ``SparseBankGrad`` keyed by ``U``.
+
+Dense parameter gradients (projections, router) are flattened into one bucket and all-reduced.
+Works on any ``torch.distributed`` backend (NCCL on GPUs; gloo in the CPU tests of the bookkeeping).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+def union_of_touched(counts: torch.Tensor) -> torch.Tensor:
+    """Ascending chapter ids with a non-zero count."""
+    return torch.nonzero(counts > 0, as_tuple=False).flatten()
+
+
+def compact_to_union(local_ids: torch.Tensor, local_rows: torch.Tensor, union_ids: torch.Tensor,
+                     num_chapters: int, tokens_per_chapter: int) -> torch.Tensor:
+    """Place ``local_rows`` ([n_local*T, d], chapter-major, for ``local_ids``) at their positions in the
+    union ordering; untouched positions are zero."""
+    t = tokens_per_chapter
+    d = local_rows.shape[-1]
+    pos = torch.full((num_chapters,), -1, dtype=torch.long, device=union_ids.device)
+    pos[union_ids] = torch.arange(union_ids.numel(), device=union_ids.device)
+    out = torch.zeros(union_ids.numel(), t, d, dtype=local_rows.dtype, device=local_rows.device)
+    if local_ids.numel():
+        out.index_copy_(0, pos[local_ids.long()], local_rows.view(-1, t, d)[: local_ids.numel()])
+    return out.view(-1, d)
+
+
+class GradReducer:
+    """Reduces one step's gradients across the data-parallel group (mean, as DDP does)."""
+
+    def __init__(self, num_chapters: int, tokens_per_chapter: int, dim: int, device,
+                 group: Optional[dist.ProcessGroup] = None, bank_dtype: torch.dtype = torch.float32):
+        self.c, self.t, self.d = int(num_chapters), int(tokens_per_chapter), int(dim)
+        self.device = torch.device(device)
+        self.group = group
+        self.bank_dtype = bank_dtype
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.last_union_size = 0
+
+    def reduce_dense(self, grads: Sequence[Optional[torch.Tensor]]) -> None:
+        live = [g for g in grads if g is not None]
+        if not live or self.world == 1:
+            return
+        flat = torch.cat([g.reshape(-1).float() for g in live])
+        dist.all_reduce(flat, group=self.group)
+        flat.div_(self.world)
+        off = 0
+        for g in live:
+            n = g.numel()
+            g.copy_(flat[off:off + n].view_as(g))
+            off += n
+
+    def reduce_bank(self, sink) -> None:
+        """``sink`` is a SparseBankGrad holding this rank's entries; on return it holds one entry: the
+        union chapter list and the mean gradient rows."""
+        counts = torch.zeros(self.c, dtype=torch.int32, device=self.device)
+        merged_ids, merged_rows = self._merge_local(sink)
+        if merged_ids.numel():
+            counts[merged_ids.long()] = 1
+        if self.world > 1:
+            dist.all_reduce(counts, group=self.group)
+        union = union_of_touched(counts)
+        self.last_union_size = int(union.numel())
+        buf = compact_to_union(merged_ids, merged_rows, union, self.c, self.t).to(self.bank_dtype)
+        if self.world > 1:
+            dist.all_reduce(buf, group=self.group)
+            buf.div_(self.world)
+        sink.clear()
+        sink.add(union.to(torch.int32), torch.tensor([union.numel()], dtype=torch.int32, device=self.device),
+                 buf.float(), self.t)
+
+    def reduce(self, dense_grads: Sequence[Optional[torch.Tensor]], sink) -> None:
+        self.reduce_dense(dense_grads)
+        if sink is not None and sink.entries:
+            self.reduce_bank(sink)
+
+    def _merge_local(self, sink):
+        """Sum this rank's entries (several memory layers may share one bank) into one id list."""
+        if len(sink.entries) == 1:
+            uniq, num_unique, rows, _ = sink.entries[0]
+            n = int(num_unique.item())
+            return uniq[:n], rows[: n * self.t]
+        acc = {}
+        dense_ids: List[torch.Tensor] = []
+        for uniq, num_unique, rows, _ in sink.entries:
+            n = int(num_unique.item())
+            dense_ids.append(uniq[:n].long())
+        ids = torch.unique(torch.cat(dense_ids)) if dense_ids else torch.empty(0, dtype=torch.long, device=self.device)
+        pos = torch.full((self.c,), -1, dtype=torch.long, device=self.device)
+        pos[ids] = torch.arange(ids.numel(), device=self.device)
+        out = torch.zeros(ids.numel(), self.t, self.d, dtype=torch.float32, device=self.device)
+        for uniq, num_unique, rows, _ in sink.entries:
+            n = int(num_unique.item())
+            out.index_add_(0, pos[uniq[:n].long()], rows[: n * self.t].view(n, self.t, self.d))
+        del acc
+        return ids.to(torch.int32), out.view(-1, self.d)

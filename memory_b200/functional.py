@@ -146,15 +146,15 @@ class _CrossAttention(torch.autograd.Function):
         m2 = ops.cast(memory.reshape(-1, memory.shape[-1]), cd)
         wq_c, wo_c = ops.cast(wq, cd), ops.cast(wo, cd)
         wkv_c = ops.cast(torch.cat([wk, wv], dim=0), cd)
-        q = ops.gemm(h2, wq_c)                                   # [B*L, H*D]
-        kv = ops.gemm(m2, wkv_c)                                 # [(B*)n_sel, 2*HK*D]
+        q = ops.gemm(h2, wq_c, tag="q_proj")                                   # [B*L, H*D]
+        kv = ops.gemm(m2, wkv_c, tag="kv_proj")                                 # [(B*)n_sel, 2*HK*D]
         if mem_shared:
             kv = kv.unsqueeze(0).expand(b, -1, -1).contiguous()
         head_dim = d // num_heads
         scale = head_dim ** -0.5
         kv = kv.view(b, n_sel, -1)
         o, lse = ops.attn_fwd(q.view(b, l, -1), kv, num_heads, num_kv_heads, scale)
-        out = ops.gemm(o.view(b * l, -1), wo_c)
+        out = ops.gemm(o.view(b * l, -1), wo_c, tag="o_proj")
         ctx.cfg = (num_heads, num_kv_heads, scale, cd, mem_shared, h.dtype, memory.dtype)
         ctx.save_for_backward(h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse)
         ctx.w_dtypes = (wq.dtype, wk.dtype, wv.dtype, wo.dtype)
@@ -169,19 +169,20 @@ class _CrossAttention(torch.autograd.Function):
         g2 = ops.cast(g.reshape(b * l, -1).contiguous(), cd)
         f32 = torch.float32
         split = 1 if cd == torch.float32 else max(1, min(16, (b * l) // 2048))
-        d_o = ops.gemm(g2, wo_c, b_kmajor=False)                                      # [B*L, H*D]
-        d_wo = ops.gemm(g2, o.view(b * l, -1), a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split)
+        d_o = ops.gemm(g2, wo_c, b_kmajor=False, tag="d_attn_out")                                      # [B*L, H*D]
+        d_wo = ops.gemm(g2, o.view(b * l, -1), a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split,
+                        tag="d_wo")
         d_q, d_kv = ops.attn_bwd(q.view(b, l, -1), kv, o, lse, d_o.view(b, l, -1), num_heads, num_kv_heads, scale)
         d_q2 = d_q.view(b * l, -1)
-        d_h = ops.gemm(d_q2, wq_c, b_kmajor=False)
-        d_wq = ops.gemm(d_q2, h2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split)
+        d_h = ops.gemm(d_q2, wq_c, b_kmajor=False, tag="d_h")
+        d_wq = ops.gemm(d_q2, h2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split, tag="d_wq")
         d_kv2 = d_kv.view(-1, d_kv.shape[-1])
         if mem_shared:
             d_kv2 = d_kv.float().sum(dim=0).to(cd)
         rows = d_kv2.shape[0]
         split_kv = 1 if cd == torch.float32 else max(1, min(16, rows // 2048))
-        d_mem = ops.gemm(d_kv2, wkv_c, b_kmajor=False, out_dtype=f32 if cd == f32 else cd)
-        d_wkv = ops.gemm(d_kv2, m2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split_kv)
+        d_mem = ops.gemm(d_kv2, wkv_c, b_kmajor=False, out_dtype=f32 if cd == f32 else cd, tag="d_mem")
+        d_wkv = ops.gemm(d_kv2, m2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split_kv, tag="d_wkv")
         dkv_dim = wkv_c.shape[0] // 2
         wdt = ctx.w_dtypes
         d_mem = d_mem.view(-1, d_mem.shape[-1]) if mem_shared else d_mem.view(b, -1, d_mem.shape[-1])

@@ -16,6 +16,35 @@ def _contig(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     return None if t is None else (t if t.is_contiguous() else t.contiguous())
 
 
+# Kernel-launch accounting and optional per-call CUDA-event timing (used by the benchmark).
+LAUNCHES = 0
+TIMER = None   # when a dict: name -> list of (start_event, end_event) on the current stream
+
+
+def _instrument(name: str, launches):
+    """Counts the kernels a wrapper launches (``launches`` is an int or a callable on the call's
+    arguments) and, when ``TIMER`` is set, brackets the call with CUDA events."""
+    def deco(fn):
+        def wrapped(*args, **kwargs):
+            global LAUNCHES
+            n = launches(*args, **kwargs) if callable(launches) else launches
+            LAUNCHES += n
+            if TIMER is None:
+                return fn(*args, **kwargs)
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*args, **kwargs)
+            e1.record()
+            label = name(*args, **kwargs) if callable(name) else name
+            TIMER.setdefault(label, []).append((e0, e1))
+            return out
+        wrapped.__name__ = fn.__name__
+        wrapped.__doc__ = fn.__doc__
+        return wrapped
+    return deco
+
+
 # --------------------------------------------------------------------------------------------
 # router
 # --------------------------------------------------------------------------------------------
@@ -28,6 +57,7 @@ def router_selected_k(num_chapters: int, top_k: int, num_shared: int) -> int:
     return max(0, min(int(top_k), int(num_chapters) - int(num_shared)))
 
 
+@_instrument("router_fwd", lambda *a, **k: 6 if (a[6] if len(a) > 6 else k.get("with_losses")) else 4)
 def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top_k: int,
                num_shared: int, routed_scale: float, with_losses: bool) -> Dict[str, torch.Tensor]:
     L.require_cuda(h, weight, bias)
@@ -62,6 +92,7 @@ def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     return out
 
 
+@_instrument("router_bwd", lambda *a, **k: 5 if (a[-1] if len(a) > 10 else k.get("want_dh")) else 4)
 def router_bwd(h_shape, h_dtype, weight: torch.Tensor, saved: Dict[str, torch.Tensor], top_k: int,
                num_shared: int, routed_scale: float, d_weights: Optional[torch.Tensor],
                d_comb_w: Optional[torch.Tensor], d_losses: Optional[torch.Tensor],
@@ -91,6 +122,7 @@ def router_bwd(h_shape, h_dtype, weight: torch.Tensor, saved: Dict[str, torch.Te
 # --------------------------------------------------------------------------------------------
 # gather
 # --------------------------------------------------------------------------------------------
+@_instrument("gather_rows_fwd", 1)
 def gather_rows_fwd(bank: torch.Tensor, tokens_per_chapter: int, comb_idx: torch.Tensor,
                     comb_w: Optional[torch.Tensor], norm_type: Optional[str], eps: float,
                     out_dtype: torch.dtype) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
@@ -111,6 +143,7 @@ def gather_rows_fwd(bank: torch.Tensor, tokens_per_chapter: int, comb_idx: torch
     return out, stats
 
 
+@_instrument("chapter_segments", 1)
 def chapter_segments(comb_idx: torch.Tensor, num_chapters: int) -> Dict[str, torch.Tensor]:
     comb_idx = _contig(comb_idx.to(torch.int32))
     n = comb_idx.numel()
@@ -127,6 +160,7 @@ def chapter_segments(comb_idx: torch.Tensor, num_chapters: int) -> Dict[str, tor
     return seg
 
 
+@_instrument("gather_rows_bwd", 2)
 def gather_rows_bwd(d_mem: torch.Tensor, bank: torch.Tensor, tokens_per_chapter: int, comb_idx: torch.Tensor,
                     comb_w: Optional[torch.Tensor], norm_type: Optional[str], eps: float,
                     row_stats: Optional[torch.Tensor], seg: Dict[str, torch.Tensor],
@@ -149,6 +183,7 @@ def gather_rows_bwd(d_mem: torch.Tensor, bank: torch.Tensor, tokens_per_chapter:
     return d_comb_w, bank_grad
 
 
+@_instrument("scatter_bank_grad", 1)
 def scatter_bank_grad(bank_grad: torch.Tensor, seg: Dict[str, torch.Tensor], tokens_per_chapter: int,
                       dense: torch.Tensor) -> None:
     """dense[uniq[u]*T + r] += bank_grad[u*T + r] for the chapters listed in ``seg``."""
@@ -162,10 +197,17 @@ def scatter_bank_grad(bank_grad: torch.Tensor, seg: Dict[str, torch.Tensor], tok
 # --------------------------------------------------------------------------------------------
 # projections
 # --------------------------------------------------------------------------------------------
+def _gemm_label(a, b, **k):
+    tag = k.get("tag")
+    return "gemm:" + tag if tag else "gemm"
+
+
+@_instrument(_gemm_label, 1)
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_kmajor: bool = True, b_kmajor: bool = True,
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, accumulate: bool = False,
          split_k: int = 1, row_scale: Optional[torch.Tensor] = None, scale_block_rows: int = 1,
-         a_row_blocks: Optional[torch.Tensor] = None, a_block_rows: int = 0, m: Optional[int] = None) -> torch.Tensor:
+         a_row_blocks: Optional[torch.Tensor] = None, a_block_rows: int = 0, m: Optional[int] = None,
+         tag: Optional[str] = None) -> torch.Tensor:
     """C[M,N] (+)= op(A) op(B).  a_kmajor: A stored [M,K] else [K,M]; b_kmajor: B stored [N,K] else [K,N]."""
     L.require_cuda(a, b)
     if a.dtype != b.dtype:
@@ -208,6 +250,7 @@ def _attn_shape(q: torch.Tensor, kv: torch.Tensor, num_heads: int, num_kv_heads:
     return L.AttnShape(b, l, n_sel, num_heads, num_kv_heads, d, float(scale), L.dtype_code(q.dtype))
 
 
+@_instrument("attn_fwd", 1)
 def attn_fwd(q: torch.Tensor, kv: torch.Tensor, num_heads: int, num_kv_heads: int,
              scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
     L.require_cuda(q, kv)
@@ -221,19 +264,41 @@ def attn_fwd(q: torch.Tensor, kv: torch.Tensor, num_heads: int, num_kv_heads: in
     return o, lse
 
 
+def _attn_bwd_launches(*a, **k):
+    parts = k.get("parts")
+    if parts is not None:
+        return bin(int(parts)).count("1")
+    return 3 if a[0].dtype == torch.bfloat16 else 4
+
+
+@_instrument(lambda *a, **k: "attn_bwd" if k.get("parts") is None else "attn_bwd:parts%d" % k["parts"],
+             _attn_bwd_launches)
 def attn_bwd(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tensor, d_o: torch.Tensor,
-             num_heads: int, num_kv_heads: int, scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
+             num_heads: int, num_kv_heads: int, scale: float, parts: Optional[int] = None,
+             buffers=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """dQ and dKV.  ``parts`` (bf16 only) restricts the call to some of its kernels for timing;
+    ``buffers`` = (d_q, d_kv, scratch) reuses outputs between such calls."""
     q, kv, o, d_o = _contig(q), _contig(kv), _contig(o), _contig(d_o)
     s = _attn_shape(q, kv, num_heads, num_kv_heads, scale)
-    d_q = torch.empty_like(q)
-    d_kv = torch.empty_like(kv)
-    scratch = torch.empty(2, s.batch, num_heads, s.seq, dtype=torch.float32, device=q.device)
-    rc = L.lib().moc_attn_bwd(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse), L.ptr(d_o), L.ptr(d_q),
-                              L.ptr(d_kv), L.ptr(scratch), L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))
+    if buffers is None:
+        d_q = torch.empty_like(q)
+        d_kv = torch.empty_like(kv)
+        scratch = torch.empty(2, s.batch, num_heads, s.seq, dtype=torch.float32, device=q.device)
+    else:
+        d_q, d_kv, scratch = buffers
+    if parts is None:
+        rc = L.lib().moc_attn_bwd(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse), L.ptr(d_o), L.ptr(d_q),
+                                  L.ptr(d_kv), L.ptr(scratch), L.ptr(L.status_word(q.device)),
+                                  L.stream_ptr(q.device))
+    else:
+        rc = L.lib().moc_attn_bwd_parts(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse), L.ptr(d_o),
+                                        L.ptr(d_q), L.ptr(d_kv), L.ptr(scratch), int(parts),
+                                        L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))
     L.check(rc, "moc_attn_bwd")
     return d_q, d_kv
 
 
+@_instrument("sparse_attn_fwd", 1)
 def sparse_attn_fwd(q, k, v, block_indices, block_size: int, scale: float):
     L.require_cuda(q, k, v, block_indices)
     b, tq, hq, d = q.shape
@@ -248,6 +313,7 @@ def sparse_attn_fwd(q, k, v, block_indices, block_size: int, scale: float):
     return o, lse
 
 
+@_instrument("sparse_attn_bwd", 1)
 def sparse_attn_bwd(q, k, v, block_indices, o, lse, d_o, block_size: int, scale: float):
     b, tq, hq, d = q.shape
     _, tk, h, _ = k.shape
@@ -267,6 +333,11 @@ def cast(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     """fp32 <-> bf16 conversion on the device (identity when the dtype already matches)."""
     if t.dtype == dtype:
         return t
+    return _cast(t, dtype)
+
+
+@_instrument("cast", 1)
+def _cast(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     L.require_cuda(t)
     t = _contig(t)
     out = torch.empty(t.shape, dtype=dtype, device=t.device)

@@ -1,0 +1,320 @@
+"""GPU parity: the CUDA path (through the C ABI) against the reference's outputs stored as golden
+fixtures and against the CPU oracle.  Bars: chapter indices bit-exact, fp32 within 1e-4 relative
+(5e-4 for gradients, the reference harness's own fp32 bar), bf16 within 2e-2 relative."""
+import numpy as np
+import pytest
+import torch
+
+from util_cases import CASES, attn_reference, load_gold, make_inputs, rel_err, run_layer_gpu, shape_of
+from oracle import moc_oracle as O
+
+pytestmark = pytest.mark.gpu
+FP32_FWD, FP32_BWD, BF16 = 1e-4, 5e-4, 2e-2
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda:0")
+
+
+def _status_ok(dev):
+    from memory_b200 import _lib as L
+    L.check_device_status(dev)
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_layer_fp32_matches_reference_golden(name, dev):
+    case = CASES[name]
+    gold = load_gold(name)
+    out, losses, info, P = run_layer_gpu(case, torch.float32, dev)
+    _status_ok(dev)
+    assert np.array_equal(info["indices"].cpu().numpy(), gold["indices"])
+    assert np.array_equal(info["combined_indices"].cpu().numpy(), gold["combined_indices"])
+    assert rel_err(info["weights"], torch.from_numpy(gold["weights"])) < 1e-5
+    assert rel_err(info["combined_weights"], torch.from_numpy(gold["combined_weights"])) < 1e-5
+    for k in ("load_balance", "auxiliary", "z_loss", "entropy"):
+        np.testing.assert_allclose(losses[k].item(), float(gold["loss_" + k]), rtol=1e-5, atol=1e-8)
+    assert rel_err(out, torch.from_numpy(gold["out"])) < FP32_FWD
+    pairs = [("d_h_router", "h_router"), ("d_router_w", "router_w"), ("d_router_b", "router_b"),
+             ("d_wq", "wq"), ("d_wk", "wk"), ("d_wv", "wv"), ("d_wo", "wo")]
+    if case.separate_router_input:
+        pairs.append(("d_h_attn", "h_attn"))
+    for g, p in pairs:
+        assert rel_err(P[p].grad, torch.from_numpy(gold[g])) < FP32_BWD, g
+    T = case.tokens_per_chapter
+    rows = (gold["bank_touched_chapters"][:, None] * T + np.arange(T)[None]).reshape(-1)
+    bg = P["bank"].grad.cpu()
+    assert rel_err(bg[rows], torch.from_numpy(gold["d_bank_touched"])) < FP32_BWD
+    mask = torch.ones(bg.shape[0], dtype=torch.bool)
+    mask[rows] = False
+    assert not bg[mask].any(), "bank gradient must be zero outside the touched chapters"
+
+
+def test_layer_bf16_matches_reference_golden(dev):
+    case = CASES["head64_t64"]
+    gold = load_gold("head64_t64")
+    out, losses, info, P = run_layer_gpu(case, torch.bfloat16, dev)
+    _status_ok(dev)
+    assert np.array_equal(info["indices"].cpu().numpy(), gold["indices"])
+    # against the fp32 reference and against the reference under bf16 autocast
+    for prefix in ("", "bf16_"):
+        assert rel_err(out, torch.from_numpy(gold[prefix + "out"])) < BF16
+        for g, p in (("d_h_router", "h_router"), ("d_wq", "wq"), ("d_wk", "wk"), ("d_wv", "wv"), ("d_wo", "wo")):
+            assert rel_err(P[p].grad, torch.from_numpy(gold[prefix + g])) < BF16, prefix + g
+    T = case.tokens_per_chapter
+    rows = (gold["bank_touched_chapters"][:, None] * T + np.arange(T)[None]).reshape(-1)
+    assert rel_err(P["bank"].grad.cpu()[rows], torch.from_numpy(gold["d_bank_touched"])) < BF16
+
+
+def test_router_matches_oracle_with_all_loss_gradients(dev):
+    import memory_b200 as M
+    for name in ("cfg0", "two_shared", "no_shared", "k_exceeds"):
+        case = CASES[name]
+        inp = {k: torch.from_numpy(v) for k, v in make_inputs(case).items()}
+        hr = inp["h_router"].clone().requires_grad_(True)
+        wr = inp["router_w"].clone().requires_grad_(True)
+        br = inp["router_b"].clone().requires_grad_(True)
+        idx, w, losses, _ = O.router_forward(hr, wr, br, case.top_k, case.num_shared_chapters)
+        cidx, cw = O.prepend_shared_chapters(idx, w, case.num_chapters, case.num_shared_chapters,
+                                             case.routed_scaling_factor)
+        g_w, g_cw = torch.randn_like(w), torch.randn_like(cw)
+        coef = {"load_balance": 0.3, "auxiliary": 700.0, "z_loss": 0.2, "entropy": 0.1}
+        (sum(coef[k] * losses[k] for k in coef) + (w * g_w).sum() + (cw * g_cw).sum()).backward()
+        h = inp["h_router"].to(dev).requires_grad_(True)
+        W = inp["router_w"].to(dev).requires_grad_(True)
+        b = inp["router_b"].to(dev).requires_grad_(True)
+        gi, gw, gci, gcw, gl = M.route(h, W, b, case.top_k, case.num_shared_chapters,
+                                       case.routed_scaling_factor, True)
+        (sum(coef[k] * gl[k] for k in coef) + (gw * g_w.to(dev)).sum() + (gcw * g_cw.to(dev)).sum()).backward()
+        _status_ok(dev)
+        assert torch.equal(gi.cpu(), idx) and torch.equal(gci.cpu().long(), cidx)
+        assert rel_err(gw, w) < 1e-5 and rel_err(gcw, cw) < 1e-5
+        assert rel_err(W.grad, wr.grad) < 1e-4 and rel_err(b.grad, br.grad) < 1e-4
+        assert rel_err(h.grad, hr.grad) < 1e-4
+
+
+def test_router_tie_break_prefers_lower_chapter_id(dev):
+    """Identical router rows give identical probabilities: the selection must be the lowest ids."""
+    import memory_b200 as M
+    d, C, k = 64, 40, 6
+    h = torch.randn(2, 16, d, device=dev)
+    row = torch.randn(d)
+    W = torch.zeros(C, d)
+    W[5:] = row            # chapters 5..39 tie exactly; 1..4 are lower (zero logit vs typical +/-)
+    W[1:5] = row * 3.0     # make 1..4 distinct from the tied block
+    idx, w, _, _, _ = M.route(h, W.to(dev), torch.zeros(C, device=dev), k, 1, 2.5, False)
+    oi, ow, _, _ = O.router_forward(h.cpu(), W, torch.zeros(C), k, 1, False)
+    assert torch.equal(idx.cpu(), oi)
+    for b in range(2):
+        tied = [c for c in idx[b].tolist() if c >= 5]
+        assert tied == sorted(tied) and (not tied or tied == list(range(5, 5 + len(tied))) or min(tied) >= 5)
+
+
+def test_router_bf16_hidden_states_use_fp32_arithmetic(dev):
+    import memory_b200 as M
+    case = CASES["cfg0"]
+    inp = {k: torch.from_numpy(v) for k, v in make_inputs(case).items()}
+    hb = inp["h_router"].bfloat16()
+    idx, w, _, _ = O.router_forward(hb.float(), inp["router_w"], inp["router_b"], case.top_k, 1, False)
+    gi, gw, _, _, _ = M.route(hb.to(dev), inp["router_w"].to(dev), inp["router_b"].to(dev), case.top_k, 1, 2.5, False)
+    assert torch.equal(gi.cpu(), idx) and rel_err(gw, w) < 1e-5
+
+
+def test_gather_bad_chapter_index_sets_status_not_fault(dev):
+    """An out-of-range chapter id is reported through the status word; the rows read as zero."""
+    import memory_b200 as M
+    from memory_b200 import _lib as L
+    bank = torch.randn(8 * 16, 32, device=dev)
+    idx = torch.tensor([[0, 3, 99]], dtype=torch.int32, device=dev)
+    rows = M.gather_chapters(bank, idx, None, 16)
+    with pytest.raises(RuntimeError, match="chapter index"):
+        L.check_device_status(dev)
+    assert not rows[0, 32:].any()
+    L.check_device_status(dev)      # cleared by the failed check
+
+
+def test_duplicate_chapters_across_batch_accumulate(dev):
+    """Every batch item selecting the same chapters: the bank gradient is the sum over items."""
+    import memory_b200 as M
+    T, d, C = 16, 64, 12
+    bank = torch.randn(C * T, d, device=dev, requires_grad=True)
+    idx = torch.tensor([[0, 4, 7]] * 5, dtype=torch.int32, device=dev)
+    w = torch.rand(5, 3, device=dev, requires_grad=True)
+    rows = M.gather_chapters(bank, idx, w, T)
+    g = torch.randn_like(rows)
+    (rows * g).sum().backward()
+    ref_bank = bank.detach().cpu().clone().requires_grad_(True)
+    ref_w = w.detach().cpu().clone().requires_grad_(True)
+    mem = O.scale_memory(O.gather_chapters(ref_bank, idx.cpu().long(), T), ref_w, T)
+    (mem * g.cpu()).sum().backward()
+    assert rel_err(rows, mem) < 1e-6
+    assert rel_err(bank.grad, ref_bank.grad) < 1e-5 and rel_err(w.grad, ref_w.grad) < 1e-5
+
+
+def test_sparse_bank_grad_sink_equals_dense(dev):
+    import memory_b200 as M
+    case = CASES["cfg0"]
+    _, _, _, P_dense = run_layer_gpu(case, torch.float32, dev)
+    inp = {k: torch.from_numpy(v).to(dev) for k, v in make_inputs(case).items()}
+    bank = inp["bank"].clone().requires_grad_(True)
+    bank.moc_sparse_grad = M.SparseBankGrad()
+    out, losses, _ = M.memory_layer(inp["h_router"], inp["h_router"], bank, inp["router_w"], inp["router_b"],
+                                    inp["wq"].requires_grad_(True), inp["wk"], inp["wv"], inp["wo"],
+                                    num_heads=case.num_heads, num_kv_heads=case.num_kv_heads,
+                                    tokens_per_chapter=case.tokens_per_chapter, top_k=case.top_k,
+                                    compute_dtype=torch.float32)
+    (out * inp["d_out"]).sum().backward()
+    assert bank.grad is None
+    dense = bank.moc_sparse_grad.to_dense(bank)
+    # the dense run also carries the router-loss terms, which do not reach the bank
+    assert rel_err(dense, P_dense["bank"].grad) < 1e-5
+
+
+@pytest.mark.parametrize("shape", [(300, 200, 136), (128, 128, 64), (257, 130, 72)])
+@pytest.mark.parametrize("a_k,b_k", [(True, True), (True, False), (False, True), (False, False)])
+def test_projection_kernels_all_operand_layouts(shape, a_k, b_k, dev):
+    from memory_b200 import ops
+    m, n, k = shape
+    a = torch.randn((m, k) if a_k else (k, m), device=dev)
+    b = torch.randn((n, k) if b_k else (k, n), device=dev)
+    for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 1e-5)):
+        if dt == torch.bfloat16 and (m % 8 or n % 8):
+            continue   # 16-byte row alignment of the MN-major operands
+        aa, bb = a.to(dt), b.to(dt)
+        ref = (aa.float() if a_k else aa.float().t()) @ (bb.float().t() if b_k else bb.float())
+        c = ops.gemm(aa, bb, a_kmajor=a_k, b_kmajor=b_k, out_dtype=torch.float32)
+        assert rel_err(c, ref) < tol
+    _status_ok(dev)
+
+
+def test_projection_split_k_accumulate_and_row_scale(dev):
+    from memory_b200 import ops
+    a = torch.randn(4096, 256, device=dev).bfloat16()
+    b = torch.randn(4096, 192, device=dev).bfloat16()
+    ref = a.float().t() @ b.float()
+    c = ops.gemm(a, b, a_kmajor=False, b_kmajor=False, out_dtype=torch.float32, split_k=8)
+    assert rel_err(c, ref) < 1e-5
+    c2 = ops.gemm(a, b, a_kmajor=False, b_kmajor=False, out=c.clone(), accumulate=True)
+    assert rel_err(c2, 2 * ref) < 1e-5
+    x = torch.randn(512, 128, device=dev).bfloat16()
+    w = torch.randn(256, 128, device=dev).bfloat16()
+    sc = torch.rand(8, device=dev) + 0.5
+    y = ops.gemm(x, w, out_dtype=torch.float32, row_scale=sc, scale_block_rows=64)
+    assert rel_err(y, (x.float() @ w.float().t()) * sc.repeat_interleave(64).unsqueeze(1)) < 1e-5
+    _status_ok(dev)
+
+
+@pytest.mark.parametrize("T", [64, 16])
+def test_fused_gather_projection_reads_chapters_from_bank(T, dev):
+    """K/V projection with the chapter rows fetched by TMA through the gather list."""
+    from memory_b200 import ops
+    C, d = 40, 256
+    bank = torch.randn(C * T, d, device=dev).bfloat16()
+    idx = torch.randperm(C, device=dev)[:8].int()
+    sc = torch.rand(8, device=dev) + 0.5
+    w = torch.randn(384, d, device=dev).bfloat16()
+    c = ops.gemm(bank, w, out_dtype=torch.float32, row_scale=sc, scale_block_rows=T, a_row_blocks=idx,
+                 a_block_rows=T, m=8 * T)
+    ref = (bank.view(C, T, d)[idx.long()].float() * sc.view(-1, 1, 1)).view(-1, d) @ w.float().t()
+    assert rel_err(c, ref) < 1e-5
+    _status_ok(dev)
+
+
+@pytest.mark.parametrize("cfg", [(1, 128, 64, 1, 1), (2, 256, 320, 2, 2), (2, 128, 80, 4, 2), (1, 192, 4160, 2, 2)])
+def test_attention_bf16_tensor_core_kernels(cfg, dev):
+    from memory_b200 import ops
+    B, L, N, H, HK = cfg
+    D = 64
+    q = torch.randn(B, L, H * D, device=dev).bfloat16().float().requires_grad_(True)
+    kv = torch.randn(B, N, 2 * HK * D, device=dev).bfloat16().float().requires_grad_(True)
+    ref, lref = attn_reference(q, kv, H, HK, D)
+    g = torch.randn_like(ref).bfloat16().float()
+    ref.backward(g)
+    o, lse = ops.attn_fwd(q.detach().bfloat16(), kv.detach().bfloat16(), H, HK, D ** -0.5)
+    dq, dkv = ops.attn_bwd(q.detach().bfloat16(), kv.detach().bfloat16(), o, lse, g.bfloat16(), H, HK, D ** -0.5)
+    _status_ok(dev)
+    assert rel_err(o, ref) < BF16 and rel_err(lse, lref) < 1e-4
+    assert rel_err(dq, q.grad) < BF16 and rel_err(dkv, kv.grad) < BF16
+
+
+@pytest.mark.parametrize("cfg", [(2, 100, 80, 4, 4, 64), (2, 64, 96, 4, 2, 32), (1, 130, 70, 2, 1, 16)])
+def test_attention_fp32_kernels(cfg, dev):
+    from memory_b200 import ops
+    B, L, N, H, HK, D = cfg
+    q = torch.randn(B, L, H * D, device=dev, requires_grad=True)
+    kv = torch.randn(B, N, 2 * HK * D, device=dev, requires_grad=True)
+    ref, lref = attn_reference(q, kv, H, HK, D)
+    g = torch.randn_like(ref)
+    ref.backward(g)
+    o, lse = ops.attn_fwd(q.detach(), kv.detach(), H, HK, D ** -0.5)
+    dq, dkv = ops.attn_bwd(q.detach(), kv.detach(), o, lse, g, H, HK, D ** -0.5)
+    assert rel_err(o, ref) < FP32_FWD and rel_err(lse, lref) < FP32_FWD
+    assert rel_err(dq, q.grad) < FP32_BWD and rel_err(dkv, kv.grad) < FP32_BWD
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_memory_cross_attn_entry_point(dtype, dev):
+    """Per-token chapter-sparse attention against the oracle's restatement of its contract."""
+    import memory_b200 as M
+    B, TQ, TK, HQ, H, D, S, BS = 2, 40, 128, 4, 2, 64, 3, 16
+    q = torch.randn(B, TQ, HQ, D, device=dev).to(dtype).requires_grad_(True)
+    k = torch.randn(B, TK, H, D, device=dev).to(dtype).requires_grad_(True)
+    v = torch.randn(B, TK, H, D, device=dev).to(dtype).requires_grad_(True)
+    bi = torch.stack([torch.randperm(TK // BS)[:S] for _ in range(B * TQ * H)]).view(B, TQ, H, S).int().to(dev)
+    o = M.memory_cross_attn(q, k, v, bi, BS)
+    ref = O.sparse_chapter_attention(q.detach().cpu().float(), k.detach().cpu().float(), v.detach().cpu().float(),
+                                     bi.cpu(), BS)
+    tol = FP32_FWD if dtype == torch.float32 else BF16
+    assert rel_err(o, ref) < tol
+    # sequence-level selection through the same entry point equals the dense joint softmax
+    bi_seq = bi[:, :1].expand(-1, TQ, -1, -1).contiguous()
+    o2 = M.memory_cross_attn(q, k, v, bi_seq, BS)
+    ref2 = O.sparse_chapter_attention(q.detach().cpu().float(), k.detach().cpu().float(),
+                                      v.detach().cpu().float(), bi_seq.cpu(), BS)
+    assert rel_err(o2, ref2) < tol
+    g = torch.randn_like(o)
+    o.backward(g)
+    assert q.grad.shape == q.shape and k.grad.dtype == dtype
+    with pytest.raises(ValueError):
+        M.memory_cross_attn(q.cpu(), k, v, bi, BS)
+    with pytest.raises(ValueError):
+        M.memory_cross_attn(q, k, v, bi, BS, dkv_strategy="z")
+
+
+def test_module_api_matches_reference_contract(dev):
+    """Drop-in classes: constructor errors, parameter names, return shapes."""
+    import memory_b200 as M
+    with pytest.raises(ValueError):
+        M.ChapterRouter(64, 8, top_k=9)
+    with pytest.raises(ValueError):
+        M.ChapteredMemoryBank(M.StandardMemoryBank(100, 8), 7)
+    with pytest.raises(ValueError):
+        M.MemoryCrossAttention(100, 3)
+    router = M.ChapterRouter(64, 9, top_k=3).to(dev)
+    bank = M.ChapteredMemoryBank(M.StandardMemoryBank(9 * 16, 64), 9).to(dev)
+    attn = M.MemoryCrossAttention(64, 1, wo_init_zero=False, use_flash_attention=False).to(dev)
+    keys = set(dict(router.named_parameters())) | set(dict(bank.named_parameters())) | set(dict(attn.named_parameters()))
+    assert {"router.weight", "router.bias", "base_bank.memory", "q_proj.weight", "k_proj.weight",
+            "v_proj.weight", "o_proj.weight"} <= keys
+    h = torch.randn(2, 32, 64, device=dev)
+    idx, w, losses = router(h, return_losses=True, exclude_prefix_chapters=1)
+    assert idx.dtype == torch.int64 and idx.shape == (2, 3) and set(losses) == {"load_balance", "auxiliary", "z_loss", "entropy"}
+    with pytest.raises(ValueError):
+        router(h, exclude_prefix_chapters=10)
+    mem, flat = bank.get_chapters_batched(idx)
+    assert mem.shape == (2, 48, 64) and flat.shape == (2, 48)
+    assert torch.equal(mem, bank.get_memory()[flat])
+    out, none = attn(h, mem * 0.5)
+    assert out.shape == h.shape and none is None
+    with pytest.raises(ValueError):
+        attn(h, None)
+    # the strict boundary equals the oracle's cross_attention
+    ref = O.cross_attention(h.cpu(), (mem * 0.5).detach().cpu(), attn.q_proj.weight.detach().cpu(),
+                            attn.k_proj.weight.detach().cpu(), attn.v_proj.weight.detach().cpu(),
+                            attn.o_proj.weight.detach().cpu(), 1, 1)
+    assert rel_err(out, ref) < FP32_FWD
+    out2, _ = attn(h, mem[0] * 0.5)     # (N, d) memory shared by the batch
+    ref2 = O.cross_attention(h.cpu(), (mem[0] * 0.5).detach().cpu(), attn.q_proj.weight.detach().cpu(),
+                             attn.k_proj.weight.detach().cpu(), attn.v_proj.weight.detach().cpu(),
+                             attn.o_proj.weight.detach().cpu(), 1, 1)
+    assert rel_err(out2, ref2) < FP32_FWD

@@ -1,0 +1,56 @@
+"""Helpers shared by the GPU parity tests."""
+import os
+
+import numpy as np
+import torch
+
+from cases import CASES, make_inputs  # noqa: F401  (tests/golden is on sys.path via conftest)
+from oracle import moc_oracle as O
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def shape_of(case):
+    return O.LayerShape(case.hidden_dim, case.num_heads, case.num_kv_heads, case.num_chapters,
+                        case.tokens_per_chapter, case.top_k, case.num_shared_chapters,
+                        case.routed_scaling_factor, case.norm_type, case.norm_eps)
+
+
+def load_gold(name):
+    return np.load(os.path.join(GOLDEN, name + ".npz"))
+
+
+def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
+    """max |a-b| / max |b| -- the tolerance form the parity bars are stated in."""
+    a = a.detach().float().cpu()
+    b = b.detach().float().cpu()
+    return float((a - b).abs().max() / (b.abs().max() + 1e-30))
+
+
+def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001):
+    import memory_b200 as M
+    inp = inputs or {k: torch.from_numpy(v) for k, v in make_inputs(case).items()}
+    inp = {k: v.to(dev) for k, v in inp.items()}
+    names = ("h_router", "bank", "router_w", "router_b", "wq", "wk", "wv", "wo")
+    P = {k: inp[k].clone().requires_grad_(True) for k in names}
+    P["h_attn"] = inp["h_attn"].clone().requires_grad_(True) if case.separate_router_input else P["h_router"]
+    out, losses, info = M.memory_layer(
+        P["h_router"], P["h_attn"], P["bank"], P["router_w"], P["router_b"], P["wq"], P["wk"], P["wv"], P["wo"],
+        num_heads=case.num_heads, num_kv_heads=case.num_kv_heads, tokens_per_chapter=case.tokens_per_chapter,
+        top_k=case.top_k, num_shared_chapters=case.num_shared_chapters,
+        routed_scaling_factor=case.routed_scaling_factor, norm_type=case.norm_type, norm_eps=case.norm_eps,
+        compute_dtype=compute_dtype)
+    loss = (out.float() * inp["d_out"]).sum() + lb * losses["load_balance"] + z * losses["z_loss"]
+    loss.backward()
+    return out, losses, info, P
+
+
+def attn_reference(q, kv, H, HK, D):
+    """Dense torch attention over q [B,L,H*D], kv [B,N,2*HK*D] (K heads then V heads)."""
+    B, L, _ = q.shape
+    N = kv.shape[1]
+    qq = q.view(B, L, H, D).transpose(1, 2)
+    k = kv[..., :HK * D].view(B, N, HK, D).transpose(1, 2).repeat_interleave(H // HK, 1)
+    v = kv[..., HK * D:].view(B, N, HK, D).transpose(1, 2).repeat_interleave(H // HK, 1)
+    s = qq @ k.transpose(-1, -2) * D ** -0.5
+    return (s.softmax(-1) @ v).transpose(1, 2).reshape(B, L, H * D), torch.logsumexp(s, -1)
