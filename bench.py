@@ -196,6 +196,8 @@ class LayerRunner:
         self.params = {k: v.requires_grad_(True) for k, v in p.items()}
         self.sink = M.SparseBankGrad()
         self.params["bank"].moc_sparse_grad = self.sink
+        self.g_lb = torch.tensor(0.01, device=device)
+        self.g_z = torch.tensor(0.001, device=device)
         self.reducer = None
         if world > 1:
             from memory_b200.distributed import GradReducer
@@ -214,8 +216,11 @@ class LayerRunner:
             tokens_per_chapter=cfg["tokens_per_chapter"], top_k=cfg["top_k"],
             num_shared_chapters=cfg["num_shared_chapters"], routed_scaling_factor=cfg["routed_scaling_factor"],
             compute_dtype=torch.bfloat16)
-        loss = (out.float() * d_out.float()).sum() + 0.01 * losses["load_balance"] + 0.001 * losses["z_loss"]
-        loss.backward()
+        # d(loss)/d(out) = d_out, loss = <out, d_out> + 0.01 load_balance + 0.001 z_loss: seed the backward
+        # directly instead of materialising the inner product on the device
+        torch.autograd.backward([out, losses["load_balance"], losses["z_loss"]],
+                                [d_out, self.g_lb, self.g_z])
+        loss = losses["load_balance"]
         if self.reducer is not None:
             dense = [P[k].grad for k in ("router_w", "router_b", "wq", "wk", "wv", "wo")]
             self.reducer.reduce(dense, self.sink)

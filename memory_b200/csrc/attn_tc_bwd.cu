@@ -27,26 +27,40 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// delta[b,h,l] = <O, dO>; nlse2[b,h,l] = -lse * log2(e)
+// delta[b,h,l] = <O, dO>; nlse2[b,h,l] = -lse * log2(e).  One warp per (b, l) row: lanes read 16-byte
+// chunks of the H*64-wide row; a head is 8 chunks, reduced across 8 adjacent lanes.
 __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                 const float* __restrict__ lse, float* __restrict__ delta,
                                 float* __restrict__ nlse2, int B, int L, int H) {
   const int lane = threadIdx.x & 31;
-  const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
-  const long long total = static_cast<long long>(B) * L * H;
-  if (w >= total) return;
-  const int h = static_cast<int>(w % H);
-  const long long bl = w / H;
+  const long long bl = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  if (bl >= static_cast<long long>(B) * L) return;
   const int l = static_cast<int>(bl % L);
   const int b = static_cast<int>(bl / L);
-  const __nv_bfloat162* po = reinterpret_cast<const __nv_bfloat162*>(o + bl * H * kD + h * kD);
-  const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(d_o + bl * H * kD + h * kD);
-  const float2 a = __bfloat1622float2(po[lane]), g = __bfloat1622float2(pd[lane]);
-  float acc = warp_sum(a.x * g.x + a.y * g.y);
-  if (lane == 0) {
-    const long long idx = (static_cast<long long>(b) * H + h) * L + l;
-    delta[idx] = acc;
-    nlse2[idx] = -lse[idx] * kLog2e;
+  const int chunks = H * (kD / 8);
+  const uint4* po = reinterpret_cast<const uint4*>(o + bl * H * kD);
+  const uint4* pd = reinterpret_cast<const uint4*>(d_o + bl * H * kD);
+  for (int c0 = 0; c0 < chunks; c0 += 32) {
+    const int c = c0 + lane;
+    float acc = 0.f;
+    if (c < chunks) {
+      const uint4 a = po[c], g = pd[c];
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(gw[i] << 16), acc);
+        acc = fmaf(__uint_as_float(aw[i] & 0xFFFF0000u), __uint_as_float(gw[i] & 0xFFFF0000u), acc);
+      }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    if (c < chunks && (lane & 7) == 0) {
+      const int h = c >> 3;
+      const long long idx = (static_cast<long long>(b) * H + h) * L + l;
+      delta[idx] = acc;
+      nlse2[idx] = -lse[idx] * kLog2e;
+    }
   }
 }
 
@@ -431,7 +445,7 @@ int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, c
   float* delta = scratch;
   float* nlse2 = scratch + static_cast<long long>(B) * H * L;
   if (parts & 1) {
-    const long long total = static_cast<long long>(B) * L * H;
+    const long long total = static_cast<long long>(B) * L;
     const int blocks = static_cast<int>((total * 32 + 255) / 256);
     bwd_prep_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(o),
                                                 static_cast<const __nv_bfloat16*>(d_o), lse, delta, nlse2, B, L, H);

@@ -19,6 +19,31 @@ template <> __device__ __forceinline__ void st<__nv_bfloat16>(__nv_bfloat16* p, 
   p[i] = __float2bfloat16(v);
 }
 
+// 8 consecutive elements (16-byte aligned for bf16, 32-byte for fp32)
+__device__ __forceinline__ void ld8(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void st8(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p) = o;
+}
+
 // statistics of one bank row as the normalisation needs them: {mean, 1/sqrt(var or meansq + eps)}
 template <typename TB>
 __device__ __forceinline__ void row_norm_stats(const TB* row, int dim, int norm_type, float eps, int lane,
@@ -66,7 +91,17 @@ __global__ void gather_rows_kernel(const TB* __restrict__ bank, long long bank_r
     row_stats[r * 2 + 1] = rinv;
   }
   const float w = comb_w ? comb_w[pair] : 1.f;
-  for (int c = lane; c < dim; c += 32) st(dst, c, (ld(row, c) - mean) * rinv * w);
+  if ((dim & 7) == 0) {
+    for (int c = lane * 8; c < dim; c += 256) {
+      float v[8];
+      ld8(row + c, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = (v[i] - mean) * rinv * w;
+      st8(dst + c, v);
+    }
+  } else {
+    for (int c = lane; c < dim; c += 32) st(dst, c, (ld(row, c) - mean) * rinv * w);
+  }
 }
 
 // Groups (batch, slot) pairs by chapter id.  Single CTA.
@@ -143,13 +178,31 @@ __global__ void dcombw_kernel(const TG* __restrict__ d_mem, const TB* __restrict
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   float acc = 0.f;
   if (chapter >= 0 && (chapter + 1) * T <= bank_rows) {
-    for (int r = warp; r < T; r += nw) {
-      const long long orow = pair * T + r;
-      const TB* row = bank + (chapter * T + r) * dim;
-      const TG* g = d_mem + orow * dim;
-      float mean = 0.f, rinv = 1.f;
-      if (norm_type != MOC_NORM_NONE) { mean = row_stats[orow * 2]; rinv = row_stats[orow * 2 + 1]; }
-      for (int c = lane; c < dim; c += 32) acc += ld(g, c) * (ld(row, c) - mean) * rinv;
+    if ((dim & 7) == 0) {
+      const int per_row = dim >> 3;
+      const int total = T * per_row;
+      for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int r = i / per_row, c = (i - r * per_row) << 3;
+        const long long orow = pair * T + r;
+        float g[8], x[8];
+        ld8(d_mem + orow * dim + c, g);
+        ld8(bank + (chapter * T + r) * dim + c, x);
+        float mean = 0.f, rinv = 1.f;
+        if (norm_type != MOC_NORM_NONE) { mean = row_stats[orow * 2]; rinv = row_stats[orow * 2 + 1]; }
+        float a = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a = fmaf(g[j], x[j] - mean, a);
+        acc = fmaf(a, rinv, acc);
+      }
+    } else {
+      for (int r = warp; r < T; r += nw) {
+        const long long orow = pair * T + r;
+        const TB* row = bank + (chapter * T + r) * dim;
+        const TG* g = d_mem + orow * dim;
+        float mean = 0.f, rinv = 1.f;
+        if (norm_type != MOC_NORM_NONE) { mean = row_stats[orow * 2]; rinv = row_stats[orow * 2 + 1]; }
+        for (int c = lane; c < dim; c += 32) acc += ld(g, c) * (ld(row, c) - mean) * rinv;
+      }
     }
   }
   acc = warp_sum(acc);
@@ -178,6 +231,21 @@ __global__ void bank_grad_kernel(const TG* __restrict__ d_mem, const TB* __restr
   const int within = static_cast<int>(r - static_cast<long long>(u) * T);
   const int p0 = seg_offsets[u], p1 = seg_offsets[u + 1];
   float* dst = bank_grad + r * dim;
+  if (norm_type == MOC_NORM_NONE && (dim & 7) == 0) {
+    for (int c = lane * 8; c < dim; c += 256) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int q = p0; q < p1; ++q) {
+        const long long pair = seg_pairs[q];
+        const float w = comb_w ? comb_w[pair] : 1.f;
+        float g[8];
+        ld8(d_mem + (pair * T + within) * dim + c, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = fmaf(w, g[j], acc[j]);
+      }
+      st8(dst + c, acc);
+    }
+    return;
+  }
   if (norm_type == MOC_NORM_NONE) {
     for (int c = lane; c < dim; c += 32) {
       float acc = 0.f;

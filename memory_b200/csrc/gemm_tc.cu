@@ -1,11 +1,13 @@
 // bf16 tensor-core projection kernel for sm_100a: TMA -> shared memory (128-byte swizzle) ->
 // tcgen05.mma with the fp32 accumulator tile in tensor memory -> tcgen05.ld epilogue.
 //
-//   C[M,N] (+)= op(A)[M,K] * op(B)[K,N], 128 x 128 output tile per CTA, 64-wide K stages.
+//   C[M,N] (+)= op(A)[M,K] * op(B)[K,N], 128 x 256 (or 128 x 128) output tiles, 64-wide K stages.
 //
-// Roles inside a CTA of 192 threads: warp 0 issues the TMA loads, warp 1 owns tensor memory and
-// issues the MMAs from one lane, warps 2-5 drain the accumulator (each warp may only touch the 32
-// TMEM lanes selected by warp_id % 4).  The A operand can be fetched through a row-block gather
+// Persistent: one CTA per SM walks a static list of (tile, K-split) items.  Roles inside a CTA of 192
+// threads: warp 0 issues the TMA loads, warp 1 owns tensor memory and issues the MMAs from one lane,
+// warps 2-5 drain the accumulator (each warp may only touch the 32 TMEM lanes selected by
+// warp_id % 4).  Two accumulator buffers in tensor memory let the epilogue of one tile run under the
+// main loop of the next.  The A operand can be fetched through a row-block gather
 // list, which is how selected chapters are read straight out of the memory bank.
 #include "moc_common.cuh"
 
@@ -14,12 +16,17 @@ namespace moc {
 namespace {
 
 constexpr int BM = 128;
-constexpr int BN = 128;
 constexpr int BK = 64;
-constexpr int kStages = 3;
-constexpr int kStageBytes = (BM * BK + BN * BK) * 2;   // 32 KiB
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 128;
+constexpr int kTmemCols = 512;          // two accumulator buffers of up to 256 columns
+
+template <int BN> struct Cfg {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+};
 
 struct GemmTcParams {
   int m, n, k;
@@ -37,6 +44,9 @@ struct GemmTcParams {
   long long a_stored_rows;
   int k_tiles_total;
   int k_tiles_per_split;
+  int splits;
+  int m_tiles, n_tiles;
+  int num_items;           // m_tiles * n_tiles * splits
   int* status;
 };
 
@@ -45,13 +55,17 @@ __device__ __forceinline__ void drain_after_abort() {
   for (int i = 0; i < 200; ++i) __nanosleep(1000);
 }
 
-__global__ void __launch_bounds__(kThreads)
+// Persistent kernel: CTA i works on items i, i + gridDim.x, ...; an item is (output tile, K split).
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                GemmTcParams p) {
+  using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[kStages];
-  __shared__ __align__(8) uint64_t empty_bar[kStages];
-  __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ __align__(8) uint64_t full_bar[C::kStages];
+  __shared__ __align__(8) uint64_t empty_bar[C::kStages];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -59,20 +73,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int lane = threadIdx.x & 31;
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
-  const int n0 = blockIdx.x * BN;
-  const int m0 = blockIdx.y * BM;
-  const int kt_begin = blockIdx.z * p.k_tiles_per_split;
-  int kt_count = p.k_tiles_total - kt_begin;
-  if (kt_count > p.k_tiles_per_split) kt_count = p.k_tiles_per_split;
-  if (kt_count < 0) kt_count = 0;
-
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&acc_bar, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);
+    }
     fence_mbar_init();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
@@ -84,142 +94,185 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_acc = tmem_slot;
+  const uint32_t tmem_base = tmem_slot;
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kt = 0; kt < kt_count; ++kt) {
-        const int s = kt % kStages;
-        const uint32_t ph = (kt / kStages) & 1;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, p.status)) break;
-        mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
-        uint8_t* a_s = tiles + s * kStageBytes;
-        uint8_t* b_s = a_s + BM * BK * 2;
-        const int k0 = (kt_begin + kt) * BK;
-        if (p.a_kmajor) {
-          const int nbox = BM / p.a_box_rows;
-          for (int i = 0; i < nbox; ++i) {
-            long long row;
-            if (p.a_row_blocks != nullptr) {
-              const int blk = m0 / p.a_box_rows + i;
-              row = (blk < p.a_num_blocks) ? static_cast<long long>(p.a_row_blocks[blk]) * p.a_box_rows
-                                           : p.a_stored_rows;
-              if (row < 0 || row > p.a_stored_rows) {
-                atomicMax(p.status, MOC_DEV_BAD_INDEX);
-                row = p.a_stored_rows;   // fully out of range: the copy zero-fills
+      uint32_t it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
+        const int split = item % p.splits;
+        const int tile = item / p.splits;
+        const int n0 = (tile % p.n_tiles) * BN;
+        const int m0 = (tile / p.n_tiles) * BM;
+        const int kt_begin = split * p.k_tiles_per_split;
+        int kt_count = p.k_tiles_total - kt_begin;
+        if (kt_count > p.k_tiles_per_split) kt_count = p.k_tiles_per_split;
+        for (int kt = 0; kt < kt_count; ++kt, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t ph = (it / C::kStages) & 1;
+          ok = mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, p.status);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&full_bar[s], C::kStageBytes);
+          uint8_t* a_s = tiles + s * C::kStageBytes;
+          uint8_t* b_s = a_s + C::kABytes;
+          const int k0 = (kt_begin + kt) * BK;
+          if (p.a_kmajor) {
+            const int nbox = BM / p.a_box_rows;
+            for (int i = 0; i < nbox; ++i) {
+              long long row;
+              if (p.a_row_blocks != nullptr) {
+                const int blk = m0 / p.a_box_rows + i;
+                row = (blk < p.a_num_blocks) ? static_cast<long long>(p.a_row_blocks[blk]) * p.a_box_rows
+                                             : p.a_stored_rows;
+                if (row < 0 || row > p.a_stored_rows) {
+                  atomicMax(p.status, MOC_DEV_BAD_INDEX);
+                  row = p.a_stored_rows;   // fully out of range: the copy zero-fills
+                }
+              } else {
+                row = m0 + i * p.a_box_rows;
               }
-            } else {
-              row = m0 + i * p.a_box_rows;
+              tma_load_2d(a_s + i * p.a_box_rows * 128, &tmap_a, &full_bar[s], k0, static_cast<int>(row));
             }
-            tma_load_2d(a_s + i * p.a_box_rows * 128, &tmap_a, &full_bar[s], k0, static_cast<int>(row));
+          } else {
+            tma_load_2d(a_s, &tmap_a, &full_bar[s], m0, k0);
+            tma_load_2d(a_s + 8192, &tmap_a, &full_bar[s], m0 + 64, k0);
           }
-        } else {
-          tma_load_2d(a_s, &tmap_a, &full_bar[s], m0, k0);
-          tma_load_2d(a_s + 8192, &tmap_a, &full_bar[s], m0 + 64, k0);
-        }
-        if (p.b_kmajor) {
-          tma_load_2d(b_s, &tmap_b, &full_bar[s], k0, n0);
-          tma_load_2d(b_s + 8192, &tmap_b, &full_bar[s], k0, n0 + 64);
-        } else {
-          tma_load_2d(b_s, &tmap_b, &full_bar[s], n0, k0);
-          tma_load_2d(b_s + 8192, &tmap_b, &full_bar[s], n0 + 64, k0);
+          if (p.b_kmajor) {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)
+              tma_load_2d(b_s + j * 16384, &tmap_b, &full_bar[s], k0, n0 + j * 128);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_s + j * 8192, &tmap_b, &full_bar[s], n0 + j * 64, k0);
+          }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(BM, BN, p.a_kmajor ? 0 : 1, p.b_kmajor ? 0 : 1);
+      uint32_t it = 0, t = 0;
       bool ok = true;
-      for (int kt = 0; kt < kt_count && ok; ++kt) {
-        const int s = kt % kStages;
-        const uint32_t ph = (kt / kStages) & 1;
-        ok = mbar_wait(&full_bar[s], ph, &abort_flag, p.status);
+      for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x, ++t) {
+        const int split = item % p.splits;
+        const int kt_begin = split * p.k_tiles_per_split;
+        int kt_count = p.k_tiles_total - kt_begin;
+        if (kt_count > p.k_tiles_per_split) kt_count = p.k_tiles_per_split;
+        const uint32_t buf = t & 1;
+        ok = mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, &abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(tiles + s * kStageBytes);
-        const uint32_t b_addr = a_addr + BM * BK * 2;
+        const uint32_t tmem_acc = tmem_base + buf * 256;
+        for (int kt = 0; kt < kt_count; ++kt, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t ph = (it / C::kStages) & 1;
+          ok = mbar_wait(&full_bar[s], ph, &abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + s * C::kStageBytes);
+          const uint32_t b_addr = a_addr + C::kABytes;
 #pragma unroll
-        for (int kk = 0; kk < BK / 16; ++kk) {
-          const uint64_t ad = p.a_kmajor ? umma_desc_sw128(a_addr + kk * 32, 16, 1024)
-                                         : umma_desc_sw128(a_addr + kk * 2048, 8192, 1024);
-          const uint64_t bd = p.b_kmajor ? umma_desc_sw128(b_addr + kk * 32, 16, 1024)
-                                         : umma_desc_sw128(b_addr + kk * 2048, 8192, 1024);
-          umma_ss(tmem_acc, ad, bd, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t ad = p.a_kmajor ? umma_desc_sw128(a_addr + kk * 32, 16, 1024)
+                                           : umma_desc_sw128(a_addr + kk * 2048, 8192, 1024);
+            const uint64_t bd = p.b_kmajor ? umma_desc_sw128(b_addr + kk * 32, 16, 1024)
+                                           : umma_desc_sw128(b_addr + kk * 2048, 8192, 1024);
+            umma_ss(tmem_acc, ad, bd, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[s]);
         }
-        tc_commit(&empty_bar[s]);
+        if (!ok) break;
+        tc_commit(&acc_full[buf]);
       }
-      tc_commit(&acc_bar);
     }
   } else {
     // epilogue: TMEM lanes [32*(warp%4), +32) <-> output rows
     const int lane_group = (warp & 3) * 32;
-    const int row = m0 + lane_group + lane;
-    bool have_acc = false;
-    if (kt_count > 0) have_acc = mbar_wait(&acc_bar, 0, &abort_flag, p.status);
-    have_acc = __all_sync(0xffffffffu, have_acc);   // tcgen05.ld below is warp-collective
-    tc_fence_after();
-    float rs = 1.0f;
-    if (p.row_scale != nullptr && row < p.m) rs = p.row_scale[row / p.scale_block_rows];
+    uint32_t t = 0;
+    for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++t) {
+      const int split = item % p.splits;
+      const int tile = item / p.splits;
+      const int n0 = (tile % p.n_tiles) * BN;
+      const int m0 = (tile / p.n_tiles) * BM;
+      const int kt_begin = split * p.k_tiles_per_split;
+      const bool has_k = kt_begin < p.k_tiles_total;
+      const uint32_t buf = t & 1;
+      bool have_acc = mbar_wait(&acc_full[buf], (t >> 1) & 1, &abort_flag, p.status);
+      have_acc = __all_sync(0xffffffffu, have_acc);   // tcgen05.ld below is warp-collective
+      if (!have_acc) break;
+      tc_fence_after();
+      const uint32_t tmem_acc = tmem_base + buf * 256;
+      const int row = m0 + lane_group + lane;
+      float rs = 1.0f;
+      if (p.row_scale != nullptr && row < p.m) rs = p.row_scale[row / p.scale_block_rows];
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-      uint32_t r[32];
-      if (have_acc) {
-        tmem_ld32(tmem_acc + (static_cast<uint32_t>(lane_group) << 16) + c * 32, r);
-        tmem_wait_ld();
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = 0u;
-      }
-      const int col0 = n0 + c * 32;
-      if (row >= p.m || col0 >= p.n || abort_flag) continue;
-      if (!have_acc && (p.atomic || p.accumulate)) continue;
-      if (p.c_bf16) {
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
-        const bool vec = ((p.ldc & 7) == 0) && (col0 + 32 <= p.n) &&
-                         ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
-        if (vec) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]) * rs, __uint_as_float(r[8 * j + 1]) * rs);
-            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * rs, __uint_as_float(r[8 * j + 3]) * rs);
-            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * rs, __uint_as_float(r[8 * j + 5]) * rs);
-            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * rs, __uint_as_float(r[8 * j + 7]) * rs);
-            *reinterpret_cast<uint4*>(dst + 8 * j) = v;
-          }
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.n) break;                       // uniform across the warp
+        if (has_k) {
+          tmem_ld32(tmem_acc + (static_cast<uint32_t>(lane_group) << 16) + c * 32, r);
+          tmem_wait_ld();
         } else {
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.n) dst[j] = __float2bfloat16(__uint_as_float(r[j]) * rs);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-      } else {
-        float* dst = reinterpret_cast<float*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
-        if (p.atomic) {
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.n) atomicAdd(dst + j, __uint_as_float(r[j]) * rs);
-        } else {
-          const bool vec = ((p.ldc & 3) == 0) && (col0 + 32 <= p.n) &&
+        if (row >= p.m) continue;
+        if (!has_k && (p.atomic || p.accumulate)) continue;
+        if (p.c_bf16) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+          const bool vec = ((p.ldc & 7) == 0) && (col0 + 32 <= p.n) &&
                            ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
           if (vec) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 v = make_float4(__uint_as_float(r[4 * j + 0]) * rs, __uint_as_float(r[4 * j + 1]) * rs,
-                                     __uint_as_float(r[4 * j + 2]) * rs, __uint_as_float(r[4 * j + 3]) * rs);
-              float4* d4 = reinterpret_cast<float4*>(dst + 4 * j);
-              if (p.accumulate) {
-                const float4 o = *d4;
-                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-              }
-              *d4 = v;
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]) * rs, __uint_as_float(r[8 * j + 1]) * rs);
+              v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * rs, __uint_as_float(r[8 * j + 3]) * rs);
+              v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * rs, __uint_as_float(r[8 * j + 5]) * rs);
+              v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * rs, __uint_as_float(r[8 * j + 7]) * rs);
+              *reinterpret_cast<uint4*>(dst + 8 * j) = v;
             }
           } else {
             for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.n) {
-                const float v = __uint_as_float(r[j]) * rs;
-                dst[j] = p.accumulate ? dst[j] + v : v;
+              if (col0 + j < p.n) dst[j] = __float2bfloat16(__uint_as_float(r[j]) * rs);
+          }
+        } else {
+          float* dst = reinterpret_cast<float*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+          if (p.atomic) {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.n) atomicAdd(dst + j, __uint_as_float(r[j]) * rs);
+          } else {
+            const bool vec = ((p.ldc & 3) == 0) && (col0 + 32 <= p.n) &&
+                             ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
+            if (vec) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(__uint_as_float(r[4 * j + 0]) * rs, __uint_as_float(r[4 * j + 1]) * rs,
+                                       __uint_as_float(r[4 * j + 2]) * rs, __uint_as_float(r[4 * j + 3]) * rs);
+                float4* d4 = reinterpret_cast<float4*>(dst + 4 * j);
+                if (p.accumulate) {
+                  const float4 o = *d4;
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *d4 = v;
               }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.n) {
+                  const float v = __uint_as_float(r[j]) * rs;
+                  dst[j] = p.accumulate ? dst[j] + v : v;
+                }
+            }
           }
         }
       }
+      // this warp is done reading the accumulator buffer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
     tc_fence_before();
   }
@@ -228,8 +281,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (abort_flag) drain_after_abort();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, kTmemCols);
+    tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
 }
 
 }  // namespace
@@ -257,8 +320,15 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
     MOC_REQUIRE(a_stored_rows > 0, "a_stored_rows missing");
   }
 
-  const int smem_bytes = kStages * kStageBytes + 1024;
-  MOC_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  // tile width: 256 columns when that does not leave SMs idle in the last wave, else 128
+  const int sms = sm_count();
+  const int m_tiles = ceil_div(g->m, BM);
+  auto waves_cost = [&](int bn) {
+    const long long items = static_cast<long long>(m_tiles) * ceil_div(g->n, bn) * split;
+    const long long rounds = (items + sms - 1) / sms;
+    return static_cast<double>(rounds) * bn;
+  };
+  const int bn = (g->n > 128 && waves_cost(256) <= waves_cost(128)) ? 256 : 128;
 
   CUtensorMap tmap_a, tmap_b;
   int rc;
@@ -272,7 +342,7 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
   if (rc != MOC_OK) return rc;
   if (g->b_kmajor) {
     rc = make_tmap_bf16_2d(&tmap_b, b, static_cast<uint64_t>(g->n), static_cast<uint64_t>(g->k),
-                           static_cast<uint64_t>(g->ldb), 64, 64);
+                           static_cast<uint64_t>(g->ldb), 128, 64);
   } else {
     rc = make_tmap_bf16_2d(&tmap_b, b, static_cast<uint64_t>(g->k), static_cast<uint64_t>(g->n),
                            static_cast<uint64_t>(g->ldb), 64, 64);
@@ -289,10 +359,22 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
   p.a_stored_rows = a_stored_rows;
   p.k_tiles_total = ceil_div(g->k, BK);
   p.k_tiles_per_split = ceil_div(p.k_tiles_total, split);
+  p.splits = ceil_div(p.k_tiles_total, p.k_tiles_per_split);   // no empty splits
+  p.m_tiles = m_tiles;
+  p.n_tiles = ceil_div(g->n, bn);
+  p.num_items = p.m_tiles * p.n_tiles * p.splits;
   p.status = status;
 
-  dim3 grid(ceil_div(g->n, BN), ceil_div(g->m, BM), split);
-  gemm_tc_kernel<<<grid, kThreads, smem_bytes, stream>>>(tmap_a, tmap_b, p);
+  const int grid = p.num_items < sms ? p.num_items : sms;
+  if (bn == 256) {
+    MOC_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg<256>::kSmemBytes));
+    gemm_tc_kernel<256><<<grid, kThreads, Cfg<256>::kSmemBytes, stream>>>(tmap_a, tmap_b, p);
+  } else {
+    MOC_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg<128>::kSmemBytes));
+    gemm_tc_kernel<128><<<grid, kThreads, Cfg<128>::kSmemBytes, stream>>>(tmap_a, tmap_b, p);
+  }
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
 }

@@ -14,7 +14,7 @@ namespace {
 constexpr int kPoolSplits = 32;       // sequence splits of the mean-pool
 constexpr int kSelectThreads = 1024;  // one CTA per batch row in the select / dlogits kernels
 constexpr int kLossChunk = 256;       // chapters per CTA in the loss kernels
-constexpr int kDpChunk = 128;         // chapters per CTA in the d_pooled kernel
+constexpr int kDpChunk = 16;          // chapters per CTA in the d_pooled kernel
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
@@ -82,6 +82,7 @@ __global__ void logits_kernel(const float* __restrict__ pooled, const float* __r
   extern __shared__ float sp[];   // [8][d]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = blockIdx.x * (blockDim.x >> 5) + warp;
+  const bool vec = (d & 3) == 0;
   for (int b0 = 0; b0 < B; b0 += 8) {
     const int nb = min(8, B - b0);
     __syncthreads();
@@ -92,11 +93,24 @@ __global__ void logits_kernel(const float* __restrict__ pooled, const float* __r
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
       const float* wr = w + static_cast<long long>(c) * d;
-      for (int k = lane; k < d; k += 32) {
-        const float wv = wr[k];
+      if (vec) {
+        const float4* w4 = reinterpret_cast<const float4*>(wr);
+        for (int k = lane; k < d / 4; k += 32) {
+          const float4 wv = w4[k];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (j < nb) acc[j] = fmaf(wv, sp[j * d + k], acc[j]);
+          for (int j = 0; j < 8; ++j)
+            if (j < nb) {
+              const float4 pv = reinterpret_cast<const float4*>(sp + j * d)[k];
+              acc[j] = fmaf(wv.x, pv.x, fmaf(wv.y, pv.y, fmaf(wv.z, pv.z, fmaf(wv.w, pv.w, acc[j]))));
+            }
+        }
+      } else {
+        for (int k = lane; k < d; k += 32) {
+          const float wv = wr[k];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (j < nb) acc[j] = fmaf(wv, sp[j * d + k], acc[j]);
+        }
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -202,37 +216,41 @@ select_kernel(const float* __restrict__ logits, float* __restrict__ probs, long 
       }
     }
     __syncthreads();
-    // rank sort of the k selected entries: value descending, chapter id ascending
+    // rank sort of the k selected entries: value descending, chapter id ascending (shared memory)
+    float* srt_w = sm;                         // p~ is no longer needed: reuse its first 2k words
+    int* srt_i = reinterpret_cast<int*>(sm + k_sel);
+    uint32_t kt_reg[1]; int it_reg[1]; int rk_reg[1];
+    {
+      const int t = threadIdx.x;
+      if (t < k_sel) {
+        const uint32_t kt = sel_key[t];
+        const int it = sel_idx[t];
+        int rank = 0;
+        for (int j = 0; j < k_sel; ++j) {
+          const uint32_t kj = sel_key[j];
+          rank += (kj > kt) || (kj == kt && sel_idx[j] < it);
+        }
+        kt_reg[0] = kt; it_reg[0] = it; rk_reg[0] = rank;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < k_sel) { srt_w[rk_reg[0]] = __uint_as_float(kt_reg[0]); srt_i[rk_reg[0]] = it_reg[0]; }
+    __syncthreads();
+    float part = 0.f;
+    for (int j = threadIdx.x; j < k_sel; j += blockDim.x) part += srt_w[j];
+    topk_mass = block_sum(part, red);
+    const float dn = fmaxf(topk_mass, 1e-12f);
     long long* out_idx = idx + static_cast<long long>(b) * k_sel;
     float* out_w = weights + static_cast<long long>(b) * k_sel;
-    for (int t = threadIdx.x; t < k_sel; t += blockDim.x) {
-      const uint32_t kt = sel_key[t];
-      const int it = sel_idx[t];
-      int rank = 0;
-      for (int j = 0; j < k_sel; ++j) {
-        const uint32_t kj = sel_key[j];
-        rank += (kj > kt) || (kj == kt && sel_idx[j] < it);
-      }
-      out_idx[rank] = it;
-      out_w[rank] = __uint_as_float(kt);
+    float cpart = 0.f;
+    for (int j = threadIdx.x; j < k_sel; j += blockDim.x) {
+      const float wj = srt_w[j] / dn;
+      srt_w[j] = wj;
+      out_w[j] = wj;
+      out_idx[j] = srt_i[j];
+      cpart += wj * rho;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float sum = 0.f;
-      for (int j = 0; j < k_sel; ++j) sum += out_w[j];
-      topk_mass = sum;
-      const float dn = fmaxf(sum, 1e-12f);
-      float csum = static_cast<float>(S);
-      for (int j = 0; j < k_sel; ++j) {
-        const float wj = out_w[j] / dn;
-        out_w[j] = wj;
-        csum += wj * rho;
-      }
-      comb_mass = csum;
-      red[0] = topk_mass; red[1] = comb_mass;
-    }
-    __syncthreads();
-    topk_mass = red[0]; comb_mass = red[1];
+    comb_mass = static_cast<float>(S) + block_sum(cpart, red);
   }
   // shared prefix + renormalised combined weights (only meaningful when S > 0; with S == 0 the
   // combined lists are the routed lists unchanged)
@@ -240,8 +258,7 @@ select_kernel(const float* __restrict__ logits, float* __restrict__ probs, long 
   for (int j = threadIdx.x; j < kc; j += blockDim.x) {
     int ci; float u;
     if (j < S) { ci = j; u = 1.f; }
-    else { ci = static_cast<int>(idx[static_cast<long long>(b) * k_sel + (j - S)]);
-           u = weights[static_cast<long long>(b) * k_sel + (j - S)] * (S > 0 ? rho : 1.f); }
+    else { ci = reinterpret_cast<int*>(sm + k_sel)[j - S]; u = sm[j - S] * (S > 0 ? rho : 1.f); }
     comb_idx[static_cast<long long>(b) * kc + j] = ci;
     comb_w[static_cast<long long>(b) * kc + j] = (S > 0) ? u / fmaxf(comb_mass, 1e-12f) : u;
   }
@@ -332,29 +349,34 @@ dlogits_kernel(const float* __restrict__ probs, const long long* __restrict__ id
   const int kc = S + k_sel;
 
   // (a)+(b): gradients of the k selected (unnormalised) masked probabilities v_j
-  if (threadIdx.x == 0) {
-    float dotu = 0.f;
-    if (d_comb_w != nullptr && S > 0)
-      for (int i = 0; i < kc; ++i) dotu += d_comb_w[static_cast<long long>(b) * kc + i] * comb_w[static_cast<long long>(b) * kc + i];
-    float dotw = 0.f;
-    for (int j = 0; j < k_sel; ++j) {
-      float dw = d_weights ? d_weights[static_cast<long long>(b) * k_sel + j] : 0.f;
-      if (d_comb_w != nullptr) {
-        const float dcu = d_comb_w[static_cast<long long>(b) * kc + S + j];
-        if (S > 0) dw += rho * ((u_mass >= 1e-12f) ? (dcu - dotu) / u_mass : dcu / 1e-12f);
-        else dw += dcu;
-      }
-      s_dv[j] = dw;
-      dotw += dw * weights[static_cast<long long>(b) * k_sel + j];
+  __shared__ float s_w[1024];
+  float dotu_p = 0.f;
+  if (d_comb_w != nullptr && S > 0)
+    for (int i = threadIdx.x; i < kc; i += blockDim.x)
+      dotu_p += d_comb_w[static_cast<long long>(b) * kc + i] * comb_w[static_cast<long long>(b) * kc + i];
+  const float dotu = block_sum(dotu_p, red);
+  float dotw_p = 0.f;
+  for (int j = threadIdx.x; j < k_sel; j += blockDim.x) {
+    float dw = d_weights ? d_weights[static_cast<long long>(b) * k_sel + j] : 0.f;
+    if (d_comb_w != nullptr) {
+      const float dcu = d_comb_w[static_cast<long long>(b) * kc + S + j];
+      if (S > 0) dw += rho * ((u_mass >= 1e-12f) ? (dcu - dotu) / u_mass : dcu / 1e-12f);
+      else dw += dcu;
     }
-    float A = 0.f;
-    for (int j = 0; j < k_sel; ++j) {
-      const float dv = (v_mass >= 1e-12f) ? (s_dv[j] - dotw) / v_mass : s_dv[j] / 1e-12f;
-      s_dv[j] = dv;
-      A += dv * (weights[static_cast<long long>(b) * k_sel + j] * fmaxf(v_mass, 1e-12f));   // v_j
-    }
-    s_scal[0] = A;
+    const float wj = weights[static_cast<long long>(b) * k_sel + j];
+    s_dv[j] = dw;
+    s_w[j] = wj;
+    dotw_p += dw * wj;
   }
+  const float dotw = block_sum(dotw_p, red);
+  float a_p = 0.f;
+  for (int j = threadIdx.x; j < k_sel; j += blockDim.x) {
+    const float dv = (v_mass >= 1e-12f) ? (s_dv[j] - dotw) / v_mass : s_dv[j] / 1e-12f;
+    s_dv[j] = dv;
+    a_p += dv * (s_w[j] * fmaxf(v_mass, 1e-12f));   // v_j
+  }
+  const float a_tot = block_sum(a_p, red);
+  if (threadIdx.x == 0) s_scal[0] = a_tot;
   __syncthreads();
   const float A = s_scal[0];
   const bool renorm = (S > 0);
@@ -383,20 +405,35 @@ dlogits_kernel(const float* __restrict__ probs, const long long* __restrict__ id
     d_logits[static_cast<long long>(b) * C + c] = p[c] * (dp[c] - dot + zc);
 }
 
-// d_w[c,:] = sum_b d_logits[b,c] * pooled[b,:]; d_bias[c] = sum_b d_logits[b,c]; one warp per chapter
+// d_w[c,:] = sum_b d_logits[b,c] * pooled[b,:]; d_bias[c] = sum_b d_logits[b,c]; one warp per chapter,
+// 8 batch rows of `pooled` staged in shared memory per pass
 __global__ void dweight_kernel(const float* __restrict__ d_logits, const float* __restrict__ pooled,
                                float* __restrict__ d_w, float* __restrict__ d_bias, int B, int d, int C) {
+  extern __shared__ float sp[];   // [8][d]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (c >= C) return;
   float bsum = 0.f;
-  for (int b = 0; b < B; ++b) bsum += d_logits[static_cast<long long>(b) * C + c];
-  if (lane == 0 && d_bias) d_bias[c] = bsum;
-  for (int k = lane; k < d; k += 32) {
-    float acc = 0.f;
-    for (int b = 0; b < B; ++b) acc = fmaf(d_logits[static_cast<long long>(b) * C + c], pooled[static_cast<long long>(b) * d + k], acc);
-    d_w[static_cast<long long>(c) * d + k] = acc;
+  for (int b0 = 0; b0 < B; b0 += 8) {
+    const int nb = min(8, B - b0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb * d; i += blockDim.x) sp[i] = pooled[static_cast<long long>(b0) * d + i];
+    __syncthreads();
+    if (c >= C) continue;
+    float dz[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      dz[j] = j < nb ? d_logits[static_cast<long long>(b0 + j) * C + c] : 0.f;
+      bsum += dz[j];
+    }
+    float* dst = d_w + static_cast<long long>(c) * d;
+    for (int k = lane; k < d; k += 32) {
+      float acc = (b0 == 0) ? 0.f : dst[k];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc = fmaf(dz[j], sp[j * d + k], acc);
+      dst[k] = acc;
+    }
   }
+  if (c < C && lane == 0 && d_bias) d_bias[c] = bsum;
 }
 
 // partial[chunk][b][k] = sum over the chunk's chapters of d_logits[b,c] * w[c,k]
@@ -436,18 +473,49 @@ __global__ void dpooled_finish_kernel(const float* __restrict__ partial, float* 
   for (int ch = 0; ch < nchunks; ++ch) acc += partial[static_cast<long long>(ch) * total + i];
   d_pooled[i] = acc;
 }
+// d_h[b, t, :] (+)= d_pooled[b, :] / L; one thread per 8 consecutive columns of one row (d % 8 == 0),
+// falling back to one element per thread otherwise
 template <typename T>
 __global__ void dh_broadcast_kernel(const float* __restrict__ d_pooled, T* __restrict__ d_h, int L, int d,
-                                    long long total, int accumulate) {
+                                    long long rows, int accumulate) {
   const float invL = 1.f / static_cast<float>(L);
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long row = i / d;
-    const int c = static_cast<int>(i - row * d);
-    const int b = static_cast<int>(row / L);
-    float v = d_pooled[static_cast<long long>(b) * d + c] * invL;
-    if (accumulate) v += to_f32(d_h[i]);
-    if constexpr (sizeof(T) == 4) d_h[i] = v; else d_h[i] = __float2bfloat16(v);
+  if ((d & 7) == 0) {
+    const int per_row = d >> 3;
+    const long long total = rows * per_row;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long row = i / per_row;
+      const int c = static_cast<int>(i - row * per_row) << 3;
+      const int b = static_cast<int>(row / L);
+      const float4 p0 = *reinterpret_cast<const float4*>(d_pooled + static_cast<long long>(b) * d + c);
+      const float4 p1 = *reinterpret_cast<const float4*>(d_pooled + static_cast<long long>(b) * d + c + 4);
+      float v[8] = {p0.x * invL, p0.y * invL, p0.z * invL, p0.w * invL, p1.x * invL, p1.y * invL, p1.z * invL, p1.w * invL};
+      T* dst = d_h + row * d + c;
+      if (accumulate) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] += to_f32(dst[j]);
+      }
+      if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      } else {
+        uint4 o;
+        o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+        o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(dst) = o;
+      }
+    }
+  } else {
+    const long long total = rows * d;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long row = i / d;
+      const int c = static_cast<int>(i - row * d);
+      const int b = static_cast<int>(row / L);
+      float v = d_pooled[static_cast<long long>(b) * d + c] * invL;
+      if (accumulate) v += to_f32(d_h[i]);
+      if constexpr (sizeof(T) == 4) d_h[i] = v; else d_h[i] = __float2bfloat16(v);
+    }
   }
 }
 
@@ -554,17 +622,23 @@ extern "C" int moc_router_bwd(const moc_router_shape* s, const float* w, const f
                                                       comb_w, row_stats, chapter_stats, d_weights, d_comb_w,
                                                       d_losses, d_logits, B, C, k_sel, S, s->routed_scale);
   }
-  dweight_kernel<<<ceil_div(C, 8), 256, 0, stream>>>(d_logits, pooled, d_w, d_bias, B, d, C);
+  {
+    const size_t sm = static_cast<size_t>(8) * d * sizeof(float);
+    MOC_CUDA_OK(cudaFuncSetAttribute(dweight_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
+    dweight_kernel<<<ceil_div(C, 8), 256, sm, stream>>>(d_logits, pooled, d_w, d_bias, B, d, C);
+  }
   const int nchunks = ceil_div(C, kDpChunk);
   dpooled_partial_kernel<<<nchunks, 256, 0, stream>>>(d_logits, w, ws, B, d, C);
   dpooled_finish_kernel<<<ceil_div(B * d, 256), 256, 0, stream>>>(ws, d_pooled, nchunks, B * d);
   if (d_h != nullptr) {
-    const long long total = static_cast<long long>(B) * L * d;
-    const int blocks = static_cast<int>(total / 256 / 4 + 1 < 148 * 16 ? total / 256 / 4 + 1 : 148 * 16);
+    const long long rows = static_cast<long long>(B) * L;
+    const long long work = (d & 7) == 0 ? rows * (d >> 3) : rows * d;
+    long long blocks = (work + 255) / 256;
+    if (blocks > 148LL * 32) blocks = 148LL * 32;
     if (s->h_dtype == MOC_F32)
-      dh_broadcast_kernel<float><<<blocks, 256, 0, stream>>>(d_pooled, static_cast<float*>(d_h), L, d, total, accumulate_dh);
+      dh_broadcast_kernel<float><<<static_cast<int>(blocks), 256, 0, stream>>>(d_pooled, static_cast<float*>(d_h), L, d, rows, accumulate_dh);
     else
-      dh_broadcast_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(d_pooled, static_cast<__nv_bfloat16*>(d_h), L, d, total, accumulate_dh);
+      dh_broadcast_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, stream>>>(d_pooled, static_cast<__nv_bfloat16*>(d_h), L, d, rows, accumulate_dh);
   }
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
