@@ -1,5 +1,8 @@
 // bf16 joint-softmax cross attention, backward, for sm_100a: two tcgen05 kernels, no atomics.
 //
+//  In both kernels two groups of four warps own the 128 rows of a tile: group g works on columns
+//  [32g, 32g+32) of the score tile, which puts four row-owning warps on every scheduler partition.
+//
 //  dQ kernel  (query stationary, CTA = 128 queries of one head): per 64-key tile
 //        S = Q K^T, dP = dO V^T            (SS MMAs into tensor memory)
 //        dS = exp2(S*c - lse*log2e) * (dP - delta) * scale   (one query row per thread)
@@ -17,7 +20,7 @@ namespace moc {
 namespace {
 
 constexpr int kD = 64;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;      // two groups of 4 row-owning warps + TMA warp + MMA warp
 constexpr int kStages = 3;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -103,18 +106,18 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     mbar_init(&q_bar, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(&sdp_full, 1);
-    mbar_init(&sdp_free, 128);
-    mbar_init(&ds_full, 128);
+    mbar_init(&sdp_free, 256);
+    mbar_init(&ds_full, 256);
     mbar_init(&dq_bar, 1);
     fence_mbar_init();
     prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_kv);
   }
-  if (warp == 5) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); tc_fence_before(); }
+  if (warp == 9) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); tc_fence_before(); }
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       mbar_arrive_expect_tx(&q_bar, 2 * kQBytes);
       tma_load_2d(q_s, &tmap_q, &q_bar, h * kD, b * p.L + q0);
@@ -129,7 +132,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         tma_load_2d(k_s + kKvBytes, &tmap_kv, &kv_full[s], p.HK * kD + kh * kD, row);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc_kk = umma_idesc_bf16(kQ, kKeys, 0, 0);   // S and dP: both operands K-major
       const uint32_t idesc_dq = umma_idesc_bf16(kQ, kD, 0, 1);      // dQ: B = K tile, MN-major
@@ -169,8 +172,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       }
     }
   } else {
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
-    const int row = warp * 32 + lane;
+    // row-owning warps: warp & 3 selects the 32 TMEM lanes, warp >> 2 the column half
+    const int half = warp >> 2;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int row = (warp & 3) * 32 + lane;
     const int l = q0 + row;
     const long long sidx = (static_cast<long long>(b) * p.H + h) * p.L + (l < p.L ? l : 0);
     const float nl = p.nlse2[sidx], dl = p.delta[sidx];
@@ -180,32 +185,37 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int valid = p.n_sel - j * kKeys;
-      uint32_t pk[32];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      const int valid = p.n_sel - j * kKeys - half * 32;   // columns of this half that are real keys
+      uint32_t pk[16];
+      {
         uint32_t rs[32], rd[32];
         tmem_ld32(tmem + lane_sel + kDqColS + half * 32, rs);
         tmem_ld32(tmem + lane_sel + kDqColDP + half * 32, rd);
         tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&sdp_free);          // S / dP may be overwritten by the next tile's MMAs
+        // dS without the softmax scale: it is applied once when dQ is written
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          float d0 = ex2(fmaf(__uint_as_float(rs[c]), p.scale_log2, nl)) * (__uint_as_float(rd[c]) - dl) * p.scale;
-          float d1 = ex2(fmaf(__uint_as_float(rs[c + 1]), p.scale_log2, nl)) * (__uint_as_float(rd[c + 1]) - dl) * p.scale;
-          if (half * 32 + c >= valid) d0 = 0.f;
-          if (half * 32 + c + 1 >= valid) d1 = 0.f;
-          pk[half * 16 + c / 2] = pack_bf16x2(d0, d1);
+          const float d0 = ex2(fmaf(__uint_as_float(rs[c]), p.scale_log2, nl)) * (__uint_as_float(rd[c]) - dl);
+          const float d1 = ex2(fmaf(__uint_as_float(rs[c + 1]), p.scale_log2, nl)) * (__uint_as_float(rd[c + 1]) - dl);
+          pk[c / 2] = pack_bf16x2(d0, d1);
+        }
+        if (valid < 32) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            if (c >= valid) pk[c / 2] = 0u;
+            else if (c + 1 >= valid) pk[c / 2] &= 0x0000FFFFu;
+          }
         }
       }
-      tc_fence_before();
-      mbar_arrive(&sdp_free);          // S / dP may be overwritten by the next tile's MMAs
       if (j > 0) {
         ok = mbar_wait(&dq_bar, (j - 1) & 1, &abort_flag, p.status);   // previous dS consumed
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
       }
-      tmem_st32(tmem + lane_sel + kDqColDS, pk);
+      tmem_st16(tmem + lane_sel + kDqColDS + half * 16, pk);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&ds_full);
@@ -216,22 +226,19 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     }
     if (ok) {
       tc_fence_after();
-      __nv_bfloat16* dst = p.d_q + (static_cast<long long>(b) * p.L + l) * (p.H * kD) + h * kD;
+      __nv_bfloat16* dst = p.d_q + (static_cast<long long>(b) * p.L + l) * (p.H * kD) + h * kD + half * 32;
+      uint32_t r[32];
+      tmem_ld32(tmem + lane_sel + kDqColDQ + half * 32, r);
+      tmem_wait_ld();
+      if (l < p.L) {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_sel + kDqColDQ + half * 32, r);
-        tmem_wait_ld();
-        if (l < p.L) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * c + 0]), __uint_as_float(r[8 * c + 1]));
-            v.y = pack_bf16x2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3]));
-            v.z = pack_bf16x2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5]));
-            v.w = pack_bf16x2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7]));
-            *reinterpret_cast<uint4*>(dst + half * 32 + c * 8) = v;
-          }
+        for (int c = 0; c < 4; ++c) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(r[8 * c + 0]) * p.scale, __uint_as_float(r[8 * c + 1]) * p.scale);
+          v.y = pack_bf16x2(__uint_as_float(r[8 * c + 2]) * p.scale, __uint_as_float(r[8 * c + 3]) * p.scale);
+          v.z = pack_bf16x2(__uint_as_float(r[8 * c + 4]) * p.scale, __uint_as_float(r[8 * c + 5]) * p.scale);
+          v.w = pack_bf16x2(__uint_as_float(r[8 * c + 6]) * p.scale, __uint_as_float(r[8 * c + 7]) * p.scale);
+          *reinterpret_cast<uint4*>(dst + c * 8) = v;
         }
       }
     }
@@ -239,7 +246,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   }
   __syncthreads();
   if (abort_flag) { for (int i = 0; i < 200; ++i) __nanosleep(1000); }
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem, 256); }
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem, 256); }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -292,17 +299,17 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     mbar_init(&k_bar, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     mbar_init(&sdp_full, 1);
-    mbar_init(&pt_full, 128);
+    mbar_init(&pt_full, 256);
     mbar_init(&acc_bar, 1);
     fence_mbar_init();
     prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_kv);
   }
-  if (warp == 5) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); tc_fence_before(); }
+  if (warp == 9) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); tc_fence_before(); }
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       mbar_arrive_expect_tx(&k_bar, 2 * kKBytes);
       const int row = b * p.n_sel + key0;
@@ -323,7 +330,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         bulk_load_1d(stats + s * 2 * kStatBytes + kStatBytes, p.delta + soff, kStatBytes, &q_full[s]);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_bf16(kKeysB, kQB, 0, 0);   // S^T, dP^T
       const uint32_t idesc_g = umma_idesc_bf16(kKeysB, kD, 0, 1);    // dV, dK: B = dO / Q tile, MN-major
@@ -347,21 +354,23 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         ok = mbar_wait(&pt_full, it & 1, &abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
+        // P^T / dS^T for queries [32g, 32g+32) sit in the first 16 columns of column half g
 #pragma unroll
         for (int kk = 0; kk < kQB / 16; ++kk)
-          umma_ts(tmem + kColDV, tmem + kColST + kk * 8, umma_desc_sw128(do_addr + kk * 2048, 8192, 1024),
-                  idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tmem + kColDV, tmem + kColST + (kk >> 1) * 32 + (kk & 1) * 8,
+                  umma_desc_sw128(do_addr + kk * 2048, 8192, 1024), idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < kQB / 16; ++kk)
-          umma_ts(tmem + kColDK, tmem + kColDPT + kk * 8, umma_desc_sw128(q_addr + kk * 2048, 8192, 1024),
-                  idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tmem + kColDK, tmem + kColDPT + (kk >> 1) * 32 + (kk & 1) * 8,
+                  umma_desc_sw128(q_addr + kk * 2048, 8192, 1024), idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
         tc_commit(&q_empty[s]);
       }
       tc_commit(&acc_bar);
     }
   } else {
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
-    const int row = warp * 32 + lane;
+    const int half = warp >> 2;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int row = (warp & 3) * 32 + lane;
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int s = it % kStages;
@@ -369,29 +378,31 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const float* nl = reinterpret_cast<const float*>(stats + s * 2 * kStatBytes);
-      const float* dl = nl + kQB;
-      uint32_t pp[32], pd[32];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      const float4* nl4 = reinterpret_cast<const float4*>(stats + s * 2 * kStatBytes) + half * 8;
+      const float4* dl4 = nl4 + kQB / 4;
+      uint32_t pp[16], pd[16];
+      {
         uint32_t rs[32], rd[32];
         tmem_ld32(tmem + lane_sel + kColST + half * 32, rs);
         tmem_ld32(tmem + lane_sel + kColDPT + half * 32, rd);
         tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const int qi = half * 32 + c;
-          const float p0 = ex2(fmaf(__uint_as_float(rs[c]), p.scale_log2, nl[qi]));
-          const float p1 = ex2(fmaf(__uint_as_float(rs[c + 1]), p.scale_log2, nl[qi + 1]));
-          const float d0 = p0 * (__uint_as_float(rd[c]) - dl[qi]) * p.scale;
-          const float d1 = p1 * (__uint_as_float(rd[c + 1]) - dl[qi + 1]) * p.scale;
-          pp[half * 16 + c / 2] = pack_bf16x2(p0, p1);
-          pd[half * 16 + c / 2] = pack_bf16x2(d0, d1);
+        for (int c = 0; c < 32; c += 4) {
+          const float4 n = nl4[c / 4], d = dl4[c / 4];
+          const float p0 = ex2(fmaf(__uint_as_float(rs[c + 0]), p.scale_log2, n.x));
+          const float p1 = ex2(fmaf(__uint_as_float(rs[c + 1]), p.scale_log2, n.y));
+          const float p2 = ex2(fmaf(__uint_as_float(rs[c + 2]), p.scale_log2, n.z));
+          const float p3 = ex2(fmaf(__uint_as_float(rs[c + 3]), p.scale_log2, n.w));
+          pp[c / 2] = pack_bf16x2(p0, p1);
+          pp[c / 2 + 1] = pack_bf16x2(p2, p3);
+          // dS^T without the softmax scale: it is applied once when dK is written
+          pd[c / 2] = pack_bf16x2(p0 * (__uint_as_float(rd[c + 0]) - d.x), p1 * (__uint_as_float(rd[c + 1]) - d.y));
+          pd[c / 2 + 1] = pack_bf16x2(p2 * (__uint_as_float(rd[c + 2]) - d.z), p3 * (__uint_as_float(rd[c + 3]) - d.w));
         }
       }
-      // every fp32 value of this row has been read: overwrite the first 32 columns of each region
-      tmem_st32(tmem + lane_sel + kColST, pp);
-      tmem_st32(tmem + lane_sel + kColDPT, pd);
+      // this thread has read every fp32 value of its row in this column half: overwrite its first 16 columns
+      tmem_st16(tmem + lane_sel + kColST + half * 32, pp);
+      tmem_st16(tmem + lane_sel + kColDPT + half * 32, pd);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&pt_full);
@@ -403,25 +414,23 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     if (ok) {
       tc_fence_after();
       const int key = key0 + row;
-      __nv_bfloat16* dst = p.d_kv + (static_cast<long long>(b) * p.n_sel + key) * (2 * p.HK * kD) + kh * kD;
+      __nv_bfloat16* dst = p.d_kv + (static_cast<long long>(b) * p.n_sel + key) * (2 * p.HK * kD) + kh * kD + half * 32;
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {      // 0: dK, 1: dV
+      for (int which = 0; which < 2; ++which) {      // 0: dK (carries the softmax scale), 1: dV
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_sel + (which ? kColDV : kColDK) + half * 32, r);
+        tmem_wait_ld();
+        const float f = which ? 1.f : p.scale;
+        if (key < p.n_sel) {
+          __nv_bfloat16* d2 = dst + (which ? p.HK * kD : 0);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t r[32];
-          tmem_ld32(tmem + lane_sel + (which ? kColDV : kColDK) + half * 32, r);
-          tmem_wait_ld();
-          if (key < p.n_sel) {
-            __nv_bfloat16* d2 = dst + (which ? p.HK * kD : 0) + half * 32;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(r[8 * c + 0]), __uint_as_float(r[8 * c + 1]));
-              v.y = pack_bf16x2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3]));
-              v.z = pack_bf16x2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5]));
-              v.w = pack_bf16x2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7]));
-              *reinterpret_cast<uint4*>(d2 + c * 8) = v;
-            }
+          for (int c = 0; c < 4; ++c) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * c + 0]) * f, __uint_as_float(r[8 * c + 1]) * f);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * c + 2]) * f, __uint_as_float(r[8 * c + 3]) * f);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * c + 4]) * f, __uint_as_float(r[8 * c + 5]) * f);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * c + 6]) * f, __uint_as_float(r[8 * c + 7]) * f);
+            *reinterpret_cast<uint4*>(d2 + c * 8) = v;
           }
         }
       }
@@ -430,7 +439,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   }
   __syncthreads();
   if (abort_flag) { for (int i = 0; i < 200; ++i) __nanosleep(1000); }
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem, 256); }
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem, 256); }
 }
 
 }  // namespace

@@ -5,10 +5,12 @@
 // accumulator in tensor memory) -> online softmax by 128 threads that each own one query row
 // (tcgen05.ld, exp2 on the scaled scores, P written back to tensor memory as packed bf16) ->
 // O += P_j V_j (tcgen05.mma with A = P from tensor memory, B = the V tile as an MN-major operand).
-// S is double buffered in tensor memory so the next QK^T runs under the current softmax; two CTAs
-// share an SM (256 TMEM columns and ~81 KiB of shared memory each) so one CTA's exponentials
-// overlap the other's MMAs.  The running maximum is only raised (and O rescaled) when it grows by
-// more than 2^8, which keeps P within bf16 range while skipping almost every rescale.
+// A CTA is deliberately small -- 128 TMEM columns (S, with P written over its first 32 columns, and
+// O), ~49 KiB of shared memory, 192 threads -- so that four CTAs share an SM: while one CTA's row
+// owners are in their exponentials the other CTAs' MMAs and loads run, which is what hides the
+// TMEM / barrier latencies of the strictly ordered S -> softmax -> PV chain inside one CTA.  The
+// running maximum is only raised (and O rescaled) when it grows by more than 2^8, which keeps P
+// within bf16 range while skipping almost every rescale.
 #include "moc_common.cuh"
 
 namespace moc {
@@ -17,15 +19,15 @@ namespace {
 constexpr int kQ = 128;          // queries per CTA
 constexpr int kKeys = 64;        // keys per tile
 constexpr int kD = 64;           // head dim
-constexpr int kStages = 4;       // K/V ring depth
+constexpr int kStages = 2;       // K/V ring depth
 constexpr int kThreads = 192;    // 4 softmax warps + TMA warp + MMA warp
 constexpr int kQBytes = kQ * kD * 2;
 constexpr int kTileBytes = kKeys * kD * 2;
 constexpr int kSmemBytes = kQBytes + kStages * 2 * kTileBytes + 1024;
-constexpr int kTmemCols = 256;
-constexpr uint32_t kColS = 0;      // two S buffers: columns [0,64) and [64,128)
-constexpr uint32_t kColO = 128;    // O accumulator: 64 columns
-constexpr uint32_t kColP = 192;    // P as packed bf16: 32 columns
+constexpr int kTmemCols = 128;
+constexpr uint32_t kColS = 0;      // S: columns [0,64)
+constexpr uint32_t kColP = 0;      // P as packed bf16 over the first 32 columns of S
+constexpr uint32_t kColO = 64;     // O accumulator: 64 columns
 constexpr float kRescaleThreshold = 8.0f;
 
 struct FwdParams {
@@ -42,11 +44,11 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 4)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
                    FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t q_bar, kv_full[kStages], kv_empty[kStages], s_full[2], p_full, pv_bar;
+  __shared__ __align__(8) uint64_t q_bar, kv_full[kStages], kv_empty[kStages], s_full, p_full, pv_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -64,8 +66,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     abort_flag = 0;
     mbar_init(&q_bar, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(&s_full[0], 1);
-    mbar_init(&s_full[1], 1);
+    mbar_init(&s_full, 1);
     mbar_init(&p_full, 128);
     mbar_init(&pv_bar, 1);
     fence_mbar_init();
@@ -104,19 +105,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const uint32_t idesc_o = umma_idesc_bf16(kQ, kD, 0, 1);
       const uint32_t q_addr = smem_u32(q_s);
       bool ok = mbar_wait(&q_bar, 0, &abort_flag, p.status);
+      // order: S_0, then per tile PV_j followed by S_{j+1}.  S_{j+1} overwrites the columns P_j lives
+      // in; tcgen05.mma instructions of one thread execute in issue order, so PV_j has read them.
       for (int j = 0; j <= n_tiles && ok; ++j) {
-        if (j < n_tiles) {
-          const int s = j % kStages;
-          ok = mbar_wait(&kv_full[s], (j / kStages) & 1, &abort_flag, p.status);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t k_addr = smem_u32(kv_s + s * 2 * kTileBytes);
-#pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk)
-            umma_ss(tmem + kColS + (j & 1) * 64, umma_desc_sw128(q_addr + kk * 32, 16, 1024),
-                    umma_desc_sw128(k_addr + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-          tc_commit(&s_full[j & 1]);
-        }
         if (j > 0) {
           const int jp = j - 1, s = jp % kStages;
           ok = mbar_wait(&p_full, jp & 1, &abort_flag, p.status);
@@ -130,6 +121,18 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           tc_commit(&kv_empty[s]);
           tc_commit(&pv_bar);
         }
+        if (j < n_tiles) {
+          const int s = j % kStages;
+          ok = mbar_wait(&kv_full[s], (j / kStages) & 1, &abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(kv_s + s * 2 * kTileBytes);
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk)
+            umma_ss(tmem + kColS, umma_desc_sw128(q_addr + kk * 32, 16, 1024),
+                    umma_desc_sw128(k_addr + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          tc_commit(&s_full);
+        }
       }
     }
   } else {
@@ -139,29 +142,37 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, &abort_flag, p.status);
+      ok = mbar_wait(&s_full, j & 1, &abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_addr = tmem + lane_sel + kColS + (j & 1) * 64;
+      const uint32_t s_addr = tmem + lane_sel + kColS;
       const int valid = p.n_sel - j * kKeys;   // keys of this tile that exist
       uint32_t r[32];
       float tmax = -INFINITY;
+      if (valid >= kKeys) {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        tmem_ld32(s_addr + half * 32, r);
-        tmem_wait_ld();
+        for (int half = 0; half < 2; ++half) {
+          tmem_ld32(s_addr + half * 32, r);
+          tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float v = __uint_as_float(r[c]);
-          tmax = fmaxf(tmax, (half * 32 + c < valid) ? v : -INFINITY);
+          for (int c = 0; c < 32; ++c) tmax = fmaxf(tmax, __uint_as_float(r[c]));
+        }
+      } else {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          tmem_ld32(s_addr + half * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            tmax = fmaxf(tmax, (half * 32 + c < valid) ? __uint_as_float(r[c]) : -INFINITY);
         }
       }
       const float m_new = fmaxf(m_used, tmax * p.scale_log2);
       const bool need = (j == 0) || (m_new - m_used > kRescaleThreshold);
       const bool any_need = __any_sync(0xffffffffu, need);
       if (j > 0) {
-        ok = mbar_wait(&pv_bar, (j - 1) & 1, &abort_flag, p.status);   // O and P are free again
+        ok = mbar_wait(&pv_bar, (j - 1) & 1, &abort_flag, p.status);   // O is complete up to tile j-1
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -180,22 +191,34 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       }
       if (need) m_used = m_new;
       uint32_t pk[32];
-      float psum = 0.f;
+      float psum0 = 0.f, psum1 = 0.f;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         tmem_ld32(s_addr + half * 32, r);
         tmem_wait_ld();
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          float e0 = ex2(fmaf(__uint_as_float(r[c]), p.scale_log2, -m_used));
-          float e1 = ex2(fmaf(__uint_as_float(r[c + 1]), p.scale_log2, -m_used));
-          if (half * 32 + c >= valid) e0 = 0.f;
-          if (half * 32 + c + 1 >= valid) e1 = 0.f;
-          psum += e0 + e1;
+          const float e0 = ex2(fmaf(__uint_as_float(r[c]), p.scale_log2, -m_used));
+          const float e1 = ex2(fmaf(__uint_as_float(r[c + 1]), p.scale_log2, -m_used));
+          psum0 += e0;
+          psum1 += e1;
           pk[half * 16 + c / 2] = pack_bf16x2(e0, e1);
         }
       }
-      l_sum += psum;
+      if (valid < kKeys) {       // last, partial tile: zero the columns past the end and redo the sum
+        psum0 = 0.f; psum1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          uint32_t v = pk[c / 2];
+          if (c >= valid) v = 0u;
+          else if (c + 1 >= valid) v &= 0x0000FFFFu;
+          pk[c / 2] = v;
+          psum0 += __uint_as_float(v << 16);
+          psum1 += __uint_as_float(v & 0xFFFF0000u);
+        }
+      }
+      l_sum += psum0 + psum1;
+      // every S value of this row is in registers by now: P goes over the first 32 columns of S
       tmem_st32(tmem + lane_sel + kColP, pk);
       tmem_wait_st();
       tc_fence_before();
