@@ -196,6 +196,11 @@ int moc_sparse_attn_bwd(const moc_sparse_attn_shape* s, const void* q, const voi
 /* Element-wise helpers used by the host layer (device pointers, n elements). */
 int moc_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream);
 int moc_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream);
+/* dst[c, r] = src[r, c] for a row-major [rows, cols] matrix, converting between the dtype codes.  Used to
+ * keep the nn.Linear weights (memory_attention.py:140-143) in the K-major layout the input-gradient
+ * projections want. */
+int moc_transpose(const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, int32_t rows, int32_t cols,
+                  void* stream);
 
 #ifdef __cplusplus
 }

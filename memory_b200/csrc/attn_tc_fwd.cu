@@ -192,29 +192,35 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       if (need) m_used = m_new;
       uint32_t pk[32];
       float psum0 = 0.f, psum1 = 0.f;
+      if (valid >= kKeys) {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        tmem_ld32(s_addr + half * 32, r);
-        tmem_wait_ld();
+        for (int half = 0; half < 2; ++half) {
+          tmem_ld32(s_addr + half * 32, r);
+          tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float e0 = ex2(fmaf(__uint_as_float(r[c]), p.scale_log2, -m_used));
-          const float e1 = ex2(fmaf(__uint_as_float(r[c + 1]), p.scale_log2, -m_used));
-          psum0 += e0;
-          psum1 += e1;
-          pk[half * 16 + c / 2] = pack_bf16x2(e0, e1);
+          for (int c = 0; c < 32; c += 2) {
+            const float e0 = ex2(fmaf(__uint_as_float(r[c]), p.scale_log2, -m_used));
+            const float e1 = ex2(fmaf(__uint_as_float(r[c + 1]), p.scale_log2, -m_used));
+            psum0 += e0;
+            psum1 += e1;
+            pk[half * 16 + c / 2] = pack_bf16x2(e0, e1);
+          }
         }
-      }
-      if (valid < kKeys) {       // last, partial tile: zero the columns past the end and redo the sum
-        psum0 = 0.f; psum1 = 0.f;
+      } else {       // last, partial tile: columns past the end contribute nothing
 #pragma unroll
-        for (int c = 0; c < 64; c += 2) {
-          uint32_t v = pk[c / 2];
-          if (c >= valid) v = 0u;
-          else if (c + 1 >= valid) v &= 0x0000FFFFu;
-          pk[c / 2] = v;
-          psum0 += __uint_as_float(v << 16);
-          psum1 += __uint_as_float(v & 0xFFFF0000u);
+        for (int half = 0; half < 2; ++half) {
+          tmem_ld32(s_addr + half * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            float e0 = ex2(fmaf(__uint_as_float(r[c]), p.scale_log2, -m_used));
+            float e1 = ex2(fmaf(__uint_as_float(r[c + 1]), p.scale_log2, -m_used));
+            if (half * 32 + c >= valid) e0 = 0.f;
+            if (half * 32 + c + 1 >= valid) e1 = 0.f;
+            psum0 += e0;
+            psum1 += e1;
+            pk[half * 16 + c / 2] = pack_bf16x2(e0, e1);
+          }
         }
       }
       l_sum += psum0 + psum1;

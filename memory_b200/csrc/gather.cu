@@ -307,6 +307,22 @@ __global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ src, floa
     dst[i] = __bfloat162float(src[i]);
 }
 
+// dst[c, r] = src[r, c] with dtype conversion; 32 x 32 tiles through shared memory
+template <typename TS, typename TD>
+__global__ void transpose_kernel(const TS* __restrict__ src, TD* __restrict__ dst, int rows, int cols) {
+  __shared__ float tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int r = r0 + i, c = c0 + threadIdx.x;
+    tile[i][threadIdx.x] = (r < rows && c < cols) ? ld(src, static_cast<long long>(r) * cols + c) : 0.f;
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int c = c0 + i, r = r0 + threadIdx.x;
+    if (c < cols && r < rows) st(dst, static_cast<long long>(c) * rows + r, tile[threadIdx.x][i]);
+  }
+}
+
 inline int grid_for(long long n, int per_block) {
   long long g = (n + per_block - 1) / per_block;
   const long long cap = 148LL * 32;
@@ -420,6 +436,24 @@ extern "C" int moc_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void
   if (n == 0) return MOC_OK;
   cast_bf16_f32_kernel<<<grid_for(n, 256 * 8), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
       static_cast<const __nv_bfloat16*>(src), dst, n);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+extern "C" int moc_transpose(const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, int32_t rows,
+                             int32_t cols, void* stream_) {
+  MOC_REQUIRE(src && dst && rows > 0 && cols > 0, "bad transpose arguments");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  dim3 grid(ceil_div(cols, 32), ceil_div(rows, 32)), block(32, 8);
+  if (src_dtype == MOC_F32 && dst_dtype == MOC_BF16)
+    transpose_kernel<float, __nv_bfloat16><<<grid, block, 0, stream>>>(static_cast<const float*>(src), static_cast<__nv_bfloat16*>(dst), rows, cols);
+  else if (src_dtype == MOC_BF16 && dst_dtype == MOC_BF16)
+    transpose_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), rows, cols);
+  else if (src_dtype == MOC_F32 && dst_dtype == MOC_F32)
+    transpose_kernel<float, float><<<grid, block, 0, stream>>>(static_cast<const float*>(src), static_cast<float*>(dst), rows, cols);
+  else if (src_dtype == MOC_BF16 && dst_dtype == MOC_F32)
+    transpose_kernel<__nv_bfloat16, float><<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), static_cast<float*>(dst), rows, cols);
+  else MOC_REQUIRE(false, "bad dtype");
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
 }

@@ -168,20 +168,35 @@ class _CrossAttention(torch.autograd.Function):
         d = h2.shape[1]
         g2 = ops.cast(g.reshape(b * l, -1).contiguous(), cd)
         f32 = torch.float32
-        split = 1 if cd == torch.float32 else max(1, min(16, (b * l) // 2048))
-        d_o = ops.gemm(g2, wo_c, b_kmajor=False, tag="d_attn_out")                                      # [B*L, H*D]
+        # K-splits of the weight-gradient projections: enough (tile, split) items to fill the SMs once
+        def splits(rows, out_rows, out_cols):
+            if cd == torch.float32:
+                return 1
+            tiles = -(-out_rows // 128) * -(-out_cols // 256)
+            return max(1, min(148 // max(tiles, 1), rows // 512))
+        split = splits(b * l, d, d)
+        tc = cd == torch.bfloat16
+
+        def grad_in(dy, w_c, tag):
+            """dX = dY W.  The tensor-core kernel is fastest with both operands K-major, so the small
+            weight is transposed first; the fp32 kernel takes the strided operand directly."""
+            if tc:
+                return ops.gemm(dy, ops.transpose(w_c), tag=tag)
+            return ops.gemm(dy, w_c, b_kmajor=False, tag=tag)
+
+        d_o = grad_in(g2, wo_c, "d_attn_out")                                      # [B*L, H*D]
         d_wo = ops.gemm(g2, o.view(b * l, -1), a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split,
                         tag="d_wo")
         d_q, d_kv = ops.attn_bwd(q.view(b, l, -1), kv, o, lse, d_o.view(b, l, -1), num_heads, num_kv_heads, scale)
         d_q2 = d_q.view(b * l, -1)
-        d_h = ops.gemm(d_q2, wq_c, b_kmajor=False, tag="d_h")
+        d_h = grad_in(d_q2, wq_c, "d_h")
         d_wq = ops.gemm(d_q2, h2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split, tag="d_wq")
         d_kv2 = d_kv.view(-1, d_kv.shape[-1])
         if mem_shared:
             d_kv2 = d_kv.float().sum(dim=0).to(cd)
         rows = d_kv2.shape[0]
-        split_kv = 1 if cd == torch.float32 else max(1, min(16, rows // 2048))
-        d_mem = ops.gemm(d_kv2, wkv_c, b_kmajor=False, out_dtype=f32 if cd == f32 else cd, tag="d_mem")
+        split_kv = splits(rows, wkv_c.shape[0], d)
+        d_mem = grad_in(d_kv2, wkv_c, "d_mem")
         d_wkv = ops.gemm(d_kv2, m2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split_kv, tag="d_wkv")
         dkv_dim = wkv_c.shape[0] // 2
         wdt = ctx.w_dtypes

@@ -350,3 +350,17 @@ def _cast(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
         raise TypeError(f"unsupported cast {t.dtype} -> {dtype}")
     L.check(rc, "moc_cast")
     return out
+
+
+@_instrument("transpose", 1)
+def transpose(t: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """[R, C] -> contiguous [C, R] in ``dtype`` (default: same dtype)."""
+    L.require_cuda(t)
+    t = _contig(t)
+    dtype = dtype or t.dtype
+    r, c = t.shape
+    out = torch.empty(c, r, dtype=dtype, device=t.device)
+    rc = L.lib().moc_transpose(L.ptr(t), L.dtype_code(t.dtype), L.ptr(out), L.dtype_code(dtype), r, c,
+                               L.stream_ptr(t.device))
+    L.check(rc, "moc_transpose")
+    return out
