@@ -179,15 +179,19 @@ def workload_config(cfg, n_gpus):
             "shared_chapters": cfg["num_shared_chapters"], "routed_scale": cfg["routed_scaling_factor"],
             "row_norm": "off", "parallelism": f"dp{n_gpus} (batch sharded, bank replicated)",
             "l2_policy": f"inputs larger than L2: {N_INPUT_SETS} rotating hidden-state batches, "
-                         "per-step working set > 400 MB against a 126 MB L2"}
+                         "per-step working set > 400 MB against a 126 MB L2",
+            "launch": "one CUDA graph replay per step (forward + backward captured once)"}
 
 
 # ----------------------------------------------------------------------------------------------
 # CUDA arm
 # ----------------------------------------------------------------------------------------------
 class LayerRunner:
-    def __init__(self, cfg, device, world=1, group=None):
+    """One memory layer with its parameters; ``step`` = forward + backward (+ gradient reduction)."""
+
+    def __init__(self, cfg, device, world=1, group=None, use_graph=True):
         import memory_b200 as M
+        from memory_b200.graph import GraphedStep
         self.M = M
         self.cfg = cfg
         self.device = device
@@ -203,8 +207,15 @@ class LayerRunner:
             from memory_b200.distributed import GradReducer
             self.reducer = GradReducer(cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["hidden_dim"], device,
                                        group=group)
+        self.graphed = None
+        if use_graph:
+            shape = (cfg["batch"], cfg["seq"], cfg["hidden_dim"])
+            h0 = torch.zeros(shape, dtype=torch.bfloat16, device=device).requires_grad_(True)
+            g0 = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+            h0.data.normal_()
+            self.graphed = GraphedStep(self._fwd_bwd, [h0, g0])
 
-    def step(self, h, d_out):
+    def _fwd_bwd(self, h, d_out):
         P, cfg = self.params, self.cfg
         for v in P.values():
             v.grad = None
@@ -220,11 +231,29 @@ class LayerRunner:
         # directly instead of materialising the inner product on the device
         torch.autograd.backward([out, losses["load_balance"], losses["z_loss"]],
                                 [d_out, self.g_lb, self.g_z])
-        loss = losses["load_balance"]
+        return losses["load_balance"]
+
+    def step(self, h, d_out, eager=False):
+        if self.graphed is not None and not eager:
+            loss = self.graphed(h, d_out)
+        else:
+            loss = self._fwd_bwd(h, d_out)
         if self.reducer is not None:
+            P = self.params
             dense = [P[k].grad for k in ("router_w", "router_b", "wq", "wk", "wv", "wo")]
             self.reducer.reduce(dense, self.sink)
         return loss
+
+    def launches_per_step(self):
+        """Kernels of this library one step launches (counted on an eager pass)."""
+        from memory_b200 import ops
+        shape = (self.cfg["batch"], self.cfg["seq"], self.cfg["hidden_dim"])
+        h = torch.randn(shape, device=self.device).bfloat16().requires_grad_(True)
+        g = torch.randn(shape, device=self.device).bfloat16()
+        n0 = ops.LAUNCHES
+        self._fwd_bwd(h, g)
+        torch.cuda.synchronize()
+        return ops.LAUNCHES - n0
 
 
 def time_op_breakdown(runner, hs, gs, steps):
@@ -232,7 +261,7 @@ def time_op_breakdown(runner, hs, gs, steps):
     from memory_b200 import ops
     ops.TIMER = {}
     for i in range(steps):
-        runner.step(hs[i % len(hs)], gs[i % len(gs)])
+        runner.step(hs[i % len(hs)], gs[i % len(gs)], eager=True)
     torch.cuda.synchronize()
     table = {k: sum(a.elapsed_time(b) for a, b in v) / steps for k, v in ops.TIMER.items()}
     ops.TIMER = None
@@ -295,7 +324,7 @@ def run_cuda_arm(args):
     L.lib()
 
     cfg = dict(PAPER)
-    runner = LayerRunner(cfg, device, world)
+    runner = LayerRunner(cfg, device, world, use_graph=not args.no_graph)
     hs_cpu, gs_cpu = make_hidden(cfg, N_INPUT_SETS, 1234 + rank, torch.bfloat16)
     hs = [t.to(device).requires_grad_(True) for t in hs_cpu]
     gs = [t.to(device) for t in gs_cpu]
@@ -314,7 +343,7 @@ def run_cuda_arm(args):
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    launches0 = ops.LAUNCHES
+    per_step_launches = runner.launches_per_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -323,7 +352,7 @@ def run_cuda_arm(args):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    launches = ops.LAUNCHES - launches0
+    launches = per_step_launches * args.steps
     clocks = sampler.stop() if sampler else None
     L.check_device_status(device)
     if world > 1:
@@ -438,6 +467,7 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--cpu-sample-batch", type=int, default=2)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="issue every kernel from Python instead of a CUDA graph")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "cuda":
         args.warmup = 3
