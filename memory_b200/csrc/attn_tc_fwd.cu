@@ -103,7 +103,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_bf16(kQ, kKeys, 0, 0);
       const uint32_t idesc_o = umma_idesc_bf16(kQ, kD, 0, 1);
-      const uint32_t q_addr = smem_u32(q_s);
+      // descriptors are built once; a stage or K step only adds a constant to the address field
+      const uint64_t q_desc = umma_desc_sw128(smem_u32(q_s), 16, 1024);
+      const uint64_t k_desc0 = umma_desc_sw128(smem_u32(kv_s), 16, 1024);
+      const uint64_t v_desc0 = umma_desc_sw128(smem_u32(kv_s) + kTileBytes, 8192, 1024);
+      constexpr uint64_t kStageOff = (2 * kTileBytes) >> 4;
       bool ok = mbar_wait(&q_bar, 0, &abort_flag, p.status);
       // order: S_0, then per tile PV_j followed by S_{j+1}.  S_{j+1} overwrites the columns P_j lives
       // in; tcgen05.mma instructions of one thread execute in issue order, so PV_j has read them.
@@ -113,11 +117,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           ok = mbar_wait(&p_full, jp & 1, &abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t v_addr = smem_u32(kv_s + s * 2 * kTileBytes + kTileBytes);
+          const uint64_t vd = v_desc0 + s * kStageOff;
+          umma_ts(tmem + kColO, tmem + kColP, vd, idesc_o, jp > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < kKeys / 16; ++kk)
-            umma_ts(tmem + kColO, tmem + kColP + kk * 8, umma_desc_sw128(v_addr + kk * 2048, 8192, 1024),
-                    idesc_o, (jp > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 1; kk < kKeys / 16; ++kk)
+            umma_ts(tmem + kColO, tmem + kColP + kk * 8, vd + kk * (2048 >> 4), idesc_o, 1u);
           tc_commit(&kv_empty[s]);
           tc_commit(&pv_bar);
         }
@@ -126,11 +130,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           ok = mbar_wait(&kv_full[s], (j / kStages) & 1, &abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t k_addr = smem_u32(kv_s + s * 2 * kTileBytes);
+          const uint64_t kd = k_desc0 + s * kStageOff;
+          umma_ss(tmem + kColS, q_desc, kd, idesc_s, 0u);
 #pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk)
-            umma_ss(tmem + kColS, umma_desc_sw128(q_addr + kk * 32, 16, 1024),
-                    umma_desc_sw128(k_addr + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          for (int kk = 1; kk < kD / 16; ++kk)
+            umma_ss(tmem + kColS, q_desc + kk * (32 >> 4), kd + kk * (32 >> 4), idesc_s, 1u);
           tc_commit(&s_full);
         }
       }

@@ -153,6 +153,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(BM, BN, p.a_kmajor ? 0 : 1, p.b_kmajor ? 0 : 1);
+      // Descriptors are built once: a stage or K step only adds a constant to the 16-byte-unit address
+      // field, so issuing an MMA costs two 64-bit adds instead of rebuilding both descriptors.
+      const uint32_t tiles_addr = smem_u32(tiles);
+      const uint64_t a_base = p.a_kmajor ? umma_desc_sw128(tiles_addr, 16, 1024) : umma_desc_sw128(tiles_addr, 8192, 1024);
+      const uint64_t b_base = p.b_kmajor ? umma_desc_sw128(tiles_addr + C::kABytes, 16, 1024)
+                                         : umma_desc_sw128(tiles_addr + C::kABytes, 8192, 1024);
+      const uint64_t a_step = p.a_kmajor ? (32 >> 4) : (2048 >> 4);
+      const uint64_t b_step = p.b_kmajor ? (32 >> 4) : (2048 >> 4);
       uint32_t it = 0, t = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x, ++t) {
@@ -171,16 +179,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           ok = mbar_wait(&full_bar[s], ph, &abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(tiles + s * C::kStageBytes);
-          const uint32_t b_addr = a_addr + C::kABytes;
+          const uint64_t stage_off = static_cast<uint64_t>(s) * (C::kStageBytes >> 4);
+          const uint64_t ad = a_base + stage_off, bd = b_base + stage_off;
+          umma_ss(tmem_acc, ad, bd, idesc, kt > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint64_t ad = p.a_kmajor ? umma_desc_sw128(a_addr + kk * 32, 16, 1024)
-                                           : umma_desc_sw128(a_addr + kk * 2048, 8192, 1024);
-            const uint64_t bd = p.b_kmajor ? umma_desc_sw128(b_addr + kk * 32, 16, 1024)
-                                           : umma_desc_sw128(b_addr + kk * 2048, 8192, 1024);
-            umma_ss(tmem_acc, ad, bd, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
-          }
+          for (int kk = 1; kk < BK / 16; ++kk) umma_ss(tmem_acc, ad + kk * a_step, bd + kk * b_step, idesc, 1u);
           tc_commit(&empty_bar[s]);
         }
         if (!ok) break;
