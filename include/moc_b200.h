@@ -175,6 +175,20 @@ int moc_attn_bwd_parts(const moc_attn_shape* s, const void* q, const void* kv, c
                        const void* d_o, void* d_q, void* d_kv, float* delta, int32_t parts, int32_t* status,
                        void* stream);
 
+/* moc_attn_bwd without caller-provided scratch and without any allocation.  It has no counterpart in the
+ * reference.  It exists for callers that are not allowed to allocate device memory when they run the
+ * backward pass (a serving process whose memory pool is frozen, a callback in which cudaMalloc is
+ * forbidden, a host program whose allocator cannot be reached from C).  The delta / log-sum-exp scratch
+ * lives in a fixed 4 MiB array inside the library image, so 2 * batch * num_heads * seq must not exceed
+ * MOC_ATTN_BWD_STATIC_MAX_FLOATS; larger problems are rejected with MOC_ERR_INVALID.
+ * The first call on each device looks the array's device address up (with that device current): make
+ * that first call outside any stream capture.  All calls on a device share the one array: two calls
+ * whose kernels can overlap on the GPU (different streams, no dependency) race on it and must be
+ * serialised by the caller.  Results equal moc_attn_bwd's. */
+#define MOC_ATTN_BWD_STATIC_MAX_FLOATS 1048576
+int moc_attn_bwd_static(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
+                        const void* d_o, void* d_q, void* d_kv, int32_t* status, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Per-token chapter-sparse attention: the contract of memory_cross_attn(q, k, v, block_indices,
  * block_size, scale) (kernels-final/memory_cross_attn.py:1310-1366, 1387-1603, 1639-1652).

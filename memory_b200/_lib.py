@@ -14,6 +14,7 @@ import torch
 from .build import LIB_PATH
 
 MOC_F32, MOC_BF16 = 0, 1
+ATTN_BWD_STATIC_MAX_FLOATS = 1 << 20   # MOC_ATTN_BWD_STATIC_MAX_FLOATS in include/moc_b200.h
 NORM_NONE, NORM_RMS, NORM_LAYERNORM = 0, 1, 2
 NORM_CODES = {None: NORM_NONE, "none": NORM_NONE, "rms": NORM_RMS, "layernorm": NORM_LAYERNORM}
 DEV_STATUS_TEXT = {1: "a bounded device wait timed out", 2: "a chapter index was out of range"}
@@ -62,6 +63,7 @@ _PROTOTYPES = {
     "moc_attn_fwd": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P]),
     "moc_attn_bwd": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P, P, P, P, P]),
     "moc_attn_bwd_parts": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P, P, P, C.c_int32, P, P]),
+    "moc_attn_bwd_static": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P, P, P, P]),
     "moc_sparse_attn_fwd": (C.c_int, [C.POINTER(SparseAttnShape), P, P, P, P, P, P, P, P]),
     "moc_sparse_attn_bwd": (C.c_int, [C.POINTER(SparseAttnShape), P, P, P, P, P, P, P, P, P, P, P, P]),
     "moc_cast_f32_to_bf16": (C.c_int, [P, P, C.c_int64, P]),

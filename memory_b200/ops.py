@@ -298,6 +298,23 @@ def attn_bwd(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tens
     return d_q, d_kv
 
 
+@_instrument("attn_bwd_static", _attn_bwd_launches)
+def attn_bwd_static(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tensor, d_o: torch.Tensor,
+                    num_heads: int, num_kv_heads: int, scale: float, out=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """dQ and dKV through the entry point that allocates nothing: its scratch is a fixed array inside
+    the library (2*B*H*L must not exceed ``_lib.ATTN_BWD_STATIC_MAX_FLOATS``).  Pass ``out`` =
+    (d_q, d_kv) to keep this wrapper from allocating the outputs either.  Calls that may overlap on
+    the GPU must be serialised by the caller, because they share that array."""
+    q, kv, o, d_o = _contig(q), _contig(kv), _contig(o), _contig(d_o)
+    s = _attn_shape(q, kv, num_heads, num_kv_heads, scale)
+    d_q, d_kv = out if out is not None else (torch.empty_like(q), torch.empty_like(kv))
+    rc = L.lib().moc_attn_bwd_static(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse), L.ptr(d_o),
+                                     L.ptr(d_q), L.ptr(d_kv), L.ptr(L.status_word(q.device)),
+                                     L.stream_ptr(q.device))
+    L.check(rc, "moc_attn_bwd_static")
+    return d_q, d_kv
+
+
 @_instrument("sparse_attn_fwd", 1)
 def sparse_attn_fwd(q, k, v, block_indices, block_size: int, scale: float):
     L.require_cuda(q, k, v, block_indices)
