@@ -241,7 +241,7 @@ class LayerRunner:
         if self.reducer is not None:
             P = self.params
             dense = [P[k].grad for k in ("router_w", "router_b", "wq", "wk", "wv", "wo")]
-            self.reducer.reduce(dense, self.sink)
+            self.reduced_bank = self.reducer.reduce(dense, self.sink)
         return loss
 
     def launches_per_step(self):
@@ -261,7 +261,7 @@ def time_op_breakdown(runner, hs, gs, steps):
     from memory_b200 import ops
     ops.TIMER = {}
     for i in range(steps):
-        runner.step(hs[i % len(hs)], gs[i % len(gs)], eager=True)
+        runner._fwd_bwd(hs[i % len(hs)], gs[i % len(gs)])      # rank-local: no gradient reduction here
     torch.cuda.synchronize()
     table = {k: sum(a.elapsed_time(b) for a, b in v) / steps for k, v in ops.TIMER.items()}
     ops.TIMER = None

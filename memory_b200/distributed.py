@@ -65,9 +65,10 @@ class GradReducer:
             g.copy_(flat[off:off + n].view_as(g))
             off += n
 
-    def reduce_bank(self, sink) -> None:
-        """``sink`` is a SparseBankGrad holding this rank's entries; on return it holds one entry: the
-        union chapter list and the mean gradient rows."""
+    def reduce_bank(self, sink):
+        """``sink`` is a SparseBankGrad holding this rank's entries (left untouched, so entries captured in
+        a CUDA graph stay valid).  Returns a new SparseBankGrad with one entry: the union chapter list
+        and the mean gradient rows."""
         counts = torch.zeros(self.c, dtype=torch.int32, device=self.device)
         merged_ids, merged_rows = self._merge_local(sink)
         if merged_ids.numel():
@@ -80,14 +81,17 @@ class GradReducer:
         if self.world > 1:
             dist.all_reduce(buf, group=self.group)
             buf.div_(self.world)
-        sink.clear()
-        sink.add(union.to(torch.int32), torch.tensor([union.numel()], dtype=torch.int32, device=self.device),
-                 buf.float(), self.t)
+        out = type(sink)()
+        out.add(union.to(torch.int32), torch.tensor([union.numel()], dtype=torch.int32, device=self.device),
+                buf.float(), self.t)
+        return out
 
-    def reduce(self, dense_grads: Sequence[Optional[torch.Tensor]], sink) -> None:
+    def reduce(self, dense_grads: Sequence[Optional[torch.Tensor]], sink):
+        """All-reduce the dense gradients in place and return the reduced bank gradient (or None)."""
         self.reduce_dense(dense_grads)
         if sink is not None and sink.entries:
-            self.reduce_bank(sink)
+            return self.reduce_bank(sink)
+        return None
 
     def _merge_local(self, sink):
         """Sum this rank's entries (several memory layers may share one bank) into one id list."""

@@ -28,6 +28,10 @@ class GraphedStep:
             s.requires_grad_(t.requires_grad)
             self.static_inputs.append(s)
         device = self.static_inputs[0].device
+        # warm-up runs on a side stream, capture on the capture stream: the AccumulateGrad nodes of the
+        # parameters are created under different streams by design
+        if hasattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch"):
+            torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)
         side = torch.cuda.Stream(device)
         side.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(side):

@@ -54,9 +54,10 @@ def _worker(rank, world, port, q):
         dense = [torch.randn(5, 3, generator=g), None, torch.randn(4, generator=g)]
         want_dense = [d.clone() if d is not None else None for d in dense]
         red = GradReducer(C_, T_, D_, "cpu")
-        red.reduce(dense, sink)
-        uniq, n, rows, t = sink.entries[0]
-        got = _dense_of(sink.entries)
+        reduced = red.reduce(dense, sink)
+        assert len(sink.entries) == 2, "the local entries must be left in place"
+        uniq, n, rows, t = reduced.entries[0]
+        got = _dense_of(reduced.entries)
         q.put((rank, got, [d for d in dense if d is not None], uniq[:int(n)].tolist(), red.last_union_size,
                [d for d in want_dense if d is not None]))
     finally:
