@@ -203,6 +203,7 @@ class LayerRunner:
         self.g_lb = torch.tensor(0.01, device=device)
         self.g_z = torch.tensor(0.001, device=device)
         self.reducer = None
+        self.pending = None
         if world > 1:
             from memory_b200.distributed import GradReducer
             self.reducer = GradReducer(cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["hidden_dim"], device,
@@ -239,10 +240,20 @@ class LayerRunner:
         else:
             loss = self._fwd_bwd(h, d_out)
         if self.reducer is not None:
+            # the reduction of step i runs on the communication stream under the compute of step i+1;
+            # at most one reduction is in flight
+            if self.pending is not None:
+                self.pending.wait()
             P = self.params
             dense = [P[k].grad for k in ("router_w", "router_b", "wq", "wk", "wv", "wo")]
-            self.reduced_bank = self.reducer.reduce(dense, self.sink)
+            self.pending = self.reducer.reduce_async(dense, self.sink)
         return loss
+
+    def finish(self):
+        """Wait (on the stream) for the reduction still in flight."""
+        if self.reducer is not None and self.pending is not None:
+            self.pending.wait()
+            self.pending = None
 
     def launches_per_step(self):
         """Kernels of this library one step launches (counted on an eager pass)."""
@@ -349,6 +360,7 @@ def run_cuda_arm(args):
     e0.record()
     for i in range(args.steps):
         runner.step(hs[i % N_INPUT_SETS], gs[i % N_INPUT_SETS])
+    runner.finish()
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
@@ -390,6 +402,7 @@ def run_cuda_arm(args):
             loss = runner.step(stage[i % 2], gs[i % N_INPUT_SETS])
             consumed[i % 2].record(cur)
             loss_host.copy_(loss.detach(), non_blocking=True)
+        runner.finish()
         torch.cuda.synchronize()
 
     e2e_loop(max(3, args.warmup))

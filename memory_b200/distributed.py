@@ -86,6 +86,34 @@ class GradReducer:
                 buf.float(), self.t)
         return out
 
+    def reduce_async(self, dense_grads: Sequence[Optional[torch.Tensor]], sink) -> "PendingReduction":
+        """Start the reduction without blocking later work on the calling stream.
+
+        Gradients are first copied into fresh staging buffers (on the calling stream), so the caller may
+        overwrite its gradient tensors -- e.g. by replaying a captured step -- while the all-reduces run on
+        the communication stream.  The one host synchronisation is the read of the union size.
+        """
+        live = [g for g in dense_grads if g is not None]
+        works = []
+        flat = torch.cat([g.reshape(-1).float() for g in live]) if live else None
+        if flat is not None and self.world > 1:
+            works.append(dist.all_reduce(flat, group=self.group, async_op=True))
+        bank = None
+        if sink is not None and sink.entries:
+            counts = torch.zeros(self.c, dtype=torch.int32, device=self.device)
+            ids, rows = self._merge_local(sink)
+            if ids.numel():
+                counts[ids.long()] = 1
+            if self.world > 1:
+                dist.all_reduce(counts, group=self.group)
+            union = union_of_touched(counts)
+            self.last_union_size = int(union.numel())
+            buf = compact_to_union(ids, rows, union, self.c, self.t).to(self.bank_dtype)
+            if self.world > 1:
+                works.append(dist.all_reduce(buf, group=self.group, async_op=True))
+            bank = (union, buf)
+        return PendingReduction(self, works, flat, [g.shape for g in live], bank, type(sink) if sink is not None else None)
+
     def reduce(self, dense_grads: Sequence[Optional[torch.Tensor]], sink):
         """All-reduce the dense gradients in place and return the reduced bank gradient (or None)."""
         self.reduce_dense(dense_grads)
@@ -113,3 +141,37 @@ class GradReducer:
             out.index_add_(0, pos[uniq[:n].long()], rows[: n * self.t].view(n, self.t, self.d))
         del acc
         return ids.to(torch.int32), out.view(-1, self.d)
+
+
+class PendingReduction:
+    """Handle of a reduction started by :meth:`GradReducer.reduce_async`."""
+
+    def __init__(self, reducer, works, flat, shapes, bank, sink_type):
+        self.reducer, self.works, self.flat, self.shapes, self.bank, self.sink_type = \
+            reducer, works, flat, shapes, bank, sink_type
+
+    def wait(self) -> None:
+        """Make the current stream wait for the collectives (no host block)."""
+        for w in self.works:
+            w.wait()
+        self.works = []
+
+    def result(self):
+        """(list of mean dense gradients in the order given, reduced SparseBankGrad or None)."""
+        self.wait()
+        r = self.reducer
+        dense = []
+        if self.flat is not None:
+            flat = self.flat / r.world
+            off = 0
+            for shp in self.shapes:
+                n = int(torch.tensor(shp).prod()) if len(shp) else 1
+                dense.append(flat[off:off + n].view(shp))
+                off += n
+        bank = None
+        if self.bank is not None:
+            union, buf = self.bank
+            bank = self.sink_type()
+            bank.add(union.to(torch.int32), torch.tensor([union.numel()], dtype=torch.int32, device=r.device),
+                     buf.float() / r.world, r.t)
+        return dense, bank

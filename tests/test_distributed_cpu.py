@@ -54,8 +54,13 @@ def _worker(rank, world, port, q):
         dense = [torch.randn(5, 3, generator=g), None, torch.randn(4, generator=g)]
         want_dense = [d.clone() if d is not None else None for d in dense]
         red = GradReducer(C_, T_, D_, "cpu")
+        pending = red.reduce_async([d.clone() if d is not None else None for d in dense], sink)
+        dense_async, bank_async = pending.result()
         reduced = red.reduce(dense, sink)
         assert len(sink.entries) == 2, "the local entries must be left in place"
+        for a, b in zip(dense_async, [d for d in dense if d is not None]):
+            torch.testing.assert_close(a, b)
+        torch.testing.assert_close(_dense_of(bank_async.entries), _dense_of(reduced.entries))
         uniq, n, rows, t = reduced.entries[0]
         got = _dense_of(reduced.entries)
         q.put((rank, got, [d for d in dense if d is not None], uniq[:int(n)].tolist(), red.last_union_size,
