@@ -133,7 +133,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       }
     }
   } else if (warp == 9) {
-    if (lane == 0) {
+    {   // warp-uniform: every lane runs the loop, one elected lane issues
       const uint32_t idesc_kk = umma_idesc_bf16(kQ, kKeys, 0, 0);   // S and dP: both operands K-major
       const uint32_t idesc_dq = umma_idesc_bf16(kQ, kD, 0, 1);      // dQ: B = K tile, MN-major
       // descriptors are built once; a stage or K step only adds a constant to the address field
@@ -143,35 +143,35 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       const uint64_t v_desc0 = umma_desc_sw128(smem_u32(kv_s) + kKvBytes, 16, 1024);       // V tile, K-major
       const uint64_t kmn_desc0 = umma_desc_sw128(smem_u32(kv_s), 8192, 1024);              // K tile, MN-major
       constexpr uint64_t kStageOff = (2 * kKvBytes) >> 4;
-      bool ok = mbar_wait(&q_bar, 0, &abort_flag, p.status);
+      bool ok = mbar_wait_w(&q_bar, 0, &abort_flag, p.status);
       for (int j = 0; j <= n_tiles && ok; ++j) {
         if (j < n_tiles) {
           const int s = j % kStages;
-          ok = mbar_wait(&kv_full[s], (j / kStages) & 1, &abort_flag, p.status);
-          if (ok && j > 0) ok = mbar_wait(&sdp_free, (j - 1) & 1, &abort_flag, p.status);
+          ok = mbar_wait_w(&kv_full[s], (j / kStages) & 1, &abort_flag, p.status);
+          if (ok && j > 0) ok = mbar_wait_w(&sdp_free, (j - 1) & 1, &abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
           const uint64_t kd = k_desc0 + s * kStageOff, vd = v_desc0 + s * kStageOff;
           // the two score products accumulate into different columns: interleave them
 #pragma unroll
           for (int kk = 0; kk < kD / 16; ++kk) {
-            umma_ss(tmem + kDqColS, q_desc + kk * 2, kd + kk * 2, idesc_kk, kk > 0 ? 1u : 0u);
-            umma_ss(tmem + kDqColDP, do_desc + kk * 2, vd + kk * 2, idesc_kk, kk > 0 ? 1u : 0u);
+            umma_ss_w(tmem + kDqColS, q_desc + kk * 2, kd + kk * 2, idesc_kk, kk > 0 ? 1u : 0u);
+            umma_ss_w(tmem + kDqColDP, do_desc + kk * 2, vd + kk * 2, idesc_kk, kk > 0 ? 1u : 0u);
           }
-          tc_commit(&sdp_full);
+          tc_commit_w(&sdp_full);
         }
         if (j > 0) {
           const int jp = j - 1, s = jp % kStages;
-          ok = mbar_wait(&ds_full, jp & 1, &abort_flag, p.status);
+          ok = mbar_wait_w(&ds_full, jp & 1, &abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
           const uint64_t kd = kmn_desc0 + s * kStageOff;
-          umma_ts(tmem + kDqColDQ, tmem + kDqColDS, kd, idesc_dq, jp > 0 ? 1u : 0u);
+          umma_ts_w(tmem + kDqColDQ, tmem + kDqColDS, kd, idesc_dq, jp > 0 ? 1u : 0u);
 #pragma unroll
           for (int kk = 1; kk < kKeys / 16; ++kk)
-            umma_ts(tmem + kDqColDQ, tmem + kDqColDS + kk * 8, kd + kk * 128, idesc_dq, 1u);
-          tc_commit(&kv_empty[s]);
-          tc_commit(&dq_bar);
+            umma_ts_w(tmem + kDqColDQ, tmem + kDqColDS + kk * 8, kd + kk * 128, idesc_dq, 1u);
+          tc_commit_w(&kv_empty[s]);
+          tc_commit_w(&dq_bar);
         }
       }
     }
@@ -335,7 +335,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       }
     }
   } else if (warp == 9) {
-    if (lane == 0) {
+    {   // warp-uniform: every lane runs the loop, one elected lane issues
       const uint32_t idesc_s = umma_idesc_bf16(kKeysB, kQB, 0, 0);   // S^T, dP^T
       const uint32_t idesc_g = umma_idesc_bf16(kKeysB, kD, 0, 1);    // dV, dK: B = dO / Q tile, MN-major
       // descriptors are built once; a stage or K step only adds a constant to the address field
@@ -346,34 +346,34 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const uint64_t qmn_desc0 = umma_desc_sw128(smem_u32(ring), 8192, 1024);                  // Q tile, MN-major
       const uint64_t domn_desc0 = umma_desc_sw128(smem_u32(ring) + kQTileBytes, 8192, 1024);   // dO tile, MN-major
       constexpr uint64_t kStageOff = kStageB >> 4;
-      bool ok = mbar_wait(&k_bar, 0, &abort_flag, p.status);
+      bool ok = mbar_wait_w(&k_bar, 0, &abort_flag, p.status);
       for (int it = 0; it < n_iter && ok; ++it) {
         const int s = it % kStages;
-        ok = mbar_wait(&q_full[s], (it / kStages) & 1, &abort_flag, p.status);
+        ok = mbar_wait_w(&q_full[s], (it / kStages) & 1, &abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
         // independent accumulators are interleaved so consecutive MMAs never wait on each other
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk) {
-          umma_ss(tmem + kColST, k_desc + kk * 2, q_desc0 + s * kStageOff + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
-          umma_ss(tmem + kColDPT, v_desc + kk * 2, do_desc0 + s * kStageOff + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
+          umma_ss_w(tmem + kColST, k_desc + kk * 2, q_desc0 + s * kStageOff + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
+          umma_ss_w(tmem + kColDPT, v_desc + kk * 2, do_desc0 + s * kStageOff + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
         }
-        tc_commit(&sdp_full);
-        ok = mbar_wait(&pt_full, it & 1, &abort_flag, p.status);
+        tc_commit_w(&sdp_full);
+        ok = mbar_wait_w(&pt_full, it & 1, &abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
         // P^T / dS^T for queries [32g, 32g+32) sit in the first 16 columns of column half g
 #pragma unroll
         for (int kk = 0; kk < kQB / 16; ++kk) {
           const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
-          umma_ts(tmem + kColDV, tmem + kColST + a_col, domn_desc0 + s * kStageOff + kk * 128, idesc_g,
+          umma_ts_w(tmem + kColDV, tmem + kColST + a_col, domn_desc0 + s * kStageOff + kk * 128, idesc_g,
                   (it > 0 || kk > 0) ? 1u : 0u);
-          umma_ts(tmem + kColDK, tmem + kColDPT + a_col, qmn_desc0 + s * kStageOff + kk * 128, idesc_g,
+          umma_ts_w(tmem + kColDK, tmem + kColDPT + a_col, qmn_desc0 + s * kStageOff + kk * 128, idesc_g,
                   (it > 0 || kk > 0) ? 1u : 0u);
         }
-        tc_commit(&q_empty[s]);
+        tc_commit_w(&q_empty[s]);
       }
-      tc_commit(&acc_bar);
+      tc_commit_w(&acc_bar);
     }
   } else {
     const int half = warp >> 2;

@@ -100,7 +100,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
   } else if (warp == 5) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    {   // warp-uniform: every lane runs the loop, one elected lane issues
       const uint32_t idesc_s = umma_idesc_bf16(kQ, kKeys, 0, 0);
       const uint32_t idesc_o = umma_idesc_bf16(kQ, kD, 0, 1);
       // descriptors are built once; a stage or K step only adds a constant to the address field
@@ -108,34 +108,34 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const uint64_t k_desc0 = umma_desc_sw128(smem_u32(kv_s), 16, 1024);
       const uint64_t v_desc0 = umma_desc_sw128(smem_u32(kv_s) + kTileBytes, 8192, 1024);
       constexpr uint64_t kStageOff = (2 * kTileBytes) >> 4;
-      bool ok = mbar_wait(&q_bar, 0, &abort_flag, p.status);
+      bool ok = mbar_wait_w(&q_bar, 0, &abort_flag, p.status);
       // order: S_0, then per tile PV_j followed by S_{j+1}.  S_{j+1} overwrites the columns P_j lives
       // in; tcgen05.mma instructions of one thread execute in issue order, so PV_j has read them.
       for (int j = 0; j <= n_tiles && ok; ++j) {
         if (j > 0) {
           const int jp = j - 1, s = jp % kStages;
-          ok = mbar_wait(&p_full, jp & 1, &abort_flag, p.status);
+          ok = mbar_wait_w(&p_full, jp & 1, &abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
           const uint64_t vd = v_desc0 + s * kStageOff;
-          umma_ts(tmem + kColO, tmem + kColP, vd, idesc_o, jp > 0 ? 1u : 0u);
+          umma_ts_w(tmem + kColO, tmem + kColP, vd, idesc_o, jp > 0 ? 1u : 0u);
 #pragma unroll
           for (int kk = 1; kk < kKeys / 16; ++kk)
-            umma_ts(tmem + kColO, tmem + kColP + kk * 8, vd + kk * (2048 >> 4), idesc_o, 1u);
-          tc_commit(&kv_empty[s]);
-          tc_commit(&pv_bar);
+            umma_ts_w(tmem + kColO, tmem + kColP + kk * 8, vd + kk * (2048 >> 4), idesc_o, 1u);
+          tc_commit_w(&kv_empty[s]);
+          tc_commit_w(&pv_bar);
         }
         if (j < n_tiles) {
           const int s = j % kStages;
-          ok = mbar_wait(&kv_full[s], (j / kStages) & 1, &abort_flag, p.status);
+          ok = mbar_wait_w(&kv_full[s], (j / kStages) & 1, &abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
           const uint64_t kd = k_desc0 + s * kStageOff;
-          umma_ss(tmem + kColS, q_desc, kd, idesc_s, 0u);
+          umma_ss_w(tmem + kColS, q_desc, kd, idesc_s, 0u);
 #pragma unroll
           for (int kk = 1; kk < kD / 16; ++kk)
-            umma_ss(tmem + kColS, q_desc + kk * (32 >> 4), kd + kk * (32 >> 4), idesc_s, 1u);
-          tc_commit(&s_full);
+            umma_ss_w(tmem + kColS, q_desc + kk * (32 >> 4), kd + kk * (32 >> 4), idesc_s, 1u);
+          tc_commit_w(&s_full);
         }
       }
     }

@@ -151,7 +151,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {   // warp-uniform: every lane runs the loop, one elected lane issues
       const uint32_t idesc = umma_idesc_bf16(BM, BN, p.a_kmajor ? 0 : 1, p.b_kmajor ? 0 : 1);
       // Descriptors are built once: a stage or K step only adds a constant to the 16-byte-unit address
       // field, so issuing an MMA costs two 64-bit adds instead of rebuilding both descriptors.
@@ -169,25 +169,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         int kt_count = p.k_tiles_total - kt_begin;
         if (kt_count > p.k_tiles_per_split) kt_count = p.k_tiles_per_split;
         const uint32_t buf = t & 1;
-        ok = mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, &abort_flag, p.status);
+        ok = mbar_wait_w(&acc_empty[buf], ((t >> 1) & 1) ^ 1, &abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + buf * 256;
         for (int kt = 0; kt < kt_count; ++kt, ++it) {
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
-          ok = mbar_wait(&full_bar[s], ph, &abort_flag, p.status);
+          ok = mbar_wait_w(&full_bar[s], ph, &abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
           const uint64_t stage_off = static_cast<uint64_t>(s) * (C::kStageBytes >> 4);
           const uint64_t ad = a_base + stage_off, bd = b_base + stage_off;
-          umma_ss(tmem_acc, ad, bd, idesc, kt > 0 ? 1u : 0u);
+          umma_ss_w(tmem_acc, ad, bd, idesc, kt > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 1; kk < BK / 16; ++kk) umma_ss(tmem_acc, ad + kk * a_step, bd + kk * b_step, idesc, 1u);
-          tc_commit(&empty_bar[s]);
+          for (int kk = 1; kk < BK / 16; ++kk) umma_ss_w(tmem_acc, ad + kk * a_step, bd + kk * b_step, idesc, 1u);
+          tc_commit_w(&empty_bar[s]);
         }
         if (!ok) break;
-        tc_commit(&acc_full[buf]);
+        tc_commit_w(&acc_full[buf]);
       }
     }
   } else {
