@@ -67,6 +67,68 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
   }
 }
 
+
+// ---- MMA groups issued as one instruction block by one elected lane --------------------------------------
+// The MMA warp shares its scheduler partition with busy row-owning warps, so the number of instructions per
+// MMA, not the tensor pipe, sets the issue rate.  These blocks spend ~3 instructions per MMA (two address adds
+// and the MMA) and interleave two independent accumulators: back-to-back MMAs into the same columns cannot
+// start closer than ~94 cycles apart.
+// Two K-major SS products over 4 K steps:  [d0] = A0 * B0^T,  [d1] = A1 * B1^T  (accumulators overwritten).
+__device__ __forceinline__ void issue_ss_pair(uint32_t d0, uint32_t d1, uint64_t a0, uint64_t b0, uint64_t a1,
+                                              uint64_t b1, uint32_t idesc) {
+#define MOC_SS_STEP(KK, PACC)                                                                  \
+  "add.s64 ta, %2, " #KK "*2;\n\t add.s64 tb, %3, " #KK "*2;\n\t"                               \
+  "@q tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %6, " PACC ";\n\t"                      \
+  "add.s64 ta, %4, " #KK "*2;\n\t add.s64 tb, %5, " #KK "*2;\n\t"                               \
+  "@q tcgen05.mma.cta_group::1.kind::f16 [%1], ta, tb, %6, " PACC ";\n\t"
+  asm volatile(
+      "{\n\t.reg .pred q, pt, pf;\n\t.reg .b64 ta, tb;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "setp.ne.b32 pf, 0, 0;\n\t"
+      MOC_SS_STEP(0, "pf") MOC_SS_STEP(1, "pt") MOC_SS_STEP(2, "pt") MOC_SS_STEP(3, "pt")
+      "}"
+      ::"r"(d0), "r"(d1), "l"(a0), "l"(b0), "l"(a1), "l"(b1), "r"(idesc)
+      : "memory");
+#undef MOC_SS_STEP
+}
+// Two TS products over 4 K steps with MN-major B:  [d0] += A0 * B0,  [d1] += A1 * B1, where A is packed bf16 in
+// tensor memory and K step kk of A starts at column a + (kk >> 1) * a_hi + (kk & 1) * 8.
+__device__ __forceinline__ void issue_ts_pair(uint32_t d0, uint32_t d1, uint32_t a0, uint32_t a1, uint32_t a_hi,
+                                              uint64_t b0, uint64_t b1, uint32_t idesc, uint32_t acc) {
+#define MOC_TS_STEP(KK, HI, LO, PACC)                                                          \
+  "mad.lo.u32 ca, %4, " #HI ", %2;\n\t add.u32 ca, ca, " #LO ";\n\t add.s64 tb, %5, " #KK "*128;\n\t" \
+  "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [ca], tb, %7, " PACC ";\n\t"                     \
+  "mad.lo.u32 ca, %4, " #HI ", %3;\n\t add.u32 ca, ca, " #LO ";\n\t add.s64 tb, %6, " #KK "*128;\n\t" \
+  "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [ca], tb, %7, " PACC ";\n\t"
+  asm volatile(
+      "{\n\t.reg .pred q, pa, pt;\n\t.reg .b64 tb;\n\t.reg .b32 ca;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.ne.b32 pa, %8, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      MOC_TS_STEP(0, 0, 0, "pa") MOC_TS_STEP(1, 0, 8, "pt") MOC_TS_STEP(2, 1, 0, "pt") MOC_TS_STEP(3, 1, 8, "pt")
+      "}"
+      ::"r"(d0), "r"(d1), "r"(a0), "r"(a1), "r"(a_hi), "l"(b0), "l"(b1), "r"(idesc), "r"(acc)
+      : "memory");
+#undef MOC_TS_STEP
+}
+// One TS product over 4 K steps with MN-major B: [d] += A * B, A K step kk at column a + 8 kk.
+__device__ __forceinline__ void issue_ts_single(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+#define MOC_TS1_STEP(KK, PACC)                                                                 \
+  "add.u32 ca, %1, " #KK "*8;\n\t add.s64 tb, %2, " #KK "*128;\n\t"                              \
+  "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [ca], tb, %3, " PACC ";\n\t"
+  asm volatile(
+      "{\n\t.reg .pred q, pa, pt;\n\t.reg .b64 tb;\n\t.reg .b32 ca;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.ne.b32 pa, %4, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      MOC_TS1_STEP(0, "pa") MOC_TS1_STEP(1, "pt") MOC_TS1_STEP(2, "pt") MOC_TS1_STEP(3, "pt")
+      "}"
+      ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+#undef MOC_TS1_STEP
+}
+
 // ------------------------------------------------------------------------------------------------
 // dQ
 // ------------------------------------------------------------------------------------------------
@@ -152,12 +214,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           if (!ok) break;
           tc_fence_after();
           const uint64_t kd = k_desc0 + s * kStageOff, vd = v_desc0 + s * kStageOff;
-          // the two score products accumulate into different columns: interleave them
-#pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk) {
-            umma_ss_w(tmem + kDqColS, q_desc + kk * 2, kd + kk * 2, idesc_kk, kk > 0 ? 1u : 0u);
-            umma_ss_w(tmem + kDqColDP, do_desc + kk * 2, vd + kk * 2, idesc_kk, kk > 0 ? 1u : 0u);
-          }
+          issue_ss_pair(tmem + kDqColS, tmem + kDqColDP, q_desc, kd, do_desc, vd, idesc_kk);
           tc_commit_w(&sdp_full);
         }
         if (j > 0) {
@@ -166,10 +223,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           if (!ok) break;
           tc_fence_after();
           const uint64_t kd = kmn_desc0 + s * kStageOff;
-          umma_ts_w(tmem + kDqColDQ, tmem + kDqColDS, kd, idesc_dq, jp > 0 ? 1u : 0u);
-#pragma unroll
-          for (int kk = 1; kk < kKeys / 16; ++kk)
-            umma_ts_w(tmem + kDqColDQ, tmem + kDqColDS + kk * 8, kd + kk * 128, idesc_dq, 1u);
+          issue_ts_single(tmem + kDqColDQ, tmem + kDqColDS, kd, idesc_dq, jp > 0 ? 1u : 0u);
           tc_commit_w(&kv_empty[s]);
           tc_commit_w(&dq_bar);
         }
@@ -352,25 +406,15 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         ok = mbar_wait_w(&q_full[s], (it / kStages) & 1, &abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
-        // independent accumulators are interleaved so consecutive MMAs never wait on each other
-#pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          umma_ss_w(tmem + kColST, k_desc + kk * 2, q_desc0 + s * kStageOff + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
-          umma_ss_w(tmem + kColDPT, v_desc + kk * 2, do_desc0 + s * kStageOff + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
-        }
+        issue_ss_pair(tmem + kColST, tmem + kColDPT, k_desc, q_desc0 + s * kStageOff, v_desc, do_desc0 + s * kStageOff,
+                      idesc_s);
         tc_commit_w(&sdp_full);
         ok = mbar_wait_w(&pt_full, it & 1, &abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
         // P^T / dS^T for queries [32g, 32g+32) sit in the first 16 columns of column half g
-#pragma unroll
-        for (int kk = 0; kk < kQB / 16; ++kk) {
-          const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
-          umma_ts_w(tmem + kColDV, tmem + kColST + a_col, domn_desc0 + s * kStageOff + kk * 128, idesc_g,
-                  (it > 0 || kk > 0) ? 1u : 0u);
-          umma_ts_w(tmem + kColDK, tmem + kColDPT + a_col, qmn_desc0 + s * kStageOff + kk * 128, idesc_g,
-                  (it > 0 || kk > 0) ? 1u : 0u);
-        }
+        issue_ts_pair(tmem + kColDV, tmem + kColDK, tmem + kColST, tmem + kColDPT, 32, domn_desc0 + s * kStageOff,
+                      qmn_desc0 + s * kStageOff, idesc_g, it > 0 ? 1u : 0u);
         tc_commit_w(&q_empty[s]);
       }
       tc_commit_w(&acc_bar);

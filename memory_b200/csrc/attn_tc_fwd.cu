@@ -44,6 +44,42 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+
+// MMA groups issued as one instruction block by one elected lane (~3 instructions per MMA): the MMA warp
+// shares its scheduler partition with busy row-owning warps, so instructions per MMA set the issue rate.
+// [d] = A * B^T over 4 K steps, both operands K-major in shared memory.
+__device__ __forceinline__ void issue_ss_single(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc) {
+#define MOC_SS1_STEP(KK, PACC)                                                  \
+  "add.s64 ta, %1, " #KK "*2;\n\t add.s64 tb, %2, " #KK "*2;\n\t"                \
+  "@q tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, " PACC ";\n\t"
+  asm volatile(
+      "{\n\t.reg .pred q, pt, pf;\n\t.reg .b64 ta, tb;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "setp.ne.b32 pf, 0, 0;\n\t"
+      MOC_SS1_STEP(0, "pf") MOC_SS1_STEP(1, "pt") MOC_SS1_STEP(2, "pt") MOC_SS1_STEP(3, "pt")
+      "}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc)
+      : "memory");
+#undef MOC_SS1_STEP
+}
+// [d] += A * B over 4 K steps: A packed bf16 in tensor memory (K step kk at column a + 8 kk), B MN-major.
+__device__ __forceinline__ void issue_ts_single(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+#define MOC_TS1_STEP(KK, PACC)                                                  \
+  "add.u32 ca, %1, " #KK "*8;\n\t add.s64 tb, %2, " #KK "*128;\n\t"               \
+  "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [ca], tb, %3, " PACC ";\n\t"
+  asm volatile(
+      "{\n\t.reg .pred q, pa, pt;\n\t.reg .b64 tb;\n\t.reg .b32 ca;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.ne.b32 pa, %4, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      MOC_TS1_STEP(0, "pa") MOC_TS1_STEP(1, "pt") MOC_TS1_STEP(2, "pt") MOC_TS1_STEP(3, "pt")
+      "}"
+      ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+#undef MOC_TS1_STEP
+}
+
 __global__ void __launch_bounds__(kThreads, 4)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
                    FwdParams p) {
@@ -118,10 +154,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           if (!ok) break;
           tc_fence_after();
           const uint64_t vd = v_desc0 + s * kStageOff;
-          umma_ts_w(tmem + kColO, tmem + kColP, vd, idesc_o, jp > 0 ? 1u : 0u);
-#pragma unroll
-          for (int kk = 1; kk < kKeys / 16; ++kk)
-            umma_ts_w(tmem + kColO, tmem + kColP + kk * 8, vd + kk * (2048 >> 4), idesc_o, 1u);
+          issue_ts_single(tmem + kColO, tmem + kColP, vd, idesc_o, jp > 0 ? 1u : 0u);
           tc_commit_w(&kv_empty[s]);
           tc_commit_w(&pv_bar);
         }
@@ -131,10 +164,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           if (!ok) break;
           tc_fence_after();
           const uint64_t kd = k_desc0 + s * kStageOff;
-          umma_ss_w(tmem + kColS, q_desc, kd, idesc_s, 0u);
-#pragma unroll
-          for (int kk = 1; kk < kD / 16; ++kk)
-            umma_ss_w(tmem + kColS, q_desc + kk * (32 >> 4), kd + kk * (32 >> 4), idesc_s, 1u);
+          issue_ss_single(tmem + kColS, q_desc, kd, idesc_s);
           tc_commit_w(&s_full);
         }
       }
