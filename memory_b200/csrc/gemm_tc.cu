@@ -245,8 +245,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         } else {
           float* dst = reinterpret_cast<float*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
           if (p.atomic) {
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.n) atomicAdd(dst + j, __uint_as_float(r[j]) * rs);
+            const bool vec4 = ((p.ldc & 3) == 0) && (col0 + 32 <= p.n) &&
+                              ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
+            if (vec4) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                atomicAdd(reinterpret_cast<float4*>(dst + 4 * j),
+                          make_float4(__uint_as_float(r[4 * j + 0]) * rs, __uint_as_float(r[4 * j + 1]) * rs,
+                                      __uint_as_float(r[4 * j + 2]) * rs, __uint_as_float(r[4 * j + 3]) * rs));
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.n) atomicAdd(dst + j, __uint_as_float(r[j]) * rs);
+            }
           } else {
             const bool vec = ((p.ldc & 3) == 0) && (col0 + 32 <= p.n) &&
                              ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
@@ -323,13 +333,14 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
     MOC_REQUIRE(a_stored_rows > 0, "a_stored_rows missing");
   }
 
-  // tile width: 256 columns when that does not leave SMs idle in the last wave, else 128
+  // Tile width.  The kernel is fed from L2 (~8.4 TB/s measured over all SMs), so a tile's time goes with the
+  // bytes it loads per K step, (BM + BN) * 128: the cost of a width is rounds-of-items times that.
   const int sms = sm_count();
   const int m_tiles = ceil_div(g->m, BM);
   auto waves_cost = [&](int bn) {
     const long long items = static_cast<long long>(m_tiles) * ceil_div(g->n, bn) * split;
     const long long rounds = (items + sms - 1) / sms;
-    return static_cast<double>(rounds) * bn;
+    return static_cast<double>(rounds) * (BM + bn);
   };
   const int bn = (g->n > 128 && waves_cost(256) <= waves_cost(128)) ? 256 : 128;
 
