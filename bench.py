@@ -200,8 +200,7 @@ class LayerRunner:
         self.params = {k: v.requires_grad_(True) for k, v in p.items()}
         self.sink = M.SparseBankGrad()
         self.params["bank"].moc_sparse_grad = self.sink
-        self.g_lb = torch.tensor(0.01, device=device)
-        self.g_z = torch.tensor(0.001, device=device)
+        self.g_losses = torch.tensor([0.01, 0.0, 0.001, 0.0], device=device)   # load_balance, auxiliary, z, entropy
         self.reducer = None
         self.pending = None
         if world > 1:
@@ -230,9 +229,8 @@ class LayerRunner:
             compute_dtype=torch.bfloat16)
         # d(loss)/d(out) = d_out, loss = <out, d_out> + 0.01 load_balance + 0.001 z_loss: seed the backward
         # directly instead of materialising the inner product on the device
-        torch.autograd.backward([out, losses["load_balance"], losses["z_loss"]],
-                                [d_out, self.g_lb, self.g_z])
-        return losses["load_balance"]
+        torch.autograd.backward([out, losses.vector], [d_out, self.g_losses])
+        return losses.vector
 
     def step(self, h, d_out, eager=False):
         if self.graphed is not None and not eager:
@@ -380,7 +378,7 @@ def run_cuda_arm(args):
     stage = [torch.empty_like(hs[0]).requires_grad_(True) for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
-    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+    loss_host = torch.empty(4, dtype=torch.float32).pin_memory()
 
     def prefetch(i):
         slot = i % 2
@@ -462,7 +460,7 @@ def run_cuda_arm(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(cfg, world),
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d * world,
-                "d2h_bytes_per_step": 4 * world, "ms_per_step": e2e_ms / args.steps},
+                "d2h_bytes_per_step": 16 * world, "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu_baseline,
         "pct_of_bf16_tc_roofline": 100.0 * roofline["layer"]["frac"],
     }

@@ -14,6 +14,7 @@ namespace {
 constexpr int kPoolSplits = 32;       // sequence splits of the mean-pool
 constexpr int kSelectThreads = 1024;  // one CTA per batch row in the select / dlogits kernels
 constexpr int kLossChunk = 256;       // chapters per CTA in the loss kernels
+constexpr int kLogitsPerWarp = 4;    // chapters per warp in the logits / d_w kernels
 constexpr int kDpChunk = 16;          // chapters per CTA in the d_pooled kernel
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
@@ -81,14 +82,15 @@ __global__ void logits_kernel(const float* __restrict__ pooled, const float* __r
                               const float* __restrict__ bias, float* __restrict__ logits, int B, int d, int C) {
   extern __shared__ float sp[];   // [8][d]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int c = blockIdx.x * (blockDim.x >> 5) + warp;
   const bool vec = (d & 3) == 0;
   for (int b0 = 0; b0 < B; b0 += 8) {
     const int nb = min(8, B - b0);
     __syncthreads();
     for (int i = threadIdx.x; i < nb * d; i += blockDim.x) sp[i] = pooled[static_cast<long long>(b0) * d + i];
     __syncthreads();
-    if (c < C) {
+    for (int cc = 0; cc < kLogitsPerWarp; ++cc) {
+      const int c = (blockIdx.x * (blockDim.x >> 5) + warp) * kLogitsPerWarp + cc;
+      if (c >= C) break;
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -180,15 +182,34 @@ select_kernel(const float* __restrict__ logits, float* __restrict__ probs, long 
         if ((key & mask) == prefix) atomicAdd(&hist[(key >> (8 * pass)) & 255u], 1);
       }
       __syncthreads();
-      if (threadIdx.x == 0) {
-        int rem = s_krem, bin = 255;
-        for (; bin > 0; --bin) {
-          if (hist[bin] >= rem) break;
-          rem -= hist[bin];
+      if (threadIdx.x < 32) {
+        // warp 0 finds, from the top bin down, the bin in which the running count reaches s_krem
+        const int lane = threadIdx.x;
+        int h8[8], sl = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { h8[i] = hist[lane * 8 + i]; sl += h8[i]; }
+        int incl = sl;                       // inclusive suffix sum over lanes lane..31
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int t = __shfl_down_sync(0xffffffffu, incl, o);
+          if (lane + o < 32) incl += t;
         }
-        s_krem = rem;
-        s_prefix = prefix | (static_cast<uint32_t>(bin) << (8 * pass));
-        s_ties = hist[bin];
+        const int above = incl - sl;         // elements in bins owned by higher lanes
+        const int rem0 = s_krem;
+        const bool mine = (above < rem0) && (rem0 <= incl);
+        const unsigned who = __ballot_sync(0xffffffffu, mine);
+        // all remaining elements sit in bin 0 of lane 0 when no lane qualifies (cannot happen while rem0 <= count)
+        const int owner = who ? (31 - __clz(who)) : 0;
+        if (lane == owner) {
+          int rem = rem0 - above, i = 7;
+          for (; i > 0; --i) {
+            if (h8[i] >= rem) break;
+            rem -= h8[i];
+          }
+          s_krem = rem;
+          s_prefix = prefix | (static_cast<uint32_t>(lane * 8 + i) << (8 * pass));
+          s_ties = h8[i];
+        }
       }
       mask |= 0xFFu << (8 * pass);
       __syncthreads();
@@ -411,29 +432,37 @@ __global__ void dweight_kernel(const float* __restrict__ d_logits, const float* 
                                float* __restrict__ d_w, float* __restrict__ d_bias, int B, int d, int C) {
   extern __shared__ float sp[];   // [8][d]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int c = blockIdx.x * (blockDim.x >> 5) + warp;
-  float bsum = 0.f;
+  const int c_first = (blockIdx.x * (blockDim.x >> 5) + warp) * kLogitsPerWarp;
+  float bsum[kLogitsPerWarp];
+#pragma unroll
+  for (int cc = 0; cc < kLogitsPerWarp; ++cc) bsum[cc] = 0.f;
   for (int b0 = 0; b0 < B; b0 += 8) {
     const int nb = min(8, B - b0);
     __syncthreads();
     for (int i = threadIdx.x; i < nb * d; i += blockDim.x) sp[i] = pooled[static_cast<long long>(b0) * d + i];
     __syncthreads();
-    if (c >= C) continue;
-    float dz[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      dz[j] = j < nb ? d_logits[static_cast<long long>(b0 + j) * C + c] : 0.f;
-      bsum += dz[j];
-    }
-    float* dst = d_w + static_cast<long long>(c) * d;
-    for (int k = lane; k < d; k += 32) {
-      float acc = (b0 == 0) ? 0.f : dst[k];
+    for (int cc = 0; cc < kLogitsPerWarp; ++cc) {
+      const int c = c_first + cc;
+      if (c >= C) break;
+      float dz[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc = fmaf(dz[j], sp[j * d + k], acc);
-      dst[k] = acc;
+      for (int j = 0; j < 8; ++j) {
+        dz[j] = j < nb ? d_logits[static_cast<long long>(b0 + j) * C + c] : 0.f;
+        bsum[cc] += dz[j];
+      }
+      float* dst = d_w + static_cast<long long>(c) * d;
+      for (int k = lane; k < d; k += 32) {
+        float acc = (b0 == 0) ? 0.f : dst[k];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = fmaf(dz[j], sp[j * d + k], acc);
+        dst[k] = acc;
+      }
     }
   }
-  if (c < C && lane == 0 && d_bias) d_bias[c] = bsum;
+#pragma unroll
+  for (int cc = 0; cc < kLogitsPerWarp; ++cc)
+    if (c_first + cc < C && lane == 0 && d_bias) d_bias[c_first + cc] = bsum[cc];
 }
 
 // partial[chunk][b][k] = sum over the chunk's chapters of d_logits[b,c] * w[c,k]
@@ -454,10 +483,14 @@ __global__ void dpooled_partial_kernel(const float* __restrict__ d_logits, const
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int cc = 0; cc < nc; ++cc) {
-        const float wv = w[static_cast<long long>(c0 + cc) * d + k];
+      float wv[kDpChunk];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = fmaf(dz[j][cc], wv, acc[j]);
+      for (int cc = 0; cc < kDpChunk; ++cc)            // all loads first: they are independent
+        wv[cc] = cc < nc ? w[static_cast<long long>(c0 + cc) * d + k] : 0.f;
+#pragma unroll
+      for (int cc = 0; cc < kDpChunk; ++cc) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = fmaf(dz[j][cc], wv[cc], acc[j]);
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j)
@@ -467,11 +500,16 @@ __global__ void dpooled_partial_kernel(const float* __restrict__ d_logits, const
 }
 __global__ void dpooled_finish_kernel(const float* __restrict__ partial, float* __restrict__ d_pooled,
                                       int nchunks, int total) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
+  // eight adjacent lanes share one output: each sums every eighth partial, then a fixed-order shuffle reduce
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int i = t >> 3, sub = t & 7;
   float acc = 0.f;
-  for (int ch = 0; ch < nchunks; ++ch) acc += partial[static_cast<long long>(ch) * total + i];
-  d_pooled[i] = acc;
+  if (i < total)
+    for (int ch = sub; ch < nchunks; ch += 8) acc += partial[static_cast<long long>(ch) * total + i];
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  if (i < total && sub == 0) d_pooled[i] = acc;
 }
 // d_h[b, t, :] (+)= d_pooled[b, :] / L; one thread per 8 consecutive columns of one row (d % 8 == 0),
 // falling back to one element per thread otherwise
@@ -579,7 +617,7 @@ extern "C" int moc_router_fwd(const moc_router_shape* s, const void* h, const fl
     const int warps = 8;
     const size_t sm = static_cast<size_t>(8) * d * sizeof(float);
     MOC_CUDA_OK(cudaFuncSetAttribute(logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
-    logits_kernel<<<ceil_div(C, warps), warps * 32, sm, stream>>>(pooled, w, bias, logits, B, d, C);
+    logits_kernel<<<ceil_div(C, warps * kLogitsPerWarp), warps * 32, sm, stream>>>(pooled, w, bias, logits, B, d, C);
   }
   {
     const size_t sm = (static_cast<size_t>(C) + 2 * static_cast<size_t>(k_sel > 0 ? k_sel : 1)) * 4;
@@ -625,11 +663,11 @@ extern "C" int moc_router_bwd(const moc_router_shape* s, const float* w, const f
   {
     const size_t sm = static_cast<size_t>(8) * d * sizeof(float);
     MOC_CUDA_OK(cudaFuncSetAttribute(dweight_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
-    dweight_kernel<<<ceil_div(C, 8), 256, sm, stream>>>(d_logits, pooled, d_w, d_bias, B, d, C);
+    dweight_kernel<<<ceil_div(C, 8 * kLogitsPerWarp), 256, sm, stream>>>(d_logits, pooled, d_w, d_bias, B, d, C);
   }
   const int nchunks = ceil_div(C, kDpChunk);
   dpooled_partial_kernel<<<nchunks, 256, 0, stream>>>(d_logits, w, ws, B, d, C);
-  dpooled_finish_kernel<<<ceil_div(B * d, 256), 256, 0, stream>>>(ws, d_pooled, nchunks, B * d);
+  dpooled_finish_kernel<<<ceil_div(B * d * 8, 256), 256, 0, stream>>>(ws, d_pooled, nchunks, B * d);
   if (d_h != nullptr) {
     const long long rows = static_cast<long long>(B) * L;
     const long long work = (d & 7) == 0 ? rows * (d >> 3) : rows * d;

@@ -22,6 +22,11 @@ from . import ops
 LOSS_KEYS = ("load_balance", "auxiliary", "z_loss", "entropy")
 
 
+class _LossDict(dict):
+    """Router loss dict (same keys as the reference) that also carries the raw 4-vector as ``.vector``."""
+    vector = None
+
+
 class SparseBankGrad:
     """Receives bank gradients as (chapter ids, [U*T, d] rows) instead of a dense tensor.
 
@@ -82,6 +87,9 @@ def route(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], t
     idx, w, cidx, cw, lv = _Route.apply(h, weight, bias, int(top_k), int(num_shared), float(routed_scale),
                                         bool(with_losses))
     losses = {k: lv[i] for i, k in enumerate(LOSS_KEYS)} if with_losses else {}
+    if with_losses:
+        losses = _LossDict(losses)
+        losses.vector = lv          # the four losses as one tensor (order of LOSS_KEYS), for a single backward seed
     return idx, w, cidx, cw, losses
 
 
