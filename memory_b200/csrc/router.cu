@@ -14,7 +14,7 @@ namespace {
 constexpr int kPoolSplits = 32;       // sequence splits of the mean-pool
 constexpr int kSelectThreads = 1024;  // one CTA per batch row in the select / dlogits kernels
 constexpr int kLossChunk = 256;       // chapters per CTA in the loss kernels
-constexpr int kLogitsPerWarp = 4;    // chapters per warp in the logits / d_w kernels
+constexpr int kLogitsPerWarp = 1;    // chapters per warp in the logits / d_w kernels
 constexpr int kDpChunk = 16;          // chapters per CTA in the d_pooled kernel
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
