@@ -203,6 +203,7 @@ class LayerRunner:
         self.g_losses = torch.tensor([0.01, 0.0, 0.001, 0.0], device=device)   # load_balance, auxiliary, z, entropy
         self.reducer = None
         self.pending = None
+        self.prev_snap = None
         if world > 1:
             from memory_b200.distributed import GradReducer
             self.reducer = GradReducer(cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["hidden_dim"], device,
@@ -238,20 +239,29 @@ class LayerRunner:
         else:
             loss = self._fwd_bwd(h, d_out)
         if self.reducer is not None:
-            # the reduction of step i runs on the communication stream under the compute of step i+1;
-            # at most one reduction is in flight
-            if self.pending is not None:
-                self.pending.wait()
+            # gradients of step i are staged on the compute stream (no host sync); their reduction runs on
+            # the reducer's stream one step later, under the compute of step i+1
             P = self.params
             dense = [P[k].grad for k in ("router_w", "router_b", "wq", "wk", "wv", "wo")]
-            self.pending = self.reducer.reduce_async(dense, self.sink)
+            snap = self.reducer.snapshot(dense, self.sink)
+            if self.prev_snap is not None:
+                if self.pending is not None:
+                    self.pending.wait()
+                self.pending = self.reducer.reduce_snapshot_async(self.prev_snap)
+            self.prev_snap = snap
         return loss
 
     def finish(self):
-        """Wait (on the stream) for the reduction still in flight."""
-        if self.reducer is not None and self.pending is not None:
+        """Reduce the last staged step and wait (on the stream) for everything in flight."""
+        if self.reducer is None:
+            return
+        if self.pending is not None:
             self.pending.wait()
             self.pending = None
+        if self.prev_snap is not None:
+            last = self.reducer.reduce_snapshot_async(self.prev_snap)
+            last.wait()
+            self.prev_snap = None
 
     def launches_per_step(self):
         """Kernels of this library one step launches (counted on an eager pass)."""
@@ -317,6 +327,11 @@ def time_dominant_kernels(cfg, device, iters=10):
 
 
 def run_cuda_arm(args):
+    # libraries (NCCL) may print to stdout; the contract is ONE JSON line there, so stdout is pointed at
+    # stderr for the run and the line is written to the saved descriptor at the end
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -464,7 +479,8 @@ def run_cuda_arm(args):
         "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu_baseline,
         "pct_of_bf16_tc_roofline": 100.0 * roofline["layer"]["frac"],
     }
-    print(json.dumps(line), flush=True)
+    sys.stdout.flush()
+    os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -114,6 +114,57 @@ class GradReducer:
             bank = (union, buf)
         return PendingReduction(self, works, flat, [g.shape for g in live], bank, type(sink) if sink is not None else None)
 
+    # ---- pipelined form: snapshot on the compute stream, reduce on a side stream one step later ----------
+    def snapshot(self, dense_grads: Sequence[Optional[torch.Tensor]], sink) -> "GradSnapshot":
+        """Copy this step's gradients into staging buffers on the current stream (no host
+        synchronisation).  The caller may overwrite its gradient tensors right afterwards, e.g. by
+        replaying a captured step."""
+        live = [g for g in dense_grads if g is not None]
+        flat = torch.cat([g.reshape(-1).float() for g in live]) if live else None
+        entries = []
+        if sink is not None:
+            for uniq, num_unique, rows, t in sink.entries:
+                entries.append((uniq.clone(), num_unique.clone(), rows.clone(), t))
+        ev = torch.cuda.Event() if self.device.type == "cuda" else None
+        if ev is not None:
+            ev.record(torch.cuda.current_stream(self.device))
+        return GradSnapshot(flat, [g.shape for g in live], entries, ev, type(sink) if sink is not None else None)
+
+    def reduce_snapshot_async(self, snap: "GradSnapshot") -> "PendingReduction":
+        """Reduce a snapshot on the reducer's own stream.  The host waits only for that stream (to read the
+        union size), so work already queued on the compute stream keeps running underneath."""
+        if self.device.type != "cuda":
+            holder = snap.sink_type() if snap.sink_type is not None else None
+            if holder is not None:
+                for e in snap.entries:
+                    holder.add(*e)
+            dense = self._split(snap.flat, snap.shapes)
+            return self.reduce_async(dense, holder)
+        if getattr(self, "_stream", None) is None:
+            self._stream = torch.cuda.Stream(self.device)
+        with torch.cuda.stream(self._stream):
+            self._stream.wait_event(snap.event)
+            holder = snap.sink_type() if snap.sink_type is not None else None
+            if holder is not None:
+                for e in snap.entries:
+                    holder.add(*e)
+            pending = self.reduce_async(self._split(snap.flat, snap.shapes), holder)
+            pending.stream = self._stream
+        return pending
+
+    @staticmethod
+    def _split(flat, shapes):
+        out, off = [], 0
+        if flat is None:
+            return out
+        for shp in shapes:
+            n = 1
+            for v in shp:
+                n *= int(v)
+            out.append(flat[off:off + n].view(shp))
+            off += n
+        return out
+
     def reduce(self, dense_grads: Sequence[Optional[torch.Tensor]], sink):
         """All-reduce the dense gradients in place and return the reduced bank gradient (or None)."""
         self.reduce_dense(dense_grads)
@@ -143,8 +194,16 @@ class GradReducer:
         return ids.to(torch.int32), out.view(-1, self.d)
 
 
+class GradSnapshot:
+    """Staged copy of one step's gradients (see :meth:`GradReducer.snapshot`)."""
+
+    def __init__(self, flat, shapes, entries, event, sink_type):
+        self.flat, self.shapes, self.entries, self.event, self.sink_type = flat, shapes, entries, event, sink_type
+
+
 class PendingReduction:
     """Handle of a reduction started by :meth:`GradReducer.reduce_async`."""
+    stream = None
 
     def __init__(self, reducer, works, flat, shapes, bank, sink_type):
         self.reducer, self.works, self.flat, self.shapes, self.bank, self.sink_type = \
@@ -152,8 +211,14 @@ class PendingReduction:
 
     def wait(self) -> None:
         """Make the current stream wait for the collectives (no host block)."""
-        for w in self.works:
-            w.wait()
+        if self.stream is not None:
+            with torch.cuda.stream(self.stream):
+                for w in self.works:
+                    w.wait()
+            torch.cuda.current_stream(self.stream.device).wait_stream(self.stream)
+        else:
+            for w in self.works:
+                w.wait()
         self.works = []
 
     def result(self):

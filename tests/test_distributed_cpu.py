@@ -56,6 +56,11 @@ def _worker(rank, world, port, q):
         red = GradReducer(C_, T_, D_, "cpu")
         pending = red.reduce_async([d.clone() if d is not None else None for d in dense], sink)
         dense_async, bank_async = pending.result()
+        snap = red.snapshot([d.clone() if d is not None else None for d in dense], sink)
+        dense_snap, bank_snap = red.reduce_snapshot_async(snap).result()
+        for a, b in zip(dense_snap, dense_async):
+            torch.testing.assert_close(a, b)
+        torch.testing.assert_close(_dense_of(bank_snap.entries), _dense_of(bank_async.entries))
         reduced = red.reduce(dense, sink)
         assert len(sink.entries) == 2, "the local entries must be left in place"
         for a, b in zip(dense_async, [d for d in dense if d is not None]):
