@@ -28,6 +28,9 @@ PAPER = dict(batch=8, seq=1024, hidden_dim=768, num_heads=12, num_kv_heads=12, n
              tokens_per_chapter=64, top_k=64, num_shared_chapters=1, routed_scaling_factor=2.5)
 METRIC = "memory-xattn fwd+bwd tokens/sec/GPU at L=1024,k=64; % of bf16 TC roofline"
 N_INPUT_SETS = 4       # distinct hidden-state batches rotated between steps
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at this shape, from the ncu captures summarised under
+# profiles/ (bytes); kernels without a capture report null
+DOMINANT_KERNEL_DRAM_BYTES = {"attn_bwd_dkv": 188.2e6}
 
 
 def layer_flops(cfg) -> float:
@@ -453,7 +456,7 @@ def run_cuda_arm(args):
     dom = max(kern, key=kern.get)
     achieved = alg[dom] / (kern[dom] * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                "frac": achieved / peaks["tflops"], "traffic": None, "peak_source": peaks["source"] + " (burst, kernel timed alone)",
+                "frac": achieved / peaks["tflops"], "traffic": DOMINANT_KERNEL_DRAM_BYTES.get(dom), "peak_source": peaks["source"] + " (burst, kernel timed alone)",
                 "executed_tflops": executed[dom] / (kern[dom] * 1e-3) / 1e12,
                 "kernel_ms": {k: round(v, 4) for k, v in kern.items()},
                 "layer": {"algorithmic_flops_per_step": f_step, "achieved": f_step / (ms_per_step * 1e-3) / 1e12,
