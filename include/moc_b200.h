@@ -215,6 +215,12 @@ int moc_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream);
  * projections want. */
 int moc_transpose(const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, int32_t rows, int32_t cols,
                   void* stream);
+/* One launch for up to four weight matrices (host arrays of n device pointers / sizes): dst[i] (may be NULL) receives
+ * src[i] as bf16 in the same [rows, cols] layout, dst_t[i] (may be NULL) its transpose [cols, rows] with row stride
+ * ldt[i] (0 = rows[i]; a larger stride lets Wk^T and Wv^T share one [d, 2*dkv] matrix).  This is the bf16 working
+ * copy of the q/k/v/o nn.Linear weights (memory_attention.py:140-143) for one step. */
+int moc_pack_weights(int32_t n, const void* const* src, int32_t src_dtype, void* const* dst, void* const* dst_t,
+                     const int32_t* rows, const int32_t* cols, const int32_t* ldt, void* stream);
 
 #ifdef __cplusplus
 }

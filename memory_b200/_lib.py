@@ -69,6 +69,7 @@ _PROTOTYPES = {
     "moc_cast_f32_to_bf16": (C.c_int, [P, P, C.c_int64, P]),
     "moc_cast_bf16_to_f32": (C.c_int, [P, P, C.c_int64, P]),
     "moc_transpose": (C.c_int, [P, C.c_int32, P, C.c_int32, C.c_int32, C.c_int32, P]),
+    "moc_pack_weights": (C.c_int, [C.c_int32, P, C.c_int32, P, P, P, P, P, P]),
 }
 # symbols every build must export (checked by the CPU test-suite against include/moc_b200.h)
 EXPORTED = tuple(_PROTOTYPES)

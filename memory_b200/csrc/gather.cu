@@ -323,6 +323,36 @@ __global__ void transpose_kernel(const TS* __restrict__ src, TD* __restrict__ ds
   }
 }
 
+// Up to four row-major matrices converted in one launch: dst[i] = src[i] in the output dtype and, when
+// dst_t[i] is given, dst_t[i] = src[i]^T.  blockIdx.z selects the matrix.
+struct PackJob { const void* src; void* dst; void* dst_t; int rows, cols, ldt; };
+struct PackJobs { PackJob j[4]; int n; };
+template <typename TS>
+__global__ void pack_weights_kernel(PackJobs jobs) {
+  const PackJob jb = jobs.j[blockIdx.z];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  if (r0 >= jb.rows || c0 >= jb.cols) return;
+  __shared__ float tile[32][33];
+  const TS* src = static_cast<const TS*>(jb.src);
+  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(jb.dst);
+  __nv_bfloat16* dst_t = static_cast<__nv_bfloat16*>(jb.dst_t);
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int r = r0 + i, c = c0 + threadIdx.x;
+    float v = 0.f;
+    if (r < jb.rows && c < jb.cols) {
+      v = ld(src, static_cast<long long>(r) * jb.cols + c);
+      if (dst != nullptr) dst[static_cast<long long>(r) * jb.cols + c] = __float2bfloat16(v);
+    }
+    tile[i][threadIdx.x] = v;
+  }
+  if (dst_t == nullptr) return;
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int c = c0 + i, r = r0 + threadIdx.x;
+    if (c < jb.cols && r < jb.rows) dst_t[static_cast<long long>(c) * jb.ldt + r] = __float2bfloat16(tile[threadIdx.x][i]);
+  }
+}
+
 inline int grid_for(long long n, int per_block) {
   long long g = (n + per_block - 1) / per_block;
   const long long cap = 148LL * 32;
@@ -453,6 +483,28 @@ extern "C" int moc_transpose(const void* src, int32_t src_dtype, void* dst, int3
     transpose_kernel<float, float><<<grid, block, 0, stream>>>(static_cast<const float*>(src), static_cast<float*>(dst), rows, cols);
   else if (src_dtype == MOC_BF16 && dst_dtype == MOC_F32)
     transpose_kernel<__nv_bfloat16, float><<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), static_cast<float*>(dst), rows, cols);
+  else MOC_REQUIRE(false, "bad dtype");
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+extern "C" int moc_pack_weights(int32_t n, const void* const* src, int32_t src_dtype, void* const* dst,
+                                void* const* dst_t, const int32_t* rows, const int32_t* cols,
+                                const int32_t* ldt, void* stream_) {
+  MOC_REQUIRE(n >= 1 && n <= 4 && src && dst && dst_t && rows && cols && ldt, "bad pack arguments");
+  PackJobs jobs;
+  jobs.n = n;
+  int max_r = 0, max_c = 0;
+  for (int i = 0; i < n; ++i) {
+    MOC_REQUIRE(src[i] != nullptr && rows[i] > 0 && cols[i] > 0, "bad pack job");
+    jobs.j[i] = PackJob{src[i], dst[i], dst_t[i], rows[i], cols[i], ldt[i] > 0 ? ldt[i] : rows[i]};
+    if (rows[i] > max_r) max_r = rows[i];
+    if (cols[i] > max_c) max_c = cols[i];
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  dim3 grid(ceil_div(max_c, 32), ceil_div(max_r, 32), n), block(32, 8);
+  if (src_dtype == MOC_F32) pack_weights_kernel<float><<<grid, block, 0, stream>>>(jobs);
+  else if (src_dtype == MOC_BF16) pack_weights_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(jobs);
   else MOC_REQUIRE(false, "bad dtype");
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;

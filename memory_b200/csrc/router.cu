@@ -95,7 +95,28 @@ __global__ void logits_kernel(const float* __restrict__ pooled, const float* __r
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
       const float* wr = w + static_cast<long long>(c) * d;
-      if (vec) {
+      if (vec && d <= 1024) {
+        // the whole weight row is requested before any arithmetic: 8 independent 16-byte loads per lane
+        const float4* w4 = reinterpret_cast<const float4*>(wr);
+        float4 wv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int k = lane + 32 * i;
+          wv[i] = (k < d / 4) ? w4[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int k = lane + 32 * i;
+          if (k < d / 4) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (j < nb) {
+                const float4 pv = reinterpret_cast<const float4*>(sp + j * d)[k];
+                acc[j] = fmaf(wv[i].x, pv.x, fmaf(wv[i].y, pv.y, fmaf(wv[i].z, pv.z, fmaf(wv[i].w, pv.w, acc[j]))));
+              }
+          }
+        }
+      } else if (vec) {
         const float4* w4 = reinterpret_cast<const float4*>(wr);
         for (int k = lane; k < d / 4; k += 32) {
           const float4 wv = w4[k];

@@ -152,8 +152,23 @@ class _CrossAttention(torch.autograd.Function):
         mem_shared = memory.dim() == 2
         h2 = ops.cast(h.reshape(b * l, d), cd)
         m2 = ops.cast(memory.reshape(-1, memory.shape[-1]), cd)
-        wq_c, wo_c = ops.cast(wq, cd), ops.cast(wo, cd)
-        wkv_c = ops.cast(torch.cat([wk, wv], dim=0), cd)
+        dkv = wk.shape[0]
+        wt = None
+        if cd == torch.bfloat16 and wq.dtype == wk.dtype == wv.dtype == wo.dtype:
+            # one launch: bf16 working copies of the four weights (Wk and Wv stacked) and, for the backward
+            # pass, their transposes, so every input-gradient projection has K-major operands
+            w_all = torch.empty(2 * d + 2 * dkv, d, dtype=cd, device=h.device)
+            wq_c, wkv_c, wo_c = w_all[:d], w_all[d:d + 2 * dkv], w_all[d + 2 * dkv:]
+            need_t = any(ctx.needs_input_grad[:6])
+            wq_t = torch.empty(d, d, dtype=cd, device=h.device) if need_t else None
+            wkv_t = torch.empty(d, 2 * dkv, dtype=cd, device=h.device) if need_t else None
+            wo_t = torch.empty(d, d, dtype=cd, device=h.device) if need_t else None
+            ops.pack_weights([wq, wk, wv, wo], [wq_c, wkv_c[:dkv], wkv_c[dkv:], wo_c],
+                             [wq_t, wkv_t, wkv_t[:, dkv:] if need_t else None, wo_t], [0, 2 * dkv, 2 * dkv, 0])
+            wt = (wq_t, wkv_t, wo_t)
+        else:
+            wq_c, wo_c = ops.cast(wq, cd), ops.cast(wo, cd)
+            wkv_c = ops.cast(torch.cat([wk, wv], dim=0), cd)
         q = ops.gemm(h2, wq_c, tag="q_proj")                                   # [B*L, H*D]
         kv = ops.gemm(m2, wkv_c, tag="kv_proj")                                 # [(B*)n_sel, 2*HK*D]
         if mem_shared:
@@ -165,6 +180,7 @@ class _CrossAttention(torch.autograd.Function):
         out = ops.gemm(o.view(b * l, -1), wo_c, tag="o_proj")
         ctx.cfg = (num_heads, num_kv_heads, scale, cd, mem_shared, h.dtype, memory.dtype)
         ctx.save_for_backward(h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse)
+        ctx.wt = wt
         ctx.w_dtypes = (wq.dtype, wk.dtype, wv.dtype, wo.dtype)
         return out.view(b, l, -1).to(h.dtype)
 
@@ -185,26 +201,28 @@ class _CrossAttention(torch.autograd.Function):
         split = splits(b * l, d, d)
         tc = cd == torch.bfloat16
 
-        def grad_in(dy, w_c, tag):
-            """dX = dY W.  The tensor-core kernel is fastest with both operands K-major, so the small
-            weight is transposed first; the fp32 kernel takes the strided operand directly."""
+        wt = ctx.wt
+
+        def grad_in(dy, w_c, w_t, tag):
+            """dX = dY W.  The tensor-core kernel is fastest with both operands K-major, so it takes the
+            transposed copy of the small weight; the fp32 kernel takes the strided operand directly."""
             if tc:
-                return ops.gemm(dy, ops.transpose(w_c), tag=tag)
+                return ops.gemm(dy, w_t if w_t is not None else ops.transpose(w_c), tag=tag)
             return ops.gemm(dy, w_c, b_kmajor=False, tag=tag)
 
-        d_o = grad_in(g2, wo_c, "d_attn_out")                                      # [B*L, H*D]
+        d_o = grad_in(g2, wo_c, wt[2] if wt else None, "d_attn_out")                                      # [B*L, H*D]
         d_wo = ops.gemm(g2, o.view(b * l, -1), a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split,
                         tag="d_wo")
         d_q, d_kv = ops.attn_bwd(q.view(b, l, -1), kv, o, lse, d_o.view(b, l, -1), num_heads, num_kv_heads, scale)
         d_q2 = d_q.view(b * l, -1)
-        d_h = grad_in(d_q2, wq_c, "d_h")
+        d_h = grad_in(d_q2, wq_c, wt[0] if wt else None, "d_h")
         d_wq = ops.gemm(d_q2, h2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split, tag="d_wq")
         d_kv2 = d_kv.view(-1, d_kv.shape[-1])
         if mem_shared:
             d_kv2 = d_kv.float().sum(dim=0).to(cd)
         rows = d_kv2.shape[0]
         split_kv = splits(rows, wkv_c.shape[0], d)
-        d_mem = grad_in(d_kv2, wkv_c, "d_mem")
+        d_mem = grad_in(d_kv2, wkv_c, wt[1] if wt else None, "d_mem")
         d_wkv = ops.gemm(d_kv2, m2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split_kv, tag="d_wkv")
         dkv_dim = wkv_c.shape[0] // 2
         wdt = ctx.w_dtypes

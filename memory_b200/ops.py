@@ -381,3 +381,21 @@ def transpose(t: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Ten
                                L.stream_ptr(t.device))
     L.check(rc, "moc_transpose")
     return out
+
+
+@_instrument("pack_weights", 1)
+def pack_weights(mats, outs, outs_t, ldt=None) -> None:
+    """bf16 copies (``outs[i]``, may be None) and bf16 transposes (``outs_t[i]``, may be None; row stride
+    ``ldt[i]``, 0 = dense) of up to four same-dtype row-major matrices, in one launch."""
+    n = len(mats)
+    L.require_cuda(*mats)
+    mats = [_contig(m) for m in mats]
+    arr = C.c_void_p * n
+    iarr = C.c_int32 * n
+    rc = L.lib().moc_pack_weights(
+        n, arr(*[m.data_ptr() for m in mats]), L.dtype_code(mats[0].dtype),
+        arr(*[(o.data_ptr() if o is not None else None) for o in outs]),
+        arr(*[(o.data_ptr() if o is not None else None) for o in outs_t]),
+        iarr(*[m.shape[0] for m in mats]), iarr(*[m.shape[1] for m in mats]),
+        iarr(*(ldt if ldt is not None else [0] * n)), L.stream_ptr(mats[0].device))
+    L.check(rc, "moc_pack_weights")
