@@ -134,7 +134,10 @@ int moc_scatter_bank_grad(const float* bank_grad, const int32_t* uniq, const int
  * a_block_rows (8..128, divides 128): this is the fused chapter gather + Wk/Wv projection, with the
  * chapter rows fetched by TMA straight from the bank.
  * accumulate != 0 adds into C (fp32 C only); split_k > 1 splits K over CTAs with fp32 atomics
- * (fp32 C only, C must be pre-zeroed or accumulate set). */
+ * (fp32 C only, C must be pre-zeroed or accumulate set).
+ * residual (device fp32 [M,N], row stride ldr, may be NULL): added to the product before it is stored,
+ * C = row_scale * (A B) + residual -- the residual add that follows the output projection in the
+ * reference's block (memory_block.py:558) done in the projection's epilogue. */
 typedef struct {
   int32_t dtype, c_dtype;
   int32_t m, n, k;
@@ -144,10 +147,32 @@ typedef struct {
   int32_t scale_block_rows;
   int32_t a_block_rows;
   int64_t a_stored_rows;   /* rows of the stored A when a gather list is used */
+  const float* residual;
+  int64_t ldr;
 } moc_gemm_desc;
 
 int moc_gemm(const moc_gemm_desc* g, const void* a, const void* b, void* c, const float* row_scale,
              const int32_t* a_row_blocks, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Normalisation in front of the memory cross-attention.  Replaces `memory_layernorm` of
+ * MemoryTransformerBlock (memory_block.py:475, 551, 578): RMSNorm (memory_block.py:18-28,
+ * x / sqrt(mean(x^2) + eps) * weight) when kind = MOC_NORM_RMS, torch.nn.LayerNorm when kind =
+ * MOC_NORM_LAYERNORM (bias may be NULL).
+ *   x [rows, dim] fp32, dim % 4 == 0; y_f32 and / or y_bf16 [rows, dim] receive the result (either may be
+ *   NULL, not both): the bf16 copy is the operand of the query projection, so no separate cast runs;
+ *   stats [rows, 2] fp32 = (mean, 1 / sqrt(var + eps)) per row, kept for the backward pass.
+ * moc_norm_bwd: dy is the gradient of the normalised rows; dx = norm-gradient + residual_grad (fp32
+ * [rows, dim] or NULL: the gradient that reaches x through the residual connection, memory_block.py:558);
+ * dweight / dbias [dim] (may be NULL; dbias only for LayerNorm); workspace of
+ * moc_norm_bwd_workspace_bytes(rows, dim) bytes holds per-block column sums.
+ * ---------------------------------------------------------------------------------------------- */
+size_t moc_norm_bwd_workspace_bytes(int64_t rows, int32_t dim);
+int moc_norm_fwd(const float* x, const float* weight, const float* bias, int32_t kind, float eps,
+                 int64_t rows, int32_t dim, float* y_f32, void* y_bf16, float* stats, void* stream);
+int moc_norm_bwd(const float* dy, const float* x, const float* weight, const float* stats,
+                 const float* residual_grad, int32_t kind, int64_t rows, int32_t dim, float* dx,
+                 float* dweight, float* dbias, void* workspace, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Joint-softmax cross attention over the gathered chapters.  Replaces MemoryCrossAttention._attention

@@ -6,12 +6,13 @@ modules for this path.
 """
 from .functional import (SparseBankGrad, cross_attention, gather_chapters, memory_layer, route)
 from .memory_attention import MemoryCrossAttention
+from .memory_block import MemorySubBlock, RMSNorm
 from .memory_bank import ChapteredMemoryBank, StandardMemoryBank
 from .memory_cross_attn import memory_cross_attn, memory_cross_attn_forward
 from .router import ChapterRouter, compute_total_router_loss
 
 __all__ = [
     "ChapterRouter", "compute_total_router_loss", "StandardMemoryBank", "ChapteredMemoryBank",
-    "MemoryCrossAttention", "memory_cross_attn", "memory_cross_attn_forward", "memory_layer", "route",
+    "MemoryCrossAttention", "MemorySubBlock", "RMSNorm", "memory_cross_attn", "memory_cross_attn_forward", "memory_layer", "route",
     "gather_chapters", "cross_attention", "SparseBankGrad",
 ]

@@ -31,7 +31,8 @@ class GemmDesc(C.Structure):
                 ("k", C.c_int32), ("a_kmajor", C.c_int32), ("b_kmajor", C.c_int32),
                 ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64),
                 ("accumulate", C.c_int32), ("split_k", C.c_int32), ("scale_block_rows", C.c_int32),
-                ("a_block_rows", C.c_int32), ("a_stored_rows", C.c_int64)]
+                ("a_block_rows", C.c_int32), ("a_stored_rows", C.c_int64),
+                ("residual", C.c_void_p), ("ldr", C.c_int64)]
 
 
 class AttnShape(C.Structure):
@@ -70,6 +71,9 @@ _PROTOTYPES = {
     "moc_cast_bf16_to_f32": (C.c_int, [P, P, C.c_int64, P]),
     "moc_transpose": (C.c_int, [P, C.c_int32, P, C.c_int32, C.c_int32, C.c_int32, P]),
     "moc_pack_weights": (C.c_int, [C.c_int32, P, C.c_int32, P, P, P, P, P, P]),
+    "moc_norm_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
+    "moc_norm_fwd": (C.c_int, [P, P, P, C.c_int32, C.c_float, C.c_int64, C.c_int32, P, P, P, P]),
+    "moc_norm_bwd": (C.c_int, [P, P, P, P, P, C.c_int32, C.c_int64, C.c_int32, P, P, P, P, P]),
 }
 # symbols every build must export (checked by the CPU test-suite against include/moc_b200.h)
 EXPORTED = tuple(_PROTOTYPES)

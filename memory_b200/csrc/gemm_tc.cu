@@ -38,6 +38,8 @@ struct GemmTcParams {
   int atomic;
   const float* row_scale;
   int scale_block_rows;
+  const float* residual;   // fp32 [m, n] added to the product by the first K split, or nullptr
+  long long ldr;
   const int* a_row_blocks;
   int a_box_rows;          // rows per A box when A is K-major
   int a_num_blocks;        // entries in the gather list
@@ -223,7 +225,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
         if (row >= p.m) continue;
-        if (!has_k && (p.atomic || p.accumulate)) continue;
+        if (p.residual != nullptr && split == 0) {
+          // fold the row scale and the residual into the registers; the stores below then see rs = 1
+          const float* res = p.residual + static_cast<long long>(row) * p.ldr + col0;
+          const bool vec4 = ((p.ldr & 3) == 0) && (col0 + 32 <= p.n) &&
+                            ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
+          if (vec4) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 v = *reinterpret_cast<const float4*>(res + 4 * j);
+              r[4 * j + 0] = __float_as_uint(__uint_as_float(r[4 * j + 0]) * rs + v.x);
+              r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) * rs + v.y);
+              r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) * rs + v.z);
+              r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) * rs + v.w);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.n) r[j] = __float_as_uint(__uint_as_float(r[j]) * rs + res[j]);
+          }
+        } else if (!has_k && (p.atomic || p.accumulate)) {
+          continue;
+        }
+        const float rs_store = (p.residual != nullptr && split == 0) ? 1.0f : rs;
         if (p.c_bf16) {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
           const bool vec = ((p.ldc & 7) == 0) && (col0 + 32 <= p.n) &&
@@ -232,15 +256,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]) * rs, __uint_as_float(r[8 * j + 1]) * rs);
-              v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * rs, __uint_as_float(r[8 * j + 3]) * rs);
-              v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * rs, __uint_as_float(r[8 * j + 5]) * rs);
-              v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * rs, __uint_as_float(r[8 * j + 7]) * rs);
+              v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]) * rs_store, __uint_as_float(r[8 * j + 1]) * rs_store);
+              v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * rs_store, __uint_as_float(r[8 * j + 3]) * rs_store);
+              v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * rs_store, __uint_as_float(r[8 * j + 5]) * rs_store);
+              v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * rs_store, __uint_as_float(r[8 * j + 7]) * rs_store);
               *reinterpret_cast<uint4*>(dst + 8 * j) = v;
             }
           } else {
             for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.n) dst[j] = __float2bfloat16(__uint_as_float(r[j]) * rs);
+              if (col0 + j < p.n) dst[j] = __float2bfloat16(__uint_as_float(r[j]) * rs_store);
           }
         } else {
           float* dst = reinterpret_cast<float*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
@@ -251,11 +275,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
               for (int j = 0; j < 8; ++j)
                 atomicAdd(reinterpret_cast<float4*>(dst + 4 * j),
-                          make_float4(__uint_as_float(r[4 * j + 0]) * rs, __uint_as_float(r[4 * j + 1]) * rs,
-                                      __uint_as_float(r[4 * j + 2]) * rs, __uint_as_float(r[4 * j + 3]) * rs));
+                          make_float4(__uint_as_float(r[4 * j + 0]) * rs_store, __uint_as_float(r[4 * j + 1]) * rs_store,
+                                      __uint_as_float(r[4 * j + 2]) * rs_store, __uint_as_float(r[4 * j + 3]) * rs_store));
             } else {
               for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.n) atomicAdd(dst + j, __uint_as_float(r[j]) * rs);
+                if (col0 + j < p.n) atomicAdd(dst + j, __uint_as_float(r[j]) * rs_store);
             }
           } else {
             const bool vec = ((p.ldc & 3) == 0) && (col0 + 32 <= p.n) &&
@@ -263,8 +287,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (vec) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                float4 v = make_float4(__uint_as_float(r[4 * j + 0]) * rs, __uint_as_float(r[4 * j + 1]) * rs,
-                                       __uint_as_float(r[4 * j + 2]) * rs, __uint_as_float(r[4 * j + 3]) * rs);
+                float4 v = make_float4(__uint_as_float(r[4 * j + 0]) * rs_store, __uint_as_float(r[4 * j + 1]) * rs_store,
+                                       __uint_as_float(r[4 * j + 2]) * rs_store, __uint_as_float(r[4 * j + 3]) * rs_store);
                 float4* d4 = reinterpret_cast<float4*>(dst + 4 * j);
                 if (p.accumulate) {
                   const float4 o = *d4;
@@ -275,7 +299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             } else {
               for (int j = 0; j < 32; ++j)
                 if (col0 + j < p.n) {
-                  const float v = __uint_as_float(r[j]) * rs;
+                  const float v = __uint_as_float(r[j]) * rs_store;
                   dst[j] = p.accumulate ? dst[j] + v : v;
                 }
             }
@@ -369,6 +393,7 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
   p.c = c; p.ldc = g->ldc; p.c_bf16 = (g->c_dtype == MOC_BF16);
   p.accumulate = g->accumulate; p.atomic = split > 1;
   p.row_scale = row_scale; p.scale_block_rows = g->scale_block_rows > 0 ? g->scale_block_rows : 1;
+  p.residual = g->residual; p.ldr = g->ldr;
   p.a_row_blocks = a_row_blocks; p.a_box_rows = a_box_rows; p.a_num_blocks = a_num_blocks;
   p.a_stored_rows = a_stored_rows;
   p.k_tiles_total = ceil_div(g->k, BK);

@@ -57,4 +57,4 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_
 }  // namespace moc
 
 extern "C" const char* moc_last_error(void) { return moc::g_last_error.c_str(); }
-extern "C" int moc_abi_version(void) { return 1; }
+extern "C" int moc_abi_version(void) { return 2; }

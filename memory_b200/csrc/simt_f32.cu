@@ -16,7 +16,8 @@ constexpr int GT = 64, GK = 16;
 __global__ void __launch_bounds__(256)
 sgemm_kernel(const float* __restrict__ a, long long sa_m, long long sa_k, const float* __restrict__ b,
              long long sb_k, long long sb_n, float* __restrict__ c, long long ldc, int M, int N, int K,
-             const float* __restrict__ row_scale, int scale_block, int accumulate) {
+             const float* __restrict__ row_scale, int scale_block, int accumulate,
+             const float* __restrict__ residual, long long ldr) {
   __shared__ float As[GK][GT + 4];
   __shared__ float Bs[GK][GT + 4];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -62,7 +63,8 @@ sgemm_kernel(const float* __restrict__ a, long long sa_m, long long sa_k, const 
       const int gn = n0 + tx * 4 + j;
       if (gn >= N) continue;
       float* dst = c + gm * ldc + gn;
-      const float v = acc[i][j] * rs;
+      float v = acc[i][j] * rs;
+      if (residual != nullptr) v += residual[gm * ldr + gn];
       *dst = accumulate ? *dst + v : v;
     }
   }
@@ -274,7 +276,8 @@ int launch_sgemm(const moc_gemm_desc* g, const float* a, const float* b, float* 
   const long long sb_k = g->b_kmajor ? 1 : g->ldb, sb_n = g->b_kmajor ? g->ldb : 1;
   dim3 grid(ceil_div(g->n, GT), ceil_div(g->m, GT));
   sgemm_kernel<<<grid, 256, 0, stream>>>(a, sa_m, sa_k, b, sb_k, sb_n, c, g->ldc, g->m, g->n, g->k, row_scale,
-                                         g->scale_block_rows > 0 ? g->scale_block_rows : 1, g->accumulate);
+                                         g->scale_block_rows > 0 ? g->scale_block_rows : 1, g->accumulate,
+                                         g->residual, g->ldr);
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
 }

@@ -145,12 +145,21 @@ def gather_chapters(bank: torch.Tensor, comb_idx: torch.Tensor, comb_w: Optional
 # --------------------------------------------------------------------------------------------
 class _CrossAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, h, memory, wq, wk, wv, wo, num_heads, num_kv_heads, compute_dtype):
+    def forward(ctx, h, memory, wq, wk, wv, wo, norm_w, norm_b, num_heads, num_kv_heads, compute_dtype,
+                norm_kind, norm_eps, add_residual):
         b, l, d = h.shape
         cd = compute_dtype
         n_sel = memory.shape[-2]
         mem_shared = memory.dim() == 2
-        h2 = ops.cast(h.reshape(b * l, d), cd)
+        x2 = h.reshape(b * l, d)
+        stats = None
+        if norm_kind is not None:
+            # the normalisation writes the projection operand in the compute dtype: no separate cast
+            x2 = x2.float()
+            h2, stats = ops.norm_fwd(x2, norm_w.float(), None if norm_b is None else norm_b.float(), norm_kind,
+                                     norm_eps, cd)
+        else:
+            h2 = ops.cast(x2, cd)
         m2 = ops.cast(memory.reshape(-1, memory.shape[-1]), cd)
         dkv = wk.shape[0]
         wt = None
@@ -177,17 +186,26 @@ class _CrossAttention(torch.autograd.Function):
         scale = head_dim ** -0.5
         kv = kv.view(b, n_sel, -1)
         o, lse = ops.attn_fwd(q.view(b, l, -1), kv, num_heads, num_kv_heads, scale)
-        out = ops.gemm(o.view(b * l, -1), wo_c, tag="o_proj")
+        # the output projection writes the caller's dtype; the residual connection of the enclosing block
+        # (memory_block.py:558) is added in its epilogue
+        res = (x2 if x2.dtype == torch.float32 else x2.float()) if add_residual else None
+        out = ops.gemm(o.view(b * l, -1), wo_c, out_dtype=h.dtype if h.dtype in (torch.float32, cd) else cd,
+                       residual=res, tag="o_proj")
         ctx.cfg = (num_heads, num_kv_heads, scale, cd, mem_shared, h.dtype, memory.dtype)
-        ctx.save_for_backward(h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse)
+        ctx.norm = (norm_kind, norm_b is not None, add_residual,
+                    None if norm_w is None else norm_w.dtype, None if norm_b is None else norm_b.dtype)
+        ctx.save_for_backward(h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse,
+                              x2 if norm_kind is not None else None, stats,
+                              norm_w.float() if norm_kind is not None else None)
         ctx.wt = wt
         ctx.w_dtypes = (wq.dtype, wk.dtype, wv.dtype, wo.dtype)
         return out.view(b, l, -1).to(h.dtype)
 
     @staticmethod
     def backward(ctx, g):
-        h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse = ctx.saved_tensors
+        h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse, x2, stats, norm_w = ctx.saved_tensors
         num_heads, num_kv_heads, scale, cd, mem_shared, h_dtype, mem_dtype = ctx.cfg
+        norm_kind, norm_has_bias, add_residual, nw_dtype, nb_dtype = ctx.norm
         b, l, _ = o.shape
         d = h2.shape[1]
         g2 = ops.cast(g.reshape(b * l, -1).contiguous(), cd)
@@ -203,11 +221,11 @@ class _CrossAttention(torch.autograd.Function):
 
         wt = ctx.wt
 
-        def grad_in(dy, w_c, w_t, tag):
+        def grad_in(dy, w_c, w_t, tag, out_dtype=None):
             """dX = dY W.  The tensor-core kernel is fastest with both operands K-major, so it takes the
             transposed copy of the small weight; the fp32 kernel takes the strided operand directly."""
             if tc:
-                return ops.gemm(dy, w_t if w_t is not None else ops.transpose(w_c), tag=tag)
+                return ops.gemm(dy, w_t if w_t is not None else ops.transpose(w_c), out_dtype=out_dtype, tag=tag)
             return ops.gemm(dy, w_c, b_kmajor=False, tag=tag)
 
         d_o = grad_in(g2, wo_c, wt[2] if wt else None, "d_attn_out")                                      # [B*L, H*D]
@@ -215,7 +233,17 @@ class _CrossAttention(torch.autograd.Function):
                         tag="d_wo")
         d_q, d_kv = ops.attn_bwd(q.view(b, l, -1), kv, o, lse, d_o.view(b, l, -1), num_heads, num_kv_heads, scale)
         d_q2 = d_q.view(b * l, -1)
-        d_h = grad_in(d_q2, wq_c, wt[0] if wt else None, "d_h")
+        # gradient of the (normalised) attention input; fp32 when the normalisation's backward consumes it
+        d_h = grad_in(d_q2, wq_c, wt[0] if wt else None, "d_h", f32 if norm_kind is not None else None)
+        d_nw = d_nb = None
+        g_res = g.reshape(b * l, -1) if add_residual else None
+        if norm_kind is not None:
+            d_h, d_nw, d_nb = ops.norm_bwd(d_h, x2, norm_w, stats, None if g_res is None else g_res.float(),
+                                           norm_kind, norm_has_bias)
+            d_nw = d_nw.to(nw_dtype)
+            d_nb = None if d_nb is None else d_nb.to(nb_dtype)
+        elif add_residual:
+            d_h = d_h.float() + g_res.float()
         d_wq = ops.gemm(d_q2, h2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=split, tag="d_wq")
         d_kv2 = d_kv.view(-1, d_kv.shape[-1])
         if mem_shared:
@@ -228,14 +256,31 @@ class _CrossAttention(torch.autograd.Function):
         wdt = ctx.w_dtypes
         d_mem = d_mem.view(-1, d_mem.shape[-1]) if mem_shared else d_mem.view(b, -1, d_mem.shape[-1])
         return (d_h.view(b, l, d).to(h_dtype), d_mem.to(mem_dtype), d_wq.to(wdt[0]), d_wkv[:dkv_dim].to(wdt[1]),
-                d_wkv[dkv_dim:].to(wdt[2]), d_wo.to(wdt[3]), None, None, None)
+                d_wkv[dkv_dim:].to(wdt[2]), d_wo.to(wdt[3]), d_nw, d_nb, None, None, None, None, None, None)
 
 
 def cross_attention(h: torch.Tensor, memory: torch.Tensor, wq, wk, wv, wo, num_heads: int,
-                    num_kv_heads: Optional[int] = None, compute_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """softmax(Q K^T / sqrt(D)) V over the given memory rows, with the four projections."""
-    return _CrossAttention.apply(h, memory, wq, wk, wv, wo, int(num_heads), int(num_kv_heads or num_heads),
-                                 compute_dtype or h.dtype)
+                    num_kv_heads: Optional[int] = None, compute_dtype: Optional[torch.dtype] = None, *,
+                    pre_norm: Optional[str] = None, norm_weight: Optional[torch.Tensor] = None,
+                    norm_bias: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
+                    add_residual: bool = False) -> torch.Tensor:
+    """softmax(Q K^T / sqrt(D)) V over the given memory rows, with the four projections.
+
+    ``pre_norm`` ("rms" or "layernorm") normalises ``h`` first and ``add_residual`` adds ``h`` to the result:
+    together they are the memory sub-block of the reference's transformer block, h + attn(norm(h), memory)
+    (memory_block.py:549-558), with the normalisation fused into the query projection's operand and the
+    residual add into the output projection's epilogue.
+    """
+    if pre_norm is not None:
+        if pre_norm not in ops.NORM_KINDS:
+            raise ValueError(f"unknown pre_norm {pre_norm!r}")
+        if norm_weight is None:
+            raise ValueError("pre_norm needs norm_weight")
+        if pre_norm in ("rms", "rmsnorm"):
+            norm_bias = None
+    return _CrossAttention.apply(h, memory, wq, wk, wv, wo, norm_weight if pre_norm else None,
+                                 norm_bias if pre_norm else None, int(num_heads), int(num_kv_heads or num_heads),
+                                 compute_dtype or h.dtype, pre_norm, float(norm_eps), bool(add_residual))
 
 
 # --------------------------------------------------------------------------------------------
@@ -246,10 +291,15 @@ def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tenso
                  wq, wk, wv, wo, *, num_heads: int, num_kv_heads: Optional[int], tokens_per_chapter: int,
                  top_k: int, num_shared_chapters: int = 1, routed_scaling_factor: float = 2.5,
                  norm_type: Optional[str] = None, norm_eps: float = 1e-5, with_losses: bool = True,
-                 compute_dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, Dict[str, torch.Tensor], Dict]:
+                 compute_dtype: Optional[torch.dtype] = None, pre_norm: Optional[str] = None,
+                 pre_norm_weight: Optional[torch.Tensor] = None, pre_norm_bias: Optional[torch.Tensor] = None,
+                 pre_norm_eps: float = 1e-6,
+                 add_residual: bool = False) -> Tuple[torch.Tensor, Dict[str, torch.Tensor], Dict]:
     """Sequence-level Mixture-of-Chapters memory layer on the GPU.
 
     Returns (out [B,L,d], router losses, info) with info = indices / weights of the routing.
+    ``norm_type`` normalises the gathered bank rows; ``pre_norm`` / ``add_residual`` wrap the attention as
+    h_attn + attn(pre_norm(h_attn), memory) (see :func:`cross_attention`).
     """
     cd = compute_dtype or h_attn.dtype
     idx, w, cidx, cw, losses = route(h_router, router_weight, router_bias, top_k, num_shared_chapters,
@@ -258,5 +308,7 @@ def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tenso
     # the reference only normalises when both a shared and a routed slice exist (model.py:413-418)
     norm = norm_type if (num_shared_chapters > 0 and k_sel > 0) else None
     memory = gather_chapters(bank, cidx, cw, tokens_per_chapter, norm, norm_eps, out_dtype=cd)
-    out = cross_attention(h_attn, memory, wq, wk, wv, wo, num_heads, num_kv_heads, cd)
+    out = cross_attention(h_attn, memory, wq, wk, wv, wo, num_heads, num_kv_heads, cd, pre_norm=pre_norm,
+                          norm_weight=pre_norm_weight, norm_bias=pre_norm_bias, norm_eps=pre_norm_eps,
+                          add_residual=add_residual)
     return out, losses, {"indices": idx, "weights": w, "combined_indices": cidx, "combined_weights": cw}

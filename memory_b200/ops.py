@@ -207,8 +207,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_kmajor: bool = True, b_kmajor: b
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, accumulate: bool = False,
          split_k: int = 1, row_scale: Optional[torch.Tensor] = None, scale_block_rows: int = 1,
          a_row_blocks: Optional[torch.Tensor] = None, a_block_rows: int = 0, m: Optional[int] = None,
-         tag: Optional[str] = None) -> torch.Tensor:
-    """C[M,N] (+)= op(A) op(B).  a_kmajor: A stored [M,K] else [K,M]; b_kmajor: B stored [N,K] else [K,N]."""
+         residual: Optional[torch.Tensor] = None, tag: Optional[str] = None) -> torch.Tensor:
+    """C[M,N] (+)= op(A) op(B) (+ residual).  a_kmajor: A stored [M,K] else [K,M]; b_kmajor: B stored [N,K]
+    else [K,N]; residual: fp32 [M,N] added in the epilogue."""
     L.require_cuda(a, b)
     if a.dtype != b.dtype:
         raise TypeError("projection operands must share a dtype")
@@ -231,7 +232,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_kmajor: bool = True, b_kmajor: b
         out = (torch.zeros if (split_k > 1 and not accumulate) else torch.empty)(mm, nn, dtype=out_dtype, device=a.device)
     g = L.GemmDesc(L.dtype_code(a.dtype), L.dtype_code(out_dtype), mm, nn, kk, int(a_kmajor), int(b_kmajor),
                    a.stride(0), b.stride(0), out.stride(0), int(accumulate), int(split_k), int(scale_block_rows),
-                   int(a_block_rows), a.shape[0])
+                   int(a_block_rows), a.shape[0], None, 0)
+    if residual is not None:
+        if residual.dtype != torch.float32 or tuple(residual.shape) != (mm, nn) or residual.stride(1) != 1:
+            raise ValueError("residual must be fp32 [M, N] with unit column stride")
+        L.require_cuda(residual)
+        g.residual, g.ldr = L.ptr(residual), residual.stride(0)
     rc = L.lib().moc_gemm(C.byref(g), L.ptr(a), L.ptr(b), L.ptr(out), L.ptr(_contig(row_scale)),
                           L.ptr(_contig(a_row_blocks)), L.ptr(L.status_word(a.device)), L.stream_ptr(a.device))
     L.check(rc, "moc_gemm")
@@ -399,3 +405,46 @@ def pack_weights(mats, outs, outs_t, ldt=None) -> None:
         iarr(*[m.shape[0] for m in mats]), iarr(*[m.shape[1] for m in mats]),
         iarr(*(ldt if ldt is not None else [0] * n)), L.stream_ptr(mats[0].device))
     L.check(rc, "moc_pack_weights")
+
+
+# --------------------------------------------------------------------------------------------
+# normalisation in front of the memory cross-attention
+# --------------------------------------------------------------------------------------------
+NORM_KINDS = {"rms": 1, "rmsnorm": 1, "layernorm": 2, "layer": 2}
+
+
+@_instrument("norm_fwd", 1)
+def norm_fwd(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], kind: str, eps: float,
+             out_dtype: torch.dtype):
+    """Rows of ``x`` [rows, dim] (fp32) normalised; returns (y in ``out_dtype``, stats [rows, 2])."""
+    L.require_cuda(x, weight)
+    if x.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise TypeError("normalisation runs on fp32 rows and fp32 weights")
+    x = _contig(x)
+    rows, dim = x.shape
+    y = torch.empty(rows, dim, dtype=out_dtype, device=x.device)
+    stats = torch.empty(rows, 2, dtype=torch.float32, device=x.device)
+    f32 = out_dtype == torch.float32
+    rc = L.lib().moc_norm_fwd(L.ptr(x), L.ptr(_contig(weight)), L.ptr(_contig(bias)), NORM_KINDS[kind], float(eps),
+                              rows, dim, L.ptr(y) if f32 else None, None if f32 else L.ptr(y), L.ptr(stats),
+                              L.stream_ptr(x.device))
+    L.check(rc, "moc_norm_fwd")
+    return y, stats
+
+
+@_instrument("norm_bwd", 2)
+def norm_bwd(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, stats: torch.Tensor,
+             residual_grad: Optional[torch.Tensor], kind: str, with_bias: bool):
+    """Gradients of :func:`norm_fwd`: (dx [+ residual_grad], dweight, dbias or None)."""
+    L.require_cuda(dy, x, weight, stats)
+    dy, x = _contig(dy), _contig(x)
+    rows, dim = x.shape
+    dx = torch.empty_like(x)
+    dweight = torch.empty(dim, dtype=torch.float32, device=x.device)
+    dbias = torch.empty(dim, dtype=torch.float32, device=x.device) if with_bias else None
+    ws = torch.empty(L.lib().moc_norm_bwd_workspace_bytes(rows, dim), dtype=torch.uint8, device=x.device)
+    rc = L.lib().moc_norm_bwd(L.ptr(dy), L.ptr(x), L.ptr(_contig(weight)), L.ptr(stats),
+                              L.ptr(_contig(residual_grad)), NORM_KINDS[kind], rows, dim, L.ptr(dx), L.ptr(dweight),
+                              L.ptr(dbias), L.ptr(ws), L.stream_ptr(x.device))
+    L.check(rc, "moc_norm_bwd")
+    return dx, dweight, dbias

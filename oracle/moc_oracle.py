@@ -42,6 +42,8 @@ class LayerShape:
     routed_scaling_factor: float = 2.5
     norm_type: Optional[str] = None   # None | "rms" | "layernorm"
     norm_eps: float = 1e-5
+    pre_norm: Optional[str] = None    # None | "rms" | "layernorm": out = h + attn(pre_norm(h), memory)
+    pre_norm_eps: float = 1e-6
 
     @property
     def head_dim(self) -> int:
@@ -262,15 +264,43 @@ def sparse_chapter_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
 # --------------------------------------------------------------------------
 # the whole layer (sequence-level routing) and its gradients
 # --------------------------------------------------------------------------
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """RMSNorm of the transformer blocks (memory_block.py:26-28): x / sqrt(mean(x^2) + eps) * weight."""
+    rms = torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    return x / rms * weight
+
+
+def block_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], kind: str,
+               eps: float = 1e-6) -> torch.Tensor:
+    """``norm_cls`` of a block (memory_block.py:448): RMSNorm when use_rms_norm else torch.nn.LayerNorm."""
+    if kind in ("rms", "rmsnorm"):
+        return rms_norm(x, weight, eps)
+    if kind in ("layernorm", "layer"):
+        return torch.nn.functional.layer_norm(x, (x.shape[-1],), weight, bias, eps)
+    raise ValueError(f"unknown norm kind {kind!r}")
+
+
+def memory_sub_block(hidden_states: torch.Tensor, memory: torch.Tensor, norm_weight: torch.Tensor,
+                     norm_bias: Optional[torch.Tensor], norm_kind: str, norm_eps: float,
+                     wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, wo: torch.Tensor,
+                     num_heads: int, num_kv_heads: int) -> torch.Tensor:
+    """The memory step of MemoryTransformerBlock.forward (memory_block.py:549-558 and 576-586):
+    residual = h; h = memory_layernorm(h); h = residual + memory_attn(h, memory)."""
+    normed = block_norm(hidden_states, norm_weight, norm_bias, norm_kind, norm_eps)
+    return hidden_states + cross_attention(normed, memory, wq, wk, wv, wo, num_heads, num_kv_heads)
+
+
 def memory_layer(
     shape: LayerShape,
     h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tensor,
     router_w: torch.Tensor, router_b: torch.Tensor,
     wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, wo: torch.Tensor,
     return_losses: bool = True, autocast_bf16: bool = False,
+    pre_norm_w: Optional[torch.Tensor] = None, pre_norm_b: Optional[torch.Tensor] = None,
 ) -> Dict[str, torch.Tensor]:
     """Router -> shared prefix -> gather -> (norm) -> weight -> cross attention
-    (model.py:624-692 followed by memory_block.py:549-558).  With
+    (model.py:624-692 followed by memory_block.py:549-558).  With ``shape.pre_norm`` the attention is
+    wrapped as the block's memory step, h + attn(norm(h), memory).  With
     ``autocast_bf16`` the attention part runs under CPU bf16 autocast while the
     router stays in fp32, the arrangement the paper-shape configuration asks for."""
     idx, w, losses, internals = router_forward(
@@ -283,11 +313,17 @@ def memory_layer(
         memory = normalize_memory_rows(memory, shape.num_shared_chapters, shape.tokens_per_chapter,
                                        shape.norm_type, shape.norm_eps)
     memory = scale_memory(memory, comb_w, shape.tokens_per_chapter)
+    def memory_step():
+        if shape.pre_norm is None:
+            return cross_attention(h_attn, memory, wq, wk, wv, wo, shape.num_heads, shape.num_kv_heads)
+        return memory_sub_block(h_attn, memory, pre_norm_w, pre_norm_b, shape.pre_norm, shape.pre_norm_eps,
+                                wq, wk, wv, wo, shape.num_heads, shape.num_kv_heads)
+
     if autocast_bf16:
         with torch.autocast(device_type="cpu", dtype=torch.bfloat16):
-            out = cross_attention(h_attn, memory, wq, wk, wv, wo, shape.num_heads, shape.num_kv_heads)
+            out = memory_step()
     else:
-        out = cross_attention(h_attn, memory, wq, wk, wv, wo, shape.num_heads, shape.num_kv_heads)
+        out = memory_step()
     return {"out": out, "indices": idx, "weights": w, "combined_indices": comb_idx,
             "combined_weights": comb_w, "losses": losses, **internals}
 
@@ -303,6 +339,8 @@ def memory_layer_fwd_bwd(
     model.py:776-806 added.  ``tensors`` holds h_router, h_attn, bank, router_w,
     router_b, wq, wk, wv, wo.  Returns outputs and one gradient per input."""
     names = ["h_router", "h_attn", "bank", "router_w", "router_b", "wq", "wk", "wv", "wo"]
+    if shape.pre_norm is not None:
+        names += ["pre_norm_w"] + (["pre_norm_b"] if shape.pre_norm not in ("rms", "rmsnorm") else [])
     leaves = {}
     shared_h = tensors["h_router"] is tensors["h_attn"]
     for n in names:
@@ -311,7 +349,8 @@ def memory_layer_fwd_bwd(
         leaves["h_attn"] = leaves["h_router"]
     res = memory_layer(shape, leaves["h_router"], leaves["h_attn"], leaves["bank"],
                        leaves["router_w"], leaves["router_b"], leaves["wq"], leaves["wk"],
-                       leaves["wv"], leaves["wo"], return_losses=True, autocast_bf16=autocast_bf16)
+                       leaves["wv"], leaves["wo"], return_losses=True, autocast_bf16=autocast_bf16,
+                       pre_norm_w=leaves.get("pre_norm_w"), pre_norm_b=leaves.get("pre_norm_b"))
     loss = (res["out"].float() * d_out.float()).sum()
     loss = loss + total_router_loss(res["losses"], load_balance_coef, auxiliary_coef, z_loss_coef)
     loss.backward()

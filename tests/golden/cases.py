@@ -32,6 +32,8 @@ class Case:
     seed: int = 1234
     separate_router_input: bool = False
     router_scale: float = 0.02       # std of the router weight
+    pre_norm: Optional[str] = None   # "rms" / "layernorm": h + attn(norm(h), memory), the block's memory step
+    pre_norm_eps: float = 1e-6
     notes: str = ""
     extra: Dict[str, float] = field(default_factory=dict)
 
@@ -53,6 +55,11 @@ CASES = {
              notes="top_k equals the chapter count, so only k = C - S routed chapters exist"),
         Case("head64_t64", 2, 128, 128, 2, 2, 17, 64, 4, seed=1242,
              notes="tensor-core tile shapes: head_dim 64, 64-row chapters"),
+        Case("block_rms", 2, 128, 128, 2, 2, 17, 64, 4, seed=1243, pre_norm="rms",
+             notes="memory step of the transformer block: RMSNorm, attention, residual add"),
+        Case("block_layernorm", 2, 64, 128, 2, 1, 33, 16, 4, seed=1244, pre_norm="layernorm",
+             separate_router_input=True,
+             notes="LayerNorm variant of the block's memory step, grouped KV heads, router fed separately"),
     ]
 }
 
@@ -78,6 +85,10 @@ def make_inputs(case: Case) -> Dict[str, np.ndarray]:
         "wo": normal((d, d), 0.02),
     }
     out["h_attn"] = normal((case.batch, case.seq, d), 1.0) if case.separate_router_input else out["h_router"]
+    if case.pre_norm is not None:
+        g2 = np.random.Generator(np.random.PCG64(case.seed + 555))
+        out["pre_norm_w"] = (1.0 + 0.1 * g2.standard_normal((d,), dtype=np.float32)).astype(np.float32)
+        out["pre_norm_b"] = (0.1 * g2.standard_normal((d,), dtype=np.float32)).astype(np.float32)
     out["d_out"] = np.random.Generator(np.random.PCG64(case.seed + 999)).standard_normal(
         (case.batch, case.seq, d), dtype=np.float32)
     return out

@@ -9,7 +9,9 @@ its model does for sequence-level routing (model.py:624-692, then
 memory_block.py:549-558): ``ChapterRouter`` -> ``_prepend_shared_chapters`` ->
 ``ChapteredMemoryBank.get_chapters_batched`` -> optional
 ``_normalize_shared_routed_memory_vectors`` -> weight multiply ->
-``MemoryCrossAttention(use_flash_attention=False)``.  The loss is
+``MemoryCrossAttention(use_flash_attention=False)``.  Cases with ``pre_norm`` wrap the attention as the
+block does (memory_block.py:549-558): ``h + memory_attn(memory_layernorm(h), memory)`` with the reference's
+``RMSNorm`` or ``torch.nn.LayerNorm``.  The loss is
 ``(out * d_out).sum() + 0.01 * load_balance + 0.001 * z_loss``.  Outputs and all
 gradients are stored as ``<case>.npz`` next to this script.  The only import
 shim is an empty ``omegaconf`` module (the reference imports it for YAML
@@ -40,11 +42,13 @@ def import_reference(path: str):
     import memory_transformer  # noqa: F401
     from memory_transformer.memory_attention import MemoryCrossAttention
     from memory_transformer.memory_bank import ChapteredMemoryBank, StandardMemoryBank
+    from memory_transformer.memory_block import RMSNorm
     from memory_transformer.model import MemoryTransformer
     from memory_transformer.router import ChapterRouter, compute_total_router_loss
     return dict(MemoryCrossAttention=MemoryCrossAttention, ChapteredMemoryBank=ChapteredMemoryBank,
                 StandardMemoryBank=StandardMemoryBank, MemoryTransformer=MemoryTransformer,
-                ChapterRouter=ChapterRouter, compute_total_router_loss=compute_total_router_loss)
+                ChapterRouter=ChapterRouter, compute_total_router_loss=compute_total_router_loss,
+                RMSNorm=RMSNorm)
 
 
 def run_reference(ref, case, inputs, autocast_bf16=False):
@@ -60,6 +64,14 @@ def run_reference(ref, case, inputs, autocast_bf16=False):
         base.memory.copy_(t["bank"])
         attn.q_proj.weight.copy_(t["wq"]); attn.k_proj.weight.copy_(t["wk"])
         attn.v_proj.weight.copy_(t["wv"]); attn.o_proj.weight.copy_(t["wo"])
+    norm = None
+    if case.pre_norm is not None:
+        norm = (ref["RMSNorm"](d, eps=case.pre_norm_eps) if case.pre_norm == "rms"
+                else torch.nn.LayerNorm(d, eps=case.pre_norm_eps))
+        with torch.no_grad():
+            norm.weight.copy_(t["pre_norm_w"])
+            if case.pre_norm != "rms":
+                norm.bias.copy_(t["pre_norm_b"])
     router.train(); attn.train()
     h_router = t["h_router"].clone().requires_grad_(True)
     h_attn = h_router if not case.separate_router_input else t["h_attn"].clone().requires_grad_(True)
@@ -77,11 +89,18 @@ def run_reference(ref, case, inputs, autocast_bf16=False):
             tokens_per_chapter=case.tokens_per_chapter, norm_type=case.norm_type, eps=case.norm_eps)
     wexp = cw.unsqueeze(-1).repeat(1, 1, case.tokens_per_chapter).reshape(memory.shape[0], -1, 1)
     memory = memory * wexp
+    def memory_step():
+        if norm is None:
+            return attn(h_attn, memory)[0]
+        residual = h_attn
+        mem_output, _ = attn(norm(h_attn), memory)
+        return residual + mem_output
+
     if autocast_bf16:
         with torch.autocast(device_type="cpu", dtype=torch.bfloat16):
-            out, _ = attn(h_attn, memory)
+            out = memory_step()
     else:
-        out, _ = attn(h_attn, memory)
+        out = memory_step()
     aux = ref["compute_total_router_loss"](losses, load_balance_coef=0.01, auxiliary_coef=0.0,
                                            z_loss_coef=0.001)
     loss = (out.float() * t["d_out"]).sum() + aux
@@ -98,6 +117,10 @@ def run_reference(ref, case, inputs, autocast_bf16=False):
     }
     for k, v in losses.items():
         res["loss_" + k] = v.detach().numpy()
+    if norm is not None:
+        res["d_pre_norm_w"] = norm.weight.grad.numpy()
+        if case.pre_norm != "rms":
+            res["d_pre_norm_b"] = norm.bias.grad.numpy()
     if case.separate_router_input:
         res["d_h_attn"] = h_attn.grad.numpy()
     # Bank gradient: dense in the reference; store the touched rows and check the rest is zero.
@@ -125,10 +148,11 @@ def main():
             continue
         inputs = make_inputs(case)
         res = run_reference(ref, case, inputs, autocast_bf16=False)
-        if name in ("head64_t64",):
+        if name in ("head64_t64", "block_rms"):
             bf = run_reference(ref, case, inputs, autocast_bf16=True)
-            for k in ("out", "d_h_router", "d_wq", "d_wk", "d_wv", "d_wo", "d_bank_touched"):
-                res["bf16_" + k] = bf[k]
+            for k in ("out", "d_h_router", "d_wq", "d_wk", "d_wv", "d_wo", "d_bank_touched", "d_pre_norm_w"):
+                if k in bf:
+                    res["bf16_" + k] = bf[k]
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **res)
         print(name, "indices", res["indices"].tolist(), "loss", float(res["loss"]),
               "size", os.path.getsize(os.path.join(HERE, name + ".npz")))

@@ -21,7 +21,7 @@ def test_library_builds_and_exports_every_declared_symbol():
         assert hasattr(handle, name), f"{name} declared in the header but not exported"
     for name in L.EXPORTED:
         assert name in declared, f"{name} bound in Python but not declared in the header"
-    assert handle.moc_abi_version() == 1
+    assert handle.moc_abi_version() == 2
 
 
 def test_host_side_argument_validation_without_a_gpu():

@@ -39,6 +39,10 @@ def test_layer_fp32_matches_reference_golden(name, dev):
              ("d_wq", "wq"), ("d_wk", "wk"), ("d_wv", "wv"), ("d_wo", "wo")]
     if case.separate_router_input:
         pairs.append(("d_h_attn", "h_attn"))
+    if case.pre_norm is not None:
+        pairs.append(("d_pre_norm_w", "pre_norm_w"))
+        if case.pre_norm != "rms":
+            pairs.append(("d_pre_norm_b", "pre_norm_b"))
     for g, p in pairs:
         assert rel_err(P[p].grad, torch.from_numpy(gold[g])) < FP32_BWD, g
     T = case.tokens_per_chapter
@@ -50,16 +54,20 @@ def test_layer_fp32_matches_reference_golden(name, dev):
     assert not bg[mask].any(), "bank gradient must be zero outside the touched chapters"
 
 
-def test_layer_bf16_matches_reference_golden(dev):
-    case = CASES["head64_t64"]
-    gold = load_gold("head64_t64")
+@pytest.mark.parametrize("name", ["head64_t64", "block_rms"])
+def test_layer_bf16_matches_reference_golden(name, dev):
+    case = CASES[name]
+    gold = load_gold(name)
     out, losses, info, P = run_layer_gpu(case, torch.bfloat16, dev)
     _status_ok(dev)
     assert np.array_equal(info["indices"].cpu().numpy(), gold["indices"])
     # against the fp32 reference and against the reference under bf16 autocast
     for prefix in ("", "bf16_"):
         assert rel_err(out, torch.from_numpy(gold[prefix + "out"])) < BF16
-        for g, p in (("d_h_router", "h_router"), ("d_wq", "wq"), ("d_wk", "wk"), ("d_wv", "wv"), ("d_wo", "wo")):
+        pairs = [("d_h_router", "h_router"), ("d_wq", "wq"), ("d_wk", "wk"), ("d_wv", "wv"), ("d_wo", "wo")]
+        if case.pre_norm is not None:
+            pairs.append(("d_pre_norm_w", "pre_norm_w"))
+        for g, p in pairs:
             assert rel_err(P[p].grad, torch.from_numpy(gold[prefix + g])) < BF16, prefix + g
     T = case.tokens_per_chapter
     rows = (gold["bank_touched_chapters"][:, None] * T + np.arange(T)[None]).reshape(-1)
@@ -318,3 +326,80 @@ def test_module_api_matches_reference_contract(dev):
                              attn.k_proj.weight.detach().cpu(), attn.v_proj.weight.detach().cpu(),
                              attn.o_proj.weight.detach().cpu(), 1, 1)
     assert rel_err(out2, ref2) < FP32_FWD
+
+
+@pytest.mark.parametrize("kind", ["rms", "layernorm"])
+@pytest.mark.parametrize("rows,dim", [(8192, 1024), (37, 1536), (5, 64)])
+def test_block_norm_matches_oracle(kind, rows, dim, dev):
+    """moc_norm_fwd / moc_norm_bwd against the restated RMSNorm / LayerNorm, residual gradient included;
+    row counts that do not fill a block and a width above one register chunk."""
+    from memory_b200 import ops
+    g = torch.Generator().manual_seed(rows + dim)
+    x = torch.randn(rows, dim, generator=g) * 1.7 + 0.3
+    w = 1.0 + 0.1 * torch.randn(dim, generator=g)
+    b = 0.1 * torch.randn(dim, generator=g) if kind == "layernorm" else None
+    dy = torch.randn(rows, dim, generator=g)
+    res = torch.randn(rows, dim, generator=g)
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    br = b.clone().requires_grad_(True) if b is not None else None
+    y_ref = O.block_norm(xr, wr, br, kind, 1e-6)
+    (y_ref * dy).sum().backward()
+    y, stats = ops.norm_fwd(x.to(dev), w.to(dev), None if b is None else b.to(dev), kind, 1e-6, torch.float32)
+    y16, _ = ops.norm_fwd(x.to(dev), w.to(dev), None if b is None else b.to(dev), kind, 1e-6, torch.bfloat16)
+    dx, dw, db = ops.norm_bwd(dy.to(dev), x.to(dev), w.to(dev), stats, res.to(dev), kind, b is not None)
+    assert rel_err(y, y_ref) < 1e-5
+    assert rel_err(y16, y_ref) < 1e-2
+    assert rel_err(dx, xr.grad + res) < 1e-4
+    assert rel_err(dw, wr.grad) < 1e-4
+    if b is not None:
+        assert rel_err(db, br.grad) < 1e-4
+    else:
+        assert db is None
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_projection_epilogue_adds_residual(dtype, dev):
+    """C = A B^T + residual, single pass and split over K, ragged edges."""
+    from memory_b200 import ops
+    g = torch.Generator().manual_seed(7)
+    m, n, k = 300, 200, 512
+    a = torch.randn(m, k, generator=g).to(dev)
+    b = (torch.randn(n, k, generator=g) * 0.05).to(dev)
+    r = torch.randn(m, n, generator=g).to(dev)
+    ref = a.to(dtype).float() @ b.to(dtype).float().T + r
+    tol = 1e-5 if dtype == torch.float32 else 1e-3
+    out = ops.gemm(a.to(dtype), b.to(dtype), out_dtype=torch.float32, residual=r)
+    assert rel_err(out, ref) < tol
+    if dtype == torch.bfloat16:
+        out = ops.gemm(a.to(dtype), b.to(dtype), out_dtype=torch.float32, residual=r, split_k=4)
+        assert rel_err(out, ref) < tol
+    _status_ok(dev)
+
+
+def test_memory_sub_block_module_matches_oracle(dev):
+    """The module form: state-dict names of the reference block's memory step, fp32 parity with the oracle."""
+    import memory_b200 as M
+    torch.manual_seed(3)
+    d, H, HK, n = 128, 4, 2, 96
+    for use_rms in (True, False):
+        blk = M.MemorySubBlock(d, H, num_kv_heads=HK, use_rms_norm=use_rms, wo_init_zero=False).to(dev)
+        with torch.no_grad():
+            blk.memory_layernorm.weight.add_(0.1 * torch.randn(d, device=dev))
+        keys = set(blk.state_dict())
+        assert {"memory_layernorm.weight", "memory_attn.q_proj.weight", "memory_attn.k_proj.weight",
+                "memory_attn.v_proj.weight", "memory_attn.o_proj.weight"} <= keys
+        h = torch.randn(2, 40, d, device=dev, requires_grad=True)
+        mem = (torch.randn(2, n, d, device=dev) * 0.5).requires_grad_(True)
+        out = blk(h, mem)
+        out.square().sum().backward()
+        sd = {k: v.detach().cpu() for k, v in blk.state_dict().items()}
+        hc, mc = h.detach().cpu().requires_grad_(True), mem.detach().cpu().requires_grad_(True)
+        ref = O.memory_sub_block(hc, mc, sd["memory_layernorm.weight"], sd.get("memory_layernorm.bias"),
+                                 "rms" if use_rms else "layernorm", blk.norm_eps, sd["memory_attn.q_proj.weight"],
+                                 sd["memory_attn.k_proj.weight"], sd["memory_attn.v_proj.weight"],
+                                 sd["memory_attn.o_proj.weight"], H, HK)
+        ref.square().sum().backward()
+        assert rel_err(out, ref) < FP32_FWD
+        assert rel_err(h.grad, hc.grad) < FP32_BWD
+        assert rel_err(mem.grad, mc.grad) < FP32_BWD
+    _status_ok(dev)

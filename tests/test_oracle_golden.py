@@ -15,7 +15,8 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 def shape_of(case):
     return O.LayerShape(case.hidden_dim, case.num_heads, case.num_kv_heads, case.num_chapters,
                         case.tokens_per_chapter, case.top_k, case.num_shared_chapters,
-                        case.routed_scaling_factor, case.norm_type, case.norm_eps)
+                        case.routed_scaling_factor, case.norm_type, case.norm_eps, case.pre_norm,
+                        case.pre_norm_eps)
 
 
 def run_oracle(case, autocast_bf16=False):
@@ -43,6 +44,9 @@ def test_oracle_matches_reference_fp32(name):
         np.testing.assert_allclose(res[k].numpy(), gold[k], rtol=1e-4, atol=2e-6, err_msg=k)
     if case.separate_router_input:
         np.testing.assert_allclose(res["d_h_attn"].numpy(), gold["d_h_attn"], rtol=1e-4, atol=2e-6)
+    for k in ("d_pre_norm_w", "d_pre_norm_b"):
+        if k in gold.files:
+            np.testing.assert_allclose(res[k].numpy(), gold[k], rtol=1e-4, atol=2e-6, err_msg=k)
     touched = gold["bank_touched_chapters"]
     T = case.tokens_per_chapter
     rows = (touched[:, None] * T + np.arange(T)[None, :]).reshape(-1)

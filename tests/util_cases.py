@@ -13,7 +13,8 @@ GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 def shape_of(case):
     return O.LayerShape(case.hidden_dim, case.num_heads, case.num_kv_heads, case.num_chapters,
                         case.tokens_per_chapter, case.top_k, case.num_shared_chapters,
-                        case.routed_scaling_factor, case.norm_type, case.norm_eps)
+                        case.routed_scaling_factor, case.norm_type, case.norm_eps, case.pre_norm,
+                        case.pre_norm_eps)
 
 
 def load_gold(name):
@@ -34,12 +35,19 @@ def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001):
     names = ("h_router", "bank", "router_w", "router_b", "wq", "wk", "wv", "wo")
     P = {k: inp[k].clone().requires_grad_(True) for k in names}
     P["h_attn"] = inp["h_attn"].clone().requires_grad_(True) if case.separate_router_input else P["h_router"]
+    extra = {}
+    if case.pre_norm is not None:
+        P["pre_norm_w"] = inp["pre_norm_w"].clone().requires_grad_(True)
+        if case.pre_norm != "rms":
+            P["pre_norm_b"] = inp["pre_norm_b"].clone().requires_grad_(True)
+        extra = dict(pre_norm=case.pre_norm, pre_norm_weight=P["pre_norm_w"], pre_norm_bias=P.get("pre_norm_b"),
+                     pre_norm_eps=case.pre_norm_eps, add_residual=True)
     out, losses, info = M.memory_layer(
         P["h_router"], P["h_attn"], P["bank"], P["router_w"], P["router_b"], P["wq"], P["wk"], P["wv"], P["wo"],
         num_heads=case.num_heads, num_kv_heads=case.num_kv_heads, tokens_per_chapter=case.tokens_per_chapter,
         top_k=case.top_k, num_shared_chapters=case.num_shared_chapters,
         routed_scaling_factor=case.routed_scaling_factor, norm_type=case.norm_type, norm_eps=case.norm_eps,
-        compute_dtype=compute_dtype)
+        compute_dtype=compute_dtype, **extra)
     loss = (out.float() * inp["d_out"]).sum() + lb * losses["load_balance"] + z * losses["z_loss"]
     loss.backward()
     return out, losses, info, P
