@@ -306,7 +306,7 @@ def time_dominant_kernels(cfg, device, iters=10):
         o, lse = ops.attn_fwd(q, kv, h, hk, dh ** -0.5)
         sets.append((q, kv, g, o, lse))
     bufs = (torch.empty_like(sets[0][0]), torch.empty_like(sets[0][1]),
-            torch.empty(2, b, h, l, dtype=torch.float32, device=device))
+            torch.empty(6, b, h, l, dtype=torch.float32, device=device))
     res = {}
 
     def timeit(fn):

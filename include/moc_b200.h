@@ -189,7 +189,8 @@ typedef struct {
 
 int moc_attn_fwd(const moc_attn_shape* s, const void* q, const void* kv, void* o, float* lse,
                  int32_t* status, void* stream);
-/* delta is scratch of 2*B*H*L floats.  d_q like q, d_kv like kv. */
+/* delta is scratch of 6*B*H*L floats, 16-byte aligned (per-row <O,dO>, rescaled log-sum-exp, and the packed
+ * bf16 rows the dK/dV kernel feeds to the tensor cores).  d_q like q, d_kv like kv. */
 int moc_attn_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
                  const void* d_o, void* d_q, void* d_kv, float* delta, int32_t* status, void* stream);
 
@@ -204,7 +205,7 @@ int moc_attn_bwd_parts(const moc_attn_shape* s, const void* q, const void* kv, c
  * reference.  It exists for callers that are not allowed to allocate device memory when they run the
  * backward pass (a serving process whose memory pool is frozen, a callback in which cudaMalloc is
  * forbidden, a host program whose allocator cannot be reached from C).  The delta / log-sum-exp scratch
- * lives in a fixed 4 MiB array inside the library image, so 2 * batch * num_heads * seq must not exceed
+ * lives in a fixed 4 MiB array inside the library image, so 6 * batch * num_heads * seq must not exceed
  * MOC_ATTN_BWD_STATIC_MAX_FLOATS; larger problems are rejected with MOC_ERR_INVALID.
  * The first call on each device looks the array's device address up (with that device current): make
  * that first call outside any stream capture.  All calls on a device share the one array: two calls

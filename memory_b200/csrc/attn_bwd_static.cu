@@ -1,6 +1,7 @@
 // Attention backward for callers that must not allocate device memory.
 //
-// moc_attn_bwd needs 2*B*H*L floats of scratch (the per-row <O,dO> sums and the rescaled log-sum-exp)
+// moc_attn_bwd needs 6*B*H*L floats of scratch (the per-row <O,dO> sums, the rescaled log-sum-exp and
+// their packed bf16 operand rows)
 // that the caller normally allocates.  Some callers cannot: code running while a CUDA memory pool is
 // frozen (a serving process that pre-sized its arena), code inside a library callback that forbids
 // cudaMalloc, or a process whose allocator is owned by another framework and is not reachable from
@@ -61,9 +62,9 @@ extern "C" int moc_attn_bwd_static(const moc_attn_shape* s, const void* q, const
   MOC_REQUIRE(s->num_heads > 0 && s->num_kv_heads > 0 && s->num_heads % s->num_kv_heads == 0,
               "num_heads must be a positive multiple of num_kv_heads");
   MOC_REQUIRE(q && kv && o && lse && d_o && d_q && d_kv && status, "NULL attention buffer");
-  const size_t need = size_t(2) * s->batch * s->num_heads * s->seq;
+  const size_t need = size_t(6) * s->batch * s->num_heads * s->seq;
   MOC_REQUIRE(need <= kStaticScratchFloats,
-              "2*batch*num_heads*seq exceeds the built-in scratch (1,048,576 floats): use moc_attn_bwd");
+              "6*batch*num_heads*seq exceeds the built-in scratch (1,048,576 floats): use moc_attn_bwd");
   float* scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);
   if (rc != MOC_OK) return rc;

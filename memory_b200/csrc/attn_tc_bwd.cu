@@ -30,11 +30,23 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Three bf16 terms whose sum is x to ~24 bits, so that a tensor-core product with ones reproduces x.
+__device__ __forceinline__ void split3_bf16(float x, uint32_t* t) {
+  const __nv_bfloat16 hi = __float2bfloat16(x);
+  const float r1 = x - __bfloat162float(hi);
+  const __nv_bfloat16 mid = __float2bfloat16(r1);
+  const __nv_bfloat16 lo = __float2bfloat16(r1 - __bfloat162float(mid));
+  t[0] = __bfloat16_as_ushort(hi); t[1] = __bfloat16_as_ushort(mid); t[2] = __bfloat16_as_ushort(lo);
+}
+
 // delta[b,h,l] = <O, dO>; nlse2[b,h,l] = -lse * log2(e).  One warp per (b, l) row: lanes read 16-byte
 // chunks of the H*64-wide row; a head is 8 chunks, reduced across 8 adjacent lanes.
+// statb[b,h,l] = eight bf16: three terms of -lse / scale, three terms of -delta, two zeros -- the per-query
+// operand row of the rank-16 products that add these per-column constants to S^T and dP^T in the dK/dV kernel.
 __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                 const float* __restrict__ lse, float* __restrict__ delta,
-                                float* __restrict__ nlse2, int B, int L, int H) {
+                                float* __restrict__ nlse2, uint4* __restrict__ statb, float inv_scale, int B, int L,
+                                int H) {
   const int lane = threadIdx.x & 31;
   const long long bl = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   if (bl >= static_cast<long long>(B) * L) return;
@@ -62,7 +74,12 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
       const int h = c >> 3;
       const long long idx = (static_cast<long long>(b) * H + h) * L + l;
       delta[idx] = acc;
-      nlse2[idx] = -lse[idx] * kLog2e;
+      const float ls = lse[idx];
+      nlse2[idx] = -ls * kLog2e;
+      uint32_t a[3], d[3];
+      split3_bf16(-ls * inv_scale, a);
+      split3_bf16(-acc, d);
+      statb[idx] = make_uint4(a[0] | (a[1] << 16), a[2] | (d[0] << 16), d[1] | (d[2] << 16), 0u);
     }
   }
 }
@@ -129,6 +146,60 @@ __device__ __forceinline__ void issue_ts_single(uint32_t d, uint32_t a, uint64_t
 #undef MOC_TS1_STEP
 }
 
+// One SS product over 4 K steps, A K-major, B K-major (BSTEP 2) or MN-major (BSTEP 128): [d] (+)= A * B.
+template <int BSTEP>
+__device__ __forceinline__ void issue_ss_one(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+#define MOC_SS1_STEP(KK, PACC)                                                                 \
+  "add.s64 ta, %1, " #KK "*2;\n\t add.s64 tb, %2, " #KK "*%5;\n\t"                              \
+  "@q tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, " PACC ";\n\t"
+  asm volatile(
+      "{\n\t.reg .pred q, pa, pt;\n\t.reg .b64 ta, tb;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.ne.b32 pa, %4, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      MOC_SS1_STEP(0, "pa") MOC_SS1_STEP(1, "pt") MOC_SS1_STEP(2, "pt") MOC_SS1_STEP(3, "pt")
+      "}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc), "n"(BSTEP)
+      : "memory");
+#undef MOC_SS1_STEP
+}
+// One accumulating SS MMA (a single K step of 16).
+__device__ __forceinline__ void issue_ss_k16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred q, pt;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pt;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc)
+      : "memory");
+}
+// Shared-memory descriptor of a K-major operand without swizzle: 8-row x 16-byte core matrices, `lbo` bytes
+// between the two core matrices of a K step, `sbo` bytes between 8-row groups.
+__device__ __forceinline__ uint64_t umma_desc_plain(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  return d;
+}
+// One TS product with MN-major B, A K step kk at column a + (kk >> 1) * a_hi + (kk & 1) * 8: [d] += A * B.
+__device__ __forceinline__ void issue_ts_one_hi(uint32_t d, uint32_t a, uint32_t a_hi, uint64_t b, uint32_t idesc,
+                                                uint32_t acc) {
+#define MOC_TSH_STEP(KK, HI, LO, PACC)                                                         \
+  "mad.lo.u32 ca, %2, " #HI ", %1;\n\t add.u32 ca, ca, " #LO ";\n\t add.s64 tb, %3, " #KK "*128;\n\t" \
+  "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [ca], tb, %4, " PACC ";\n\t"
+  asm volatile(
+      "{\n\t.reg .pred q, pa, pt;\n\t.reg .b64 tb;\n\t.reg .b32 ca;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.ne.b32 pa, %5, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      MOC_TSH_STEP(0, 0, 0, "pa") MOC_TSH_STEP(1, 0, 8, "pt") MOC_TSH_STEP(2, 1, 0, "pt") MOC_TSH_STEP(3, 1, 8, "pt")
+      "}"
+      ::"r"(d), "r"(a), "r"(a_hi), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+#undef MOC_TSH_STEP
+}
 // ------------------------------------------------------------------------------------------------
 // dQ
 // ------------------------------------------------------------------------------------------------
@@ -313,16 +384,17 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 constexpr int kKeysB = 128, kQB = 64;
 constexpr int kKBytes = kKeysB * kD * 2;     // 16 KiB (K and V tiles, stationary)
 constexpr int kQTileBytes = kQB * kD * 2;    // 8 KiB (Q and dO tiles, streamed)
-constexpr int kStatBytes = kQB * 4;          // 256 B (nlse2 and delta rows, streamed)
+constexpr int kStatBytes = kQB * 16;         // 1 KiB: the 16-byte constant row of each query, streamed
 constexpr int kStageB = 2 * kQTileBytes;      // tile ring stride (keeps every tile 1024-byte aligned)
-constexpr int kStageTx = kStageB + 2 * kStatBytes;
-constexpr int kDkvSmem = 2 * kKBytes + kStages * kStageB + kStages * 2 * kStatBytes + 1024;
-constexpr uint32_t kColST = 0, kColDPT = 64, kColDV = 128, kColDK = 192;   // P^T / dS^T alias the first two
+constexpr int kStageTx = kStageB + kStatBytes;
+constexpr int kPtBytes = kKeysB * kQB * 2;   // 16 KiB: P^T tile, the A operand of the dV product
+constexpr int kOnesBytes = kKeysB * 16;      // 2 KiB: a 128 x 8 selector operand / its zero second half
+constexpr int kDkvSmem = 2 * kKBytes + kStages * kStageB + kPtBytes + kStages * kStatBytes + 3 * kOnesBytes + 1024;
+constexpr uint32_t kColST = 0, kColDPT = 64, kColDV = 128, kColDK = 192;   // dS^T aliases dP^T
 
 struct DkvParams {
   __nv_bfloat16* d_kv;
-  const float* delta;
-  const float* nlse2;
+  const uint4* statb;
   int L, n_sel, H, HK;
   float scale, scale_log2;
   int* status;
@@ -334,11 +406,20 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
                : "memory");
 }
 
+// Software pipeline over the query tiles j of one CTA (tensor memory: S^T, dP^T, dV, dK, 64 columns each):
+//   MMA warp :  S^T_{j+1} = K Q_{j+1}^T   as soon as the row owners hold S^T_j in registers
+//               dV += P^T_j dO_j          A = P^T_j from shared memory (written by the row owners)
+//               dK += dS^T_j Q_j          A = dS^T_j from tensor memory, over dP^T_j's columns
+//               dP^T_{j+1} = V dO_{j+1}^T after dK_j in issue order, because it overwrites dS^T_j
+//   row owners: P^T_j = exp2(S^T_j c - lse c) -> shared memory;  dS^T_j = P^T_j (dP^T_j - delta) -> tensor memory
+// so the exponentials of tile j run while the tensor pipe computes S^T_{j+1}, dV_{j-1}... and neither side
+// waits for the other in steady state.  P^T lives in shared memory so that S^T's columns are free early.
 __global__ void __launch_bounds__(kThreads, 2)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                        const __grid_constant__ CUtensorMap tmap_kv, DkvParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t k_bar, q_full[kStages], q_empty[kStages], sdp_full, pt_full, acc_bar;
+  __shared__ __align__(8) uint64_t k_bar, q_full[kStages], q_empty[kStages], s_full, s_free, dp_full, p_full, p_free,
+      ds_full, acc_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -346,7 +427,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   uint8_t* k_s = base;
   uint8_t* v_s = base + kKBytes;
   uint8_t* ring = base + 2 * kKBytes;
-  uint8_t* stats = ring + kStages * kStageB;
+  uint8_t* pt_s = ring + kStages * kStageB;
+  uint8_t* stats = pt_s + kPtBytes;                  // kStages x 64 rows of 16 bytes
+  uint8_t* sel_s = stats + kStages * kStatBytes;     // 128 rows (1,1,1,0,0,0,0,0): picks the -lse terms
+  uint8_t* sel_d = sel_s + kOnesBytes;               // 128 rows (0,0,0,1,1,1,0,0): picks the -delta terms
+  uint8_t* zeros = sel_d + kOnesBytes;               // second half of every rank-16 operand
   const int key0 = blockIdx.x * kKeysB, kh = blockIdx.y, b = blockIdx.z;
   const int G = p.H / p.HK;
   const int q_tiles = p.L / kQB;
@@ -356,12 +441,22 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     abort_flag = 0;
     mbar_init(&k_bar, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
-    mbar_init(&sdp_full, 1);
-    mbar_init(&pt_full, 256);
+    mbar_init(&s_full, 1);
+    mbar_init(&s_free, 256);
+    mbar_init(&dp_full, 1);
+    mbar_init(&p_full, 256);
+    mbar_init(&p_free, 1);
+    mbar_init(&ds_full, 256);
     mbar_init(&acc_bar, 1);
     fence_mbar_init();
     prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_kv);
   }
+  if (threadIdx.x < kKeysB) {
+    reinterpret_cast<uint4*>(sel_s)[threadIdx.x] = make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u);
+    reinterpret_cast<uint4*>(sel_d)[threadIdx.x] = make_uint4(0u, 0x3F800000u, 0x3F803F80u, 0u);
+    reinterpret_cast<uint4*>(zeros)[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  fence_proxy_async();
   if (warp == 9) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); tc_fence_before(); }
   __syncthreads();
   tc_fence_after();
@@ -384,8 +479,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         tma_load_2d(st, &tmap_q, &q_full[s], h * kD, b * p.L + l0);
         tma_load_2d(st + kQTileBytes, &tmap_do, &q_full[s], h * kD, b * p.L + l0);
         const long long soff = (static_cast<long long>(b) * p.H + h) * p.L + l0;
-        bulk_load_1d(stats + s * 2 * kStatBytes, p.nlse2 + soff, kStatBytes, &q_full[s]);
-        bulk_load_1d(stats + s * 2 * kStatBytes + kStatBytes, p.delta + soff, kStatBytes, &q_full[s]);
+        bulk_load_1d(stats + s * kStatBytes, p.statb + soff, kStatBytes, &q_full[s]);
       }
     }
   } else if (warp == 9) {
@@ -395,27 +489,62 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       // descriptors are built once; a stage or K step only adds a constant to the address field
       const uint64_t k_desc = umma_desc_sw128(smem_u32(k_s), 16, 1024);
       const uint64_t v_desc = umma_desc_sw128(smem_u32(v_s), 16, 1024);
+      const uint64_t pt_desc = umma_desc_sw128(smem_u32(pt_s), 16, 1024);                      // P^T, K-major
       const uint64_t q_desc0 = umma_desc_sw128(smem_u32(ring), 16, 1024);                      // Q tile, K-major
       const uint64_t do_desc0 = umma_desc_sw128(smem_u32(ring) + kQTileBytes, 16, 1024);       // dO tile, K-major
       const uint64_t qmn_desc0 = umma_desc_sw128(smem_u32(ring), 8192, 1024);                  // Q tile, MN-major
       const uint64_t domn_desc0 = umma_desc_sw128(smem_u32(ring) + kQTileBytes, 8192, 1024);   // dO tile, MN-major
+      // rank-16 products that add the per-query constants: D[key, q] += sum_k sel[key, k] * stat[q, k]
+      const uint64_t sel_s_desc = umma_desc_plain(smem_u32(sel_s), smem_u32(zeros) - smem_u32(sel_s), 128);
+      const uint64_t sel_d_desc = umma_desc_plain(smem_u32(sel_d), smem_u32(zeros) - smem_u32(sel_d), 128);
+      const uint64_t stat_desc0 = umma_desc_plain(smem_u32(stats), smem_u32(zeros) - smem_u32(stats), 128);
       constexpr uint64_t kStageOff = kStageB >> 4;
+      constexpr uint64_t kStatOff = kStatBytes >> 4;
+      // the zero block is addressed relative to each stage's constant rows
+      constexpr uint64_t kStatLboStep = static_cast<uint64_t>(kStatBytes >> 4) << 16;
       bool ok = mbar_wait_w(&k_bar, 0, &abort_flag, p.status);
+      if (ok && n_iter > 0) {
+        ok = mbar_wait_w(&q_full[0], 0, &abort_flag, p.status);
+        if (ok) {
+          tc_fence_after();
+          issue_ss_pair(tmem + kColST, tmem + kColDPT, k_desc, q_desc0, v_desc, do_desc0, idesc_s);
+          issue_ss_k16(tmem + kColST, sel_s_desc, stat_desc0, idesc_s);
+          issue_ss_k16(tmem + kColDPT, sel_d_desc, stat_desc0, idesc_s);
+          tc_commit_w(&s_full);
+          tc_commit_w(&dp_full);
+        }
+      }
       for (int it = 0; it < n_iter && ok; ++it) {
         const int s = it % kStages;
-        ok = mbar_wait_w(&q_full[s], (it / kStages) & 1, &abort_flag, p.status);
+        const bool more = it + 1 < n_iter;
+        const int sn = (it + 1) % kStages;
+        if (more) {
+          ok = mbar_wait_w(&q_full[sn], ((it + 1) / kStages) & 1, &abort_flag, p.status);
+          if (!ok) break;
+          ok = mbar_wait_w(&s_free, it & 1, &abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          issue_ss_one<2>(tmem + kColST, k_desc, q_desc0 + sn * kStageOff, idesc_s, 0u);
+          issue_ss_k16(tmem + kColST, sel_s_desc, stat_desc0 + sn * kStatOff - sn * kStatLboStep, idesc_s);
+          tc_commit_w(&s_full);
+        }
+        ok = mbar_wait_w(&p_full, it & 1, &abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
-        issue_ss_pair(tmem + kColST, tmem + kColDPT, k_desc, q_desc0 + s * kStageOff, v_desc, do_desc0 + s * kStageOff,
-                      idesc_s);
-        tc_commit_w(&sdp_full);
-        ok = mbar_wait_w(&pt_full, it & 1, &abort_flag, p.status);
+        issue_ss_one<128>(tmem + kColDV, pt_desc, domn_desc0 + s * kStageOff, idesc_g, it > 0 ? 1u : 0u);
+        tc_commit_w(&p_free);
+        ok = mbar_wait_w(&ds_full, it & 1, &abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
-        // P^T / dS^T for queries [32g, 32g+32) sit in the first 16 columns of column half g
-        issue_ts_pair(tmem + kColDV, tmem + kColDK, tmem + kColST, tmem + kColDPT, 32, domn_desc0 + s * kStageOff,
-                      qmn_desc0 + s * kStageOff, idesc_g, it > 0 ? 1u : 0u);
+        // dS^T for queries [32g, 32g+32) sits in the first 16 columns of column half g of dP^T
+        issue_ts_one_hi(tmem + kColDK, tmem + kColDPT, 32, qmn_desc0 + s * kStageOff, idesc_g, it > 0 ? 1u : 0u);
         tc_commit_w(&q_empty[s]);
+        if (more) {
+          // strictly after dK_j: the first K step already overwrites all of dS^T_j's columns
+          issue_ss_one<2>(tmem + kColDPT, v_desc, do_desc0 + sn * kStageOff, idesc_s, 0u);
+          issue_ss_k16(tmem + kColDPT, sel_d_desc, stat_desc0 + sn * kStatOff - sn * kStatLboStep, idesc_s);
+          tc_commit_w(&dp_full);
+        }
       }
       tc_commit_w(&acc_bar);
     }
@@ -423,41 +552,61 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const int half = warp >> 2;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int row = (warp & 3) * 32 + lane;
+    // this thread's 64 bytes of P^T row `row`: 16-byte chunks 4*half .. 4*half+3 under the 128-byte swizzle
+    const uint32_t pt_row = smem_u32(pt_s) + row * 128;
+    const uint32_t sw = static_cast<uint32_t>(row & 7);
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int s = it % kStages;
-      ok = mbar_wait(&sdp_full, it & 1, &abort_flag, p.status);
+      ok = mbar_wait(&s_full, it & 1, &abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const float4* nl4 = reinterpret_cast<const float4*>(stats + s * 2 * kStatBytes) + half * 8;
-      const float4* dl4 = nl4 + kQB / 4;
-      uint32_t pp[16], pd[16];
+      float pf[32];
       {
-        uint32_t rs[32], rd[32];
+        uint32_t rs[32];
         tmem_ld32(tmem + lane_sel + kColST + half * 32, rs);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&s_free);          // S^T_j is in registers: its columns may take S^T_{j+1}
+        // the tensor core already added -lse / scale to every column
+#pragma unroll
+        for (int c = 0; c < 32; ++c) pf[c] = ex2(__uint_as_float(rs[c]) * p.scale_log2);
+      }
+      if (it > 0) {
+        ok = mbar_wait(&p_free, (it - 1) & 1, &abort_flag, p.status);   // dV_{j-1} has read the P^T tile
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t addr = pt_row + (((static_cast<uint32_t>(half) * 4 + c) ^ sw) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                     "r"(pack_bf16x2(pf[8 * c + 0], pf[8 * c + 1])), "r"(pack_bf16x2(pf[8 * c + 2], pf[8 * c + 3])),
+                     "r"(pack_bf16x2(pf[8 * c + 4], pf[8 * c + 5])), "r"(pack_bf16x2(pf[8 * c + 6], pf[8 * c + 7]))
+                     : "memory");
+      }
+      fence_proxy_async();
+      mbar_arrive(&p_full);
+      ok = mbar_wait(&dp_full, it & 1, &abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        uint32_t rd[32], pd[16];
         tmem_ld32(tmem + lane_sel + kColDPT + half * 32, rd);
         tmem_wait_ld();
+        // dS^T = P^T (dP^T - delta) without the softmax scale (applied once when dK is written); the
+        // tensor core already subtracted delta from every column
 #pragma unroll
-        for (int c = 0; c < 32; c += 4) {
-          const float4 n = nl4[c / 4], d = dl4[c / 4];
-          const float p0 = ex2(fmaf(__uint_as_float(rs[c + 0]), p.scale_log2, n.x));
-          const float p1 = ex2(fmaf(__uint_as_float(rs[c + 1]), p.scale_log2, n.y));
-          const float p2 = ex2(fmaf(__uint_as_float(rs[c + 2]), p.scale_log2, n.z));
-          const float p3 = ex2(fmaf(__uint_as_float(rs[c + 3]), p.scale_log2, n.w));
-          pp[c / 2] = pack_bf16x2(p0, p1);
-          pp[c / 2 + 1] = pack_bf16x2(p2, p3);
-          // dS^T without the softmax scale: it is applied once when dK is written
-          pd[c / 2] = pack_bf16x2(p0 * (__uint_as_float(rd[c + 0]) - d.x), p1 * (__uint_as_float(rd[c + 1]) - d.y));
-          pd[c / 2 + 1] = pack_bf16x2(p2 * (__uint_as_float(rd[c + 2]) - d.z), p3 * (__uint_as_float(rd[c + 3]) - d.w));
-        }
+        for (int c = 0; c < 32; c += 2)
+          pd[c / 2] = pack_bf16x2(pf[c] * __uint_as_float(rd[c]), pf[c + 1] * __uint_as_float(rd[c + 1]));
+        // this thread has read every fp32 value of its row in this column half: overwrite its first 16 columns
+        tmem_st16(tmem + lane_sel + kColDPT + half * 32, pd);
+        tmem_wait_st();
       }
-      // this thread has read every fp32 value of its row in this column half: overwrite its first 16 columns
-      tmem_st16(tmem + lane_sel + kColST + half * 32, pp);
-      tmem_st16(tmem + lane_sel + kColDPT + half * 32, pd);
-      tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&pt_full);
+      mbar_arrive(&ds_full);
     }
     if (ok) {
       ok = mbar_wait(&acc_bar, 0, &abort_flag, p.status);
@@ -505,11 +654,14 @@ int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, c
   const int B = s->batch, L = s->seq, H = s->num_heads, HK = s->num_kv_heads;
   float* delta = scratch;
   float* nlse2 = scratch + static_cast<long long>(B) * H * L;
+  uint4* statb = reinterpret_cast<uint4*>(scratch + 2ll * B * H * L);
+  MOC_REQUIRE((reinterpret_cast<uintptr_t>(statb) & 15) == 0, "attention backward scratch must be 16-byte aligned");
   if (parts & 1) {
     const long long total = static_cast<long long>(B) * L;
     const int blocks = static_cast<int>((total * 32 + 255) / 256);
     bwd_prep_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(o),
-                                                static_cast<const __nv_bfloat16*>(d_o), lse, delta, nlse2, B, L, H);
+                                                static_cast<const __nv_bfloat16*>(d_o), lse, delta, nlse2, statb,
+                                                1.0f / s->scale, B, L, H);
   }
   CUtensorMap tq128, tdo128, tq64, tdo64, tkv;
   const uint64_t qrows = static_cast<uint64_t>(B) * L, qcols = static_cast<uint64_t>(H) * kD;
@@ -532,7 +684,7 @@ int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, c
   }
   if (parts & 4) {
     DkvParams p;
-    p.d_kv = static_cast<__nv_bfloat16*>(d_kv); p.delta = delta; p.nlse2 = nlse2;
+    p.d_kv = static_cast<__nv_bfloat16*>(d_kv); p.statb = statb;
     p.L = L; p.n_sel = s->n_sel; p.H = H; p.HK = HK;
     p.scale = s->scale; p.scale_log2 = s->scale * kLog2e; p.status = status;
     dim3 grid(ceil_div(s->n_sel, kKeysB), HK, B);

@@ -284,6 +284,187 @@ def cross_attention(h: torch.Tensor, memory: torch.Tensor, wq, wk, wv, wo, num_h
 
 
 # --------------------------------------------------------------------------------------------
+# the whole layer as one node with two streams (bf16 path)
+# --------------------------------------------------------------------------------------------
+_side_streams: Dict[int, "torch.cuda.Stream"] = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _side_streams:
+        _side_streams[idx] = torch.cuda.Stream(device=device)
+    return _side_streams[idx]
+
+
+class _MemoryLayerTwoStream(torch.autograd.Function):
+    """Router, gather, projections and attention of one layer as a single autograd node, so that the
+    bandwidth- and latency-bound kernels (router, chapter bookkeeping, gather backward) run on a second
+    stream beside the tensor-core kernels instead of in front of or behind them:
+
+      forward   side: router, chapter segments      | main: weight pack, (norm,) query projection
+                join, then gather, K/V projection, attention, output projection on main
+      backward  main: dO projection, attention backward, memory-row gradient, bank / chapter-weight
+                gradients, router backward           | side: the four weight-gradient and the hidden-state
+                                                       projections, normalisation backward
+
+    Both streams fork from and join the caller's stream with events, which a CUDA-graph capture records as
+    ordinary dependencies.  Every tensor that crosses streams stays referenced until after the join.
+    """
+
+    @staticmethod
+    def forward(ctx, h_router, h_attn, bank, router_w, router_b, wq, wk, wv, wo, norm_w, norm_b, cfg, sink):
+        (num_heads, num_kv_heads, t, top_k, num_shared, routed_scale, row_norm, row_eps, with_losses,
+         pre_norm, pre_eps, add_residual) = cfg
+        cd = torch.bfloat16
+        dev = h_attn.device
+        b, l, d = h_attn.shape
+        dkv = wk.shape[0]
+        main, side = torch.cuda.current_stream(dev), _side_stream(dev)
+        num_chapters = bank.shape[0] // t
+
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            r = ops.router_fwd(h_router, router_w, router_b, top_k, num_shared, routed_scale, with_losses)
+            seg = ops.chapter_segments(r["comb_idx"], num_chapters)
+
+        # main stream meanwhile: bf16 weights (+ transposes for the backward pass), query projection
+        need_t = any(ctx.needs_input_grad[:11])
+        w_all = torch.empty(2 * d + 2 * dkv, d, dtype=cd, device=dev)
+        wq_c, wkv_c, wo_c = w_all[:d], w_all[d:d + 2 * dkv], w_all[d + 2 * dkv:]
+        wq_t = torch.empty(d, d, dtype=cd, device=dev) if need_t else None
+        wkv_t = torch.empty(d, 2 * dkv, dtype=cd, device=dev) if need_t else None
+        wo_t = torch.empty(d, d, dtype=cd, device=dev) if need_t else None
+        ops.pack_weights([wq, wk, wv, wo], [wq_c, wkv_c[:dkv], wkv_c[dkv:], wo_c],
+                         [wq_t, wkv_t, wkv_t[:, dkv:] if need_t else None, wo_t], [0, 2 * dkv, 2 * dkv, 0])
+        x2 = h_attn.reshape(b * l, d)
+        stats_n = None
+        if pre_norm is not None:
+            x2 = x2.float()
+            h2, stats_n = ops.norm_fwd(x2, norm_w.float(), None if norm_b is None else norm_b.float(), pre_norm,
+                                       pre_eps, cd)
+        else:
+            h2 = ops.cast(x2, cd)
+        q = ops.gemm(h2, wq_c, tag="q_proj")
+
+        main.wait_stream(side)
+        k_sel = r["idx"].shape[1]
+        # the reference only normalises when both a shared and a routed slice exist (model.py:413-418)
+        norm = row_norm if (num_shared > 0 and k_sel > 0) else None
+        memory, stats_m = ops.gather_rows_fwd(bank, t, r["comb_idx"], r["comb_w"], norm, row_eps, cd)
+        n_sel = memory.shape[-2]
+        m2 = memory.reshape(-1, d)
+        kv = ops.gemm(m2, wkv_c, tag="kv_proj").view(b, n_sel, -1)
+        scale = (d // num_heads) ** -0.5
+        o, lse = ops.attn_fwd(q.view(b, l, -1), kv, num_heads, num_kv_heads, scale)
+        res = (x2 if x2.dtype == torch.float32 else x2.float()) if add_residual else None
+        out_dtype = h_attn.dtype if h_attn.dtype in (torch.float32, cd) else cd
+        out = ops.gemm(o.view(b * l, -1), wo_c, out_dtype=out_dtype, residual=res, tag="o_proj")
+
+        ctx.cfg = cfg
+        ctx.norm_row = norm
+        ctx.scale = scale
+        ctx.router_saved = r
+        ctx.seg = seg
+        ctx.sink = sink
+        ctx.same_h = h_router is h_attn
+        ctx.shapes = (tuple(h_router.shape), h_router.dtype, h_attn.dtype, router_b is not None,
+                      (wq.dtype, wk.dtype, wv.dtype, wo.dtype), None if norm_w is None else norm_w.dtype,
+                      None if norm_b is None else norm_b.dtype)
+        ctx.wt = (wq_t, wkv_t, wo_t)
+        ctx.save_for_backward(h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse, bank, router_w, stats_m,
+                              x2 if pre_norm is not None else None, stats_n,
+                              norm_w.float() if pre_norm is not None else None)
+        ctx.mark_non_differentiable(r["idx"], r["comb_idx"])
+        losses = r["losses"] if with_losses else torch.zeros(4, dtype=torch.float32, device=dev)
+        return out.view(b, l, -1).to(h_attn.dtype), r["idx"], r["weights"], r["comb_idx"], r["comb_w"], losses
+
+    @staticmethod
+    def backward(ctx, g, _g_idx, g_w, _g_cidx, g_cw, g_losses):
+        (h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse, bank, router_w, stats_m, x2, stats_n,
+         norm_w) = ctx.saved_tensors
+        (num_heads, num_kv_heads, t, top_k, num_shared, routed_scale, _row_norm, row_eps, _with_losses,
+         pre_norm, _pre_eps, add_residual) = ctx.cfg
+        hr_shape, hr_dtype, ha_dtype, has_rbias, wdt, nw_dtype, nb_dtype = ctx.shapes
+        wq_t, wkv_t, wo_t = ctx.wt
+        r, seg = ctx.router_saved, ctx.seg
+        cd, f32 = torch.bfloat16, torch.float32
+        dev = q.device
+        b, l, _ = o.shape
+        d = h2.shape[1]
+        main, side = torch.cuda.current_stream(dev), _side_stream(dev)
+        need = ctx.needs_input_grad
+        num_chapters = bank.shape[0] // t
+
+        def splits(rows, out_rows, out_cols):
+            tiles = -(-out_rows // 128) * -(-out_cols // 256)
+            return max(1, min(148 // max(tiles, 1), rows // 512))
+
+        g2f = g.reshape(b * l, -1)
+        g2 = ops.cast(g2f.contiguous(), cd)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            d_wo = ops.gemm(g2, o.view(b * l, -1), a_kmajor=False, b_kmajor=False, out_dtype=f32,
+                            split_k=splits(b * l, d, d), tag="d_wo")
+        d_o = ops.gemm(g2, wo_t, tag="d_attn_out")
+        d_q, d_kv = ops.attn_bwd(q.view(b, l, -1), kv, o, lse, d_o.view(b, l, -1), num_heads, num_kv_heads,
+                                 ctx.scale)
+        d_q2 = d_q.view(b * l, -1)
+        d_kv2 = d_kv.view(-1, d_kv.shape[-1])
+
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            d_wq = ops.gemm(d_q2, h2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=splits(b * l, d, d),
+                            tag="d_wq")
+            # gradient of the (normalised) attention input, in the hidden-state dtype so that the router's
+            # gradient can be added into it
+            d_h = ops.gemm(d_q2, wq_t, out_dtype=f32 if (pre_norm is not None or ha_dtype == f32) else cd, tag="d_h")
+            d_nw = d_nb = None
+            g_res = g2f if add_residual else None
+            if pre_norm is not None:
+                d_h, d_nw, d_nb = ops.norm_bwd(d_h, x2, norm_w, stats_n, None if g_res is None else g_res.float(),
+                                               pre_norm, nb_dtype is not None)
+                d_nw = d_nw.to(nw_dtype)
+                d_nb = None if d_nb is None else d_nb.to(nb_dtype)
+            elif add_residual:
+                d_h = d_h.float() + g_res.float()
+            d_h = d_h.view(b, l, d).to(ha_dtype)
+            d_wkv = ops.gemm(d_kv2, m2, a_kmajor=False, b_kmajor=False, out_dtype=f32,
+                             split_k=splits(d_kv2.shape[0], wkv_c.shape[0], d), tag="d_wkv")
+
+        d_mem = ops.gemm(d_kv2, wkv_t, tag="d_mem")
+        want_bank = need[2]
+        d_cw, rows = ops.gather_rows_bwd(d_mem, bank, t, r["comb_idx"], r["comb_w"], ctx.norm_row, row_eps, stats_m,
+                                         seg, want_dw=True, want_bank=want_bank)
+        d_bank = None
+        if want_bank:
+            if ctx.sink is not None:
+                ctx.sink.add(seg["uniq"], seg["num_unique"], rows, t)
+            else:
+                d_bank = torch.zeros(bank.shape, dtype=f32, device=dev)
+                ops.scatter_bank_grad(rows, seg, t, d_bank)
+                d_bank = d_bank.to(bank.dtype)
+        if g_cw is not None:
+            d_cw = d_cw + g_cw.float()
+        fuse_dh = ctx.same_h and need[0] and hr_dtype == ha_dtype
+        if fuse_dh:
+            main.wait_stream(side)      # the attention branch's d_h must be complete before the router adds to it
+        rb = ops.router_bwd(hr_shape, hr_dtype, router_w, r, top_k, num_shared, routed_scale,
+                            None if g_w is None else g_w.float(), d_cw,
+                            None if g_losses is None else g_losses.float(), want_dh=need[0],
+                            d_h_accum=d_h if fuse_dh else None)
+        main.wait_stream(side)
+        d_rw = rb["d_w"].to(router_w.dtype) if need[3] else None
+        d_rb = rb["d_bias"] if (has_rbias and need[4]) else None
+        dkv_dim = wkv_c.shape[0] // 2
+        if fuse_dh:
+            d_hr, d_ha = rb["d_h"], None
+        else:
+            d_hr, d_ha = rb["d_h"], d_h
+        return (d_hr, d_ha, d_bank, d_rw, d_rb, d_wq.to(wdt[0]), d_wkv[:dkv_dim].to(wdt[1]),
+                d_wkv[dkv_dim:].to(wdt[2]), d_wo.to(wdt[3]), d_nw, d_nb, None, None)
+
+
+# --------------------------------------------------------------------------------------------
 # the fused layer
 # --------------------------------------------------------------------------------------------
 def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tensor,
@@ -293,15 +474,35 @@ def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tenso
                  norm_type: Optional[str] = None, norm_eps: float = 1e-5, with_losses: bool = True,
                  compute_dtype: Optional[torch.dtype] = None, pre_norm: Optional[str] = None,
                  pre_norm_weight: Optional[torch.Tensor] = None, pre_norm_bias: Optional[torch.Tensor] = None,
-                 pre_norm_eps: float = 1e-6,
-                 add_residual: bool = False) -> Tuple[torch.Tensor, Dict[str, torch.Tensor], Dict]:
+                 pre_norm_eps: float = 1e-6, add_residual: bool = False,
+                 two_stream: bool = True) -> Tuple[torch.Tensor, Dict[str, torch.Tensor], Dict]:
     """Sequence-level Mixture-of-Chapters memory layer on the GPU.
 
     Returns (out [B,L,d], router losses, info) with info = indices / weights of the routing.
     ``norm_type`` normalises the gathered bank rows; ``pre_norm`` / ``add_residual`` wrap the attention as
-    h_attn + attn(pre_norm(h_attn), memory) (see :func:`cross_attention`).
+    h_attn + attn(pre_norm(h_attn), memory) (see :func:`cross_attention`).  With bf16 compute the layer runs as
+    one autograd node that overlaps its small kernels with the tensor-core kernels on a second stream
+    (``two_stream=False`` chains the three separate nodes instead; results are the same).
     """
     cd = compute_dtype or h_attn.dtype
+    if (cd == torch.bfloat16 and two_stream and wq.dtype == wk.dtype == wv.dtype == wo.dtype
+            and bank.shape[1] == h_attn.shape[-1]):
+        cfg = (int(num_heads), int(num_kv_heads or num_heads), int(tokens_per_chapter), int(top_k),
+               int(num_shared_chapters), float(routed_scaling_factor), norm_type, float(norm_eps), bool(with_losses),
+               pre_norm, float(pre_norm_eps), bool(add_residual))
+        if pre_norm is not None and pre_norm not in ops.NORM_KINDS:
+            raise ValueError(f"unknown pre_norm {pre_norm!r}")
+        if pre_norm in ("rms", "rmsnorm"):
+            pre_norm_bias = None
+        out, idx, w, cidx, cw, lv = _MemoryLayerTwoStream.apply(
+            h_router, h_attn, bank, router_weight, router_bias, wq, wk, wv, wo,
+            pre_norm_weight if pre_norm else None, pre_norm_bias if pre_norm else None, cfg,
+            getattr(bank, "moc_sparse_grad", None))
+        losses = {}
+        if with_losses:
+            losses = _LossDict({k: lv[i] for i, k in enumerate(LOSS_KEYS)})
+            losses.vector = lv
+        return out, losses, {"indices": idx, "weights": w, "combined_indices": cidx, "combined_weights": cw}
     idx, w, cidx, cw, losses = route(h_router, router_weight, router_bias, top_k, num_shared_chapters,
                                      routed_scaling_factor, with_losses)
     k_sel = idx.shape[1]

@@ -39,7 +39,7 @@ def main():
     wkv = (torch.randn(2 * d, d, device=dev) * 0.02).bfloat16()
     wq = (torch.randn(d, d, device=dev) * 0.02).bfloat16()
     o, lse = ops.attn_fwd(q, kv, h, h, dh ** -0.5)
-    bufs = (torch.empty_like(q), torch.empty_like(kv), torch.empty(2, b, h, l, dtype=torch.float32, device=dev))
+    bufs = (torch.empty_like(q), torch.empty_like(kv), torch.empty(6, b, h, l, dtype=torch.float32, device=dev))
     ops.attn_bwd(q, kv, o, lse, g, h, h, dh ** -0.5, parts=1, buffers=bufs)
     unit = 2.0 * b * l * n_sel * d
     kv2 = kv.view(b * n_sel, 2 * d)

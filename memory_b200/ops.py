@@ -96,7 +96,9 @@ def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
 def router_bwd(h_shape, h_dtype, weight: torch.Tensor, saved: Dict[str, torch.Tensor], top_k: int,
                num_shared: int, routed_scale: float, d_weights: Optional[torch.Tensor],
                d_comb_w: Optional[torch.Tensor], d_losses: Optional[torch.Tensor],
-               want_dh: bool) -> Dict[str, torch.Tensor]:
+               want_dh: bool, d_h_accum: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
+    """``d_h_accum`` ([B, L, d] of the hidden-state dtype): the hidden-state gradient is added into it instead
+    of being written to a fresh tensor (the attention branch's gradient of the same hidden states)."""
     b, l, d = h_shape
     c = weight.shape[0]
     dev = weight.device
@@ -106,6 +108,11 @@ def router_bwd(h_shape, h_dtype, weight: torch.Tensor, saved: Dict[str, torch.Te
     out = {"d_logits": torch.empty(b, c, **f32), "d_w": torch.empty(c, d, **f32), "d_bias": torch.empty(c, **f32),
            "d_pooled": torch.empty(b, d, **f32),
            "d_h": torch.empty(b, l, d, dtype=h_dtype, device=dev) if want_dh else None}
+    accumulate = 0
+    if want_dh and d_h_accum is not None:
+        if d_h_accum.dtype != h_dtype or tuple(d_h_accum.shape) != (b, l, d) or not d_h_accum.is_contiguous():
+            raise ValueError("d_h_accum must be a contiguous [B, L, d] tensor of the hidden-state dtype")
+        out["d_h"], accumulate = d_h_accum, 1
     lib = L.lib()
     ws_bytes = lib.moc_router_workspace_bytes(C.byref(s))
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
@@ -114,7 +121,7 @@ def router_bwd(h_shape, h_dtype, weight: torch.Tensor, saved: Dict[str, torch.Te
                             L.ptr(saved["row_stats"]), L.ptr(saved["chapter_stats"]),
                             L.ptr(_contig(d_weights)), L.ptr(_contig(d_comb_w)), L.ptr(_contig(d_losses)),
                             L.ptr(out["d_logits"]), L.ptr(out["d_w"]), L.ptr(out["d_bias"]), L.ptr(out["d_pooled"]),
-                            L.ptr(out["d_h"]), 0, L.ptr(ws), ws_bytes, L.ptr(L.status_word(dev)), L.stream_ptr(dev))
+                            L.ptr(out["d_h"]), accumulate, L.ptr(ws), ws_bytes, L.ptr(L.status_word(dev)), L.stream_ptr(dev))
     L.check(rc, "moc_router_bwd")
     return out
 
@@ -289,7 +296,7 @@ def attn_bwd(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tens
     if buffers is None:
         d_q = torch.empty_like(q)
         d_kv = torch.empty_like(kv)
-        scratch = torch.empty(2, s.batch, num_heads, s.seq, dtype=torch.float32, device=q.device)
+        scratch = torch.empty(6, s.batch, num_heads, s.seq, dtype=torch.float32, device=q.device)
     else:
         d_q, d_kv, scratch = buffers
     if parts is None:
@@ -308,7 +315,7 @@ def attn_bwd(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tens
 def attn_bwd_static(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tensor, d_o: torch.Tensor,
                     num_heads: int, num_kv_heads: int, scale: float, out=None) -> Tuple[torch.Tensor, torch.Tensor]:
     """dQ and dKV through the entry point that allocates nothing: its scratch is a fixed array inside
-    the library (2*B*H*L must not exceed ``_lib.ATTN_BWD_STATIC_MAX_FLOATS``).  Pass ``out`` =
+    the library (6*B*H*L must not exceed ``_lib.ATTN_BWD_STATIC_MAX_FLOATS``).  Pass ``out`` =
     (d_q, d_kv) to keep this wrapper from allocating the outputs either.  Calls that may overlap on
     the GPU must be serialised by the caller, because they share that array."""
     q, kv, o, d_o = _contig(q), _contig(kv), _contig(o), _contig(d_o)

@@ -54,7 +54,7 @@ def test_static_scratch_backward_rejects_oversized_problems():
     assert "#define MOC_ATTN_BWD_STATIC_MAX_FLOATS 1048576" in header and L.ATTN_BWD_STATIC_MAX_FLOATS == 1048576
     dev = torch.device("cuda:0")
     dummy = torch.zeros(16, device=dev)
-    s = L.AttnShape(64, 8192, 64, 16, 16, 64, 0.125, L.MOC_BF16)     # 2*B*H*L = 16.8M floats
+    s = L.AttnShape(64, 8192, 64, 16, 16, 64, 0.125, L.MOC_BF16)     # 6*B*H*L = 50M floats
     p = dummy.data_ptr()
     rc = lib.moc_attn_bwd_static(C.byref(s), p, p, p, p, p, p, p, L.status_word(dev).data_ptr(), None)
     assert rc == -1 and b"built-in scratch" in lib.moc_last_error()
