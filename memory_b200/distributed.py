@@ -11,6 +11,14 @@ some rank touched travel:
 5. the result is handed back as a ``SparseBankGrad`` keyed by ``U``.
 
 Dense parameter gradients (projections, router) are flattened into one bucket and all-reduced.
+
+The pipelined form (``snapshot`` + ``reduce_snapshot_async``, what a training loop that replays a captured
+step uses) exchanges the same rows without any host synchronisation and without building the union: every
+rank's compact ``(chapter ids, count, rows / world)`` triple has a fixed size, so three all-gathers deliver
+all ranks' triples and the result is a ``SparseBankGrad`` with one entry per rank whose scatter-add is the
+mean gradient.  It moves (world-1) x local rows per rank instead of 2 x union rows and needs no
+compaction pass before or division pass after the collective.
+
 Works on any ``torch.distributed`` backend (NCCL on GPUs; gloo in the CPU tests of the bookkeeping).
 """
 from __future__ import annotations
@@ -116,39 +124,60 @@ class GradReducer:
 
     # ---- pipelined form: snapshot on the compute stream, reduce on a side stream one step later ----------
     def snapshot(self, dense_grads: Sequence[Optional[torch.Tensor]], sink) -> "GradSnapshot":
-        """Copy this step's gradients into staging buffers on the current stream (no host
-        synchronisation).  The caller may overwrite its gradient tensors right afterwards, e.g. by
-        replaying a captured step."""
+        """Copy this step's gradients, already divided by the world size, into staging buffers on the
+        current stream (no host synchronisation).  The caller may overwrite its gradient tensors right
+        afterwards, e.g. by replaying a captured step."""
+        inv = 1.0 / self.world
         live = [g for g in dense_grads if g is not None]
         flat = torch.cat([g.reshape(-1).float() for g in live]) if live else None
+        if flat is not None and self.world > 1:
+            flat.mul_(inv)
         entries = []
         if sink is not None:
             for uniq, num_unique, rows, t in sink.entries:
-                entries.append((uniq.clone(), num_unique.clone(), rows.clone(), t))
+                staged = rows.float() * inv if self.world > 1 else rows.float().clone()
+                entries.append((uniq.clone(), num_unique.clone(), staged, t))
         ev = torch.cuda.Event() if self.device.type == "cuda" else None
         if ev is not None:
             ev.record(torch.cuda.current_stream(self.device))
         return GradSnapshot(flat, [g.shape for g in live], entries, ev, type(sink) if sink is not None else None)
 
+    def _all_gather(self, out: torch.Tensor, inp: torch.Tensor):
+        """``out`` = the ranks' ``inp`` back to back; returns the async work handle."""
+        try:
+            return dist.all_gather_into_tensor(out, inp.contiguous(), group=self.group, async_op=True)
+        except (RuntimeError, NotImplementedError):
+            return dist.all_gather(list(out.chunk(self.world)), inp.contiguous(), group=self.group, async_op=True)
+
+    def _gather_snapshot(self, snap: "GradSnapshot") -> "PendingReduction":
+        works = []
+        if snap.flat is not None and self.world > 1:
+            works.append(dist.all_reduce(snap.flat, group=self.group, async_op=True))
+        gathered = []
+        for uniq, num_unique, rows, t in snap.entries:
+            if self.world == 1:
+                gathered.append((uniq, num_unique, rows, t))
+                continue
+            n, m = uniq.numel(), rows.shape[0]
+            ids_all = torch.empty(self.world * n, dtype=uniq.dtype, device=uniq.device)
+            num_all = torch.empty(self.world, dtype=num_unique.dtype, device=uniq.device)
+            rows_all = torch.empty(self.world * m, rows.shape[1], dtype=rows.dtype, device=rows.device)
+            works += [self._all_gather(ids_all, uniq), self._all_gather(num_all, num_unique.reshape(1)),
+                      self._all_gather(rows_all, rows)]
+            for r in range(self.world):
+                gathered.append((ids_all[r * n:(r + 1) * n], num_all[r:r + 1], rows_all[r * m:(r + 1) * m], t))
+        return PendingReduction(self, works, snap.flat, snap.shapes, None, snap.sink_type, gathered=gathered)
+
     def reduce_snapshot_async(self, snap: "GradSnapshot") -> "PendingReduction":
-        """Reduce a snapshot on the reducer's own stream.  The host waits only for that stream (to read the
-        union size), so work already queued on the compute stream keeps running underneath."""
+        """Exchange a snapshot on the reducer's own stream: one all-reduce of the dense bucket and three
+        all-gathers per bank entry, all of fixed size, so nothing here waits for the device."""
         if self.device.type != "cuda":
-            holder = snap.sink_type() if snap.sink_type is not None else None
-            if holder is not None:
-                for e in snap.entries:
-                    holder.add(*e)
-            dense = self._split(snap.flat, snap.shapes)
-            return self.reduce_async(dense, holder)
+            return self._gather_snapshot(snap)
         if getattr(self, "_stream", None) is None:
             self._stream = torch.cuda.Stream(self.device)
         with torch.cuda.stream(self._stream):
             self._stream.wait_event(snap.event)
-            holder = snap.sink_type() if snap.sink_type is not None else None
-            if holder is not None:
-                for e in snap.entries:
-                    holder.add(*e)
-            pending = self.reduce_async(self._split(snap.flat, snap.shapes), holder)
+            pending = self._gather_snapshot(snap)
             pending.stream = self._stream
         return pending
 
@@ -205,9 +234,10 @@ class PendingReduction:
     """Handle of a reduction started by :meth:`GradReducer.reduce_async`."""
     stream = None
 
-    def __init__(self, reducer, works, flat, shapes, bank, sink_type):
+    def __init__(self, reducer, works, flat, shapes, bank, sink_type, gathered=None):
         self.reducer, self.works, self.flat, self.shapes, self.bank, self.sink_type = \
             reducer, works, flat, shapes, bank, sink_type
+        self.gathered = gathered      # per-rank (ids, count, rows / world, T) of the pipelined form
 
     def wait(self) -> None:
         """Make the current stream wait for the collectives (no host block)."""
@@ -225,6 +255,13 @@ class PendingReduction:
         """(list of mean dense gradients in the order given, reduced SparseBankGrad or None)."""
         self.wait()
         r = self.reducer
+        if self.gathered is not None:
+            bank = None
+            if self.sink_type is not None:
+                bank = self.sink_type()
+                for e in self.gathered:
+                    bank.add(*e)
+            return GradReducer._split(self.flat, self.shapes), bank
         dense = []
         if self.flat is not None:
             flat = self.flat / r.world
