@@ -192,7 +192,7 @@ def workload_config(cfg, n_gpus):
 class LayerRunner:
     """One memory layer with its parameters; ``step`` = forward + backward (+ gradient reduction)."""
 
-    def __init__(self, cfg, device, world=1, group=None, use_graph=True):
+    def __init__(self, cfg, device, world=1, group=None, use_graph=True, exchange="nccl"):
         import memory_b200 as M
         from memory_b200.graph import GraphedStep
         self.M = M
@@ -210,7 +210,7 @@ class LayerRunner:
         if world > 1:
             from memory_b200.distributed import GradReducer
             self.reducer = GradReducer(cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["hidden_dim"], device,
-                                       group=group)
+                                       group=group, exchange=exchange)
         self.graphed = None
         if use_graph:
             shape = (cfg["batch"], cfg["seq"], cfg["hidden_dim"])
@@ -250,6 +250,7 @@ class LayerRunner:
             if self.prev_snap is not None:
                 if self.pending is not None:
                     self.pending.wait()
+                    self.pending.release()       # an optimizer step would read the reduced gradients here
                 self.pending = self.reducer.reduce_snapshot_async(self.prev_snap)
             self.prev_snap = snap
         return loss
@@ -260,10 +261,12 @@ class LayerRunner:
             return
         if self.pending is not None:
             self.pending.wait()
+            self.pending.release()
             self.pending = None
         if self.prev_snap is not None:
             last = self.reducer.reduce_snapshot_async(self.prev_snap)
             last.wait()
+            last.release()
             self.prev_snap = None
 
     def launches_per_step(self):
@@ -351,7 +354,7 @@ def run_cuda_arm(args):
     L.lib()
 
     cfg = dict(PAPER)
-    runner = LayerRunner(cfg, device, world, use_graph=not args.no_graph)
+    runner = LayerRunner(cfg, device, world, use_graph=not args.no_graph, exchange=args.exchange)
     hs_cpu, gs_cpu = make_hidden(cfg, N_INPUT_SETS, 1234 + rank, torch.bfloat16)
     hs = [t.to(device).requires_grad_(True) for t in hs_cpu]
     gs = [t.to(device) for t in gs_cpu]
@@ -482,6 +485,12 @@ def run_cuda_arm(args):
         "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu_baseline,
         "pct_of_bf16_tc_roofline": 100.0 * roofline["layer"]["frac"],
     }
+    if world > 1:
+        line["config"]["gradient_exchange"] = (
+            "dense bucket: one NCCL all-reduce; bank rows: sparse, " +
+            ("copy-engine pushes into symmetric-memory receive buffers" if runner.reducer.exchange == "peer"
+             and runner.reducer._peer is not None else "three fixed-size NCCL all-gathers") +
+            ", one step behind the compute on a second stream")
     sys.stdout.flush()
     os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
@@ -498,6 +507,9 @@ def main():
     ap.add_argument("--cpu-sample-batch", type=int, default=2)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="issue every kernel from Python instead of a CUDA graph")
+    ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
+                    help="N > 1: how the sparse bank-gradient rows travel (NCCL all-gathers, or copy-engine pushes "
+                         "into symmetric-memory receive buffers; falls back to NCCL when those cannot be set up)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "cuda":
         args.warmup = 3

@@ -19,6 +19,11 @@ all ranks' triples and the result is a ``SparseBankGrad`` with one entry per ran
 mean gradient.  It moves (world-1) x local rows per rank instead of 2 x union rows and needs no
 compaction pass before or division pass after the collective.
 
+With ``exchange="peer"`` (CUDA, one node) the three all-gathers are replaced by device-to-device copies into
+receive buffers that every rank holds in symmetric memory: each rank pushes its block to every peer with the copy
+engines over NVLink, bracketed by two one-element all-reduces that order the pushes against the readers.  No SM
+runs for the bulk transfer, so the compute of the next step keeps the whole GPU.
+
 Works on any ``torch.distributed`` backend (NCCL on GPUs; gloo in the CPU tests of the bookkeeping).
 """
 from __future__ import annotations
@@ -48,11 +53,75 @@ def compact_to_union(local_ids: torch.Tensor, local_rows: torch.Tensor, union_id
     return out.view(-1, d)
 
 
+class _PeerPush:
+    """Fixed-size all-gather of one (ids, count, rows) triple by peer-to-peer copies.
+
+    Every rank owns ``parities`` receive buffers ``[world, ...]`` in symmetric memory.  ``exchange`` (on the
+    current stream): wait until the local consumer released this parity, one-element all-reduce (every rank is
+    past its consumer), copy the local block into slot ``rank`` of every rank's buffer (``cudaMemcpyAsync``
+    device-to-device: copy engines, no kernel), one-element all-reduce (every push has landed everywhere).
+    """
+
+    def __init__(self, group, device, n_ids: int, rows_shape, parities: int = 2):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.n, self.m, self.d = int(n_ids), int(rows_shape[0]), int(rows_shape[1])
+        self.parities = parities
+        w = self.world
+        self.rows_words = w * self.m * self.d
+        self.ids_words = -(-(w * self.n) // 4) * 4
+        self.num_words = -(-w // 4) * 4
+        self.per_parity = self.rows_words + self.ids_words + self.num_words
+        self.buf = symm.empty(parities * self.per_parity, dtype=torch.float32, device=device)
+        handle = symm.rendezvous(self.buf, self.group)
+        self.peers = [handle.get_buffer(r, (parities * self.per_parity,), torch.float32) for r in range(w)]
+        self.handle = handle
+        self.token = torch.zeros(1, dtype=torch.float32, device=device)
+        self.consumed = [None] * parities
+
+    def _views(self, flat: torch.Tensor, parity: int):
+        base = parity * self.per_parity
+        rows = flat[base:base + self.rows_words].view(self.world, self.m, self.d)
+        ids = flat[base + self.rows_words:base + self.rows_words + self.world * self.n].view(torch.int32)
+        nums = flat[base + self.rows_words + self.ids_words:
+                    base + self.rows_words + self.ids_words + self.world].view(torch.int32)
+        return rows, ids.view(self.world, self.n), nums
+
+    def exchange(self, parity: int, uniq: torch.Tensor, num_unique: torch.Tensor, rows: torch.Tensor):
+        stream = torch.cuda.current_stream(self.buf.device)
+        if self.consumed[parity] is not None:
+            stream.wait_event(self.consumed[parity])
+        dist.all_reduce(self.token, group=self.group)
+        for k in range(1, self.world):          # the local block is used where it is: no copy to self
+            r = (self.rank + k) % self.world
+            p_rows, p_ids, p_nums = self._views(self.peers[r], parity)
+            p_rows[self.rank].copy_(rows.view(self.m, self.d), non_blocking=True)
+            p_ids[self.rank].copy_(uniq.view(torch.int32), non_blocking=True)
+            p_nums[self.rank:self.rank + 1].copy_(num_unique.view(torch.int32).reshape(1), non_blocking=True)
+        work = dist.all_reduce(self.token, group=self.group, async_op=True)
+        rows_all, ids_all, nums_all = self._views(self.buf, parity)
+        return work, [(uniq, num_unique, rows) if r == self.rank else (ids_all[r], nums_all[r:r + 1], rows_all[r])
+                      for r in range(self.world)]
+
+    def release(self, parity: int) -> None:
+        """The consumer of this parity's buffers is done (recorded on the current stream)."""
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.buf.device))
+        self.consumed[parity] = ev
+
+
 class GradReducer:
     """Reduces one step's gradients across the data-parallel group (mean, as DDP does)."""
 
     def __init__(self, num_chapters: int, tokens_per_chapter: int, dim: int, device,
-                 group: Optional[dist.ProcessGroup] = None, bank_dtype: torch.dtype = torch.float32):
+                 group: Optional[dist.ProcessGroup] = None, bank_dtype: torch.dtype = torch.float32,
+                 exchange: str = "nccl"):
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' or 'peer'")
+        self.exchange = exchange
+        self._peer = None
+        self._parity = 0
         self.c, self.t, self.d = int(num_chapters), int(tokens_per_chapter), int(dim)
         self.device = torch.device(device)
         self.group = group
@@ -154,9 +223,21 @@ class GradReducer:
         if snap.flat is not None and self.world > 1:
             works.append(dist.all_reduce(snap.flat, group=self.group, async_op=True))
         gathered = []
+        use_peer = (self.exchange == "peer" and self.world > 1 and self.device.type == "cuda"
+                    and len(snap.entries) == 1)
         for uniq, num_unique, rows, t in snap.entries:
             if self.world == 1:
                 gathered.append((uniq, num_unique, rows, t))
+                continue
+            if use_peer and self._peer is None:
+                use_peer = self._open_peer(uniq.numel(), rows.shape)
+            if use_peer:
+                parity = self._parity
+                self._parity = (parity + 1) % self._peer.parities
+                work, triples = self._peer.exchange(parity, uniq, num_unique, rows)
+                works.append(work)
+                gathered += [(i, c, r, t) for i, c, r in triples]
+                pending_parity = parity
                 continue
             n, m = uniq.numel(), rows.shape[0]
             ids_all = torch.empty(self.world * n, dtype=uniq.dtype, device=uniq.device)
@@ -166,7 +247,25 @@ class GradReducer:
                       self._all_gather(rows_all, rows)]
             for r in range(self.world):
                 gathered.append((ids_all[r * n:(r + 1) * n], num_all[r:r + 1], rows_all[r * m:(r + 1) * m], t))
-        return PendingReduction(self, works, snap.flat, snap.shapes, None, snap.sink_type, gathered=gathered)
+        pending = PendingReduction(self, works, snap.flat, snap.shapes, None, snap.sink_type, gathered=gathered)
+        if use_peer and self.world > 1 and snap.entries:
+            pending.parity = pending_parity
+        return pending
+
+    def _open_peer(self, n_ids: int, rows_shape) -> bool:
+        """Create the symmetric-memory receive buffers; every rank must succeed or all fall back to NCCL."""
+        ok = 1
+        try:
+            self._peer = _PeerPush(self.group, self.device, n_ids, rows_shape)
+        except Exception:                      # symmetric memory unavailable in this process / on this node
+            self._peer, ok = None, 0
+        flag = torch.tensor([ok], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self._peer = None
+            self.exchange = "nccl"
+            return False
+        return True
 
     def reduce_snapshot_async(self, snap: "GradSnapshot") -> "PendingReduction":
         """Exchange a snapshot on the reducer's own stream: one all-reduce of the dense bucket and three
@@ -238,6 +337,13 @@ class PendingReduction:
         self.reducer, self.works, self.flat, self.shapes, self.bank, self.sink_type = \
             reducer, works, flat, shapes, bank, sink_type
         self.gathered = gathered      # per-rank (ids, count, rows / world, T) of the pipelined form
+        self.parity = None            # receive-buffer parity of the peer exchange, if that carried the rows
+
+    def release(self) -> None:
+        """Tell the reducer that the result's tensors are no longer read after the work queued so far on the
+        current stream.  Needed with ``exchange="peer"``, whose receive buffers are reused every second step."""
+        if self.parity is not None and self.reducer._peer is not None:
+            self.reducer._peer.release(self.parity)
 
     def wait(self) -> None:
         """Make the current stream wait for the collectives (no host block)."""

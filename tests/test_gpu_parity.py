@@ -403,3 +403,30 @@ def test_memory_sub_block_module_matches_oracle(dev):
         assert rel_err(h.grad, hc.grad) < FP32_BWD
         assert rel_err(mem.grad, mc.grad) < FP32_BWD
     _status_ok(dev)
+
+
+def test_two_stream_layer_equals_chained_nodes(dev):
+    """The single two-stream autograd node and the three chained nodes run the same kernels: outputs, router
+    losses and every gradient must agree to rounding of the split-K atomics."""
+    import memory_b200 as M
+    case = CASES["block_rms"]
+    inp = {k: torch.from_numpy(v).to(dev) for k, v in make_inputs(case).items()}
+    results = []
+    for two_stream in (True, False):
+        names = ("h_router", "bank", "router_w", "router_b", "wq", "wk", "wv", "wo", "pre_norm_w")
+        P = {k: inp[k].clone().requires_grad_(True) for k in names}
+        out, losses, info = M.memory_layer(
+            P["h_router"], P["h_router"], P["bank"], P["router_w"], P["router_b"], P["wq"], P["wk"], P["wv"], P["wo"],
+            num_heads=case.num_heads, num_kv_heads=case.num_kv_heads, tokens_per_chapter=case.tokens_per_chapter,
+            top_k=case.top_k, num_shared_chapters=case.num_shared_chapters,
+            routed_scaling_factor=case.routed_scaling_factor, compute_dtype=torch.bfloat16, pre_norm="rms",
+            pre_norm_weight=P["pre_norm_w"], pre_norm_eps=case.pre_norm_eps, add_residual=True, two_stream=two_stream)
+        ((out.float() * inp["d_out"]).sum() + 0.01 * losses["load_balance"] + 0.001 * losses["z_loss"]).backward()
+        torch.cuda.synchronize()
+        results.append((out.detach(), {k: P[k].grad for k in names}, info["indices"]))
+    (o1, g1, i1), (o2, g2, i2) = results
+    assert torch.equal(i1, i2)
+    assert rel_err(o1, o2) < 1e-6
+    for k in g1:
+        assert rel_err(g1[k], g2[k]) < 2e-3, k
+    _status_ok(dev)
