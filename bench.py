@@ -201,29 +201,43 @@ class LayerRunner:
         self.world = world
         p = make_params(cfg, device)
         self.params = {k: v.requires_grad_(True) for k, v in p.items()}
-        self.sink = M.SparseBankGrad()
-        self.params["bank"].moc_sparse_grad = self.sink
         self.g_losses = torch.tensor([0.01, 0.0, 0.001, 0.0], device=device)   # load_balance, auxiliary, z, entropy
         self.reducer = None
-        self.pending = None
-        self.prev_snap = None
         if world > 1:
             from memory_b200.distributed import GradReducer
             self.reducer = GradReducer(cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["hidden_dim"], device,
                                        group=group, exchange=exchange)
+        # With a reduction the step is captured twice and the two graphs are replayed alternately: the
+        # gradients of step i stay untouched in their graph's buffers while step i+1 runs in the other graph, so
+        # the exchange reads them in place (no staging copy on the compute stream).
+        self.slots = 2 if (world > 1 and use_graph) else 1
+        self.sinks = [M.SparseBankGrad() for _ in range(self.slots)]
+        self.sink = self.sinks[0]
+        self.params["bank"].moc_sparse_grad = self.sink
+        self.pending = [None] * self.slots
+        self.step_index = 0
+        self.prev_snap = None
+        self.graphs, self.dense_by_slot = [], []
         self.graphed = None
         if use_graph:
             shape = (cfg["batch"], cfg["seq"], cfg["hidden_dim"])
             h0 = torch.zeros(shape, dtype=torch.bfloat16, device=device).requires_grad_(True)
             g0 = torch.zeros(shape, dtype=torch.bfloat16, device=device)
             h0.data.normal_()
-            self.graphed = GraphedStep(self._fwd_bwd, [h0, g0])
+            for s in range(self.slots):
+                self.graphs.append(GraphedStep(lambda h, d, s=s: self._fwd_bwd(h, d, s), [h0, g0]))
+                self.dense_by_slot.append([self.params[k].grad for k in self.DENSE_KEYS])
+            self.graphed = self.graphs[0]
 
-    def _fwd_bwd(self, h, d_out):
+    DENSE_KEYS = ("router_w", "router_b", "wq", "wk", "wv", "wo")
+
+    def _fwd_bwd(self, h, d_out, slot=0):
         P, cfg = self.params, self.cfg
         for v in P.values():
             v.grad = None
-        self.sink.clear()
+        sink = self.sinks[slot]
+        sink.clear()
+        P["bank"].moc_sparse_grad = sink
         h.grad = None
         out, losses, _ = self.M.memory_layer(
             h, h, P["bank"], P["router_w"], P["router_b"], P["wq"], P["wk"], P["wv"], P["wo"],
@@ -237,32 +251,45 @@ class LayerRunner:
         return losses.vector
 
     def step(self, h, d_out, eager=False):
-        if self.graphed is not None and not eager:
-            loss = self.graphed(h, d_out)
+        slot = self.step_index % self.slots
+        self.step_index += 1
+        if self.reducer is not None and self.pending[slot] is not None:
+            # the exchange that still reads this slot's gradient buffers (started two steps ago) must be over;
+            # an optimizer step would consume its result here
+            self.pending[slot].wait()
+            self.pending[slot].release()
+            self.pending[slot] = None
+        if self.graphs and not eager:
+            loss = self.graphs[slot](h, d_out)
+            dense = self.dense_by_slot[slot]
         else:
-            loss = self._fwd_bwd(h, d_out)
+            loss = self._fwd_bwd(h, d_out, slot)
+            dense = [self.params[k].grad for k in self.DENSE_KEYS]
         if self.reducer is not None:
-            # gradients of step i are staged on the compute stream (no host sync); their reduction runs on
-            # the reducer's stream one step later, under the compute of step i+1
-            P = self.params
-            dense = [P[k].grad for k in ("router_w", "router_b", "wq", "wk", "wv", "wo")]
-            snap = self.reducer.snapshot(dense, self.sink)
-            if self.prev_snap is not None:
-                if self.pending is not None:
-                    self.pending.wait()
-                    self.pending.release()       # an optimizer step would read the reduced gradients here
-                self.pending = self.reducer.reduce_snapshot_async(self.prev_snap)
-            self.prev_snap = snap
+            if self.slots == 2 and not eager:
+                # zero-copy: the exchange of step i runs on the reducer's stream under the compute of step i+1
+                snap = self.reducer.snapshot(dense, self.sinks[slot], copy=False)
+                self.pending[slot] = self.reducer.reduce_snapshot_async(snap)
+            else:
+                # one set of buffers: stage a copy on the compute stream, exchange it one step later
+                snap = self.reducer.snapshot(dense, self.sinks[slot])
+                if self.prev_snap is not None:
+                    if self.pending[0] is not None:
+                        self.pending[0].wait()
+                        self.pending[0].release()
+                    self.pending[0] = self.reducer.reduce_snapshot_async(self.prev_snap)
+                self.prev_snap = snap
         return loss
 
     def finish(self):
-        """Reduce the last staged step and wait (on the stream) for everything in flight."""
+        """Exchange what is still staged and wait (on the stream) for everything in flight."""
         if self.reducer is None:
             return
-        if self.pending is not None:
-            self.pending.wait()
-            self.pending.release()
-            self.pending = None
+        for i, p in enumerate(self.pending):
+            if p is not None:
+                p.wait()
+                p.release()
+                self.pending[i] = None
         if self.prev_snap is not None:
             last = self.reducer.reduce_snapshot_async(self.prev_snap)
             last.wait()

@@ -192,24 +192,38 @@ class GradReducer:
         return PendingReduction(self, works, flat, [g.shape for g in live], bank, type(sink) if sink is not None else None)
 
     # ---- pipelined form: snapshot on the compute stream, reduce on a side stream one step later ----------
-    def snapshot(self, dense_grads: Sequence[Optional[torch.Tensor]], sink) -> "GradSnapshot":
-        """Copy this step's gradients, already divided by the world size, into staging buffers on the
-        current stream (no host synchronisation).  The caller may overwrite its gradient tensors right
-        afterwards, e.g. by replaying a captured step."""
+    def snapshot(self, dense_grads: Sequence[Optional[torch.Tensor]], sink, copy: bool = True) -> "GradSnapshot":
+        """Stage this step's gradients on the current stream (no host synchronisation).
+
+        ``copy=True``: gradients are copied, already divided by the world size, so the caller may overwrite its
+        gradient tensors right afterwards (e.g. by replaying the same captured step).
+        ``copy=False``: nothing is copied; the snapshot references the caller's tensors, which must stay
+        untouched until the reduction's ``wait()`` (e.g. two captured steps used alternately); the dense bucket
+        is assembled on the reducer's stream and the bank rows travel unscaled, the result's ``scale`` says what
+        the consumer still has to apply."""
         inv = 1.0 / self.world
         live = [g for g in dense_grads if g is not None]
-        flat = torch.cat([g.reshape(-1).float() for g in live]) if live else None
-        if flat is not None and self.world > 1:
-            flat.mul_(inv)
         entries = []
-        if sink is not None:
-            for uniq, num_unique, rows, t in sink.entries:
-                staged = rows.float() * inv if self.world > 1 else rows.float().clone()
-                entries.append((uniq.clone(), num_unique.clone(), staged, t))
+        if copy:
+            flat = torch.cat([g.reshape(-1).float() for g in live]) if live else None
+            if flat is not None and self.world > 1:
+                flat.mul_(inv)
+            if sink is not None:
+                for uniq, num_unique, rows, t in sink.entries:
+                    staged = rows.float() * inv if self.world > 1 else rows.float().clone()
+                    entries.append((uniq.clone(), num_unique.clone(), staged, t))
+        else:
+            flat = None
+            if sink is not None:
+                entries = [(u, n, r if r.dtype == torch.float32 else r.float(), t) for u, n, r, t in sink.entries]
         ev = torch.cuda.Event() if self.device.type == "cuda" else None
         if ev is not None:
             ev.record(torch.cuda.current_stream(self.device))
-        return GradSnapshot(flat, [g.shape for g in live], entries, ev, type(sink) if sink is not None else None)
+        snap = GradSnapshot(flat, [g.shape for g in live], entries, ev, type(sink) if sink is not None else None)
+        if not copy:
+            snap.dense_refs = live
+            snap.bank_scale = inv if self.world > 1 else 1.0
+        return snap
 
     def _all_gather(self, out: torch.Tensor, inp: torch.Tensor):
         """``out`` = the ranks' ``inp`` back to back; returns the async work handle."""
@@ -220,6 +234,10 @@ class GradReducer:
 
     def _gather_snapshot(self, snap: "GradSnapshot") -> "PendingReduction":
         works = []
+        if snap.flat is None and snap.dense_refs:
+            snap.flat = torch.cat([g.reshape(-1).float() for g in snap.dense_refs])
+            if self.world > 1:
+                snap.flat.mul_(1.0 / self.world)
         if snap.flat is not None and self.world > 1:
             works.append(dist.all_reduce(snap.flat, group=self.group, async_op=True))
         gathered = []
@@ -248,6 +266,7 @@ class GradReducer:
             for r in range(self.world):
                 gathered.append((ids_all[r * n:(r + 1) * n], num_all[r:r + 1], rows_all[r * m:(r + 1) * m], t))
         pending = PendingReduction(self, works, snap.flat, snap.shapes, None, snap.sink_type, gathered=gathered)
+        pending.bank_scale = snap.bank_scale
         if use_peer and self.world > 1 and snap.entries:
             pending.parity = pending_parity
         return pending
@@ -278,6 +297,12 @@ class GradReducer:
             self._stream.wait_event(snap.event)
             pending = self._gather_snapshot(snap)
             pending.stream = self._stream
+            # completion of exactly this exchange (later exchanges queued on the same stream do not count)
+            for w in pending.works:
+                w.wait()
+            pending.works = []
+            pending.done = torch.cuda.Event()
+            pending.done.record(self._stream)
         return pending
 
     @staticmethod
@@ -325,6 +350,9 @@ class GradReducer:
 class GradSnapshot:
     """Staged copy of one step's gradients (see :meth:`GradReducer.snapshot`)."""
 
+    dense_refs = None     # zero-copy form: the caller's dense gradient tensors
+    bank_scale = 1.0      # factor still to be applied to the bank rows by the consumer
+
     def __init__(self, flat, shapes, entries, event, sink_type):
         self.flat, self.shapes, self.entries, self.event, self.sink_type = flat, shapes, entries, event, sink_type
 
@@ -332,12 +360,14 @@ class GradSnapshot:
 class PendingReduction:
     """Handle of a reduction started by :meth:`GradReducer.reduce_async`."""
     stream = None
+    done = None
 
     def __init__(self, reducer, works, flat, shapes, bank, sink_type, gathered=None):
         self.reducer, self.works, self.flat, self.shapes, self.bank, self.sink_type = \
             reducer, works, flat, shapes, bank, sink_type
         self.gathered = gathered      # per-rank (ids, count, rows / world, T) of the pipelined form
         self.parity = None            # receive-buffer parity of the peer exchange, if that carried the rows
+        self.bank_scale = 1.0
 
     def release(self) -> None:
         """Tell the reducer that the result's tensors are no longer read after the work queued so far on the
@@ -347,7 +377,9 @@ class PendingReduction:
 
     def wait(self) -> None:
         """Make the current stream wait for the collectives (no host block)."""
-        if self.stream is not None:
+        if self.done is not None:
+            torch.cuda.current_stream(self.stream.device).wait_event(self.done)
+        elif self.stream is not None:
             with torch.cuda.stream(self.stream):
                 for w in self.works:
                     w.wait()
@@ -367,6 +399,7 @@ class PendingReduction:
                 bank = self.sink_type()
                 for e in self.gathered:
                     bank.add(*e)
+                bank.scale = self.bank_scale
             return GradReducer._split(self.flat, self.shapes), bank
         dense = []
         if self.flat is not None:

@@ -36,6 +36,7 @@ class SparseBankGrad:
 
     def __init__(self):
         self.entries = []   # list of (uniq int32 [n_pairs], num_unique int32 [1], rows fp32 [n_pairs*T, d], T)
+        self.scale = 1.0    # factor the consumer applies to the summed rows (1 / world after a zero-copy reduction)
 
     def add(self, uniq, num_unique, rows, tokens_per_chapter):
         self.entries.append((uniq, num_unique, rows, int(tokens_per_chapter)))
@@ -47,6 +48,8 @@ class SparseBankGrad:
         dense = torch.zeros(like.shape, dtype=torch.float32, device=like.device)
         for uniq, num_unique, rows, t in self.entries:
             ops.scatter_bank_grad(rows, {"uniq": uniq, "num_unique": num_unique}, t, dense)
+        if self.scale != 1.0:
+            dense.mul_(self.scale)
         return dense
 
 

@@ -61,6 +61,14 @@ def _worker(rank, world, port, q):
         for a, b in zip(dense_snap, dense_async):
             torch.testing.assert_close(a, b)
         torch.testing.assert_close(_dense_of(bank_snap.entries), _dense_of(bank_async.entries))
+        # zero-copy staging: same result once the consumer applies the returned scale
+        refs = [d.clone() if d is not None else None for d in dense]
+        snap0 = red.snapshot(refs, sink, copy=False)
+        dense_zc, bank_zc = red.reduce_snapshot_async(snap0).result()
+        for a, b in zip(dense_zc, dense_async):
+            torch.testing.assert_close(a, b)
+        assert bank_zc.scale == 0.5
+        torch.testing.assert_close(_dense_of(bank_zc.entries) * bank_zc.scale, _dense_of(bank_async.entries))
         reduced = red.reduce(dense, sink)
         assert len(sink.entries) == 2, "the local entries must be left in place"
         for a, b in zip(dense_async, [d for d in dense if d is not None]):
