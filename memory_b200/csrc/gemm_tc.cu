@@ -17,15 +17,20 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;          // two accumulator buffers of up to 256 columns
 
-template <int BN> struct Cfg {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kABytes = BM * BK * 2;
+// MT = 128-row MMA tiles per CTA tile.  MT = 1: 128 x BN output tile, two accumulator buffers, so the epilogue of
+// one tile runs under the main loop of the next.  MT = 2: 256 x 256 output tile, both accumulators live at once
+// and the two MMAs of a K step share the B stage: a third fewer bytes from L2 per FLOP, which is what limits
+// this kernel at K <= 1536.
+template <int BN, int MT> struct Cfg {
+  static constexpr int kStages = (MT == 2) ? 3 : ((BN == 256) ? 4 : 6);
+  static constexpr int kThreads = 64 + 128 * MT;
+  static constexpr int kABytes = BM * MT * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr int kStoreBytes = 32 * 128;        // per epilogue warp: 32 rows x 64 bf16 staged for a TMA store
+  static constexpr int kSmemBytes = kStages * kStageBytes + 4 * MT * kStoreBytes + 1024;
 };
 
 struct GemmTcParams {
@@ -34,6 +39,7 @@ struct GemmTcParams {
   void* c;
   long long ldc;
   int c_bf16;
+  int c_tma;               // bf16 C written through shared memory and TMA stores (rows 16-byte aligned)
   int accumulate;
   int atomic;
   const float* row_scale;
@@ -58,11 +64,11 @@ __device__ __forceinline__ void drain_after_abort() {
 }
 
 // Persistent kernel: CTA i works on items i, i + gridDim.x, ...; an item is (output tile, K split).
-template <int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, int MT>
+__global__ void __launch_bounds__(64 + 128 * MT, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               GemmTcParams p) {
-  using C = Cfg<BN>;
+               const __grid_constant__ CUtensorMap tmap_c, GemmTcParams p) {
+  using C = Cfg<BN, MT>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[C::kStages];
   __shared__ __align__(8) uint64_t empty_bar[C::kStages];
@@ -83,7 +89,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 4);
+      mbar_init(&acc_empty[i], 4 * MT);
     }
     fence_mbar_init();
     prefetch_tmap(&tmap_a);
@@ -106,7 +112,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int split = item % p.splits;
         const int tile = item / p.splits;
         const int n0 = (tile % p.n_tiles) * BN;
-        const int m0 = (tile / p.n_tiles) * BM;
+        const int m0 = (tile / p.n_tiles) * (BM * MT);
         const int kt_begin = split * p.k_tiles_per_split;
         int kt_count = p.k_tiles_total - kt_begin;
         if (kt_count > p.k_tiles_per_split) kt_count = p.k_tiles_per_split;
@@ -120,7 +126,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           uint8_t* b_s = a_s + C::kABytes;
           const int k0 = (kt_begin + kt) * BK;
           if (p.a_kmajor) {
-            const int nbox = BM / p.a_box_rows;
+            const int nbox = BM * MT / p.a_box_rows;
             for (int i = 0; i < nbox; ++i) {
               long long row;
               if (p.a_row_blocks != nullptr) {
@@ -137,8 +143,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               tma_load_2d(a_s + i * p.a_box_rows * 128, &tmap_a, &full_bar[s], k0, static_cast<int>(row));
             }
           } else {
-            tma_load_2d(a_s, &tmap_a, &full_bar[s], m0, k0);
-            tma_load_2d(a_s + 8192, &tmap_a, &full_bar[s], m0 + 64, k0);
+#pragma unroll
+            for (int i = 0; i < 2 * MT; ++i) tma_load_2d(a_s + i * 8192, &tmap_a, &full_bar[s], m0 + 64 * i, k0);
           }
           if (p.b_kmajor) {
 #pragma unroll
@@ -170,8 +176,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int kt_begin = split * p.k_tiles_per_split;
         int kt_count = p.k_tiles_total - kt_begin;
         if (kt_count > p.k_tiles_per_split) kt_count = p.k_tiles_per_split;
-        const uint32_t buf = t & 1;
-        ok = mbar_wait_w(&acc_empty[buf], ((t >> 1) & 1) ^ 1, &abort_flag, p.status);
+        const uint32_t buf = (MT == 1) ? (t & 1) : 0;
+        ok = mbar_wait_w(&acc_empty[buf], (MT == 1 ? ((t >> 1) & 1) : (t & 1)) ^ 1, &abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + buf * 256;
@@ -183,9 +189,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           tc_fence_after();
           const uint64_t stage_off = static_cast<uint64_t>(s) * (C::kStageBytes >> 4);
           const uint64_t ad = a_base + stage_off, bd = b_base + stage_off;
-          umma_ss_w(tmem_acc, ad, bd, idesc, kt > 0 ? 1u : 0u);
+          if (MT == 1) {
+            umma_ss_w(tmem_acc, ad, bd, idesc, kt > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 1; kk < BK / 16; ++kk) umma_ss_w(tmem_acc, ad + kk * a_step, bd + kk * b_step, idesc, 1u);
+            for (int kk = 1; kk < BK / 16; ++kk) umma_ss_w(tmem_acc, ad + kk * a_step, bd + kk * b_step, idesc, 1u);
+          } else {
+            // rows [128, 256) of the A stage start 16 KiB further on in both layouts; two independent accumulators
+            constexpr uint64_t kSub = 16384 >> 4;
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk) {
+              const uint32_t acc = (kt > 0 || kk > 0) ? 1u : 0u;
+              umma_ss_w(tmem_base, ad + kk * a_step, bd + kk * b_step, idesc, acc);
+              umma_ss_w(tmem_base + 256, ad + kSub + kk * a_step, bd + kk * b_step, idesc, acc);
+            }
+          }
           tc_commit_w(&empty_bar[s]);
         }
         if (!ok) break;
@@ -195,20 +212,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else {
     // epilogue: TMEM lanes [32*(warp%4), +32) <-> output rows
     const int lane_group = (warp & 3) * 32;
+    const int sub = (MT == 2) ? (warp - 2) / 4 : 0;        // which 128-row half of the tile this warp drains
+    // One thread owns one output row, so direct stores scatter 16-byte pieces over 32 rows per instruction.
+    // bf16 tiles therefore go through a 128-byte-swizzled staging block and leave as TMA stores.
+    uint8_t* stage_c = tiles + C::kStages * C::kStageBytes + (warp - 2) * C::kStoreBytes;
+    const uint32_t stage_row = smem_u32(stage_c) + lane * 128;
     uint32_t t = 0;
     for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++t) {
       const int split = item % p.splits;
       const int tile = item / p.splits;
       const int n0 = (tile % p.n_tiles) * BN;
-      const int m0 = (tile / p.n_tiles) * BM;
+      const int m0 = (tile / p.n_tiles) * (BM * MT) + sub * BM;
       const int kt_begin = split * p.k_tiles_per_split;
       const bool has_k = kt_begin < p.k_tiles_total;
-      const uint32_t buf = t & 1;
-      bool have_acc = mbar_wait(&acc_full[buf], (t >> 1) & 1, &abort_flag, p.status);
+      const uint32_t buf = (MT == 1) ? (t & 1) : 0;
+      bool have_acc = mbar_wait(&acc_full[buf], MT == 1 ? ((t >> 1) & 1) : (t & 1), &abort_flag, p.status);
       have_acc = __all_sync(0xffffffffu, have_acc);   // tcgen05.ld below is warp-collective
       if (!have_acc) break;
       tc_fence_after();
-      const uint32_t tmem_acc = tmem_base + buf * 256;
+      const uint32_t tmem_acc = tmem_base + (MT == 1 ? buf : static_cast<uint32_t>(sub)) * 256;
       const int row = m0 + lane_group + lane;
       float rs = 1.0f;
       if (p.row_scale != nullptr && row < p.m) rs = p.row_scale[row / p.scale_block_rows];
@@ -223,6 +245,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (p.c_tma) {
+          if ((c & 1) == 0) {                          // the previous store must be done with the staging block
+            if (lane == 0) bulk_wait_read_all();
+            __syncwarp();
+          }
+          if (p.residual != nullptr && row < p.m) {
+            const float* res = p.residual + static_cast<long long>(row) * p.ldr + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.n) r[j] = __float_as_uint(__uint_as_float(r[j]) * rs + res[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rs);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t addr = stage_row + ((static_cast<uint32_t>((c & 1) * 4 + j) ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                         "r"(pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]))),
+                         "r"(pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]))),
+                         "r"(pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]))),
+                         "r"(pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])))
+                         : "memory");
+          }
+          if ((c & 1) || col0 + 32 >= p.n) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_c, stage_c, n0 + (c & ~1) * 32, m0 + lane_group);
+              bulk_commit_group();
+            }
+          }
+          continue;
         }
         if (row >= p.m) continue;
         if (p.residual != nullptr && split == 0) {
@@ -311,6 +367,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
+    if (p.c_tma && lane == 0) bulk_wait_all();       // stores still in flight read this CTA's shared memory
     tc_fence_before();
   }
 
@@ -367,6 +424,14 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
     return static_cast<double>(rounds) * (BM + bn);
   };
   const int bn = (g->n > 128 && waves_cost(256) <= waves_cost(128)) ? 256 : 128;
+  // 256 x 256 tiles: single pass over K only (no split), and only where the rounds-times-bytes cost, with the
+  // epilogue that is no longer hidden counted as 8 %, beats the 128-row tiles.
+  bool tall = false;
+  if (bn == 256 && split == 1 && g->m >= 2 * BM && (a_row_blocks == nullptr || 256 % a_box_rows == 0)) {
+    const long long items = static_cast<long long>(ceil_div(g->m, 2 * BM)) * ceil_div(g->n, 256);
+    const double cost_tall = static_cast<double>((items + sms - 1) / sms) * (2 * BM + 256) * 1.08;
+    tall = cost_tall < waves_cost(256);
+  }
 
   CUtensorMap tmap_a, tmap_b;
   int rc;
@@ -387,7 +452,16 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
   }
   if (rc != MOC_OK) return rc;
 
+  const bool c_tma = g->c_dtype == MOC_BF16 && (g->ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(c) & 15) == 0;
+  CUtensorMap tmap_c = tmap_a;      // placeholder when the TMA-store epilogue is not used
+  if (c_tma) {
+    rc = make_tmap_bf16_2d(&tmap_c, c, static_cast<uint64_t>(g->m), static_cast<uint64_t>(g->n),
+                           static_cast<uint64_t>(g->ldc), 32, 64);
+    if (rc != MOC_OK) return rc;
+  }
+
   GemmTcParams p;
+  p.c_tma = c_tma ? 1 : 0;
   p.m = g->m; p.n = g->n; p.k = g->k;
   p.a_kmajor = g->a_kmajor; p.b_kmajor = g->b_kmajor;
   p.c = c; p.ldc = g->ldc; p.c_bf16 = (g->c_dtype == MOC_BF16);
@@ -399,20 +473,24 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
   p.k_tiles_total = ceil_div(g->k, BK);
   p.k_tiles_per_split = ceil_div(p.k_tiles_total, split);
   p.splits = ceil_div(p.k_tiles_total, p.k_tiles_per_split);   // no empty splits
-  p.m_tiles = m_tiles;
+  p.m_tiles = tall ? ceil_div(g->m, 2 * BM) : m_tiles;
   p.n_tiles = ceil_div(g->n, bn);
   p.num_items = p.m_tiles * p.n_tiles * p.splits;
   p.status = status;
 
   const int grid = p.num_items < sms ? p.num_items : sms;
-  if (bn == 256) {
-    MOC_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     Cfg<256>::kSmemBytes));
-    gemm_tc_kernel<256><<<grid, kThreads, Cfg<256>::kSmemBytes, stream>>>(tmap_a, tmap_b, p);
+  if (tall) {
+    using C2 = Cfg<256, 2>;
+    MOC_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, C2::kSmemBytes));
+    gemm_tc_kernel<256, 2><<<grid, C2::kThreads, C2::kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, p);
+  } else if (bn == 256) {
+    using C1 = Cfg<256, 1>;
+    MOC_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C1::kSmemBytes));
+    gemm_tc_kernel<256, 1><<<grid, C1::kThreads, C1::kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, p);
   } else {
-    MOC_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     Cfg<128>::kSmemBytes));
-    gemm_tc_kernel<128><<<grid, kThreads, Cfg<128>::kSmemBytes, stream>>>(tmap_a, tmap_b, p);
+    using C0 = Cfg<128, 1>;
+    MOC_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C0::kSmemBytes));
+    gemm_tc_kernel<128, 1><<<grid, C0::kThreads, C0::kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, p);
   }
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
