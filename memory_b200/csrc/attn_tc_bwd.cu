@@ -109,26 +109,6 @@ __device__ __forceinline__ void issue_ss_pair(uint32_t d0, uint32_t d1, uint64_t
       : "memory");
 #undef MOC_SS_STEP
 }
-// Two TS products over 4 K steps with MN-major B:  [d0] += A0 * B0,  [d1] += A1 * B1, where A is packed bf16 in
-// tensor memory and K step kk of A starts at column a + (kk >> 1) * a_hi + (kk & 1) * 8.
-__device__ __forceinline__ void issue_ts_pair(uint32_t d0, uint32_t d1, uint32_t a0, uint32_t a1, uint32_t a_hi,
-                                              uint64_t b0, uint64_t b1, uint32_t idesc, uint32_t acc) {
-#define MOC_TS_STEP(KK, HI, LO, PACC)                                                          \
-  "mad.lo.u32 ca, %4, " #HI ", %2;\n\t add.u32 ca, ca, " #LO ";\n\t add.s64 tb, %5, " #KK "*128;\n\t" \
-  "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [ca], tb, %7, " PACC ";\n\t"                     \
-  "mad.lo.u32 ca, %4, " #HI ", %3;\n\t add.u32 ca, ca, " #LO ";\n\t add.s64 tb, %6, " #KK "*128;\n\t" \
-  "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [ca], tb, %7, " PACC ";\n\t"
-  asm volatile(
-      "{\n\t.reg .pred q, pa, pt;\n\t.reg .b64 tb;\n\t.reg .b32 ca;\n\t"
-      "elect.sync _|q, 0xffffffff;\n\t"
-      "setp.ne.b32 pa, %8, 0;\n\t"
-      "setp.eq.b32 pt, 0, 0;\n\t"
-      MOC_TS_STEP(0, 0, 0, "pa") MOC_TS_STEP(1, 0, 8, "pt") MOC_TS_STEP(2, 1, 0, "pt") MOC_TS_STEP(3, 1, 8, "pt")
-      "}"
-      ::"r"(d0), "r"(d1), "r"(a0), "r"(a1), "r"(a_hi), "l"(b0), "l"(b1), "r"(idesc), "r"(acc)
-      : "memory");
-#undef MOC_TS_STEP
-}
 // One TS product over 4 K steps with MN-major B: [d] += A * B, A K step kk at column a + 8 kk.
 __device__ __forceinline__ void issue_ts_single(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
 #define MOC_TS1_STEP(KK, PACC)                                                                 \
@@ -394,6 +374,7 @@ constexpr uint32_t kColST = 0, kColDPT = 64, kColDV = 128, kColDK = 192;   // dS
 
 struct DkvParams {
   __nv_bfloat16* d_kv;
+  int dkv_tma;             // d_kv written through staging blocks and TMA stores (n_sel % 32 == 0)
   const uint4* statb;
   int L, n_sel, H, HK;
   float scale, scale_log2;
@@ -416,7 +397,8 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
 // waits for the other in steady state.  P^T lives in shared memory so that S^T's columns are free early.
 __global__ void __launch_bounds__(kThreads, 2)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
-                       const __grid_constant__ CUtensorMap tmap_kv, DkvParams p) {
+                       const __grid_constant__ CUtensorMap tmap_kv, const __grid_constant__ CUtensorMap tmap_dkv,
+                       DkvParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t k_bar, q_full[kStages], q_empty[kStages], s_full, s_free, dp_full, p_full, p_free,
       ds_full, acc_bar;
@@ -557,7 +539,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const uint32_t sw = static_cast<uint32_t>(row & 7);
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
-      const int s = it % kStages;
       ok = mbar_wait(&s_full, it & 1, &abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -612,7 +593,42 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       ok = mbar_wait(&acc_bar, 0, &abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (ok) {
+    if (p.dkv_tma) {
+      // One thread owns one key row, so direct stores would scatter 16-byte pieces over 32 rows per instruction.
+      // The tile ring is idle now: each (lane quarter, dK | dV) gets a 32-row x 128-byte swizzled block there,
+      // filled by the two warps that own its column halves, and leaves as one TMA store.
+      const int quarter = warp & 3;
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {      // 0: dK (carries the softmax scale), 1: dV
+          uint32_t r[32];
+          tmem_ld32(tmem + lane_sel + (which ? kColDV : kColDK) + half * 32, r);
+          tmem_wait_ld();
+          const float f = which ? 1.f : p.scale;
+          const uint32_t row_addr = smem_u32(ring) + (quarter * 2 + which) * 4096 + lane * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t addr = row_addr + ((static_cast<uint32_t>(half * 4 + c) ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                         "r"(pack_bf16x2(__uint_as_float(r[8 * c + 0]) * f, __uint_as_float(r[8 * c + 1]) * f)),
+                         "r"(pack_bf16x2(__uint_as_float(r[8 * c + 2]) * f, __uint_as_float(r[8 * c + 3]) * f)),
+                         "r"(pack_bf16x2(__uint_as_float(r[8 * c + 4]) * f, __uint_as_float(r[8 * c + 5]) * f)),
+                         "r"(pack_bf16x2(__uint_as_float(r[8 * c + 6]) * f, __uint_as_float(r[8 * c + 7]) * f))
+                         : "memory");
+          }
+        }
+        fence_proxy_async();
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight row-owning warps, whatever `ok` is
+      if (ok && half == 0 && lane == 0 && key0 + quarter * 32 < p.n_sel) {
+        const int grow = b * p.n_sel + key0 + quarter * 32;
+        tma_store_2d(&tmap_dkv, ring + (quarter * 2) * 4096, kh * kD, grow);
+        tma_store_2d(&tmap_dkv, ring + (quarter * 2 + 1) * 4096, p.HK * kD + kh * kD, grow);
+        bulk_commit_group();
+        bulk_wait_all();
+      }
+    } else if (ok) {
       tc_fence_after();
       const int key = key0 + row;
       __nv_bfloat16* dst = p.d_kv + (static_cast<long long>(b) * p.n_sel + key) * (2 * p.HK * kD) + kh * kD + half * 32;
@@ -684,11 +700,14 @@ int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, c
   }
   if (parts & 4) {
     DkvParams p;
+    CUtensorMap tdkv = tkv;      // placeholder when the TMA-store epilogue is not used
+    p.dkv_tma = (s->n_sel % 32 == 0 && (reinterpret_cast<uintptr_t>(d_kv) & 15) == 0) ? 1 : 0;
+    if (p.dkv_tma && (rc = make_tmap_bf16_2d(&tdkv, d_kv, kvrows, kvcols, kvcols, 32, kD)) != MOC_OK) return rc;
     p.d_kv = static_cast<__nv_bfloat16*>(d_kv); p.statb = statb;
     p.L = L; p.n_sel = s->n_sel; p.H = H; p.HK = HK;
     p.scale = s->scale; p.scale_log2 = s->scale * kLog2e; p.status = status;
     dim3 grid(ceil_div(s->n_sel, kKeysB), HK, B);
-    attn_bwd_dkv_tc_kernel<<<grid, kThreads, kDkvSmem, stream>>>(tq64, tdo64, tkv, p);
+    attn_bwd_dkv_tc_kernel<<<grid, kThreads, kDkvSmem, stream>>>(tq64, tdo64, tkv, tdkv, p);
   }
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
