@@ -216,6 +216,27 @@ int moc_attn_bwd_static(const moc_attn_shape* s, const void* q, const void* kv, 
                         const void* d_o, void* d_q, void* d_kv, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Decode-time memory attention over a cache of projected bank rows.  The reference re-gathers and
+ * re-projects (S+k)*T bank rows per sequence at every generated token (inference/generate.py:194-210 ->
+ * model.py:624-692 -> memory_attention.py:241-243); it has no such cache.  Because the chapter weight
+ * multiplies a row before the linear projection, K = u_c * (norm(m) Wk^T): the per-layer cache
+ *   kv_bank [C*T, 2*HK*64] bf16 = norm(M) [Wk; Wv]^T   (built once per weight state with moc_gemm)
+ * gives the same attention from a gather of cached rows:
+ *   s_r = scale * u_c * <q, K_bank[r]>,  out = sum_r softmax_r(s) * u_c * V_bank[r]   (one joint softmax).
+ *   q, out [B, n_q, H*64] bf16; comb_idx [B, n_chapters] int32 (shared prefix first), comb_w [B, n_chapters]
+ *   fp32 as produced by moc_router_fwd; lse [B, n_q, H] fp32 (may be NULL).  Chapter ids outside the cache
+ *   raise MOC_DEV_BAD_INDEX in the status word and are skipped.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t batch, n_q, num_heads, num_kv_heads, head_dim, n_chapters, tokens_per_chapter;
+  float scale;
+} moc_decode_shape;
+
+int moc_decode_attn(const moc_decode_shape* s, const void* q, const void* kv_bank, int64_t bank_rows,
+                    const int32_t* comb_idx, const float* comb_w, void* out, float* lse, int32_t* status,
+                    void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Per-token chapter-sparse attention: the contract of memory_cross_attn(q, k, v, block_indices,
  * block_size, scale) (kernels-final/memory_cross_attn.py:1310-1366, 1387-1603, 1639-1652).
  *   q [B,TQ,HQ,D], k/v [B,TK,H,D], block_indices [B,TQ,H,S] int32, o [B,TQ,HQ,D], lse [B,TQ,HQ].

@@ -4,6 +4,7 @@ The operators exist only as CUDA kernels behind ``libmoc_b200.so``; build it wit
 ``python -m memory_b200.build``.  Public surface mirrors the reference's ``memory_transformer``
 modules for this path.
 """
+from .decode import MemoryDecoder, ProjectedBankCache, RoutingWindow
 from .functional import (SparseBankGrad, cross_attention, gather_chapters, memory_layer, route)
 from .memory_attention import MemoryCrossAttention
 from .memory_block import MemorySubBlock, RMSNorm
@@ -13,6 +14,6 @@ from .router import ChapterRouter, compute_total_router_loss
 
 __all__ = [
     "ChapterRouter", "compute_total_router_loss", "StandardMemoryBank", "ChapteredMemoryBank",
-    "MemoryCrossAttention", "MemorySubBlock", "RMSNorm", "memory_cross_attn", "memory_cross_attn_forward", "memory_layer", "route",
+    "MemoryCrossAttention", "MemoryDecoder", "ProjectedBankCache", "RoutingWindow", "MemorySubBlock", "RMSNorm", "memory_cross_attn", "memory_cross_attn_forward", "memory_layer", "route",
     "gather_chapters", "cross_attention", "SparseBankGrad",
 ]

@@ -47,6 +47,12 @@ class SparseAttnShape(C.Structure):
                 ("block_size", C.c_int32), ("scale", C.c_float), ("dtype", C.c_int32)]
 
 
+class DecodeShape(C.Structure):
+    _fields_ = [("batch", C.c_int32), ("n_q", C.c_int32), ("num_heads", C.c_int32), ("num_kv_heads", C.c_int32),
+                ("head_dim", C.c_int32), ("n_chapters", C.c_int32), ("tokens_per_chapter", C.c_int32),
+                ("scale", C.c_float)]
+
+
 P = C.c_void_p
 _PROTOTYPES = {
     "moc_last_error": (C.c_char_p, []),
@@ -71,6 +77,7 @@ _PROTOTYPES = {
     "moc_cast_bf16_to_f32": (C.c_int, [P, P, C.c_int64, P]),
     "moc_transpose": (C.c_int, [P, C.c_int32, P, C.c_int32, C.c_int32, C.c_int32, P]),
     "moc_pack_weights": (C.c_int, [C.c_int32, P, C.c_int32, P, P, P, P, P, P]),
+    "moc_decode_attn": (C.c_int, [P, P, P, C.c_int64, P, P, P, P, P, P]),
     "moc_norm_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "moc_norm_fwd": (C.c_int, [P, P, P, C.c_int32, C.c_float, C.c_int64, C.c_int32, P, P, P, P]),
     "moc_norm_bwd": (C.c_int, [P, P, P, P, P, C.c_int32, C.c_int64, C.c_int32, P, P, P, P, P]),

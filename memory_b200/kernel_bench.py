@@ -67,6 +67,28 @@ def main():
         torch.cuda.synchronize()
         ms = sum(a.elapsed_time(c) for a, c in evs) / len(evs)
         print(f"{name:14s} {ms:8.4f} ms  {flops / ms / 1e9:8.1f} TFLOP/s executed")
+    if "decode_attn" in only:
+        # generation step at the benchmark's decode shape: 64 sequences, one token each, 65 chapters of the cached
+        # 262,208-row K/V bank per sequence; bandwidth-bound, so the figure is bytes of cache rows per second
+        bd, c_total, t = 64, 4097, args.tokens_per_chapter
+        kv_bank = (torch.randn(c_total * t, 2 * d, device=dev) * 0.3).bfloat16()
+        qd = torch.randn(bd, 1, d, device=dev).bfloat16()
+        cidx = torch.stack([torch.cat([torch.zeros(1, dtype=torch.long), 1 + torch.randperm(c_total - 1)[:args.chapters - 1]])
+                            for _ in range(bd)]).to(torch.int32).to(dev)
+        cw = torch.rand(bd, args.chapters, device=dev) + 0.5
+        fn = lambda: ops.decode_attn(qd, kv_bank, cidx, cw, h, h, t, dh ** -0.5)
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        evs = []
+        for _ in range(args.iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        ms = sum(a.elapsed_time(c) for a, c in evs) / len(evs)
+        gbytes = bd * args.chapters * t * 2 * d * 2 / 1e9
+        print(f"{'decode_attn':14s} {ms:8.4f} ms  {gbytes / ms * 1e3:8.1f} GB/s of cached rows ({gbytes:.2f} GB per step)")
     L.check_device_status(dev)
 
 

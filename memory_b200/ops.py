@@ -455,3 +455,32 @@ def norm_bwd(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, stats: tor
                               L.ptr(dbias), L.ptr(ws), L.stream_ptr(x.device))
     L.check(rc, "moc_norm_bwd")
     return dx, dweight, dbias
+
+
+# --------------------------------------------------------------------------------------------
+# decode-time attention over cached projected bank rows
+# --------------------------------------------------------------------------------------------
+@_instrument("decode_attn", 1)
+def decode_attn(q: torch.Tensor, kv_bank: torch.Tensor, comb_idx: torch.Tensor, comb_w: torch.Tensor,
+                num_heads: int, num_kv_heads: int, tokens_per_chapter: int, scale: float, want_lse: bool = False):
+    """q [B, n_q, H*64] bf16, kv_bank [C*T, 2*HK*64] bf16, comb_idx / comb_w [B, S+k] -> out like q (and lse)."""
+    L.require_cuda(q, kv_bank, comb_idx, comb_w)
+    if q.dtype != torch.bfloat16 or kv_bank.dtype != torch.bfloat16:
+        raise TypeError("decode attention runs on a bf16 query and a bf16 K/V cache")
+    q, kv_bank = _contig(q), _contig(kv_bank)
+    b, n_q, hd = q.shape
+    d = hd // num_heads
+    if kv_bank.shape[1] != 2 * num_kv_heads * d:
+        raise ValueError("kv_bank must be [rows, 2 * num_kv_heads * head_dim]")
+    comb_idx = _contig(comb_idx.to(torch.int32))
+    comb_w = _contig(comb_w.float())
+    if tuple(comb_idx.shape) != tuple(comb_w.shape) or comb_idx.shape[0] != b:
+        raise ValueError("comb_idx and comb_w must both be [B, S+k]")
+    s = L.DecodeShape(b, n_q, num_heads, num_kv_heads, d, comb_idx.shape[1], int(tokens_per_chapter), float(scale))
+    out = torch.empty_like(q)
+    lse = torch.empty(b, n_q, num_heads, dtype=torch.float32, device=q.device) if want_lse else None
+    rc = L.lib().moc_decode_attn(C.byref(s), L.ptr(q), L.ptr(kv_bank), kv_bank.shape[0], L.ptr(comb_idx),
+                                 L.ptr(comb_w), L.ptr(out), L.ptr(lse), L.ptr(L.status_word(q.device)),
+                                 L.stream_ptr(q.device))
+    L.check(rc, "moc_decode_attn")
+    return (out, lse) if want_lse else out

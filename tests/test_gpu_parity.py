@@ -430,3 +430,36 @@ def test_two_stream_layer_equals_chained_nodes(dev):
     for k in g1:
         assert rel_err(g1[k], g2[k]) < 2e-3, k
     _status_ok(dev)
+
+
+@pytest.mark.parametrize("name,norm", [("head64_t64", None), ("gqa", None), ("gqa", "rms"), ("two_shared", "layernorm")])
+def test_decode_over_projected_bank_cache_matches_oracle(name, norm, dev):
+    """Generation mode: cached K/V rows of the whole bank, rolling routing window, one query token per sequence,
+    against the oracle's gather-and-project layer on the same states (bf16 bar)."""
+    import memory_b200 as M
+    case = CASES[name]
+    if case.hidden_dim // case.num_heads != 64:
+        pytest.skip("the cached decode path is the bf16 head_dim-64 path")
+    inp = {k: torch.from_numpy(v) for k, v in make_inputs(case).items()}
+    shape = shape_of(case)
+    shape.norm_type, shape.norm_eps = norm, 1e-5
+    g = torch.Generator().manual_seed(11)
+    cache = M.ProjectedBankCache(inp["bank"].to(dev), inp["wk"].to(dev), inp["wv"].to(dev), case.tokens_per_chapter,
+                                 case.num_shared_chapters, norm, 1e-5, chapters_per_pass=7)
+    dec = M.MemoryDecoder(cache, inp["router_w"].to(dev), inp["router_b"].to(dev), inp["wq"].to(dev),
+                          inp["wo"].to(dev), num_heads=case.num_heads, num_kv_heads=case.num_kv_heads,
+                          top_k=case.top_k, num_shared_chapters=case.num_shared_chapters,
+                          routed_scaling_factor=case.routed_scaling_factor)
+    window = M.RoutingWindow(window_size=24, strategy="hybrid")
+    prompt = inp["h_router"]                                     # [B, L, d]
+    states = window.prefill(prompt)
+    assert states.shape[1] == prompt.shape[1] and window.cache.shape[1] == 24
+    for step in range(3):
+        h_t = torch.randn(case.batch, 1, case.hidden_dim, generator=g)
+        states = window.step(h_t) if step else states           # first token routes on the whole prompt
+        out, info = dec.step(h_t.to(dev), states.to(dev))
+        ref = O.memory_layer(shape, states, h_t, inp["bank"], inp["router_w"], inp["router_b"], inp["wq"], inp["wk"],
+                             inp["wv"], inp["wo"], return_losses=False)
+        assert torch.equal(info["indices"].cpu(), ref["indices"])
+        assert rel_err(out, ref["out"]) < BF16
+    _status_ok(dev)
