@@ -84,6 +84,16 @@ int moc_router_bwd(const moc_router_shape* s, const float* w, const float* poole
                    void* d_h, int32_t accumulate_dh, void* workspace, size_t workspace_bytes,
                    int32_t* status, void* stream);
 
+/* moc_router_bwd in pieces, so that a caller can put them on different streams: parts is a bit set of
+ * 1 = d_logits, 2 = d_w and d_bias (reads d_logits), 4 = d_pooled and d_h (reads d_logits).  Same buffers in
+ * every call; moc_router_bwd is parts = 7.  No counterpart in the reference. */
+int moc_router_bwd_parts(const moc_router_shape* s, const float* w, const float* pooled, const float* probs,
+                         const int64_t* idx, const float* weights, const float* comb_w, const float* row_stats,
+                         const float* chapter_stats, const float* d_weights, const float* d_comb_w,
+                         const float* d_losses, float* d_logits, float* d_w, float* d_bias, float* d_pooled,
+                         void* d_h, int32_t accumulate_dh, void* workspace, size_t workspace_bytes, int32_t parts,
+                         int32_t* status, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Chapter gather.  Replaces ChapteredMemoryBank.get_chapters_batched (memory_bank.py:244-293), the
  * optional per-row normalisation (model.py:393-432) and the weight multiply (model.py:689-692).

@@ -657,13 +657,13 @@ extern "C" int moc_router_fwd(const moc_router_shape* s, const void* h, const fl
   return MOC_OK;
 }
 
-extern "C" int moc_router_bwd(const moc_router_shape* s, const float* w, const float* pooled,
-                              const float* probs, const int64_t* idx, const float* weights,
-                              const float* comb_w, const float* row_stats, const float* chapter_stats,
-                              const float* d_weights, const float* d_comb_w, const float* d_losses,
-                              float* d_logits, float* d_w, float* d_bias, float* d_pooled, void* d_h,
-                              int32_t accumulate_dh, void* workspace, size_t workspace_bytes,
-                              int32_t* status, void* stream_) {
+extern "C" int moc_router_bwd_parts(const moc_router_shape* s, const float* w, const float* pooled,
+                                    const float* probs, const int64_t* idx, const float* weights,
+                                    const float* comb_w, const float* row_stats, const float* chapter_stats,
+                                    const float* d_weights, const float* d_comb_w, const float* d_losses,
+                                    float* d_logits, float* d_w, float* d_bias, float* d_pooled, void* d_h,
+                                    int32_t accumulate_dh, void* workspace, size_t workspace_bytes, int32_t parts,
+                                    int32_t* status, void* stream_) {
   int rc = check_shape(s);
   if (rc != MOC_OK) return rc;
   MOC_REQUIRE(workspace_bytes >= ws_bytes(s), "router workspace too small");
@@ -674,22 +674,24 @@ extern "C" int moc_router_bwd(const moc_router_shape* s, const float* w, const f
   const int B = s->batch, L = s->seq, d = s->hidden_dim, C = s->num_chapters, S = s->num_shared;
   const int k_sel = k_selected(s);
   float* ws = static_cast<float*>(workspace);
-  {
+  if (parts & 1) {
     const size_t sm = static_cast<size_t>(C) * 4;
     MOC_CUDA_OK(cudaFuncSetAttribute(dlogits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
     dlogits_kernel<<<B, kSelectThreads, sm, stream>>>(probs, reinterpret_cast<const long long*>(idx), weights,
                                                       comb_w, row_stats, chapter_stats, d_weights, d_comb_w,
                                                       d_losses, d_logits, B, C, k_sel, S, s->routed_scale);
   }
-  {
+  if (parts & 2) {
     const size_t sm = static_cast<size_t>(8) * d * sizeof(float);
     MOC_CUDA_OK(cudaFuncSetAttribute(dweight_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
     dweight_kernel<<<ceil_div(C, 8 * kLogitsPerWarp), 256, sm, stream>>>(d_logits, pooled, d_w, d_bias, B, d, C);
   }
   const int nchunks = ceil_div(C, kDpChunk);
-  dpooled_partial_kernel<<<nchunks, 256, 0, stream>>>(d_logits, w, ws, B, d, C);
-  dpooled_finish_kernel<<<ceil_div(B * d * 8, 256), 256, 0, stream>>>(ws, d_pooled, nchunks, B * d);
-  if (d_h != nullptr) {
+  if (parts & 4) {
+    dpooled_partial_kernel<<<nchunks, 256, 0, stream>>>(d_logits, w, ws, B, d, C);
+    dpooled_finish_kernel<<<ceil_div(B * d * 8, 256), 256, 0, stream>>>(ws, d_pooled, nchunks, B * d);
+  }
+  if ((parts & 4) && d_h != nullptr) {
     const long long rows = static_cast<long long>(B) * L;
     const long long work = (d & 7) == 0 ? rows * (d >> 3) : rows * d;
     long long blocks = (work + 255) / 256;
@@ -701,4 +703,16 @@ extern "C" int moc_router_bwd(const moc_router_shape* s, const float* w, const f
   }
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
+}
+
+extern "C" int moc_router_bwd(const moc_router_shape* s, const float* w, const float* pooled,
+                              const float* probs, const int64_t* idx, const float* weights,
+                              const float* comb_w, const float* row_stats, const float* chapter_stats,
+                              const float* d_weights, const float* d_comb_w, const float* d_losses,
+                              float* d_logits, float* d_w, float* d_bias, float* d_pooled, void* d_h,
+                              int32_t accumulate_dh, void* workspace, size_t workspace_bytes,
+                              int32_t* status, void* stream_) {
+  return moc_router_bwd_parts(s, w, pooled, probs, idx, weights, comb_w, row_stats, chapter_stats, d_weights,
+                              d_comb_w, d_losses, d_logits, d_w, d_bias, d_pooled, d_h, accumulate_dh, workspace,
+                              workspace_bytes, 7, status, stream_);
 }

@@ -451,10 +451,15 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
         fuse_dh = ctx.same_h and need[0] and hr_dtype == ha_dtype
         if fuse_dh:
             main.wait_stream(side)      # the attention branch's d_h must be complete before the router adds to it
-        rb = ops.router_bwd(hr_shape, hr_dtype, router_w, r, top_k, num_shared, routed_scale,
-                            None if g_w is None else g_w.float(), d_cw,
-                            None if g_losses is None else g_losses.float(), want_dh=need[0],
-                            d_h_accum=d_h if fuse_dh else None)
+        # logit gradient on the main stream; the router-weight gradient (nothing downstream reads it) on the side
+        # stream beside the pooled / hidden-state gradient
+        rargs = (hr_shape, hr_dtype, router_w, r, top_k, num_shared, routed_scale,
+                 None if g_w is None else g_w.float(), d_cw, None if g_losses is None else g_losses.float())
+        rb = ops.router_bwd(*rargs, want_dh=need[0], parts=1)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            ops.router_bwd(*rargs, want_dh=need[0], parts=2, out=rb)
+        ops.router_bwd(*rargs, want_dh=need[0], d_h_accum=d_h if fuse_dh else None, parts=4, out=rb)
         main.wait_stream(side)
         d_rw = rb["d_w"].to(router_w.dtype) if need[3] else None
         d_rb = rb["d_bias"] if (has_rbias and need[4]) else None

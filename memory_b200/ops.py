@@ -92,37 +92,51 @@ def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     return out
 
 
-@_instrument("router_bwd", lambda *a, **k: 5 if (a[-1] if len(a) > 10 else k.get("want_dh")) else 4)
+def _router_bwd_launches(*a, **k):
+    parts = k.get("parts", 7)
+    want_dh = a[-1] if len(a) > 10 else k.get("want_dh")
+    return (1 if parts & 1 else 0) + (1 if parts & 2 else 0) + ((3 if want_dh else 2) if parts & 4 else 0)
+
+
+@_instrument(lambda *a, **k: "router_bwd" if k.get("parts", 7) == 7 else "router_bwd:parts%d" % k["parts"],
+             _router_bwd_launches)
 def router_bwd(h_shape, h_dtype, weight: torch.Tensor, saved: Dict[str, torch.Tensor], top_k: int,
                num_shared: int, routed_scale: float, d_weights: Optional[torch.Tensor],
                d_comb_w: Optional[torch.Tensor], d_losses: Optional[torch.Tensor],
-               want_dh: bool, d_h_accum: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
+               want_dh: bool, d_h_accum: Optional[torch.Tensor] = None, parts: int = 7,
+               out: Optional[Dict[str, torch.Tensor]] = None) -> Dict[str, torch.Tensor]:
     """``d_h_accum`` ([B, L, d] of the hidden-state dtype): the hidden-state gradient is added into it instead
-    of being written to a fresh tensor (the attention branch's gradient of the same hidden states)."""
+    of being written to a fresh tensor (the attention branch's gradient of the same hidden states).
+    ``parts`` (1 = d_logits, 2 = d_w / d_bias, 4 = d_pooled / d_h) runs a subset on the current stream; pass the
+    dict returned by the first call as ``out`` to the later ones so they share buffers."""
     b, l, d = h_shape
     c = weight.shape[0]
     dev = weight.device
     s = L.RouterShape(b, l, d, c, top_k, num_shared, float(routed_scale), L.dtype_code(h_dtype))
     f32 = dict(dtype=torch.float32, device=dev)
     weight = _contig(weight.float())
-    out = {"d_logits": torch.empty(b, c, **f32), "d_w": torch.empty(c, d, **f32), "d_bias": torch.empty(c, **f32),
-           "d_pooled": torch.empty(b, d, **f32),
-           "d_h": torch.empty(b, l, d, dtype=h_dtype, device=dev) if want_dh else None}
-    accumulate = 0
-    if want_dh and d_h_accum is not None:
-        if d_h_accum.dtype != h_dtype or tuple(d_h_accum.shape) != (b, l, d) or not d_h_accum.is_contiguous():
-            raise ValueError("d_h_accum must be a contiguous [B, L, d] tensor of the hidden-state dtype")
-        out["d_h"], accumulate = d_h_accum, 1
     lib = L.lib()
     ws_bytes = lib.moc_router_workspace_bytes(C.byref(s))
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-    rc = lib.moc_router_bwd(C.byref(s), L.ptr(weight), L.ptr(saved["pooled"]), L.ptr(saved["probs"]),
-                            L.ptr(saved["idx"]), L.ptr(saved["weights"]), L.ptr(saved["comb_w"]),
-                            L.ptr(saved["row_stats"]), L.ptr(saved["chapter_stats"]),
-                            L.ptr(_contig(d_weights)), L.ptr(_contig(d_comb_w)), L.ptr(_contig(d_losses)),
-                            L.ptr(out["d_logits"]), L.ptr(out["d_w"]), L.ptr(out["d_bias"]), L.ptr(out["d_pooled"]),
-                            L.ptr(out["d_h"]), accumulate, L.ptr(ws), ws_bytes, L.ptr(L.status_word(dev)), L.stream_ptr(dev))
-    L.check(rc, "moc_router_bwd")
+    if out is None:
+        out = {"d_logits": torch.empty(b, c, **f32), "d_w": torch.empty(c, d, **f32), "d_bias": torch.empty(c, **f32),
+               "d_pooled": torch.empty(b, d, **f32), "d_h": None, "_ws": torch.empty(ws_bytes, dtype=torch.uint8, device=dev)}
+    accumulate = 0
+    if want_dh and (parts & 4):
+        if d_h_accum is not None:
+            if d_h_accum.dtype != h_dtype or tuple(d_h_accum.shape) != (b, l, d) or not d_h_accum.is_contiguous():
+                raise ValueError("d_h_accum must be a contiguous [B, L, d] tensor of the hidden-state dtype")
+            out["d_h"], accumulate = d_h_accum, 1
+        else:
+            out["d_h"] = torch.empty(b, l, d, dtype=h_dtype, device=dev)
+    rc = lib.moc_router_bwd_parts(C.byref(s), L.ptr(weight), L.ptr(saved["pooled"]), L.ptr(saved["probs"]),
+                                  L.ptr(saved["idx"]), L.ptr(saved["weights"]), L.ptr(saved["comb_w"]),
+                                  L.ptr(saved["row_stats"]), L.ptr(saved["chapter_stats"]),
+                                  L.ptr(_contig(d_weights)), L.ptr(_contig(d_comb_w)), L.ptr(_contig(d_losses)),
+                                  L.ptr(out["d_logits"]), L.ptr(out["d_w"]), L.ptr(out["d_bias"]),
+                                  L.ptr(out["d_pooled"]), L.ptr(out["d_h"]) if (parts & 4) else None, accumulate,
+                                  L.ptr(out["_ws"]), ws_bytes, int(parts), L.ptr(L.status_word(dev)),
+                                  L.stream_ptr(dev))
+    L.check(rc, "moc_router_bwd_parts")
     return out
 
 
