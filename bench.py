@@ -174,7 +174,7 @@ def run_reference_arm(args):
 
 
 def workload_config(cfg, n_gpus):
-    return {"workload": "paper-shape single memory layer fwd+bwd (BASELINE configs[1])",
+    return {"workload": "paper-shape single memory layer fwd+bwd (bf16 activations, fp32 router; the configuration the headline metric is quoted on)",
             "batch_per_gpu": cfg["batch"], "global_batch": cfg["batch"] * n_gpus, "seq_len": cfg["seq"],
             "hidden_dim": cfg["hidden_dim"], "heads": f"{cfg['num_heads']}x{cfg['hidden_dim'] // cfg['num_heads']}",
             "bank_rows": cfg["num_chapters"] * cfg["tokens_per_chapter"], "chapters": cfg["num_chapters"],

@@ -137,7 +137,7 @@ def run_reference(ref, case, inputs, autocast_bf16=False):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     ref = import_reference(args.reference)
