@@ -7,9 +7,8 @@
 // and a per-layer cache  KV_bank = norm(M) [Wk; Wv]^T  (bf16, [C*T, 2*HK*64]) turns the step into a gather of
 // cached rows scaled by the chapter weight, followed by one joint softmax over all selected keys:
 //   s_r = scale * u_c * <q, K_bank[r]>,   out = sum_r softmax(s)_r * u_c * V_bank[r].
-// The kernel is bound by HBM: one CTA per (sequence, query token, head) streams 128-byte K and V rows; every lane
-// keeps its own running (max, sum, 64 accumulators) over the rows it owns, so nothing is exchanged between lanes
-// until the end.
+// The kernel is bound by HBM: one CTA per (sequence, query token, head) streams the 128-byte K and V slices of the
+// selected rows with coalesced requests and keeps the running softmax state in registers.
 #include "moc_common.cuh"
 
 namespace moc {
@@ -29,55 +28,30 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
   }
 }
 
-__global__ void __launch_bounds__(kDecThreads, 1)
+// Lane layout: eight lanes share a row (16 bytes of its 128-byte K slice and of its V slice each), so one warp load
+// instruction touches four whole 128-byte lines instead of 32 scattered 16-byte pieces; a warp walks four rows per
+// step.  Every 8-lane group keeps a running (max, sum) and each lane 8 of the 64 accumulators.
+constexpr int kDecUnroll = 8;        // steps (of four rows) whose loads are issued before any arithmetic
+
+__global__ void __launch_bounds__(kDecThreads, 2)
 decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv_bank,
                    long long bank_rows, const int* __restrict__ comb_idx, const float* __restrict__ comb_w,
                    __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int n_q, int H, int HK, int n_ch, int T,
                    float scale, int* __restrict__ status) {
   __shared__ float red[kDecWarps][kDD + 2];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rg = lane >> 3, part = lane & 7;          // row group 0..3, 8-element slice of the head dimension
   const int h = blockIdx.x, iq = blockIdx.y, b = blockIdx.z;
   const int kh = h / (H / HK);
   const long long row_elems = 2ll * HK * kDD;
 
-  // the query lives in shared memory (broadcast reads): registers go to rows in flight instead
-  __shared__ __align__(16) float q_s[kDD];
-  if (threadIdx.x < kDD)
-    q_s[threadIdx.x] = __bfloat162float(q[(static_cast<long long>(b) * n_q + iq) * H * kDD + h * kDD + threadIdx.x]);
-  __syncthreads();
-  const float4* q4 = reinterpret_cast<const float4*>(q_s);
+  float qf[8];
+  unpack8(*reinterpret_cast<const uint4*>(q + (static_cast<long long>(b) * n_q + iq) * H * kDD + h * kDD + part * 8), qf);
   const float c2 = scale * kDecLog2e;
-  float m = -INFINITY, l = 0.f;          // running maximum (log2 domain) and sum of this lane's rows
-  float acc[kDD];
+  float m = -INFINITY, l = 0.f;          // running maximum (log2 domain) and sum of this lane group's rows
+  float acc[8];
 #pragma unroll
-  for (int i = 0; i < kDD; ++i) acc[i] = 0.f;
-
-  // one row: score against the query, then fold it into this lane's running softmax state
-  auto fold = [&](const uint4 (&kr)[kDD / 8], const uint4 (&vr)[kDD / 8], float u) {
-    float dot = 0.f;
-#pragma unroll
-    for (int i = 0; i < kDD / 8; ++i) {
-      float f[8];
-      unpack8(kr[i], f);
-      const float4 qa = q4[2 * i], qb = q4[2 * i + 1];
-      dot = fmaf(qa.x, f[0], dot); dot = fmaf(qa.y, f[1], dot); dot = fmaf(qa.z, f[2], dot); dot = fmaf(qa.w, f[3], dot);
-      dot = fmaf(qb.x, f[4], dot); dot = fmaf(qb.y, f[5], dot); dot = fmaf(qb.z, f[6], dot); dot = fmaf(qb.w, f[7], dot);
-    }
-    const float s = dot * u * c2;
-    const float m_new = fmaxf(m, s);
-    const float corr = exp2f(m - m_new);      // 0 on the first row (m = -inf)
-    const float pr = exp2f(s - m_new);
-    l = l * corr + pr;
-    const float pu = pr * u;
-#pragma unroll
-    for (int i = 0; i < kDD / 8; ++i) {
-      float f[8];
-      unpack8(vr[i], f);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[8 * i + j] = fmaf(acc[8 * i + j], corr, pu * f[j]);
-    }
-    m = m_new;
-  };
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 
   for (int c = warp; c < n_ch; c += kDecWarps) {
     const int ch = comb_idx[b * n_ch + c];
@@ -86,42 +60,57 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       continue;
     }
     const float u = comb_w[b * n_ch + c];
-    const __nv_bfloat16* base = kv_bank + static_cast<long long>(ch) * T * row_elems + kh * kDD;
-    for (int r = lane; r < T; r += 64) {
-      // two rows per pass: 4 KB per lane pair of rows requested before any arithmetic
-      const bool two = r + 32 < T;
-      const uint4* kp0 = reinterpret_cast<const uint4*>(base + r * row_elems);
-      const uint4* vp0 = reinterpret_cast<const uint4*>(base + r * row_elems + HK * kDD);
-      const uint4* kp1 = reinterpret_cast<const uint4*>(base + (two ? r + 32 : r) * row_elems);
-      const uint4* vp1 = reinterpret_cast<const uint4*>(base + (two ? r + 32 : r) * row_elems + HK * kDD);
-      uint4 k0[kDD / 8], v0[kDD / 8], k1[kDD / 8], v1[kDD / 8];
+    const __nv_bfloat16* base = kv_bank + static_cast<long long>(ch) * T * row_elems + kh * kDD + part * 8;
+    for (int r0 = 0; r0 < T; r0 += 4 * kDecUnroll) {
+      uint4 kr[kDecUnroll], vr[kDecUnroll];
 #pragma unroll
-      for (int i = 0; i < kDD / 8; ++i) k0[i] = kp0[i];
+      for (int sidx = 0; sidx < kDecUnroll; ++sidx) {
+        const int r = r0 + sidx * 4 + rg;
+        const __nv_bfloat16* rp = base + static_cast<long long>(r < T ? r : 0) * row_elems;
+        kr[sidx] = *reinterpret_cast<const uint4*>(rp);
+        vr[sidx] = *reinterpret_cast<const uint4*>(rp + HK * kDD);
+      }
 #pragma unroll
-      for (int i = 0; i < kDD / 8; ++i) k1[i] = kp1[i];
+      for (int sidx = 0; sidx < kDecUnroll; ++sidx) {
+        const int r = r0 + sidx * 4 + rg;
+        float f[8];
+        unpack8(kr[sidx], f);
+        float dot = 0.f;
 #pragma unroll
-      for (int i = 0; i < kDD / 8; ++i) v0[i] = vp0[i];
+        for (int j = 0; j < 8; ++j) dot = fmaf(qf[j], f[j], dot);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+        if (r < T) {                                    // uniform within the 8-lane group
+          const float sc = dot * u * c2;
+          const float m_new = fmaxf(m, sc);
+          const float corr = exp2f(m - m_new);          // 0 on the first row (m = -inf)
+          const float pr = exp2f(sc - m_new);
+          l = l * corr + pr;
+          const float pu = pr * u;
+          unpack8(vr[sidx], f);
 #pragma unroll
-      for (int i = 0; i < kDD / 8; ++i) v1[i] = vp1[i];
-      fold(k0, v0, u);
-      if (two) fold(k1, v1, u);
+          for (int j = 0; j < 8; ++j) acc[j] = fmaf(acc[j], corr, pu * f[j]);
+          m = m_new;
+        }
+      }
     }
   }
 
-  // lanes -> warp
+  // row groups -> warp (lanes with the same `part` hold the same 8 output elements)
   float mw = m;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mw = fmaxf(mw, __shfl_xor_sync(0xffffffffu, mw, o));
+  mw = fmaxf(mw, __shfl_xor_sync(0xffffffffu, mw, 8));
+  mw = fmaxf(mw, __shfl_xor_sync(0xffffffffu, mw, 16));
   const float f_lane = (m == -INFINITY) ? 0.f : exp2f(m - mw);
   l *= f_lane;
+  l += __shfl_xor_sync(0xffffffffu, l, 8);
+  l += __shfl_xor_sync(0xffffffffu, l, 16);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-#pragma unroll
-  for (int i = 0; i < kDD; ++i) {
-    float a = acc[i] * f_lane;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-    if (lane == 0) red[warp][i] = a;
+  for (int j = 0; j < 8; ++j) {
+    float a = acc[j] * f_lane;
+    a += __shfl_xor_sync(0xffffffffu, a, 8);
+    a += __shfl_xor_sync(0xffffffffu, a, 16);
+    if (rg == 0) red[warp][part * 8 + j] = a;
   }
   if (lane == 0) {
     red[warp][kDD] = mw;
