@@ -72,6 +72,14 @@ int moc_router_fwd(const moc_router_shape* s, const void* h, const float* w, con
                    int32_t* comb_idx, float* comb_w, float* row_stats, float* chapter_stats, float* losses,
                    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
+/* moc_router_fwd in two pieces: parts bit 1 = pooling, logits, selection (everything the gather needs),
+ * bit 2 = the loss terms (reads probs / idx / row_stats of bit 1).  A caller can wait for bit 1 only and let the
+ * losses finish beside the gather.  moc_router_fwd is parts = 3.  No counterpart in the reference. */
+int moc_router_fwd_parts(const moc_router_shape* s, const void* h, const float* w, const float* bias,
+                         float* pooled, float* logits, float* probs, int64_t* idx, float* weights,
+                         int32_t* comb_idx, float* comb_w, float* row_stats, float* chapter_stats, float* losses,
+                         void* workspace, size_t workspace_bytes, int32_t parts, int32_t* status, void* stream);
+
 /* Backward of the above (autograd of router.py:94-156,197-260 and model.py:356-391).
  * d_weights [B,k'] and d_comb_w [B,S+k'] are the incoming gradients of the two weight outputs (either
  * may be NULL); d_losses [4] (device) the incoming gradients of the four loss scalars (NULL = none).

@@ -59,6 +59,7 @@ _PROTOTYPES = {
     "moc_abi_version": (C.c_int, []),
     "moc_router_workspace_bytes": (C.c_size_t, [C.POINTER(RouterShape)]),
     "moc_router_fwd": (C.c_int, [C.POINTER(RouterShape)] + [P] * 13 + [P, C.c_size_t, P, P]),
+    "moc_router_fwd_parts": (C.c_int, [C.POINTER(RouterShape)] + [P] * 13 + [P, C.c_size_t, C.c_int32, P, P]),
     "moc_router_bwd": (C.c_int, [C.POINTER(RouterShape)] + [P] * 16 + [C.c_int32, P, C.c_size_t, P, P]),
     "moc_router_bwd_parts": (C.c_int, [C.POINTER(RouterShape)] + [P] * 16 + [C.c_int32, P, C.c_size_t, C.c_int32, P, P]),
     "moc_gather_rows_fwd": (C.c_int, [P, C.c_int32, C.c_int64, C.c_int32, C.c_int32, P, P, C.c_int32,

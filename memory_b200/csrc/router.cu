@@ -611,11 +611,11 @@ using namespace moc;
 
 extern "C" size_t moc_router_workspace_bytes(const moc_router_shape* s) { return s ? ws_bytes(s) : 0; }
 
-extern "C" int moc_router_fwd(const moc_router_shape* s, const void* h, const float* w, const float* bias,
-                              float* pooled, float* logits, float* probs, int64_t* idx, float* weights,
-                              int32_t* comb_idx, float* comb_w, float* row_stats, float* chapter_stats,
-                              float* losses, void* workspace, size_t workspace_bytes, int32_t* status,
-                              void* stream_) {
+extern "C" int moc_router_fwd_parts(const moc_router_shape* s, const void* h, const float* w, const float* bias,
+                                    float* pooled, float* logits, float* probs, int64_t* idx, float* weights,
+                                    int32_t* comb_idx, float* comb_w, float* row_stats, float* chapter_stats,
+                                    float* losses, void* workspace, size_t workspace_bytes, int32_t parts,
+                                    int32_t* status, void* stream_) {
   int rc = check_shape(s);
   if (rc != MOC_OK) return rc;
   MOC_REQUIRE(workspace_bytes >= ws_bytes(s), "router workspace too small");
@@ -629,6 +629,7 @@ extern "C" int moc_router_fwd(const moc_router_shape* s, const void* h, const fl
   float* loss_partial = ws + (ws_bytes(s) / sizeof(float) - static_cast<size_t>(ceil_div(C, kLossChunk)) * 3);
 
   dim3 pg(B, kPoolSplits);
+  if (parts & 1) {
   if (s->h_dtype == MOC_F32)
     pool_partial_kernel<float><<<pg, 256, 0, stream>>>(static_cast<const float*>(h), ws, L, d);
   else
@@ -646,7 +647,8 @@ extern "C" int moc_router_fwd(const moc_router_shape* s, const void* h, const fl
     select_kernel<<<B, kSelectThreads, sm, stream>>>(logits, probs, reinterpret_cast<long long*>(idx), weights,
                                                      comb_idx, comb_w, row_stats, C, k_sel, S, s->routed_scale);
   }
-  if (losses != nullptr) {
+  }
+  if ((parts & 2) && losses != nullptr) {
     MOC_REQUIRE(chapter_stats != nullptr, "chapter_stats is NULL");
     const int nblk = ceil_div(C, kLossChunk);
     loss_partial_kernel<<<nblk, kLossChunk, 0, stream>>>(probs, reinterpret_cast<const long long*>(idx),
@@ -655,6 +657,15 @@ extern "C" int moc_router_fwd(const moc_router_shape* s, const void* h, const fl
   }
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
+}
+
+extern "C" int moc_router_fwd(const moc_router_shape* s, const void* h, const float* w, const float* bias,
+                              float* pooled, float* logits, float* probs, int64_t* idx, float* weights,
+                              int32_t* comb_idx, float* comb_w, float* row_stats, float* chapter_stats,
+                              float* losses, void* workspace, size_t workspace_bytes, int32_t* status,
+                              void* stream_) {
+  return moc_router_fwd_parts(s, h, w, bias, pooled, logits, probs, idx, weights, comb_idx, comb_w, row_stats,
+                              chapter_stats, losses, workspace, workspace_bytes, 3, status, stream_);
 }
 
 extern "C" int moc_router_bwd_parts(const moc_router_shape* s, const float* w, const float* pooled,

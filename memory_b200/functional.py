@@ -327,7 +327,12 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
 
         side.wait_stream(main)
         with torch.cuda.stream(side):
-            r = ops.router_fwd(h_router, router_w, router_b, top_k, num_shared, routed_scale, with_losses)
+            r = ops.router_fwd(h_router, router_w, router_b, top_k, num_shared, routed_scale, with_losses, parts=1)
+            routed = torch.cuda.Event()
+            routed.record(side)          # the gather needs nothing after this point of the side stream
+            if with_losses:
+                ops.router_fwd(h_router, router_w, router_b, top_k, num_shared, routed_scale, with_losses, parts=2,
+                               out=r)
             seg = ops.chapter_segments(r["comb_idx"], num_chapters)
 
         # main stream meanwhile: bf16 weights (+ transposes for the backward pass), query projection
@@ -349,7 +354,7 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
             h2 = ops.cast(x2, cd)
         q = ops.gemm(h2, wq_c, tag="q_proj")
 
-        main.wait_stream(side)
+        main.wait_event(routed)
         k_sel = r["idx"].shape[1]
         # the reference only normalises when both a shared and a routed slice exist (model.py:413-418)
         norm = row_norm if (num_shared > 0 and k_sel > 0) else None
@@ -362,6 +367,7 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
         res = (x2 if x2.dtype == torch.float32 else x2.float()) if add_residual else None
         out_dtype = h_attn.dtype if h_attn.dtype in (torch.float32, cd) else cd
         out = ops.gemm(o.view(b * l, -1), wo_c, out_dtype=out_dtype, residual=res, tag="o_proj")
+        main.wait_stream(side)           # loss terms and chapter segments finished beside the attention
 
         ctx.cfg = cfg
         ctx.norm_row = norm

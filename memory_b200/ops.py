@@ -57,9 +57,19 @@ def router_selected_k(num_chapters: int, top_k: int, num_shared: int) -> int:
     return max(0, min(int(top_k), int(num_chapters) - int(num_shared)))
 
 
-@_instrument("router_fwd", lambda *a, **k: 6 if (a[6] if len(a) > 6 else k.get("with_losses")) else 4)
+def _router_fwd_launches(*a, **k):
+    parts = k.get("parts", 3)
+    with_losses = a[6] if len(a) > 6 else k.get("with_losses")
+    return (4 if parts & 1 else 0) + (2 if (parts & 2) and with_losses else 0)
+
+
+@_instrument(lambda *a, **k: "router_fwd" if k.get("parts", 3) == 3 else "router_fwd:parts%d" % k["parts"],
+             _router_fwd_launches)
 def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top_k: int,
-               num_shared: int, routed_scale: float, with_losses: bool) -> Dict[str, torch.Tensor]:
+               num_shared: int, routed_scale: float, with_losses: bool, parts: int = 3,
+               out: Optional[Dict[str, torch.Tensor]] = None) -> Dict[str, torch.Tensor]:
+    """``parts`` (1 = pooling, logits, selection; 2 = loss terms) runs a subset on the current stream; pass the dict
+    returned by the first call as ``out`` to the second."""
     L.require_cuda(h, weight, bias)
     if h.dim() != 3:
         raise ValueError(f"hidden_states must be 3D (B, T, D), got shape {tuple(h.shape)}")
@@ -72,23 +82,24 @@ def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     dev = h.device
     s = _router_shape(h, c, top_k, num_shared, routed_scale)
     f32 = dict(dtype=torch.float32, device=dev)
-    out = {
-        "pooled": torch.empty(b, d, **f32), "logits": torch.empty(b, c, **f32), "probs": torch.empty(b, c, **f32),
-        "idx": torch.empty(b, k, dtype=torch.int64, device=dev), "weights": torch.empty(b, k, **f32),
-        "comb_idx": torch.empty(b, num_shared + k, dtype=torch.int32, device=dev),
-        "comb_w": torch.empty(b, num_shared + k, **f32),
-        "row_stats": torch.empty(b, 4, **f32), "chapter_stats": torch.empty(2, c, **f32),
-        "losses": torch.empty(4, **f32) if with_losses else None,
-    }
     lib = L.lib()
     ws_bytes = lib.moc_router_workspace_bytes(C.byref(s))
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-    rc = lib.moc_router_fwd(C.byref(s), L.ptr(h), L.ptr(weight), L.ptr(bias), L.ptr(out["pooled"]),
-                            L.ptr(out["logits"]), L.ptr(out["probs"]), L.ptr(out["idx"]), L.ptr(out["weights"]),
-                            L.ptr(out["comb_idx"]), L.ptr(out["comb_w"]), L.ptr(out["row_stats"]),
-                            L.ptr(out["chapter_stats"]), L.ptr(out["losses"]), L.ptr(ws), ws_bytes,
-                            L.ptr(L.status_word(dev)), L.stream_ptr(dev))
-    L.check(rc, "moc_router_fwd")
+    if out is None:
+        out = {
+            "pooled": torch.empty(b, d, **f32), "logits": torch.empty(b, c, **f32), "probs": torch.empty(b, c, **f32),
+            "idx": torch.empty(b, k, dtype=torch.int64, device=dev), "weights": torch.empty(b, k, **f32),
+            "comb_idx": torch.empty(b, num_shared + k, dtype=torch.int32, device=dev),
+            "comb_w": torch.empty(b, num_shared + k, **f32),
+            "row_stats": torch.empty(b, 4, **f32), "chapter_stats": torch.empty(2, c, **f32),
+            "losses": torch.empty(4, **f32) if with_losses else None,
+            "_ws": torch.empty(ws_bytes, dtype=torch.uint8, device=dev),
+        }
+    rc = lib.moc_router_fwd_parts(C.byref(s), L.ptr(h), L.ptr(weight), L.ptr(bias), L.ptr(out["pooled"]),
+                                  L.ptr(out["logits"]), L.ptr(out["probs"]), L.ptr(out["idx"]), L.ptr(out["weights"]),
+                                  L.ptr(out["comb_idx"]), L.ptr(out["comb_w"]), L.ptr(out["row_stats"]),
+                                  L.ptr(out["chapter_stats"]), L.ptr(out["losses"]), L.ptr(out["_ws"]), ws_bytes,
+                                  int(parts), L.ptr(L.status_word(dev)), L.stream_ptr(dev))
+    L.check(rc, "moc_router_fwd_parts")
     return out
 
 
