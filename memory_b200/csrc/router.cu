@@ -61,10 +61,48 @@ __global__ void pool_partial_kernel(const T* __restrict__ h, float* __restrict__
   const int t0 = sp * rows_per;
   const int t1 = min(L, t0 + rows_per);
   const T* base = h + (static_cast<long long>(b) * L) * d;
+  float* dst = partial + (static_cast<long long>(b) * kPoolSplits + sp) * d;
+  if (sizeof(T) == 2 && (d & 7) == 0 && (reinterpret_cast<uintptr_t>(h) & 15) == 0) {
+    // bf16 rows in 16-byte pieces: eight columns per thread, four independent row loads in flight
+    for (int c8 = threadIdx.x; c8 < (d >> 3); c8 += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      const uint4* col = reinterpret_cast<const uint4*>(base) + c8;
+      const long long stride = d >> 3;
+      int t = t0;
+      for (; t + 4 <= t1; t += 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = col[(t + i) * stride];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] += __uint_as_float(w[j] << 16);
+            acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+          }
+        }
+      }
+      for (; t < t1; ++t) {
+        const uint4 v = col[t * stride];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] += __uint_as_float(w[j] << 16);
+          acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dst[c8 * 8 + j] = acc[j];
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float acc = 0.f;
     for (int t = t0; t < t1; ++t) acc += to_f32(base[static_cast<long long>(t) * d + c]);
-    partial[(static_cast<long long>(b) * kPoolSplits + sp) * d + c] = acc;
+    dst[c] = acc;
   }
 }
 __global__ void pool_finish_kernel(const float* __restrict__ partial, float* __restrict__ pooled, int L, int d,
@@ -83,6 +121,18 @@ __global__ void logits_kernel(const float* __restrict__ pooled, const float* __r
   extern __shared__ float sp[];   // [8][d]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool vec = (d & 3) == 0;
+  // the first chapter's weight row is requested before the pooled states are staged, so both fetches overlap
+  float4 wpre[8];
+  const bool pre = vec && d <= 1024 && kLogitsPerWarp == 1;
+  if (pre) {
+    const int c = blockIdx.x * (blockDim.x >> 5) + warp;
+    const float4* w4 = reinterpret_cast<const float4*>(w + static_cast<long long>(c < C ? c : 0) * d);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int k = lane + 32 * i;
+      wpre[i] = (k < d / 4) ? w4[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   for (int b0 = 0; b0 < B; b0 += 8) {
     const int nb = min(8, B - b0);
     __syncthreads();
@@ -102,7 +152,7 @@ __global__ void logits_kernel(const float* __restrict__ pooled, const float* __r
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int k = lane + 32 * i;
-          wv[i] = (k < d / 4) ? w4[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+          wv[i] = pre ? wpre[i] : ((k < d / 4) ? w4[k] : make_float4(0.f, 0.f, 0.f, 0.f));
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
