@@ -19,15 +19,15 @@ namespace {
 constexpr int kQ = 128;          // queries per CTA
 constexpr int kKeys = 64;        // keys per tile
 constexpr int kD = 64;           // head dim
-constexpr int kStages = 2;       // K/V ring depth
+constexpr int kStages = 3;       // K/V ring depth (K_j is read one tile before V_j)
 constexpr int kThreads = 192;    // 4 softmax warps + TMA warp + MMA warp
 constexpr int kQBytes = kQ * kD * 2;
 constexpr int kTileBytes = kKeys * kD * 2;
 constexpr int kSmemBytes = kQBytes + kStages * 2 * kTileBytes + 1024;
-constexpr int kTmemCols = 128;
-constexpr uint32_t kColS = 0;      // S: columns [0,64)
-constexpr uint32_t kColP = 0;      // P as packed bf16 over the first 32 columns of S
-constexpr uint32_t kColO = 64;     // O accumulator: 64 columns
+constexpr int kTmemCols = 256;
+constexpr uint32_t kColS = 0;      // S buffers: columns [0,64) and [64,128), tile j uses buffer j & 1
+constexpr uint32_t kColP = 0;      // P_j as packed bf16 over the first 32 columns of its S buffer
+constexpr uint32_t kColO = 128;    // O accumulator: 64 columns
 constexpr float kRescaleThreshold = 8.0f;
 
 struct FwdParams {
@@ -80,11 +80,11 @@ __device__ __forceinline__ void issue_ts_single(uint32_t d, uint32_t a, uint64_t
 #undef MOC_TS1_STEP
 }
 
-__global__ void __launch_bounds__(kThreads, 4)
+__global__ void __launch_bounds__(kThreads, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
                    FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t q_bar, kv_full[kStages], kv_empty[kStages], s_full, p_full, pv_bar;
+  __shared__ __align__(8) uint64_t q_bar, kv_full[kStages], kv_empty[kStages], s_full[2], p_full, pv_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -102,7 +102,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     abort_flag = 0;
     mbar_init(&q_bar, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(&s_full, 1);
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
     mbar_init(&p_full, 128);
     mbar_init(&pv_bar, 1);
     fence_mbar_init();
@@ -145,28 +146,33 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const uint64_t v_desc0 = umma_desc_sw128(smem_u32(kv_s) + kTileBytes, 8192, 1024);
       constexpr uint64_t kStageOff = (2 * kTileBytes) >> 4;
       bool ok = mbar_wait_w(&q_bar, 0, &abort_flag, p.status);
-      // order: S_0, then per tile PV_j followed by S_{j+1}.  S_{j+1} overwrites the columns P_j lives
-      // in; tcgen05.mma instructions of one thread execute in issue order, so PV_j has read them.
-      for (int j = 0; j <= n_tiles && ok; ++j) {
-        if (j > 0) {
-          const int jp = j - 1, s = jp % kStages;
-          ok = mbar_wait_w(&p_full, jp & 1, &abort_flag, p.status);
+      // Two S buffers: S_{j+1} is issued before PV_j, so the tensor pipe computes the next scores while the row
+      // owners exponentiate the current ones.  S_{j+1} overwrites the buffer P_{j-1} lived in; tcgen05.mma
+      // instructions of one thread execute in issue order, so PV_{j-1} has read it.
+      if (ok && n_tiles > 0) {
+        ok = mbar_wait_w(&kv_full[0], 0, &abort_flag, p.status);
+        if (ok) {
+          tc_fence_after();
+          issue_ss_single(tmem + kColS, q_desc, k_desc0, idesc_s);
+          tc_commit_w(&s_full[0]);
+        }
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          const int sn = (j + 1) % kStages;
+          ok = mbar_wait_w(&kv_full[sn], ((j + 1) / kStages) & 1, &abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
-          const uint64_t vd = v_desc0 + s * kStageOff;
-          issue_ts_single(tmem + kColO, tmem + kColP, vd, idesc_o, jp > 0 ? 1u : 0u);
-          tc_commit_w(&kv_empty[s]);
-          tc_commit_w(&pv_bar);
+          issue_ss_single(tmem + kColS + ((j + 1) & 1) * 64, q_desc, k_desc0 + sn * kStageOff, idesc_s);
+          tc_commit_w(&s_full[(j + 1) & 1]);
         }
-        if (j < n_tiles) {
-          const int s = j % kStages;
-          ok = mbar_wait_w(&kv_full[s], (j / kStages) & 1, &abort_flag, p.status);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t kd = k_desc0 + s * kStageOff;
-          issue_ss_single(tmem + kColS, q_desc, kd, idesc_s);
-          tc_commit_w(&s_full);
-        }
+        const int s = j % kStages;
+        ok = mbar_wait_w(&p_full, j & 1, &abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        issue_ts_single(tmem + kColO, tmem + kColP + (j & 1) * 64, v_desc0 + s * kStageOff, idesc_o, j > 0 ? 1u : 0u);
+        tc_commit_w(&kv_empty[s]);
+        tc_commit_w(&pv_bar);
       }
     }
   } else {
@@ -176,90 +182,69 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = mbar_wait(&s_full, j & 1, &abort_flag, p.status);
+      ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, &abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_addr = tmem + lane_sel + kColS;
+      const uint32_t s_addr = tmem + lane_sel + kColS + (j & 1) * 64;
       const int valid = p.n_sel - j * kKeys;   // keys of this tile that exist
-      uint32_t r[32];
-      float tmax = -INFINITY;
-      if (valid >= kKeys) {
+      uint32_t r0[32], r1[32];                 // the whole score row stays in registers
+      tmem_ld32(s_addr, r0);
+      tmem_ld32(s_addr + 32, r1);
+      tmem_wait_ld();
+      if (valid < kKeys) {                     // last, partial tile: columns past the end count as -inf
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          tmem_ld32(s_addr + half * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) tmax = fmaxf(tmax, __uint_as_float(r[c]));
-        }
-      } else {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          tmem_ld32(s_addr + half * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; ++c)
-            tmax = fmaxf(tmax, (half * 32 + c < valid) ? __uint_as_float(r[c]) : -INFINITY);
+        for (int c = 0; c < 32; ++c) {
+          if (c >= valid) r0[c] = 0xFF800000u;
+          if (32 + c >= valid) r1[c] = 0xFF800000u;
         }
       }
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) tmax = fmaxf(tmax, fmaxf(__uint_as_float(r0[c]), __uint_as_float(r1[c])));
       const float m_new = fmaxf(m_used, tmax * p.scale_log2);
       const bool need = (j == 0) || (m_new - m_used > kRescaleThreshold);
       const bool any_need = __any_sync(0xffffffffu, need);
-      if (j > 0) {
+      if (j > 0 && any_need) {
         ok = mbar_wait(&pv_bar, (j - 1) & 1, &abort_flag, p.status);   // O is complete up to tile j-1
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        if (any_need) {
-          const float alpha = need ? ex2(m_used - m_new) : 1.f;
+        const float alpha = need ? ex2(m_used - m_new) : 1.f;
+        uint32_t r[32];
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            tmem_ld32(tmem + lane_sel + kColO + half * 32, r);
-            tmem_wait_ld();
+        for (int half = 0; half < 2; ++half) {
+          tmem_ld32(tmem + lane_sel + kColO + half * 32, r);
+          tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
-            tmem_st32(tmem + lane_sel + kColO + half * 32, r);
-          }
-          l_sum *= alpha;
+          for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+          tmem_st32(tmem + lane_sel + kColO + half * 32, r);
         }
+        l_sum *= alpha;
       }
       if (need) m_used = m_new;
       uint32_t pk[32];
       float psum0 = 0.f, psum1 = 0.f;
-      if (valid >= kKeys) {
+      // exp2 of -inf is 0, so masked columns add nothing
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          tmem_ld32(s_addr + half * 32, r);
-          tmem_wait_ld();
+      for (int c = 0; c < 32; c += 2) {
+        const float e0 = ex2(fmaf(__uint_as_float(r0[c]), p.scale_log2, -m_used));
+        const float e1 = ex2(fmaf(__uint_as_float(r0[c + 1]), p.scale_log2, -m_used));
+        psum0 += e0;
+        psum1 += e1;
+        pk[c / 2] = pack_bf16x2(e0, e1);
+      }
 #pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            const float e0 = ex2(fmaf(__uint_as_float(r[c]), p.scale_log2, -m_used));
-            const float e1 = ex2(fmaf(__uint_as_float(r[c + 1]), p.scale_log2, -m_used));
-            psum0 += e0;
-            psum1 += e1;
-            pk[half * 16 + c / 2] = pack_bf16x2(e0, e1);
-          }
-        }
-      } else {       // last, partial tile: columns past the end contribute nothing
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          tmem_ld32(s_addr + half * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            float e0 = ex2(fmaf(__uint_as_float(r[c]), p.scale_log2, -m_used));
-            float e1 = ex2(fmaf(__uint_as_float(r[c + 1]), p.scale_log2, -m_used));
-            if (half * 32 + c >= valid) e0 = 0.f;
-            if (half * 32 + c + 1 >= valid) e1 = 0.f;
-            psum0 += e0;
-            psum1 += e1;
-            pk[half * 16 + c / 2] = pack_bf16x2(e0, e1);
-          }
-        }
+      for (int c = 0; c < 32; c += 2) {
+        const float e0 = ex2(fmaf(__uint_as_float(r1[c]), p.scale_log2, -m_used));
+        const float e1 = ex2(fmaf(__uint_as_float(r1[c + 1]), p.scale_log2, -m_used));
+        psum0 += e0;
+        psum1 += e1;
+        pk[16 + c / 2] = pack_bf16x2(e0, e1);
       }
       l_sum += psum0 + psum1;
-      // every S value of this row is in registers by now: P goes over the first 32 columns of S
-      tmem_st32(tmem + lane_sel + kColP, pk);
+      // every S value of this row is in registers: P goes over the first 32 columns of this tile's S buffer
+      tmem_st32(tmem + lane_sel + kColP + (j & 1) * 64, pk);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full);
