@@ -463,3 +463,24 @@ def test_decode_over_projected_bank_cache_matches_oracle(name, norm, dev):
         assert torch.equal(info["indices"].cpu(), ref["indices"])
         assert rel_err(out, ref["out"]) < BF16
     _status_ok(dev)
+
+
+def test_rms_norm_module_matches_oracle(dev):
+    """The stand-alone RMSNorm module (forward and autograd) against the restated reference norm."""
+    import memory_b200 as M
+    torch.manual_seed(5)
+    d = 192
+    norm = M.RMSNorm(d, eps=1e-6).to(dev)
+    with torch.no_grad():
+        norm.weight.add_(0.2 * torch.randn(d, device=dev))
+    x = torch.randn(3, 17, d, device=dev, requires_grad=True)
+    g = torch.randn(3, 17, d, device=dev)
+    y = norm(x)
+    (y * g).sum().backward()
+    xc = x.detach().cpu().requires_grad_(True)
+    wc = norm.weight.detach().cpu().requires_grad_(True)
+    yr = O.rms_norm(xc, wc, 1e-6)
+    (yr * g.cpu()).sum().backward()
+    assert rel_err(y, yr) < 1e-5
+    assert rel_err(x.grad, xc.grad) < 1e-4
+    assert rel_err(norm.weight.grad, wc.grad) < 1e-4
