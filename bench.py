@@ -126,15 +126,33 @@ def make_hidden(cfg, n_sets, seed, dtype):
 
 
 # ----------------------------------------------------------------------------------------------
-# CPU arm: the oracle's restatement of the reference, timed on the host cores
+# CPU arm: the reference's own modules (installed copy under baseline/_ref) on the host cores; the oracle's
+# restatement of them when that copy is absent
 # ----------------------------------------------------------------------------------------------
+def host_threads() -> int:
+    """Threads the CPU arm uses: every core this process may run on (torchrun exports OMP_NUM_THREADS=1, which
+    would otherwise pin the arm to one core)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(1, n)
+
+
 def cpu_reference_step_time(cfg, sample_batch, steps, warmup, threads=None):
-    from oracle import moc_oracle as O
-    if threads:
-        torch.set_num_threads(threads)
+    """Seconds per fwd+bwd step of the layer on the host, (kind, cores).  kind = "reference": the reference's own
+    router / bank / attention modules; "port": oracle/moc_oracle.py."""
+    threads = threads or host_threads()
+    torch.set_num_threads(threads)
     small = dict(cfg, batch=sample_batch)
     params = make_params(small, "cpu")
     hs, gs = make_hidden(small, 1, 1234, torch.float32)
+    from oracle import install_reference
+    if install_reference.available():
+        from oracle.reference_layer import ReferenceLayer, time_steps
+        layer = ReferenceLayer(small, params, "cpu")
+        return time_steps(layer, hs[0], gs[0], steps, warmup), "reference", torch.get_num_threads()
+    from oracle import moc_oracle as O
     shape = O.LayerShape(cfg["hidden_dim"], cfg["num_heads"], cfg["num_kv_heads"], cfg["num_chapters"],
                          cfg["tokens_per_chapter"], cfg["top_k"], cfg["num_shared_chapters"],
                          cfg["routed_scaling_factor"])
@@ -147,7 +165,14 @@ def cpu_reference_step_time(cfg, sample_batch, steps, warmup, threads=None):
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
-    return sum(times) / len(times), torch.get_num_threads()
+    return sum(times) / len(times), "port", torch.get_num_threads()
+
+
+def cpu_sample_text(cfg, sample_b, kind, steps, warmup):
+    what = ("the reference's own ChapterRouter / ChapteredMemoryBank / MemoryCrossAttention modules (eager, fp32)"
+            if kind == "reference" else "fp32 eager restatement of the reference (oracle port)")
+    return (f"{sample_b} of {cfg['batch']} sequences per step (same L, bank, top-k), {what}, "
+            f"{warmup} warm-up + {steps} timed steps")
 
 
 def run_reference_arm(args):
@@ -156,17 +181,17 @@ def run_reference_arm(args):
         return
     cfg = dict(PAPER)
     sample_b = args.cpu_sample_batch
-    step_s, cores = cpu_reference_step_time(cfg, sample_b, args.steps, max(1, min(args.warmup, 1)))
+    warm = 1
+    step_s, kind, cores = cpu_reference_step_time(cfg, sample_b, args.steps, warm)
     tokens = sample_b * cfg["seq"]
     value = tokens / step_s
-    sample = (f"{sample_b} of {cfg['batch']} sequences per step (same L, bank, top-k), fp32 eager restatement "
-              f"of the reference, {args.steps} timed steps")
+    sample = cpu_sample_text(cfg, sample_b, kind, args.steps, warm)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(cfg, 1),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": workload_config(cfg, max(1, args.gpus)),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -308,18 +333,6 @@ class LayerRunner:
         return ops.LAUNCHES - n0
 
 
-def time_op_breakdown(runner, hs, gs, steps):
-    """Per-call CUDA-event timing (separate pass, after the headline timing)."""
-    from memory_b200 import ops
-    ops.TIMER = {}
-    for i in range(steps):
-        runner._fwd_bwd(hs[i % len(hs)], gs[i % len(gs)])      # rank-local: no gradient reduction here
-    torch.cuda.synchronize()
-    table = {k: sum(a.elapsed_time(b) for a, b in v) / steps for k, v in ops.TIMER.items()}
-    ops.TIMER = None
-    return table
-
-
 def time_dominant_kernels(cfg, device, iters=10):
     """The three attention kernels timed alone (CUDA events on the launching stream), inputs > L2:
     Q/KV/dO/O for B=8 are ~150 MB and are rotated over two copies."""
@@ -359,6 +372,113 @@ def time_dominant_kernels(cfg, device, iters=10):
     return res
 
 
+def run_kernels_mode(args):
+    """``--kernels``: the hot kernels alone at the paper shape (no bank, a few hundred MB), CUDA-event timed; the
+    small footprint is what a profiler capture of one launch needs.  Prints one JSON object (not the benchmark
+    line).  ``--only a,b`` restricts the list; ``--iters`` sets the launches per kernel."""
+    from memory_b200 import _lib as L, ops
+    from memory_b200.build import build
+    build()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    cfg = dict(PAPER, batch=args.kernels_batch)
+    b, l, d, h = cfg["batch"], cfg["seq"], cfg["hidden_dim"], cfg["num_heads"]
+    dh = d // h
+    n_sel = (cfg["top_k"] + cfg["num_shared_chapters"]) * cfg["tokens_per_chapter"]
+    only = set(x for x in args.only.split(",") if x)
+    torch.manual_seed(0)
+    q = torch.randn(b, l, d, device=dev).bfloat16()
+    kv = (torch.randn(b, n_sel, 2 * d, device=dev) * 0.3).bfloat16()
+    g = torch.randn(b, l, d, device=dev).bfloat16()
+    mem = (torch.randn(b * n_sel, d, device=dev) * 0.02).bfloat16()
+    wkv = (torch.randn(2 * d, d, device=dev) * 0.02).bfloat16()
+    wq = (torch.randn(d, d, device=dev) * 0.02).bfloat16()
+    o, lse = ops.attn_fwd(q, kv, h, h, dh ** -0.5)
+    bufs = (torch.empty_like(q), torch.empty_like(kv), torch.empty(6, b, h, l, dtype=torch.float32, device=dev))
+    ops.attn_bwd(q, kv, o, lse, g, h, h, dh ** -0.5, parts=1, buffers=bufs)
+    unit = 2.0 * b * l * n_sel * d
+    kv2 = kv.view(b * n_sel, 2 * d)
+    proj = 2.0 * b * n_sel * d * 2 * d
+    cases = {      # name -> (launch, executed FLOPs, algorithmic FLOPs)
+        "attn_fwd": (lambda: ops.attn_fwd(q, kv, h, h, dh ** -0.5), 2 * unit, 2 * unit),
+        "attn_bwd_dq": (lambda: ops.attn_bwd(q, kv, o, lse, g, h, h, dh ** -0.5, parts=2, buffers=bufs), 3 * unit, 2 * unit),
+        "attn_bwd_dkv": (lambda: ops.attn_bwd(q, kv, o, lse, g, h, h, dh ** -0.5, parts=4, buffers=bufs), 4 * unit, 2 * unit),
+        "kv_proj": (lambda: ops.gemm(mem, wkv), proj, proj),
+        "q_proj": (lambda: ops.gemm(q.view(b * l, d), wq), 2.0 * b * l * d * d, 2.0 * b * l * d * d),
+        "d_mem": (lambda: ops.gemm(kv2, wkv, b_kmajor=False), proj, proj),
+        "d_wkv": (lambda: ops.gemm(kv2, mem, a_kmajor=False, b_kmajor=False, out_dtype=torch.float32, split_k=16),
+                  proj, proj),
+    }
+    res = {}
+    for name, (fn, executed, algorithmic) in cases.items():
+        if only and name not in only:
+            continue
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        evs = []
+        for _ in range(args.iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        ms = sum(a.elapsed_time(c) for a, c in evs) / len(evs)
+        res[name] = {"ms": round(ms, 4), "tflops_executed": round(executed / ms / 1e9, 1),
+                     "tflops_algorithmic": round(algorithmic / ms / 1e9, 1)}
+    L.check_device_status(dev)
+    print(json.dumps({"kernels": res, "batch": b, "shape": "L 1024, 12 x 64 heads, 4160 keys per sequence, bf16"}))
+
+
+def verify_against_oracle(runner, cfg, h, device):
+    """One-shot check, outside every timed region, of the very tensors the timed steps use: the CUDA layer's
+    forward on ``h`` against the CPU oracle's (fp32, eager).  The benchmark draws its router weight from N(0, 0.02),
+    so neighbouring chapter ranks can sit within fp32 rounding of each other; the selection is therefore held to
+    an fp64 recomputation (exact top-k, in order, up to ties below 16 fp32 ulps) and the output is compared on the
+    sequences whose selected chapter sets equal the oracle's."""
+    from oracle import moc_oracle as O
+    P = runner.params
+    with torch.no_grad():
+        out, losses, info = runner.M.memory_layer(
+            h, h, P["bank"], P["router_w"], P["router_b"], P["wq"], P["wk"], P["wv"], P["wo"],
+            num_heads=cfg["num_heads"], num_kv_heads=cfg["num_kv_heads"],
+            tokens_per_chapter=cfg["tokens_per_chapter"], top_k=cfg["top_k"],
+            num_shared_chapters=cfg["num_shared_chapters"], routed_scaling_factor=cfg["routed_scaling_factor"],
+            compute_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    cpu = {k: v.detach().float().cpu() for k, v in P.items()}
+    hc = h.detach().float().cpu()
+    shape = O.LayerShape(cfg["hidden_dim"], cfg["num_heads"], cfg["num_kv_heads"], cfg["num_chapters"],
+                         cfg["tokens_per_chapter"], cfg["top_k"], cfg["num_shared_chapters"],
+                         cfg["routed_scaling_factor"])
+    with torch.no_grad():
+        ref = O.memory_layer(shape, hc, hc, cpu["bank"], cpu["router_w"], cpu["router_b"], cpu["wq"], cpu["wk"],
+                             cpu["wv"], cpu["wo"], return_losses=True)
+    s_ = cfg["num_shared_chapters"]
+    z = hc.double().mean(1) @ cpu["router_w"].double().t() + cpu["router_b"].double()
+    p = torch.softmax(z, -1)
+    p[:, :s_] = 0
+    gi = info["indices"].cpu()
+    tau = 16 * 1.1920929e-07
+    sel = torch.gather(p, 1, gi)
+    ordered = bool((sel[:, :-1] >= sel[:, 1:] * (1 - tau)).all())
+    rest = p.clone()
+    rest.scatter_(1, gi, 0.0)
+    topk = bool((rest.max(-1).values <= sel[:, -1] * (1 + tau)).all())
+    same_pos = gi == ref["indices"]
+    same_set = torch.tensor([set(a.tolist()) == set(b.tolist()) for a, b in zip(gi, ref["indices"])])
+    o, r = out.float().cpu()[same_set], ref["out"][same_set]
+    out_err = float((o - r).abs().max() / (r.abs().max() + 1e-30)) if o.numel() else None
+    out_bad = int(((o - r).abs() > 2e-2 + 2e-2 * r.abs()).sum()) if o.numel() else None
+    loss_err = max(abs(losses[k].item() - ref["losses"][k].item()) / (abs(ref["losses"][k].item()) + 1e-30)
+                   for k in ("load_balance", "z_loss"))
+    ok = ordered and topk and (out_err is None or out_err < 2e-2) and loss_err < 1e-4 and not out_bad
+    return {"ok": bool(ok), "indices_exact_topk_vs_fp64_up_to_16ulp_ties": ordered and topk,
+            "index_positions_equal_to_fp32_oracle": f"{int(same_pos.sum())}/{same_pos.numel()}",
+            "sequences_with_oracle_chapter_set": f"{int(same_set.sum())}/{same_set.numel()}",
+            "out_max_rel_err": out_err, "out_elementwise_violations_2e-2": out_bad,
+            "router_loss_rel_err": loss_err}
+
+
 def run_cuda_arm(args):
     # libraries (NCCL) may print to stdout; the contract is ONE JSON line there, so stdout is pointed at
     # stderr for the run and the line is written to the saved descriptor at the end
@@ -375,9 +495,12 @@ def run_cuda_arm(args):
     import torch.distributed as dist
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    from memory_b200 import _lib as L, ops
+    from memory_b200 import _lib as L
     from memory_b200.build import build
-    build()
+    if local_rank == 0:
+        build()              # one process per node compiles; the others wait and then load the finished library
+    if world > 1:
+        dist.barrier()
     L.lib()
 
     cfg = dict(PAPER)
@@ -401,23 +524,27 @@ def run_cuda_arm(args):
     if sampler:
         sampler.start()
     per_step_launches = runner.launches_per_step()
-    barrier()
+    # the timed block of exactly --steps steps is repeated; the reported time is the median block (max over
+    # ranks per block), the spread goes into the line
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        runner.step(hs[i % N_INPUT_SETS], gs[i % N_INPUT_SETS])
-    runner.finish()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
+    block_ms = []
+    for _ in range(args.blocks):
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            runner.step(hs[i % N_INPUT_SETS], gs[i % N_INPUT_SETS])
+        runner.finish()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        block_ms.append(ms / args.steps)
     launches = per_step_launches * args.steps
-    clocks = sampler.stop() if sampler else None
     L.check_device_status(device)
-    if world > 1:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_per_step = ms / args.steps
+    ms_per_step = statistics.median(block_ms)
     value = tokens_per_step / (ms_per_step * 1e-3)
 
     # ---- end to end: hidden states come from pinned host memory every step, loss read back ----
@@ -452,17 +579,22 @@ def run_cuda_arm(args):
         torch.cuda.synchronize()
 
     e2e_loop(max(3, args.warmup))
-    barrier()
-    e0.record()
-    e2e_loop(args.steps)
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = tokens_per_step / (e2e_ms / args.steps * 1e-3)
+    e2e_blocks = []
+    for _ in range(args.blocks):
+        barrier()
+        e0.record()
+        e2e_loop(args.steps)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        e2e_blocks.append(ms / args.steps)
+    clocks = sampler.stop() if sampler else None
+    e2e_ms_per_step = statistics.median(e2e_blocks)
+    e2e_value = tokens_per_step / (e2e_ms_per_step * 1e-3)
     h2d = hs[0].numel() * hs[0].element_size()
 
     if rank != 0:
@@ -476,7 +608,6 @@ def run_cuda_arm(args):
     f_fwd = layer_flops(cfg)
     f_step = 3.0 * f_fwd
     kern = time_dominant_kernels(cfg, device)
-    breakdown = time_op_breakdown(runner, hs, gs, max(3, min(args.steps, 10)))
     b, l, d = cfg["batch"], cfg["seq"], cfg["hidden_dim"]
     n_sel = (cfg["top_k"] + cfg["num_shared_chapters"]) * cfg["tokens_per_chapter"]
     attn_unit = 2.0 * b * l * n_sel * d          # one [L x n_sel x D] GEMM over all heads and batch items
@@ -491,16 +622,36 @@ def run_cuda_arm(args):
                 "kernel_ms": {k: round(v, 4) for k, v in kern.items()},
                 "layer": {"algorithmic_flops_per_step": f_step, "achieved": f_step / (ms_per_step * 1e-3) / 1e12,
                           "peak": peaks["tflops_sustained"], "frac": f_step / (ms_per_step * 1e-3) / 1e12 / peaks["tflops_sustained"],
-                          "peak_source": peaks["source"] + " (sustained, whole step)"},
-                "op_ms_per_step": {k: round(v, 4) for k, v in sorted(breakdown.items(), key=lambda kv: -kv[1])}}
+                          "peak_source": peaks["source"] + " (sustained, whole step)"}}
+
+    verify = None
+    if args.verify or (world == 1 and not args.no_verify):
+        verify = verify_against_oracle(runner, cfg, hs[0], device)
+        L.check_device_status(device)
+
+    # the reference's own eager modules on this GPU (fp32 router, attention under bf16 autocast): the comparison a
+    # user of the reference on the same hardware would make; informational, never part of `value`
+    gpu_eager = None
+    if world == 1 and not args.no_cpu_baseline:
+        from oracle import install_reference
+        if install_reference.available():
+            from oracle.reference_layer import ReferenceLayer, time_steps
+            try:
+                layer = ReferenceLayer(cfg, {k: v.detach() for k, v in runner.params.items()}, device)
+                sec = time_steps(layer, hs[0].detach(), gs[0], 5, 2, autocast_dtype=torch.bfloat16)
+                gpu_eager = {"value": cfg["batch"] * cfg["seq"] / sec, "unit": "tokens/s", "ms_per_step": sec * 1e3,
+                             "what": "reference modules (ChapterRouter, ChapteredMemoryBank, MemoryCrossAttention, "
+                                     "eager torch) on the same GPU, bf16 autocast, fp32 router, full batch"}
+                del layer
+                torch.cuda.empty_cache()
+            except Exception as exc:          # a comparator must never take the measurement down
+                gpu_eager = {"unavailable": repr(exc)[:200]}
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
-        step_s, cores = cpu_reference_step_time(cfg, args.cpu_sample_batch, 2, 1)
+        step_s, kind, cores = cpu_reference_step_time(cfg, args.cpu_sample_batch, 2, 1)
         cpu_baseline = {"value": args.cpu_sample_batch * cfg["seq"] / step_s, "unit": "tokens/s", "cores": cores,
-                        "kind": "port",
-                        "sample": f"{args.cpu_sample_batch} of {cfg['batch']} sequences per step (same L, bank, top-k), "
-                                  "fp32 eager restatement of the reference, 1 warm-up + 2 timed steps"}
+                        "kind": kind, "sample": cpu_sample_text(cfg, args.cpu_sample_batch, kind, 2, 1)}
 
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -508,8 +659,12 @@ def run_cuda_arm(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(cfg, world),
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d * world,
-                "d2h_bytes_per_step": 16 * world, "ms_per_step": e2e_ms / args.steps},
+                "d2h_bytes_per_step": 16 * world, "ms_per_step": e2e_ms_per_step,
+                "ms_per_step_min_max": [min(e2e_blocks), max(e2e_blocks)]},
+        "timed_blocks": {"blocks": args.blocks, "steps_per_block": args.steps, "statistic": "median",
+                         "ms_per_step_min_max": [min(block_ms), max(block_ms)]},
         "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu_baseline,
+        "reference_eager_same_gpu": gpu_eager, "verify": verify,
         "pct_of_bf16_tc_roofline": 100.0 * roofline["layer"]["frac"],
     }
     if world > 1:
@@ -528,16 +683,27 @@ def run_cuda_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
-    ap.add_argument("--cpu-sample-batch", type=int, default=2)
+    ap.add_argument("--cpu-sample-batch", type=int, default=8,
+                    help="sequences per CPU step (8 = the whole per-GPU batch of the workload)")
+    ap.add_argument("--blocks", type=int, default=5, help="how many times the timed block of --steps steps is repeated")
+    ap.add_argument("--verify", action="store_true", help="check the timed tensors against the CPU oracle first (default at N = 1)")
+    ap.add_argument("--no-verify", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="issue every kernel from Python instead of a CUDA graph")
     ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="N > 1: how the sparse bank-gradient rows travel (NCCL all-gathers, or copy-engine pushes "
                          "into symmetric-memory receive buffers; falls back to NCCL when those cannot be set up)")
+    ap.add_argument("--kernels", action="store_true", help="time the hot kernels alone (small footprint) and exit")
+    ap.add_argument("--only", default="", help="--kernels: comma-separated kernel names")
+    ap.add_argument("--iters", type=int, default=5, help="--kernels: launches per kernel")
+    ap.add_argument("--kernels-batch", type=int, default=8)
     args = ap.parse_args()
+    if args.kernels:
+        run_kernels_mode(args)
+        return
     if args.warmup < 3 and args.impl == "cuda":
         args.warmup = 3
     if args.impl == "reference":

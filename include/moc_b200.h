@@ -43,6 +43,14 @@ const char* moc_last_error(void);
 /* ABI version of this library. */
 int moc_abi_version(void);
 
+/* Self-test of the bounded device wait every kernel of this library uses on its barriers.  One CTA waits on a
+ * barrier that expects `expected` arrivals while only `arrivals` are made; the wait polls at most `poll_limit`
+ * times, then raises MOC_DEV_TIMEOUT in `status` and the kernel returns normally.  out[0] = 1 if the wait
+ * succeeded, out[1] = result of a second wait, out[2] = the CTA's abort flag.  No counterpart in the reference
+ * (its kernels have no device-side waits). */
+int moc_wait_probe(int32_t expected, int32_t arrivals, uint32_t poll_limit, int32_t* status, int32_t* out,
+                   void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Router.  Replaces ChapterRouter.forward / _compute_losses (memory_transformer/router.py:94-156,
  * 197-260) and MemoryTransformer._prepend_shared_chapters (memory_transformer/model.py:356-391).
@@ -73,7 +81,8 @@ int moc_router_fwd(const moc_router_shape* s, const void* h, const float* w, con
                    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* moc_router_fwd in two pieces: parts bit 1 = pooling, logits, selection (everything the gather needs),
- * bit 2 = the loss terms (reads probs / idx / row_stats of bit 1).  A caller can wait for bit 1 only and let the
+ * bit 2 = the loss terms (reads probs / idx / row_stats of bit 1), bit 8 (with bit 1) = `pooled` already holds
+ * the pooled states, e.g. from moc_pool_weighted_fwd, and `h` is not read.  A caller can wait for bit 1 only and let the
  * losses finish beside the gather.  moc_router_fwd is parts = 3.  No counterpart in the reference. */
 int moc_router_fwd_parts(const moc_router_shape* s, const void* h, const float* w, const float* bias,
                          float* pooled, float* logits, float* probs, int64_t* idx, float* weights,
@@ -101,6 +110,16 @@ int moc_router_bwd_parts(const moc_router_shape* s, const float* w, const float*
                          const float* d_losses, float* d_logits, float* d_w, float* d_bias, float* d_pooled,
                          void* d_h, int32_t accumulate_dh, void* workspace, size_t workspace_bytes, int32_t parts,
                          int32_t* status, void* stream);
+
+/* Position-weighted pooling: pooled[b, :] = sum_t pos_weight[t] * h[b, t, :] (fp32 accumulation), and its
+ * backward d_h[b, t, :] (+)= pos_weight[t] * d_pooled[b, :].  With the coefficients of the rolling-window rule this
+ * replaces ChapterRouter._sequence_rolling_pool (memory_transformer/router.py:159-195): the average over t of the
+ * window means mean(h[max(0, t-w+1) .. t]) is linear in h, so it is one coefficient per position.  Feed the result to
+ * moc_router_fwd_parts with parts bit 8.  workspace: batch * 32 * dim floats. */
+int moc_pool_weighted_fwd(const void* h, int32_t h_dtype, const float* pos_weight, float* pooled, int32_t batch,
+                          int32_t seq, int32_t dim, void* workspace, size_t workspace_bytes, void* stream);
+int moc_pool_weighted_bwd(const float* d_pooled, const float* pos_weight, void* d_h, int32_t h_dtype,
+                          int32_t batch, int32_t seq, int32_t dim, int32_t accumulate, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Chapter gather.  Replaces ChapteredMemoryBank.get_chapters_batched (memory_bank.py:244-293), the

@@ -62,6 +62,9 @@ _PROTOTYPES = {
     "moc_router_fwd_parts": (C.c_int, [C.POINTER(RouterShape)] + [P] * 13 + [P, C.c_size_t, C.c_int32, P, P]),
     "moc_router_bwd": (C.c_int, [C.POINTER(RouterShape)] + [P] * 16 + [C.c_int32, P, C.c_size_t, P, P]),
     "moc_router_bwd_parts": (C.c_int, [C.POINTER(RouterShape)] + [P] * 16 + [C.c_int32, P, C.c_size_t, C.c_int32, P, P]),
+    "moc_pool_weighted_fwd": (C.c_int, [P, C.c_int32, P, P, C.c_int32, C.c_int32, C.c_int32, P, C.c_size_t, P]),
+    "moc_pool_weighted_bwd": (C.c_int, [P, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P]),
+    "moc_wait_probe": (C.c_int, [C.c_int32, C.c_int32, C.c_uint32, P, P, P]),
     "moc_gather_rows_fwd": (C.c_int, [P, C.c_int32, C.c_int64, C.c_int32, C.c_int32, P, P, C.c_int32,
                                       C.c_int32, C.c_int32, C.c_float, P, C.c_int32, P, P, P]),
     "moc_chapter_segments": (C.c_int, [P, C.c_int32, C.c_int32, P, P, P, P, P, P, P]),

@@ -5,10 +5,11 @@
 // accumulator in tensor memory) -> online softmax by 128 threads that each own one query row
 // (tcgen05.ld, exp2 on the scaled scores, P written back to tensor memory as packed bf16) ->
 // O += P_j V_j (tcgen05.mma with A = P from tensor memory, B = the V tile as an MN-major operand).
-// A CTA is deliberately small -- 128 TMEM columns (S, with P written over its first 32 columns, and
-// O), ~49 KiB of shared memory, 192 threads -- so that four CTAs share an SM: while one CTA's row
-// owners are in their exponentials the other CTAs' MMAs and loads run, which is what hides the
-// TMEM / barrier latencies of the strictly ordered S -> softmax -> PV chain inside one CTA.  The
+// A CTA holds 256 TMEM columns -- two 64-column score buffers (tile j uses buffer j & 1; P_j is written
+// as packed bf16 over the first 32 columns of its own buffer) and the 64-column O accumulator -- about
+// 65 KiB of shared memory and 192 threads, and two CTAs share an SM (__launch_bounds__(192, 2)).  S_{j+1}
+// is issued before PV_j, so the tensor pipe computes the next scores while the row owners run the softmax
+// of the current ones; the second CTA fills what is left of the strictly ordered chain.  The
 // running maximum is only raised (and O rescaled) when it grows by more than 2^8, which keeps P
 // within bf16 range while skipping almost every rescale.
 #include "moc_common.cuh"

@@ -54,7 +54,39 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_
   return MOC_OK;
 }
 
+// One CTA whose first warp waits, with the library's bounded wait, on an mbarrier that `arrivals` of the
+// other threads arrive at.  With arrivals below the barrier's count the wait can only run out: that is how
+// the give-up path (status word, abort flag, normal return) is exercised without a hung kernel.
+__global__ void wait_probe_kernel(int expected, int arrivals, uint32_t poll_limit, int* status, int* out) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, static_cast<uint32_t>(expected));
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x >= 32 && static_cast<int>(threadIdx.x) - 32 < arrivals) mbar_arrive(&bar);
+  if (threadIdx.x < 32) {
+    const bool ok = mbar_wait_limited(&bar, 0, &abort_flag, status, poll_limit);
+    // a second wait after a give-up must return at once (the CTA-wide abort flag)
+    const bool again = ok ? true : mbar_wait_limited(&bar, 0, &abort_flag, status, poll_limit);
+    if (threadIdx.x == 0) { out[0] = ok ? 1 : 0; out[1] = again ? 1 : 0; out[2] = abort_flag; }
+  }
+}
+
 }  // namespace moc
+
+extern "C" int moc_wait_probe(int32_t expected, int32_t arrivals, uint32_t poll_limit, int32_t* status,
+                              int32_t* out, void* stream_) {
+  using namespace moc;
+  MOC_REQUIRE(status && out, "NULL buffer");
+  MOC_REQUIRE(expected >= 1 && expected <= 96 && arrivals >= 0 && arrivals <= expected, "bad arrival counts");
+  MOC_REQUIRE(poll_limit >= 1 && poll_limit <= (1u << 20), "poll_limit must be in [1, 2^20]");
+  wait_probe_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream_)>>>(expected, arrivals, poll_limit, status, out);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
 
 extern "C" const char* moc_last_error(void) { return moc::g_last_error.c_str(); }
 extern "C" int moc_abi_version(void) { return 2; }

@@ -87,17 +87,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  `abort_flag` lives in shared memory; `status` in global memory.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status) {
+// Bounded wait.  `abort_flag` lives in shared memory; `status` in global memory.  After `limit` polls the
+// waiter gives up: it raises the CTA's abort flag, records MOC_DEV_TIMEOUT and returns false.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  int* status, uint32_t limit) {
   if (*abort_flag) return false;
-  for (uint32_t it = 0; it < kWaitPollLimit; ++it) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u && *abort_flag) return false;
   }
   *abort_flag = 1;
   atomicMax(status, MOC_DEV_TIMEOUT);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status) {
+  return mbar_wait_limited(bar, parity, abort_flag, status, kWaitPollLimit);
 }
 
 // TMA: 2-D tiled load global -> shared, completion on an mbarrier.

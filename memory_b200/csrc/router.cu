@@ -115,6 +115,48 @@ __global__ void pool_finish_kernel(const float* __restrict__ partial, float* __r
   pooled[i] = acc / static_cast<float>(L);
 }
 
+// pooled[b, c] = sum_t pos_weight[t] * h[b, t, c]: the sequence-rolling pooling of the reference collapses to one
+// coefficient per position (the average over t of the rolling-window means is linear in h).  Same split layout
+// as the plain mean: partial sums per (batch row, sequence split), then a fixed-order sum over the splits.
+template <typename T>
+__global__ void pool_weighted_partial_kernel(const T* __restrict__ h, const float* __restrict__ pos_weight,
+                                             float* __restrict__ partial, int L, int d) {
+  const int b = blockIdx.x, sp = blockIdx.y;
+  const int rows_per = (L + kPoolSplits - 1) / kPoolSplits;
+  const int t0 = sp * rows_per;
+  const int t1 = min(L, t0 + rows_per);
+  const T* base = h + (static_cast<long long>(b) * L) * d;
+  float* dst = partial + (static_cast<long long>(b) * kPoolSplits + sp) * d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float acc = 0.f;
+    for (int t = t0; t < t1; ++t) acc = fmaf(pos_weight[t], to_f32(base[static_cast<long long>(t) * d + c]), acc);
+    dst[c] = acc;
+  }
+}
+__global__ void pool_weighted_finish_kernel(const float* __restrict__ partial, float* __restrict__ pooled, int d,
+                                            int total) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int b = i / d, c = i - b * d;
+  float acc = 0.f;
+  for (int sp = 0; sp < kPoolSplits; ++sp) acc += partial[(static_cast<long long>(b) * kPoolSplits + sp) * d + c];
+  pooled[i] = acc;
+}
+// d_h[b, t, :] (+)= pos_weight[t] * d_pooled[b, :]
+template <typename T>
+__global__ void pool_weighted_bwd_kernel(const float* __restrict__ d_pooled, const float* __restrict__ pos_weight,
+                                         T* __restrict__ d_h, int L, int d, long long total, int accumulate) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / d;
+    const int c = static_cast<int>(i - row * d);
+    const int b = static_cast<int>(row / L), t = static_cast<int>(row - static_cast<long long>(b) * L);
+    float v = d_pooled[static_cast<long long>(b) * d + c] * pos_weight[t];
+    if (accumulate) v += to_f32(d_h[i]);
+    if constexpr (sizeof(T) == 4) d_h[i] = v; else d_h[i] = __float2bfloat16(v);
+  }
+}
+
 // logits[b,c] = <pooled[b,:], w[c,:]> + bias[c]; one warp per chapter, 8 batch rows per pass
 __global__ void logits_kernel(const float* __restrict__ pooled, const float* __restrict__ w,
                               const float* __restrict__ bias, float* __restrict__ logits, int B, int d, int C) {
@@ -669,7 +711,8 @@ extern "C" int moc_router_fwd_parts(const moc_router_shape* s, const void* h, co
   int rc = check_shape(s);
   if (rc != MOC_OK) return rc;
   MOC_REQUIRE(workspace_bytes >= ws_bytes(s), "router workspace too small");
-  MOC_REQUIRE(h && w && pooled && logits && probs && comb_idx && comb_w && row_stats, "NULL router buffer");
+  MOC_REQUIRE((h || (parts & 8)) && w && pooled && logits && probs && comb_idx && comb_w && row_stats,
+              "NULL router buffer");
   (void)status;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int B = s->batch, L = s->seq, d = s->hidden_dim, C = s->num_chapters, S = s->num_shared;
@@ -680,11 +723,13 @@ extern "C" int moc_router_fwd_parts(const moc_router_shape* s, const void* h, co
 
   dim3 pg(B, kPoolSplits);
   if (parts & 1) {
+  if (!(parts & 8)) {      // bit 8: `pooled` already holds the pooled states (another pooling rule ran first)
   if (s->h_dtype == MOC_F32)
     pool_partial_kernel<float><<<pg, 256, 0, stream>>>(static_cast<const float*>(h), ws, L, d);
   else
     pool_partial_kernel<__nv_bfloat16><<<pg, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(h), ws, L, d);
   pool_finish_kernel<<<ceil_div(B * d, 256), 256, 0, stream>>>(ws, pooled, L, d, B * d);
+  }
   {
     const int warps = 8;
     const size_t sm = static_cast<size_t>(8) * d * sizeof(float);
@@ -776,4 +821,45 @@ extern "C" int moc_router_bwd(const moc_router_shape* s, const float* w, const f
   return moc_router_bwd_parts(s, w, pooled, probs, idx, weights, comb_w, row_stats, chapter_stats, d_weights,
                               d_comb_w, d_losses, d_logits, d_w, d_bias, d_pooled, d_h, accumulate_dh, workspace,
                               workspace_bytes, 7, status, stream_);
+}
+
+
+extern "C" int moc_pool_weighted_fwd(const void* h, int32_t h_dtype, const float* pos_weight, float* pooled,
+                                     int32_t batch, int32_t seq, int32_t dim, void* workspace,
+                                     size_t workspace_bytes, void* stream_) {
+  MOC_REQUIRE(h && pos_weight && pooled && workspace, "NULL buffer");
+  MOC_REQUIRE(batch > 0 && seq > 0 && dim > 0, "empty input");
+  MOC_REQUIRE(h_dtype == MOC_F32 || h_dtype == MOC_BF16, "bad h_dtype");
+  MOC_REQUIRE(workspace_bytes >= static_cast<size_t>(batch) * kPoolSplits * dim * sizeof(float),
+              "pooling workspace too small");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  float* ws = static_cast<float*>(workspace);
+  dim3 pg(batch, kPoolSplits);
+  if (h_dtype == MOC_F32)
+    pool_weighted_partial_kernel<float><<<pg, 256, 0, stream>>>(static_cast<const float*>(h), pos_weight, ws, seq, dim);
+  else
+    pool_weighted_partial_kernel<__nv_bfloat16><<<pg, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(h),
+                                                                        pos_weight, ws, seq, dim);
+  pool_weighted_finish_kernel<<<ceil_div(batch * dim, 256), 256, 0, stream>>>(ws, pooled, dim, batch * dim);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+extern "C" int moc_pool_weighted_bwd(const float* d_pooled, const float* pos_weight, void* d_h, int32_t h_dtype,
+                                     int32_t batch, int32_t seq, int32_t dim, int32_t accumulate, void* stream_) {
+  MOC_REQUIRE(d_pooled && pos_weight && d_h, "NULL buffer");
+  MOC_REQUIRE(batch > 0 && seq > 0 && dim > 0, "empty input");
+  MOC_REQUIRE(h_dtype == MOC_F32 || h_dtype == MOC_BF16, "bad h_dtype");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long total = static_cast<long long>(batch) * seq * dim;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  if (h_dtype == MOC_F32)
+    pool_weighted_bwd_kernel<float><<<static_cast<int>(blocks), 256, 0, stream>>>(
+        d_pooled, pos_weight, static_cast<float*>(d_h), seq, dim, total, accumulate);
+  else
+    pool_weighted_bwd_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, stream>>>(
+        d_pooled, pos_weight, static_cast<__nv_bfloat16*>(d_h), seq, dim, total, accumulate);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
 }

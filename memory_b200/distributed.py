@@ -331,7 +331,6 @@ class GradReducer:
             uniq, num_unique, rows, _ = sink.entries[0]
             n = int(num_unique.item())
             return uniq[:n], rows[: n * self.t]
-        acc = {}
         dense_ids: List[torch.Tensor] = []
         for uniq, num_unique, rows, _ in sink.entries:
             n = int(num_unique.item())
@@ -343,7 +342,6 @@ class GradReducer:
         for uniq, num_unique, rows, _ in sink.entries:
             n = int(num_unique.item())
             out.index_add_(0, pos[uniq[:n].long()], rows[: n * self.t].view(n, self.t, self.d))
-        del acc
         return ids.to(torch.int32), out.view(-1, self.d)
 
 

@@ -58,18 +58,24 @@ class SparseBankGrad:
 # --------------------------------------------------------------------------------------------
 class _Route(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, h, weight, bias, top_k, num_shared, routed_scale, with_losses):
-        r = ops.router_fwd(h, weight, bias, top_k, num_shared, routed_scale, with_losses)
+    def forward(ctx, h, weight, bias, top_k, num_shared, routed_scale, with_losses, pos_weight):
+        pooled = ops.pool_weighted_fwd(h, pos_weight) if pos_weight is not None else None
+        r = ops.router_fwd(h, weight, bias, top_k, num_shared, routed_scale, with_losses, pooled=pooled)
         ctx.cfg = (tuple(h.shape), h.dtype, int(top_k), int(num_shared), float(routed_scale), bias is not None)
-        ctx.saved = r
-        ctx.save_for_backward(weight)
+        # Output tensors go through save_for_backward (autograd handles a node's own outputs there without a
+        # reference cycle); only tensors that are not outputs stay as attributes, so the node and its buffers
+        # are released by reference counting as soon as the graph is.
+        ctx.internals = {k: r[k] for k in ("pooled", "probs", "idx", "row_stats", "chapter_stats", "_ws")}
+        ctx.pos_weight = pos_weight
+        ctx.save_for_backward(weight, r["weights"], r["comb_w"])
         ctx.mark_non_differentiable(r["idx"], r["comb_idx"])
         losses = r["losses"] if with_losses else torch.zeros(4, dtype=torch.float32, device=h.device)
         return r["idx"], r["weights"], r["comb_idx"], r["comb_w"], losses
 
     @staticmethod
     def backward(ctx, _g_idx, g_w, _g_cidx, g_cw, g_losses):
-        (weight,) = ctx.saved_tensors
+        weight, weights, comb_w = ctx.saved_tensors
+        saved = dict(ctx.internals, weights=weights, comb_w=comb_w)
         h_shape, h_dtype, top_k, num_shared, routed_scale, has_bias = ctx.cfg
         if g_w is not None:
             g_w = g_w.float()
@@ -77,18 +83,25 @@ class _Route(torch.autograd.Function):
             g_cw = g_cw.float()
         if g_losses is not None:
             g_losses = g_losses.float()
-        r = ops.router_bwd(h_shape, h_dtype, weight, ctx.saved, top_k, num_shared, routed_scale,
-                           g_w, g_cw, g_losses, want_dh=ctx.needs_input_grad[0])
+        want_dh = ctx.needs_input_grad[0]
+        rolling = ctx.pos_weight is not None
+        r = ops.router_bwd(h_shape, h_dtype, weight, saved, top_k, num_shared, routed_scale,
+                           g_w, g_cw, g_losses, want_dh=want_dh and not rolling)
+        d_h = r["d_h"]
+        if rolling and want_dh:
+            d_h = ops.pool_weighted_bwd(r["d_pooled"], ctx.pos_weight, h_shape, h_dtype)
         d_w = r["d_w"].to(weight.dtype) if ctx.needs_input_grad[1] else None
         d_b = r["d_bias"] if (has_bias and ctx.needs_input_grad[2]) else None
-        return r["d_h"], d_w, d_b, None, None, None, None
+        return d_h, d_w, d_b, None, None, None, None, None
 
 
 def route(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, num_shared: int,
-          routed_scale: float = 1.0, with_losses: bool = True):
-    """Returns (idx int64 [B,k'], weights [B,k'], comb_idx int32 [B,S+k'], comb_w [B,S+k'], losses dict)."""
+          routed_scale: float = 1.0, with_losses: bool = True, pos_weight: Optional[torch.Tensor] = None):
+    """Returns (idx int64 [B,k'], weights [B,k'], comb_idx int32 [B,S+k'], comb_w [B,S+k'], losses dict).
+    ``pos_weight`` [L]: pool with these per-position coefficients instead of the plain mean (the
+    sequence-rolling rule, see :func:`ops.rolling_pool_coefficients`)."""
     idx, w, cidx, cw, lv = _Route.apply(h, weight, bias, int(top_k), int(num_shared), float(routed_scale),
-                                        bool(with_losses))
+                                        bool(with_losses), pos_weight)
     losses = {k: lv[i] for i, k in enumerate(LOSS_KEYS)} if with_losses else {}
     if with_losses:
         losses = _LossDict(losses)
@@ -372,7 +385,9 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
         ctx.cfg = cfg
         ctx.norm_row = norm
         ctx.scale = scale
-        ctx.router_saved = r
+        # outputs of this node (weights, combined weights, losses) are saved through save_for_backward below:
+        # kept as attributes they would tie the node to its own outputs in a reference cycle
+        ctx.router_saved = {k: r[k] for k in ("pooled", "probs", "idx", "comb_idx", "row_stats", "chapter_stats", "_ws")}
         ctx.seg = seg
         ctx.sink = sink
         ctx.same_h = h_router is h_attn
@@ -382,7 +397,7 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
         ctx.wt = (wq_t, wkv_t, wo_t)
         ctx.save_for_backward(h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse, bank, router_w, stats_m,
                               x2 if pre_norm is not None else None, stats_n,
-                              norm_w.float() if pre_norm is not None else None)
+                              norm_w.float() if pre_norm is not None else None, r["weights"], r["comb_w"])
         ctx.mark_non_differentiable(r["idx"], r["comb_idx"])
         losses = r["losses"] if with_losses else torch.zeros(4, dtype=torch.float32, device=dev)
         return out.view(b, l, -1).to(h_attn.dtype), r["idx"], r["weights"], r["comb_idx"], r["comb_w"], losses
@@ -390,12 +405,12 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g, _g_idx, g_w, _g_cidx, g_cw, g_losses):
         (h2, m2, wq_c, wkv_c, wo_c, q, kv, o, lse, bank, router_w, stats_m, x2, stats_n,
-         norm_w) = ctx.saved_tensors
+         norm_w, r_weights, r_comb_w) = ctx.saved_tensors
         (num_heads, num_kv_heads, t, top_k, num_shared, routed_scale, _row_norm, row_eps, _with_losses,
          pre_norm, _pre_eps, add_residual) = ctx.cfg
         hr_shape, hr_dtype, ha_dtype, has_rbias, wdt, nw_dtype, nb_dtype = ctx.shapes
         wq_t, wkv_t, wo_t = ctx.wt
-        r, seg = ctx.router_saved, ctx.seg
+        r, seg = dict(ctx.router_saved, weights=r_weights, comb_w=r_comb_w), ctx.seg
         cd, f32 = torch.bfloat16, torch.float32
         dev = q.device
         b, l, _ = o.shape

@@ -75,5 +75,20 @@ class MemoryCrossAttention(nn.Module):
             raise NotImplementedError("attention weights are never materialised by the fused kernels")
         out = F_moc.cross_attention(hidden_states, memory, self.q_proj.weight, self.k_proj.weight,
                                     self.v_proj.weight, self.o_proj.weight, self.num_heads, self.num_kv_heads,
-                                    self.compute_dtype or hidden_states.dtype)
+                                    self._compute_dtype(hidden_states))
         return out, None
+
+    def _compute_dtype(self, hidden_states: torch.Tensor) -> torch.dtype:
+        """Arithmetic type of the projections and the attention.  An explicit ``compute_dtype`` wins; otherwise
+        an active CUDA autocast region decides, as it does for the reference's ``nn.Linear`` layers (the trainer
+        wraps the model in bf16 autocast, training/trainer.py:100-103, while parameters and the residual
+        stream stay fp32) -- autocast never reaches inside a custom autograd function, so it is read here.
+        Outside autocast the hidden states' own dtype is used."""
+        if self.compute_dtype is not None:
+            return self.compute_dtype
+        if hidden_states.is_cuda and torch.is_autocast_enabled("cuda"):
+            dt = torch.get_autocast_dtype("cuda")
+            if dt == torch.bfloat16:
+                return dt
+            raise NotImplementedError(f"autocast to {dt}: the tensor-core kernels compute in bf16")
+        return hidden_states.dtype

@@ -70,6 +70,6 @@ class MemorySubBlock(nn.Module):
         a = self.memory_attn
         return F_moc.cross_attention(
             hidden_states, memory, a.q_proj.weight, a.k_proj.weight, a.v_proj.weight, a.o_proj.weight,
-            a.num_heads, a.num_kv_heads, a.compute_dtype or hidden_states.dtype,
+            a.num_heads, a.num_kv_heads, a._compute_dtype(hidden_states),
             pre_norm="rms" if self.use_rms_norm else "layernorm", norm_weight=self.memory_layernorm.weight,
             norm_bias=getattr(self.memory_layernorm, "bias", None), norm_eps=self.norm_eps, add_residual=True)

@@ -19,6 +19,10 @@ def _contig(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
 # Kernel-launch accounting and optional per-call CUDA-event timing (used by the benchmark).
 LAUNCHES = 0
 TIMER = None   # when a dict: name -> list of (start_event, end_event) on the current stream
+LAUNCH_HOOK = None   # when callable: called with "<operator>:<bf16|f32|...>" for every operator call (tests use it to
+                     # assert which arithmetic path ran)
+
+_DTYPE_TAG = {torch.bfloat16: "bf16", torch.float32: "f32", torch.float16: "f16"}
 
 
 def _instrument(name: str, launches):
@@ -29,6 +33,10 @@ def _instrument(name: str, launches):
             global LAUNCHES
             n = launches(*args, **kwargs) if callable(launches) else launches
             LAUNCHES += n
+            if LAUNCH_HOOK is not None:
+                base = (name(*args, **kwargs) if callable(name) else name).split(":")[0]
+                first = next((a for a in args if torch.is_tensor(a)), None)
+                LAUNCH_HOOK(base + ":" + (_DTYPE_TAG.get(first.dtype, str(first.dtype)) if first is not None else "-"))
             if TIMER is None:
                 return fn(*args, **kwargs)
             e0 = torch.cuda.Event(enable_timing=True)
@@ -67,9 +75,11 @@ def _router_fwd_launches(*a, **k):
              _router_fwd_launches)
 def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top_k: int,
                num_shared: int, routed_scale: float, with_losses: bool, parts: int = 3,
-               out: Optional[Dict[str, torch.Tensor]] = None) -> Dict[str, torch.Tensor]:
+               out: Optional[Dict[str, torch.Tensor]] = None,
+               pooled: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
     """``parts`` (1 = pooling, logits, selection; 2 = loss terms) runs a subset on the current stream; pass the dict
-    returned by the first call as ``out`` to the second."""
+    returned by the first call as ``out`` to the second.  ``pooled`` ([B, d] fp32): pooled states computed by
+    another rule (see :func:`pool_weighted_fwd`); the mean-pool is then skipped."""
     L.require_cuda(h, weight, bias)
     if h.dim() != 3:
         raise ValueError(f"hidden_states must be 3D (B, T, D), got shape {tuple(h.shape)}")
@@ -94,6 +104,9 @@ def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
             "losses": torch.empty(4, **f32) if with_losses else None,
             "_ws": torch.empty(ws_bytes, dtype=torch.uint8, device=dev),
         }
+    if pooled is not None:
+        out["pooled"] = _contig(pooled.float())
+        parts = int(parts) | 8
     rc = lib.moc_router_fwd_parts(C.byref(s), L.ptr(h), L.ptr(weight), L.ptr(bias), L.ptr(out["pooled"]),
                                   L.ptr(out["logits"]), L.ptr(out["probs"]), L.ptr(out["idx"]), L.ptr(out["weights"]),
                                   L.ptr(out["comb_idx"]), L.ptr(out["comb_w"]), L.ptr(out["row_stats"]),
@@ -149,6 +162,57 @@ def router_bwd(h_shape, h_dtype, weight: torch.Tensor, saved: Dict[str, torch.Te
                                   L.stream_ptr(dev))
     L.check(rc, "moc_router_bwd_parts")
     return out
+
+
+def rolling_pool_coefficients(seq: int, window) -> torch.Tensor:
+    """c[s] such that sum_s c[s] h[:, s] equals the reference's ``_sequence_rolling_pool`` (router.py:159-195):
+    the mean over t of mean(h[max(0, t-w+1) .. t]).  Position s belongs to the windows ending at t = s .. s+w-1
+    (clipped to the sequence), each contributing 1 / (L * window_length(t)).  Host arithmetic in fp64."""
+    if seq <= 0:
+        raise ValueError("sequence length must be > 0")
+    w = seq if window is None else int(window)
+    if w <= 0:
+        raise ValueError(f"rolling_window_size must be > 0, got {window}")
+    w = min(w, seq)
+    t = torch.arange(seq, dtype=torch.float64)
+    inv_len = 1.0 / torch.clamp(t + 1, max=w)                  # window ending at t holds min(t + 1, w) positions
+    csum = torch.cat([torch.zeros(1, dtype=torch.float64), inv_len.cumsum(0)])
+    hi = torch.clamp(torch.arange(seq) + w, max=seq)            # windows ending at s .. min(s + w, L) - 1 cover s
+    return ((csum[hi] - csum[torch.arange(seq)]) / seq).float()
+
+
+@_instrument("pool_weighted_fwd", 2)
+def pool_weighted_fwd(h: torch.Tensor, pos_weight: torch.Tensor) -> torch.Tensor:
+    L.require_cuda(h, pos_weight)
+    h = _contig(h)
+    b, l, d = h.shape
+    pooled = torch.empty(b, d, dtype=torch.float32, device=h.device)
+    ws = torch.empty(b * 32 * d, dtype=torch.float32, device=h.device)
+    rc = L.lib().moc_pool_weighted_fwd(L.ptr(h), L.dtype_code(h.dtype), L.ptr(_contig(pos_weight.float())),
+                                       L.ptr(pooled), b, l, d, L.ptr(ws), ws.numel() * 4, L.stream_ptr(h.device))
+    L.check(rc, "moc_pool_weighted_fwd")
+    return pooled
+
+
+@_instrument("pool_weighted_bwd", 1)
+def pool_weighted_bwd(d_pooled: torch.Tensor, pos_weight: torch.Tensor, h_shape, h_dtype,
+                      d_h_accum: Optional[torch.Tensor] = None) -> torch.Tensor:
+    b, l, d = h_shape
+    d_h = d_h_accum if d_h_accum is not None else torch.empty(b, l, d, dtype=h_dtype, device=d_pooled.device)
+    rc = L.lib().moc_pool_weighted_bwd(L.ptr(_contig(d_pooled)), L.ptr(_contig(pos_weight.float())), L.ptr(d_h),
+                                       L.dtype_code(h_dtype), b, l, d, 1 if d_h_accum is not None else 0,
+                                       L.stream_ptr(d_pooled.device))
+    L.check(rc, "moc_pool_weighted_bwd")
+    return d_h
+
+
+def wait_probe(device, expected: int, arrivals: int, poll_limit: int):
+    """Runs the bounded-wait self-test kernel; returns (wait succeeded, second wait result, abort flag)."""
+    out = torch.zeros(3, dtype=torch.int32, device=device)
+    rc = L.lib().moc_wait_probe(int(expected), int(arrivals), int(poll_limit), L.ptr(L.status_word(device)),
+                                L.ptr(out), L.stream_ptr(device))
+    L.check(rc, "moc_wait_probe")
+    return tuple(int(v) for v in out.tolist())
 
 
 # --------------------------------------------------------------------------------------------

@@ -38,15 +38,33 @@ class ChapterRouter(nn.Module):
     def forward(self, hidden_states: torch.Tensor, return_losses: bool = True, exclude_prefix_chapters: int = 0,
                 rolling_window_size: Optional[int] = None
                 ) -> Tuple[torch.Tensor, torch.Tensor, Dict[str, torch.Tensor]]:
-        if self.routing_strategy != "sequence":
-            raise NotImplementedError(
-                f"routing_strategy {self.routing_strategy!r}: only 'sequence' pooling runs on the CUDA router")
+        pos_weight = None
+        if self.routing_strategy in ("sequence-rolling", "sequence_rolling"):
+            # router.py:100-105, 159-195: the mean over t of the rolling-window means is one coefficient per position
+            if hidden_states.dim() != 3:
+                raise ValueError(f"hidden_states must be 3D (B, T, D), got shape {tuple(hidden_states.shape)}")
+            pos_weight = self._rolling_coefficients(hidden_states.shape[1], rolling_window_size, hidden_states.device)
+        elif self.routing_strategy == "token":
+            # router.py:106-110 projects every token and averages the logits; the projection is linear, so this is
+            # the router applied to the mean state (equal up to rounding)
+            pass
+        elif self.routing_strategy != "sequence":
+            raise ValueError(f"Unknown routing_strategy: {self.routing_strategy}")
         if exclude_prefix_chapters < 0 or exclude_prefix_chapters > self.num_chapters:
             raise ValueError(
                 f"exclude_prefix_chapters must be in [0, {self.num_chapters}], got {exclude_prefix_chapters}")
         idx, w, _, _, losses = F_moc.route(hidden_states, self.router.weight, self.router.bias, self.top_k,
-                                           exclude_prefix_chapters, 1.0, return_losses)
+                                           exclude_prefix_chapters, 1.0, return_losses, pos_weight=pos_weight)
         return idx, w, losses
+
+    def _rolling_coefficients(self, seq: int, window: Optional[int], device) -> torch.Tensor:
+        key = (int(seq), None if window is None else int(window), str(device))
+        cache = self.__dict__.setdefault("_rolling_cache", {})
+        if key not in cache:
+            if len(cache) > 16:
+                cache.clear()
+            cache[key] = F_moc.ops.rolling_pool_coefficients(seq, window).to(device)
+        return cache[key]
 
     def route_with_shared(self, hidden_states: torch.Tensor, num_shared_chapters: int,
                           routed_scaling_factor: float, return_losses: bool = True):

@@ -74,6 +74,22 @@ def router_pool(hidden_states: torch.Tensor) -> torch.Tensor:
     return hidden_states.float().mean(dim=1)
 
 
+def router_pool_rolling(hidden_states: torch.Tensor, rolling_window_size: Optional[int] = None) -> torch.Tensor:
+    """Mean over t of the rolling-window means mean(h[max(0, t-w+1) .. t]) (router.py:159-195), by prefix sums
+    as the reference does."""
+    h = hidden_states.float()
+    batch, seq, dim = h.shape
+    window = seq if rolling_window_size is None else int(rolling_window_size)
+    if window <= 0:
+        raise ValueError(f"rolling_window_size must be > 0, got {rolling_window_size}")   # router.py:179-180
+    window = min(window, seq)
+    csum = torch.cat([h.new_zeros((batch, 1, dim)), h.cumsum(dim=1)], dim=1)             # router.py:184-186
+    end = torch.arange(seq) + 1
+    start = torch.clamp(end - window, min=0)                                             # router.py:188-190
+    sums = csum[:, end, :] - csum[:, start, :]                                           # router.py:192
+    return (sums / (end - start).to(h.dtype).view(1, seq, 1)).mean(dim=1)                # router.py:193-195
+
+
 def router_forward(
     hidden_states: torch.Tensor,
     weight: torch.Tensor,
@@ -81,15 +97,21 @@ def router_forward(
     top_k: int,
     exclude_prefix_chapters: int = 0,
     return_losses: bool = True,
+    routing_strategy: str = "sequence",
+    rolling_window_size: Optional[int] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, Dict[str, torch.Tensor], Dict[str, torch.Tensor]]:
-    """Sequence-level routing (router.py:94-156).
+    """Sequence-level routing (router.py:94-156); ``routing_strategy`` "sequence" or "sequence-rolling"
+    (router.py:96-105).
 
     Returns (indices (B,k') int64, weights (B,k'), losses, internals).
     """
     num_chapters = weight.shape[0]
     if exclude_prefix_chapters < 0 or exclude_prefix_chapters > num_chapters:
         raise ValueError("exclude_prefix_chapters out of range")        # router.py:117-121
-    pooled = router_pool(hidden_states)                                  # router.py:98
+    if routing_strategy in ("sequence-rolling", "sequence_rolling"):
+        pooled = router_pool_rolling(hidden_states, rolling_window_size) # router.py:100-104
+    else:
+        pooled = router_pool(hidden_states)                              # router.py:98
     logits = pooled @ weight.float().t() + bias.float()                  # router.py:99
     probs = F.softmax(logits, dim=-1)                                    # router.py:115
     batch = hidden_states.shape[0]
@@ -382,7 +404,7 @@ def layer_flops(batch: int, seq: int, shape: LayerShape) -> float:
 
 
 __all__ = [
-    "LayerShape", "topk_lower_index_first", "router_pool", "router_forward", "router_losses",
+    "LayerShape", "topk_lower_index_first", "router_pool", "router_pool_rolling", "router_forward", "router_losses",
     "total_router_loss", "route_token_level", "prepend_shared_chapters", "gather_chapters",
     "normalize_memory_rows", "scale_memory", "cross_attention", "sparse_chapter_attention",
     "memory_layer", "memory_layer_fwd_bwd", "layer_flops",

@@ -60,8 +60,15 @@ CASES = {
         Case("block_layernorm", 2, 64, 128, 2, 1, 33, 16, 4, seed=1244, pre_norm="layernorm",
              separate_router_input=True,
              notes="LayerNorm variant of the block's memory step, grouped KV heads, router fed separately"),
+        Case("head64_t64_rms", 2, 128, 128, 2, 2, 17, 64, 4, norm_type="rms", seed=1245,
+             notes="the paper's setting (per-row RMS normalisation of the gathered rows) at tensor-core tile shapes"),
+        Case("head64_t64_ln", 2, 128, 128, 2, 1, 17, 64, 4, norm_type="layernorm", seed=1246,
+             notes="affine-free LayerNorm of the gathered rows at tensor-core tile shapes, grouped KV heads"),
     ]
 }
+
+# cases whose fixtures also hold the reference's outputs under bf16 autocast (head_dim 64: the tensor-core path)
+BF16_CASES = ("head64_t64", "block_rms", "head64_t64_rms", "head64_t64_ln")
 
 
 def make_inputs(case: Case) -> Dict[str, np.ndarray]:

@@ -29,7 +29,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
-from cases import CASES, make_inputs  # noqa: E402
+from cases import BF16_CASES, CASES, make_inputs  # noqa: E402
 
 
 def import_reference(path: str):
@@ -135,6 +135,31 @@ def run_reference(ref, case, inputs, autocast_bf16=False):
     return res
 
 
+ROLLING = dict(case="rms_norm", window=8, coef={"load_balance": 0.3, "auxiliary": 700.0, "z_loss": 0.2, "entropy": 0.1})
+
+
+def run_reference_rolling(ref):
+    """``ChapterRouter`` with ``routing_strategy="sequence-rolling"`` (router.py:100-105, 159-195) on the inputs
+    of one small case: selection, weights, losses and the gradients of a weighted sum of all of them."""
+    case = CASES[ROLLING["case"]]
+    t = {k: torch.from_numpy(v.copy()) for k, v in make_inputs(case).items()}
+    router = ref["ChapterRouter"](case.hidden_dim, case.num_chapters, top_k=case.top_k,
+                                  routing_strategy="sequence-rolling")
+    with torch.no_grad():
+        router.router.weight.copy_(t["router_w"]); router.router.bias.copy_(t["router_b"])
+    router.train()
+    h = t["h_router"].clone().requires_grad_(True)
+    idx, w, losses = router(h, return_losses=True, exclude_prefix_chapters=case.num_shared_chapters,
+                            rolling_window_size=ROLLING["window"])
+    g_w = torch.from_numpy(np.random.Generator(np.random.PCG64(77)).standard_normal(tuple(w.shape), dtype=np.float32))
+    (sum(c * losses[k] for k, c in ROLLING["coef"].items()) + (w * g_w).sum()).backward()
+    res = {"indices": idx.numpy(), "weights": w.detach().numpy(), "g_w": g_w.numpy(), "d_h": h.grad.numpy(),
+           "d_router_w": router.router.weight.grad.numpy(), "d_router_b": router.router.bias.grad.numpy()}
+    for k, v in losses.items():
+        res["loss_" + k] = v.detach().numpy()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
@@ -143,12 +168,15 @@ def main():
     ref = import_reference(args.reference)
     torch.manual_seed(0)
     torch.set_num_threads(8)
+    if not args.only or args.only == "rolling":
+        np.savez_compressed(os.path.join(HERE, "rolling.npz"), **run_reference_rolling(ref))
+        print("rolling", os.path.getsize(os.path.join(HERE, "rolling.npz")))
     for name, case in CASES.items():
         if args.only and name != args.only:
             continue
         inputs = make_inputs(case)
         res = run_reference(ref, case, inputs, autocast_bf16=False)
-        if name in ("head64_t64", "block_rms"):
+        if name in BF16_CASES:
             bf = run_reference(ref, case, inputs, autocast_bf16=True)
             for k in ("out", "d_h_router", "d_wq", "d_wk", "d_wv", "d_wo", "d_bank_touched", "d_pre_norm_w"):
                 if k in bf:

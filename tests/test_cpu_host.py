@@ -73,3 +73,17 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text, f"{f} mentions the oracle"
+
+
+def test_rolling_pool_coefficients_reproduce_the_window_means():
+    """sum_s c[s] h[s] must equal the mean over t of the rolling-window means (router.py:159-195)."""
+    from memory_b200.ops import rolling_pool_coefficients
+    from oracle import moc_oracle as O
+    for seq, window in ((37, 8), (16, None), (5, 100), (128, 1), (64, 64)):
+        h = torch.randn(3, seq, 16, dtype=torch.float64)
+        c = rolling_pool_coefficients(seq, window).double()
+        ref = O.router_pool_rolling(h.float(), window).double()
+        assert float((ref - (h * c.view(1, -1, 1)).sum(1)).abs().max()) < 1e-5
+        assert abs(float(c.sum()) - 1.0) < 1e-6
+    with pytest.raises(ValueError):
+        rolling_pool_coefficients(8, 0)

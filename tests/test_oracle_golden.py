@@ -65,6 +65,26 @@ def test_oracle_matches_reference_bf16_autocast():
     np.testing.assert_allclose(res["d_wq"].numpy(), gold["bf16_d_wq"], rtol=2e-2, atol=2e-3)
 
 
+def test_oracle_rolling_pool_router_matches_reference():
+    """routing_strategy "sequence-rolling" (router.py:100-105, 159-195)."""
+    from make_golden import ROLLING
+    case = CASES[ROLLING["case"]]
+    gold = np.load(os.path.join(GOLDEN, "rolling.npz"))
+    inp = {k: torch.from_numpy(v) for k, v in make_inputs(case).items()}
+    h = inp["h_router"].clone().requires_grad_(True)
+    W = inp["router_w"].clone().requires_grad_(True)
+    b = inp["router_b"].clone().requires_grad_(True)
+    idx, w, losses, _ = O.router_forward(h, W, b, case.top_k, case.num_shared_chapters, True,
+                                         routing_strategy="sequence-rolling", rolling_window_size=ROLLING["window"])
+    (sum(c * losses[k] for k, c in ROLLING["coef"].items()) + (w * torch.from_numpy(gold["g_w"])).sum()).backward()
+    assert np.array_equal(idx.numpy(), gold["indices"])
+    np.testing.assert_allclose(w.detach().numpy(), gold["weights"], rtol=1e-5, atol=1e-7)
+    for k in ("load_balance", "auxiliary", "z_loss", "entropy"):
+        np.testing.assert_allclose(losses[k].item(), gold["loss_" + k], rtol=1e-5, atol=1e-8)
+    np.testing.assert_allclose(h.grad.numpy(), gold["d_h"], rtol=1e-4, atol=1e-8)
+    np.testing.assert_allclose(W.grad.numpy(), gold["d_router_w"], rtol=1e-4, atol=1e-8)
+
+
 def test_topk_order_is_value_desc_then_index_asc():
     p = torch.tensor([[0.5, 1.0, 1.0, 0.2, 1.0, 1.0, 0.1]])
     v, i = O.topk_lower_index_first(p, 3)

@@ -4,7 +4,7 @@ import os
 import numpy as np
 import torch
 
-from cases import CASES, make_inputs  # noqa: F401  (tests/golden is on sys.path via conftest)
+from cases import BF16_CASES, CASES, make_inputs  # noqa: F401  (tests/golden is on sys.path via conftest)
 from oracle import moc_oracle as O
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -26,6 +26,34 @@ def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
     a = a.detach().float().cpu()
     b = b.detach().float().cpu()
     return float((a - b).abs().max() / (b.abs().max() + 1e-30))
+
+
+def close_stats(a: torch.Tensor, b: torch.Tensor, tol: float) -> dict:
+    """The three forms a tolerance is checked in.
+
+    ``max_rel``   max |a-b| / max |b|            (one number per tensor)
+    ``l2_rel``    ||a-b||_2 / ||b||_2            (catches errors spread over many small entries)
+    ``bad``       entries failing |a-b| <= tol + tol |b|, the element-wise form of the reference's kernel
+                  harness (kernels-final/benchmark_kernels_final.py:676-682), with the worst one's index
+    """
+    a = a.detach().float().cpu()
+    b = b.detach().float().cpu()
+    diff = (a - b).abs()
+    viol = diff > (tol + tol * b.abs())
+    n_bad = int(viol.sum())
+    worst = None
+    if n_bad:
+        flat = int((diff - tol * b.abs()).reshape(-1).argmax())
+        worst = (flat, float(a.reshape(-1)[flat]), float(b.reshape(-1)[flat]))
+    return {"max_rel": float(diff.max() / (b.abs().max() + 1e-30)),
+            "l2_rel": float(diff.double().pow(2).sum().sqrt() / (b.double().pow(2).sum().sqrt() + 1e-30)),
+            "bad": n_bad, "numel": b.numel(), "worst": worst}
+
+
+def assert_close_all_forms(a, b, tol, what=""):
+    s = close_stats(a, b, tol)
+    assert s["max_rel"] < tol and s["l2_rel"] < tol and s["bad"] == 0, (what, s)
+    return s
 
 
 def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001):
