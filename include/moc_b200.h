@@ -68,6 +68,10 @@ typedef struct {
 
 /* Bytes of device scratch moc_router_fwd / moc_router_bwd need. */
 size_t moc_router_workspace_bytes(const moc_router_shape* s);
+/* The same for a call restricted to some parts (bit sets as in moc_router_fwd_parts / moc_router_bwd_parts; 0 = that
+ * direction is not called with this workspace).  A token-level call (fwd bits 8 + 16, bwd bit 1 only) needs a few
+ * hundred bytes where the sequence-level layout would reserve batch-sized pooling scratch. */
+size_t moc_router_workspace_bytes_parts(const moc_router_shape* s, int32_t fwd_parts, int32_t bwd_parts);
 
 /* Forward.  Outputs (device): pooled [B,d], logits [B,C], probs [B,C] (fp32);
  * idx [B,k'] int64 and weights [B,k'] (sorted by weight descending, ties to the lower chapter id);
@@ -82,7 +86,10 @@ int moc_router_fwd(const moc_router_shape* s, const void* h, const float* w, con
 
 /* moc_router_fwd in two pieces: parts bit 1 = pooling, logits, selection (everything the gather needs),
  * bit 2 = the loss terms (reads probs / idx / row_stats of bit 1), bit 8 (with bit 1) = `pooled` already holds
- * the pooled states, e.g. from moc_pool_weighted_fwd, and `h` is not read.  A caller can wait for bit 1 only and let the
+ * the pooled states, e.g. from moc_pool_weighted_fwd, and `h` is not read; bit 16 (with bit 1) = `logits` already
+ * holds pooled x W^T from a projection kernel and only the bias is added before the selection.  Bits 8 + 16 with
+ * batch = B*L rows and seq = 1 are ChapterRouter.route_token_level (memory_transformer/router.py:262-340): every
+ * token is its own routing row.  A caller can wait for bit 1 only and let the
  * losses finish beside the gather.  moc_router_fwd is parts = 3.  No counterpart in the reference. */
 int moc_router_fwd_parts(const moc_router_shape* s, const void* h, const float* w, const float* bias,
                          float* pooled, float* logits, float* probs, int64_t* idx, float* weights,
@@ -120,6 +127,10 @@ int moc_pool_weighted_fwd(const void* h, int32_t h_dtype, const float* pos_weigh
                           int32_t seq, int32_t dim, void* workspace, size_t workspace_bytes, void* stream);
 int moc_pool_weighted_bwd(const float* d_pooled, const float* pos_weight, void* d_h, int32_t h_dtype,
                           int32_t batch, int32_t seq, int32_t dim, int32_t accumulate, void* stream);
+
+/* out[c] = sum over rows of x[r, c] (fp32, fixed summation order): the router bias gradient of the token-level
+ * path, where the logit gradient has one row per token (autograd of router.py:294). */
+int moc_col_sum(const float* x, float* out, int64_t rows, int32_t cols, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Chapter gather.  Replaces ChapteredMemoryBank.get_chapters_batched (memory_bank.py:244-293), the
@@ -290,6 +301,31 @@ int moc_sparse_attn_fwd(const moc_sparse_attn_shape* s, const void* q, const voi
 int moc_sparse_attn_bwd(const moc_sparse_attn_shape* s, const void* q, const void* k, const void* v,
                         const int32_t* block_indices, const void* o, const float* lse, const void* d_o,
                         void* d_q, float* d_k, float* d_v, int32_t* status, void* stream);
+
+/* out[r] = <a[r, :], b[r, :]> in fp32 for contiguous [rows, dim] operands: the per-(token, head) delta = <o, do> of
+ * memory_cross_attn_preprocess_delta (kernels-final/memory_cross_attn.py:1369-1384). */
+int moc_row_dot(const void* a, const void* b, int32_t dtype, float* out, int64_t rows, int32_t dim, void* stream);
+
+/* Weighted mixture rule: every selected chapter has its own softmax and the per-chapter outputs are mixed by
+ * router weights, o = base + out_scale * sum_s w[b,t,s] * softmax(q K_s^T * scale) V_s -- the contract of
+ * FSA_topk_sparse_attention_weighted_bthd (kernels-final/kernel_v4.py:972-1027, 1313-1340) and, with base = the
+ * dense shared-chapter branch and out_scale = routed_scale, the routed branch of
+ * MemoryCrossAttention._forward_token_routed_attention (memory_transformer/memory_attention.py:550-551, 596-714).
+ *   weights fp32 [B,TQ,S]; base like o or NULL; lse_slots fp32 [B,TQ,HQ,S] (every chapter's own log-sum-exp);
+ *   kv_row_stride: elements between consecutive rows of k (and of v), H*D when contiguous -- larger when K and V
+ *   of one bank row share a projected row. */
+int moc_sparse_attn_weighted_fwd(const moc_sparse_attn_shape* s, const void* q, const void* k, const void* v,
+                                 int64_t kv_row_stride, const int32_t* block_indices, const float* weights,
+                                 const void* base, float out_scale, void* o, float* lse_slots, int32_t* status,
+                                 void* stream);
+/* Backward (kernels-final/kernel_v4.py:1029-1231).  d_o is the gradient of o.  d_q is written, or added to when
+ * accumulate_dq != 0; d_k / d_v are fp32 accumulators with row stride dkv_row_stride that the CALLER has zeroed
+ * (atomic adds); d_w_heads fp32 [B,TQ,HQ,S] holds every head's share of the weight gradient (sum over HQ). */
+int moc_sparse_attn_weighted_bwd(const moc_sparse_attn_shape* s, const void* q, const void* k, const void* v,
+                                 int64_t kv_row_stride, const int32_t* block_indices, const float* weights,
+                                 float out_scale, const float* lse_slots, const void* d_o, void* d_q,
+                                 int32_t accumulate_dq, float* d_k, float* d_v, int64_t dkv_row_stride,
+                                 float* d_w_heads, int32_t* status, void* stream);
 
 /* Element-wise helpers used by the host layer (device pointers, n elements). */
 int moc_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream);

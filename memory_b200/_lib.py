@@ -58,6 +58,7 @@ _PROTOTYPES = {
     "moc_last_error": (C.c_char_p, []),
     "moc_abi_version": (C.c_int, []),
     "moc_router_workspace_bytes": (C.c_size_t, [C.POINTER(RouterShape)]),
+    "moc_router_workspace_bytes_parts": (C.c_size_t, [C.POINTER(RouterShape), C.c_int32, C.c_int32]),
     "moc_router_fwd": (C.c_int, [C.POINTER(RouterShape)] + [P] * 13 + [P, C.c_size_t, P, P]),
     "moc_router_fwd_parts": (C.c_int, [C.POINTER(RouterShape)] + [P] * 13 + [P, C.c_size_t, C.c_int32, P, P]),
     "moc_router_bwd": (C.c_int, [C.POINTER(RouterShape)] + [P] * 16 + [C.c_int32, P, C.c_size_t, P, P]),
@@ -78,6 +79,12 @@ _PROTOTYPES = {
     "moc_attn_bwd_static": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P, P, P, P]),
     "moc_sparse_attn_fwd": (C.c_int, [C.POINTER(SparseAttnShape), P, P, P, P, P, P, P, P]),
     "moc_sparse_attn_bwd": (C.c_int, [C.POINTER(SparseAttnShape), P, P, P, P, P, P, P, P, P, P, P, P]),
+    "moc_sparse_attn_weighted_fwd": (C.c_int, [C.POINTER(SparseAttnShape), P, P, P, C.c_int64, P, P, P, C.c_float,
+                                               P, P, P, P]),
+    "moc_sparse_attn_weighted_bwd": (C.c_int, [C.POINTER(SparseAttnShape), P, P, P, C.c_int64, P, P, C.c_float, P,
+                                               P, P, C.c_int32, P, P, C.c_int64, P, P, P]),
+    "moc_row_dot": (C.c_int, [P, P, C.c_int32, P, C.c_int64, C.c_int32, P]),
+    "moc_col_sum": (C.c_int, [P, P, C.c_int64, C.c_int32, P]),
     "moc_cast_f32_to_bf16": (C.c_int, [P, P, C.c_int64, P]),
     "moc_cast_bf16_to_f32": (C.c_int, [P, P, C.c_int64, P]),
     "moc_transpose": (C.c_int, [P, C.c_int32, P, C.c_int32, C.c_int32, C.c_int32, P]),

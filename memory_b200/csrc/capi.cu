@@ -88,3 +88,13 @@ extern "C" int moc_attn_bwd(const moc_attn_shape* s, const void* q, const void* 
   set_last_error("dtype", "unknown dtype");
   return MOC_ERR_INVALID;
 }
+
+
+extern "C" int moc_row_dot(const void* a, const void* b, int32_t dtype, float* out, int64_t rows, int32_t dim,
+                           void* stream_) {
+  MOC_REQUIRE(a && b && out && rows > 0 && dim > 0, "bad row-dot arguments");
+  MOC_REQUIRE(dtype == MOC_F32 || dtype == MOC_BF16, "bad dtype");
+  MOC_REQUIRE(rows <= 0x7fffffffLL, "too many rows");
+  // one (batch, head) with `rows` positions: delta[l] = <a[l, :], b[l, :]>
+  return launch_delta(dtype, a, b, out, 1, static_cast<int>(rows), 1, dim, static_cast<cudaStream_t>(stream_));
+}

@@ -451,14 +451,42 @@ __global__ void loss_partial_kernel(const float* __restrict__ probs, const long 
 }
 __global__ void loss_finish_kernel(const float* __restrict__ partial, const float* __restrict__ row_stats,
                                    float* __restrict__ losses, int nblk, int B, int C) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  // one warp; every lane sums a strided share in a fixed order, then a fixed-order shuffle tree
+  if (blockIdx.x != 0 || threadIdx.x >= 32) return;
+  const int lane = threadIdx.x;
   float lb = 0.f, aux = 0.f, ent = 0.f, z = 0.f;
-  for (int i = 0; i < nblk; ++i) { lb += partial[i * 3]; aux += partial[i * 3 + 1]; ent += partial[i * 3 + 2]; }
-  for (int b = 0; b < B; ++b) { const float l = row_stats[b * 4]; z += l * l; }
-  losses[0] = static_cast<float>(C) * lb;
-  losses[1] = aux / static_cast<float>(C);
-  losses[2] = z / static_cast<float>(B);
-  losses[3] = -ent / static_cast<float>(B);
+  for (int i = lane; i < nblk; i += 32) { lb += partial[i * 3]; aux += partial[i * 3 + 1]; ent += partial[i * 3 + 2]; }
+  for (int b = lane; b < B; b += 32) { const float l = row_stats[static_cast<long long>(b) * 4]; z += l * l; }
+  lb = warp_sum(lb); aux = warp_sum(aux); ent = warp_sum(ent); z = warp_sum(z);
+  if (lane == 0) {
+    losses[0] = static_cast<float>(C) * lb;
+    losses[1] = aux / static_cast<float>(C);
+    losses[2] = z / static_cast<float>(B);
+    losses[3] = -ent / static_cast<float>(B);
+  }
+}
+
+// logits[r, c] += bias[c]
+__global__ void add_bias_kernel(float* __restrict__ logits, const float* __restrict__ bias, long long total, int C) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    logits[i] += bias[static_cast<int>(i % C)];
+}
+// out[c] = sum_r x[r, c]: one CTA per 32 columns, 8 row groups, fixed-order sums
+__global__ void col_sum_kernel(const float* __restrict__ x, float* __restrict__ out, long long rows, int cols) {
+  __shared__ float part[8][32];
+  const int c = blockIdx.x * 32 + (threadIdx.x & 31), g = threadIdx.x >> 5;
+  float acc = 0.f;
+  if (c < cols)
+    for (long long r = g; r < rows; r += 8) acc += x[r * cols + c];
+  part[g][threadIdx.x & 31] = acc;
+  __syncthreads();
+  if (g == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += part[i][threadIdx.x];
+    out[c] = t;
+  }
 }
 
 // ---- backward --------------------------------------------------------------------------------
@@ -552,7 +580,9 @@ __global__ void dweight_kernel(const float* __restrict__ d_logits, const float* 
   for (int b0 = 0; b0 < B; b0 += 8) {
     const int nb = min(8, B - b0);
     __syncthreads();
-    for (int i = threadIdx.x; i < nb * d; i += blockDim.x) sp[i] = pooled[static_cast<long long>(b0) * d + i];
+    // rows past the batch are zero-filled: they are multiplied by dz = 0 below, and 0 x stale NaN would be NaN
+    for (int i = threadIdx.x; i < 8 * d; i += blockDim.x)
+      sp[i] = (i < nb * d) ? pooled[static_cast<long long>(b0) * d + i] : 0.f;
     __syncthreads();
 #pragma unroll
     for (int cc = 0; cc < kLogitsPerWarp; ++cc) {
@@ -676,14 +706,17 @@ inline int k_selected(const moc_router_shape* s) {
   if (k > avail) k = avail;
   return k < 0 ? 0 : k;
 }
-inline size_t ws_bytes(const moc_router_shape* s) {
-  const size_t pool = static_cast<size_t>(s->batch) * kPoolSplits * s->hidden_dim;
-  const size_t dp = static_cast<size_t>(ceil_div(s->num_chapters, kDpChunk)) * s->batch * s->hidden_dim;
-  const size_t loss = static_cast<size_t>(ceil_div(s->num_chapters, kLossChunk)) * 3;
-  size_t n = pool > dp ? pool : dp;
-  n += loss;
-  return n * sizeof(float);
+// Scratch layout: [ pooling partials | d_pooled partials ] (they never live at once), then the loss partials.
+// A call that neither pools (token rows, or pooled states handed in) nor produces d_pooled needs the loss part only.
+inline size_t ws_floats(const moc_router_shape* s, bool pool, bool dpooled) {
+  const size_t p = pool ? static_cast<size_t>(s->batch) * kPoolSplits * s->hidden_dim : 0;
+  const size_t dp = dpooled ? static_cast<size_t>(ceil_div(s->num_chapters, kDpChunk)) * s->batch * s->hidden_dim : 0;
+  return p > dp ? p : dp;
 }
+inline size_t loss_floats(const moc_router_shape* s) {
+  return static_cast<size_t>(ceil_div(s->num_chapters, kLossChunk)) * 3;
+}
+inline size_t ws_bytes(const moc_router_shape* s) { return (ws_floats(s, true, true) + loss_floats(s)) * sizeof(float); }
 inline int check_shape(const moc_router_shape* s) {
   MOC_REQUIRE(s != nullptr, "shape is NULL");
   MOC_REQUIRE(s->batch > 0 && s->seq > 0 && s->hidden_dim > 0, "empty router input");
@@ -702,6 +735,11 @@ inline int check_shape(const moc_router_shape* s) {
 using namespace moc;
 
 extern "C" size_t moc_router_workspace_bytes(const moc_router_shape* s) { return s ? ws_bytes(s) : 0; }
+extern "C" size_t moc_router_workspace_bytes_parts(const moc_router_shape* s, int32_t fwd_parts, int32_t bwd_parts) {
+  if (!s) return 0;
+  const bool pool = (fwd_parts & 1) && !(fwd_parts & 8);
+  return (ws_floats(s, pool, (bwd_parts & 4) != 0) + loss_floats(s)) * sizeof(float);
+}
 
 extern "C" int moc_router_fwd_parts(const moc_router_shape* s, const void* h, const float* w, const float* bias,
                                     float* pooled, float* logits, float* probs, int64_t* idx, float* weights,
@@ -710,7 +748,8 @@ extern "C" int moc_router_fwd_parts(const moc_router_shape* s, const void* h, co
                                     int32_t* status, void* stream_) {
   int rc = check_shape(s);
   if (rc != MOC_OK) return rc;
-  MOC_REQUIRE(workspace_bytes >= ws_bytes(s), "router workspace too small");
+  const size_t front = ws_floats(s, (parts & 1) && !(parts & 8), false);
+  MOC_REQUIRE(workspace_bytes >= (front + loss_floats(s)) * sizeof(float), "router workspace too small");
   MOC_REQUIRE((h || (parts & 8)) && w && pooled && logits && probs && comb_idx && comb_w && row_stats,
               "NULL router buffer");
   (void)status;
@@ -719,7 +758,8 @@ extern "C" int moc_router_fwd_parts(const moc_router_shape* s, const void* h, co
   const int k_sel = k_selected(s);
   MOC_REQUIRE(k_sel == 0 || (idx && weights), "NULL index / weight buffer");
   float* ws = static_cast<float*>(workspace);
-  float* loss_partial = ws + (ws_bytes(s) / sizeof(float) - static_cast<size_t>(ceil_div(C, kLossChunk)) * 3);
+  // the loss partials sit behind the front part of whatever layout the caller sized the workspace for
+  float* loss_partial = ws + (workspace_bytes / sizeof(float) - loss_floats(s));
 
   dim3 pg(B, kPoolSplits);
   if (parts & 1) {
@@ -730,7 +770,14 @@ extern "C" int moc_router_fwd_parts(const moc_router_shape* s, const void* h, co
     pool_partial_kernel<__nv_bfloat16><<<pg, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(h), ws, L, d);
   pool_finish_kernel<<<ceil_div(B * d, 256), 256, 0, stream>>>(ws, pooled, L, d, B * d);
   }
-  {
+  if (parts & 16) {        // bit 16: `logits` already holds pooled x W^T (a projection kernel ran); only the bias is missing
+    if (bias != nullptr) {
+      const long long total = static_cast<long long>(B) * C;
+      long long blocks = (total + 255) / 256;
+      if (blocks > 148LL * 16) blocks = 148LL * 16;
+      add_bias_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(logits, bias, total, C);
+    }
+  } else {
     const int warps = 8;
     const size_t sm = static_cast<size_t>(8) * d * sizeof(float);
     MOC_CUDA_OK(cudaFuncSetAttribute(logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
@@ -772,7 +819,7 @@ extern "C" int moc_router_bwd_parts(const moc_router_shape* s, const float* w, c
                                     int32_t* status, void* stream_) {
   int rc = check_shape(s);
   if (rc != MOC_OK) return rc;
-  MOC_REQUIRE(workspace_bytes >= ws_bytes(s), "router workspace too small");
+  MOC_REQUIRE(workspace_bytes >= ws_floats(s, false, (parts & 4) != 0) * sizeof(float), "router workspace too small");
   MOC_REQUIRE(w && pooled && probs && comb_w && row_stats && d_logits && d_w && d_pooled, "NULL router buffer");
   MOC_REQUIRE(d_losses == nullptr || chapter_stats != nullptr, "loss gradients need chapter_stats");
   (void)status;
@@ -860,6 +907,14 @@ extern "C" int moc_pool_weighted_bwd(const float* d_pooled, const float* pos_wei
   else
     pool_weighted_bwd_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, stream>>>(
         d_pooled, pos_weight, static_cast<__nv_bfloat16*>(d_h), seq, dim, total, accumulate);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+
+extern "C" int moc_col_sum(const float* x, float* out, int64_t rows, int32_t cols, void* stream_) {
+  MOC_REQUIRE(x && out && rows > 0 && cols > 0, "bad column-sum arguments");
+  col_sum_kernel<<<ceil_div(cols, 32), 256, 0, static_cast<cudaStream_t>(stream_)>>>(x, out, rows, cols);
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
 }

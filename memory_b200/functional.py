@@ -542,3 +542,262 @@ def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tenso
                           norm_weight=pre_norm_weight, norm_bias=pre_norm_bias, norm_eps=pre_norm_eps,
                           add_residual=add_residual)
     return out, losses, {"indices": idx, "weights": w, "combined_indices": cidx, "combined_weights": cw}
+
+
+# --------------------------------------------------------------------------------------------
+# token-level routing (every token selects its own chapters)
+# --------------------------------------------------------------------------------------------
+class _RouteTokens(torch.autograd.Function):
+    """ChapterRouter.route_token_level (router.py:262-340): logits of every token by an fp32 projection, then the
+    same softmax / prefix mask / top-k / renormalisation / loss kernels as the sequence router with one routing
+    row per token."""
+
+    @staticmethod
+    def forward(ctx, h, weight, bias, top_k, num_shared, with_losses):
+        b, l, d = h.shape
+        rows = b * l
+        h32 = ops.cast(h.reshape(rows, d).contiguous(), torch.float32)
+        w32 = weight.float().contiguous()
+        logits = ops.gemm(h32, w32, tag="token_router_logits")                     # [rows, C] fp32, no bias yet
+        r = ops.router_fwd(h32.view(rows, 1, d), w32, bias, top_k, num_shared, 1.0, with_losses, pooled=h32,
+                           logits=logits)
+        k = r["idx"].shape[1]
+        ctx.cfg = ((b, l, d), h.dtype, int(top_k), int(num_shared), bias is not None)
+        ctx.internals = {n: r[n] for n in ("pooled", "probs", "idx", "row_stats", "chapter_stats", "_ws", "comb_w")}
+        ctx.save_for_backward(w32, r["weights"])
+        idx = r["idx"].view(b, l, k)
+        ctx.mark_non_differentiable(idx)
+        losses = r["losses"] if with_losses else torch.zeros(4, dtype=torch.float32, device=h.device)
+        return idx, r["weights"].view(b, l, k), losses
+
+    @staticmethod
+    def backward(ctx, _g_idx, g_w, g_losses):
+        w32, weights = ctx.saved_tensors
+        (b, l, d), h_dtype, top_k, num_shared, has_bias = ctx.cfg
+        rows = b * l
+        saved = dict(ctx.internals, weights=weights)
+        g_w = None if g_w is None else g_w.reshape(rows, -1).float().contiguous()
+        g_losses = None if g_losses is None else g_losses.float()
+        r = ops.router_bwd((rows, 1, d), torch.float32, w32, saved, top_k, num_shared, 1.0, g_w, None, g_losses,
+                           want_dh=False, parts=1)
+        d_logits = r["d_logits"]
+        h32 = saved["pooled"]
+        d_h = d_w = d_b = None
+        if ctx.needs_input_grad[0]:
+            d_h = ops.gemm(d_logits, w32, b_kmajor=False, tag="token_router_dh").view(b, l, d).to(h_dtype)
+        if ctx.needs_input_grad[1]:
+            d_w = ops.gemm(d_logits, h32, a_kmajor=False, b_kmajor=False, tag="token_router_dw")
+        if has_bias and ctx.needs_input_grad[2]:
+            d_b = ops.col_sum(d_logits)
+        return d_h, d_w, d_b, None, None, None
+
+
+def route_tokens(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, num_shared: int,
+                 with_losses: bool = True):
+    """Returns (global chapter ids int64 [B,L,k'], weights [B,L,k'], losses dict); k' = min(k, C - num_shared)."""
+    idx, w, lv = _RouteTokens.apply(h, weight, bias, int(top_k), int(num_shared), bool(with_losses))
+    losses = {}
+    if with_losses:
+        losses = _LossDict({k: lv[i] for i, k in enumerate(LOSS_KEYS)})
+        losses.vector = lv
+    return idx, w, losses
+
+
+class _TokenRoutedAttention(torch.autograd.Function):
+    """MemoryCrossAttention._forward_token_routed_attention + o_proj (memory_attention.py:480-716, 452-456) with
+    per-token chapter weights:
+
+        out = Wo [ attn(q, shared rows)  +  rho * sum_s w[t,s] softmax(q K_{c(t,s)}^T) V_{c(t,s)} ]
+
+    The routed bank is projected once (the reference projects it once per batch item); the shared branch is the
+    dense attention kernel over the S*T shared rows with all B*L tokens as one sequence."""
+
+    @staticmethod
+    def forward(ctx, h, shared_mem, routed_mem, idx_local, weights, wq, wk, wv, wo, cfg):
+        num_heads, num_kv_heads, t, rho, cd = cfg
+        b, l, d = h.shape
+        rows = b * l
+        dkv = wk.shape[0]
+        head_dim = d // num_heads
+        scale = head_dim ** -0.5
+        h2 = ops.cast(h.reshape(rows, d).contiguous(), cd)
+        wq_c, wo_c = ops.cast(wq, cd), ops.cast(wo, cd)
+        wkv_c = ops.cast(torch.cat([wk, wv], dim=0), cd)
+        q = ops.gemm(h2, wq_c, tag="q_proj")                                            # [rows, H*D]
+        comb = None
+        sh = None
+        if shared_mem is not None and shared_mem.numel() > 0:
+            sm2 = ops.cast(shared_mem.contiguous(), cd)
+            kv_sh = ops.gemm(sm2, wkv_c, tag="kv_proj_shared")                          # [S*T, 2*dkv]
+            # bf16 attention backward wants the query count in multiples of 64: pad with zero rows
+            pad = (-rows) % 64 if cd == torch.bfloat16 else 0
+            q_sh = q if pad == 0 else torch.cat([q, q.new_zeros(pad, q.shape[1])], dim=0)
+            o_sh, lse_sh = ops.attn_fwd(q_sh.view(1, rows + pad, -1), kv_sh.view(1, kv_sh.shape[0], -1), num_heads,
+                                        num_kv_heads, scale)
+            sh = (sm2, kv_sh, q_sh, o_sh, lse_sh, pad)
+            comb = o_sh.view(rows + pad, -1)[:rows]
+        rt = None
+        k_sel = idx_local.shape[-1]
+        if routed_mem is not None and routed_mem.numel() > 0 and k_sel > 0:
+            rm2 = ops.cast(routed_mem.contiguous(), cd)
+            kv_rt = ops.gemm(rm2, wkv_c, tag="kv_proj_routed")                          # [(C-S)*T, 2*dkv]
+            n_rt = kv_rt.shape[0]
+            k4 = kv_rt[:, :dkv].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
+            v4 = kv_rt[:, dkv:].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
+            bidx = idx_local.reshape(1, rows, 1, k_sel).expand(1, rows, num_kv_heads, k_sel).to(torch.int32).contiguous()
+            w2 = weights.reshape(1, rows, k_sel).float().contiguous()
+            q4 = q.view(1, rows, num_heads, head_dim)
+            base = None if comb is None else comb.contiguous().view(1, rows, num_heads, head_dim)
+            comb4, lse_slots = ops.sparse_attn_weighted_fwd(q4, k4, v4, bidx, w2, t, scale, base=base, out_scale=rho)
+            comb = comb4.view(rows, -1)
+            rt = (rm2, kv_rt, bidx, w2, lse_slots, n_rt)
+        if comb is None:
+            comb = q.new_zeros(rows, d)
+        out = ops.gemm(comb.contiguous(), wo_c, out_dtype=h.dtype if h.dtype in (torch.float32, cd) else cd, tag="o_proj")
+        ctx.cfg = cfg
+        ctx.meta = (b, l, d, dkv, scale, h.dtype, None if shared_mem is None else shared_mem.dtype,
+                    None if routed_mem is None else routed_mem.dtype, weights.dtype,
+                    (wq.dtype, wk.dtype, wv.dtype, wo.dtype))
+        ctx.sh, ctx.rt = sh, rt
+        ctx.save_for_backward(h2, q, comb, wq_c, wkv_c, wo_c)
+        return out.view(b, l, -1).to(h.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        h2, q, comb, wq_c, wkv_c, wo_c = ctx.saved_tensors
+        num_heads, num_kv_heads, t, rho, cd = ctx.cfg
+        b, l, d, dkv, scale, h_dtype, sh_dtype, rt_dtype, w_dtype, wdt = ctx.meta
+        rows = b * l
+        head_dim = d // num_heads
+        f32 = torch.float32
+        g2 = ops.cast(g.reshape(rows, -1).contiguous(), cd)
+        d_comb = ops.gemm(g2, wo_c, b_kmajor=False, tag="d_attn_out")                   # [rows, H*D]
+        d_wo = ops.gemm(g2, comb, a_kmajor=False, b_kmajor=False, out_dtype=f32, tag="d_wo")
+        d_q = None
+        d_wkv = None
+        d_shared = d_routed = d_weights = None
+        if ctx.sh is not None:
+            sm2, kv_sh, q_sh, o_sh, lse_sh, pad = ctx.sh
+            dc = d_comb if pad == 0 else torch.cat([d_comb, d_comb.new_zeros(pad, d_comb.shape[1])], dim=0)
+            d_q_sh, d_kv_sh = ops.attn_bwd(q_sh.view(1, rows + pad, -1), kv_sh.view(1, kv_sh.shape[0], -1), o_sh, lse_sh,
+                                           dc.view(1, rows + pad, -1), num_heads, num_kv_heads, scale)
+            d_q = d_q_sh.view(rows + pad, -1)[:rows].contiguous()
+            d_kv_sh2 = d_kv_sh.view(kv_sh.shape[0], -1)
+            d_shared = ops.gemm(d_kv_sh2, wkv_c, b_kmajor=False, tag="d_shared_mem").to(sh_dtype)
+            d_wkv = ops.gemm(d_kv_sh2, sm2, a_kmajor=False, b_kmajor=False, out_dtype=f32, tag="d_wkv_shared")
+        if ctx.rt is not None:
+            rm2, kv_rt, bidx, w2, lse_slots, n_rt = ctx.rt
+            k4 = kv_rt[:, :dkv].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
+            v4 = kv_rt[:, dkv:].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
+            d_kv_rt = torch.zeros(n_rt, 2 * dkv, dtype=f32, device=q.device)
+            dk4 = d_kv_rt[:, :dkv].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
+            dv4 = d_kv_rt[:, dkv:].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
+            d_q, d_w = ops.sparse_attn_weighted_bwd(
+                q.view(1, rows, num_heads, head_dim), k4, v4, bidx, w2, lse_slots,
+                d_comb.view(1, rows, num_heads, head_dim), t, scale, rho, dk4, dv4,
+                d_q_accum=None if d_q is None else d_q.view(1, rows, num_heads, head_dim))
+            d_q = d_q.view(rows, -1)
+            d_weights = d_w.view(b, l, -1).to(w_dtype)
+            d_kv_c = ops.cast(d_kv_rt, cd)
+            d_routed = ops.gemm(d_kv_c, wkv_c, b_kmajor=False, tag="d_routed_mem").to(rt_dtype)
+            g_wkv = ops.gemm(d_kv_c, rm2, a_kmajor=False, b_kmajor=False, out_dtype=f32, tag="d_wkv_routed")
+            d_wkv = g_wkv if d_wkv is None else d_wkv + g_wkv
+        if d_q is None:
+            d_q = q.new_zeros(rows, d)
+        d_h = ops.gemm(d_q, wq_c, b_kmajor=False, tag="d_h").view(b, l, d).to(h_dtype)
+        d_wq = ops.gemm(d_q, h2, a_kmajor=False, b_kmajor=False, out_dtype=f32, tag="d_wq")
+        if d_wkv is None:
+            d_wkv = torch.zeros(2 * dkv, d, dtype=f32, device=q.device)
+        return (d_h, d_shared, d_routed, None, d_weights, d_wq.to(wdt[0]), d_wkv[:dkv].to(wdt[1]),
+                d_wkv[dkv:].to(wdt[2]), d_wo.to(wdt[3]), None)
+
+
+def token_routed_attention(h: torch.Tensor, shared_memory: Optional[torch.Tensor],
+                           routed_memory: Optional[torch.Tensor], token_chapter_indices: torch.Tensor,
+                           chapter_weights: torch.Tensor, wq, wk, wv, wo, *, num_heads: int,
+                           num_kv_heads: Optional[int], tokens_per_chapter: int, routed_scale: float = 1.0,
+                           compute_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Token-routed memory cross-attention with router-weighted chapters, output projection included.
+    ``token_chapter_indices`` [B,L,k] are ids LOCAL to ``routed_memory`` (global id minus the shared prefix,
+    model.py:583-595); ``chapter_weights`` [B,L,k] carry the router's gradient."""
+    cfg = (int(num_heads), int(num_kv_heads or num_heads), int(tokens_per_chapter), float(routed_scale),
+           compute_dtype or h.dtype)
+    return _TokenRoutedAttention.apply(h, shared_memory, routed_memory, token_chapter_indices, chapter_weights,
+                                       wq, wk, wv, wo, cfg)
+
+
+class _Linear(torch.autograd.Function):
+    """y = x W^T by the projection kernels (nn.Linear without bias), differentiable in x and W."""
+
+    @staticmethod
+    def forward(ctx, x, w, cd):
+        x2 = ops.cast(x.reshape(-1, x.shape[-1]).contiguous(), cd)
+        wc = ops.cast(w.contiguous(), cd)
+        ctx.save_for_backward(x2, wc)
+        ctx.meta = (x.shape, x.dtype, w.dtype, cd)
+        return ops.gemm(x2, wc).view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, g):
+        x2, wc = ctx.saved_tensors
+        shape, x_dtype, w_dtype, cd = ctx.meta
+        g2 = ops.cast(g.reshape(-1, g.shape[-1]).contiguous(), cd)
+        d_x = ops.gemm(g2, wc, b_kmajor=False).view(shape).to(x_dtype) if ctx.needs_input_grad[0] else None
+        d_w = (ops.gemm(g2, x2, a_kmajor=False, b_kmajor=False, out_dtype=torch.float32).to(w_dtype)
+               if ctx.needs_input_grad[1] else None)
+        return d_x, d_w, None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, compute_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    return _Linear.apply(x, w, compute_dtype or x.dtype)
+
+
+class _DenseAttention(torch.autograd.Function):
+    """softmax(q K^T scale) V for q [B, L, H*D] and kv [B, N, 2*HK*D] (K heads then V heads per row)."""
+
+    @staticmethod
+    def forward(ctx, q, kv, num_heads, num_kv_heads, scale):
+        o, lse = ops.attn_fwd(q, kv, num_heads, num_kv_heads, scale)
+        ctx.save_for_backward(q, kv, o, lse)
+        ctx.cfg = (num_heads, num_kv_heads, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, g):
+        q, kv, o, lse = ctx.saved_tensors
+        d_q, d_kv = ops.attn_bwd(q, kv, o, lse, g.contiguous(), *ctx.cfg)
+        return d_q, d_kv, None, None, None
+
+
+def token_routed_attention_joint(h, shared_memory, routed_memory, token_chapter_indices, wq, wk, wv, wo, *,
+                                 num_heads: int, num_kv_heads: Optional[int], tokens_per_chapter: int,
+                                 routed_scale: float = 1.0, compute_dtype: Optional[torch.dtype] = None):
+    """Token-routed attention WITHOUT chapter weights (memory_attention.py:688-704): the selected chapters of a
+    token share one softmax; out = Wo [ attn(q, shared) + rho * attn(q, selected chapters) ].  Composed from the
+    differentiable projection, dense-attention and per-token sparse-attention operators."""
+    from .memory_cross_attn import MemoryCrossAttnFunction
+    cd = compute_dtype or h.dtype
+    hk = int(num_kv_heads or num_heads)
+    b, l, d = h.shape
+    rows = b * l
+    head_dim = d // num_heads
+    scale = head_dim ** -0.5
+    q = linear(h.reshape(1, rows, d), wq, cd)                                        # [1, rows, H*D]
+    comb = None
+    if shared_memory is not None and shared_memory.numel() > 0:
+        kv_sh = torch.cat([linear(shared_memory, wk, cd), linear(shared_memory, wv, cd)], dim=-1).unsqueeze(0)
+        pad = (-rows) % 64 if cd == torch.bfloat16 else 0
+        q_sh = q if pad == 0 else torch.cat([q, q.new_zeros(1, pad, q.shape[-1])], dim=1)
+        comb = _DenseAttention.apply(q_sh, kv_sh, num_heads, hk, scale)[:, :rows]
+    k_sel = token_chapter_indices.shape[-1]
+    if routed_memory is not None and routed_memory.numel() > 0 and k_sel > 0 and tokens_per_chapter > 0:
+        k4 = linear(routed_memory, wk, cd).view(1, -1, hk, head_dim)
+        v4 = linear(routed_memory, wv, cd).view(1, -1, hk, head_dim)
+        bidx = token_chapter_indices.reshape(1, rows, 1, k_sel).expand(1, rows, hk, k_sel).to(torch.int32).contiguous()
+        routed = MemoryCrossAttnFunction.apply(q.view(1, rows, num_heads, head_dim).contiguous(), k4.contiguous(),
+                                               v4.contiguous(), bidx, int(tokens_per_chapter), scale)
+        routed = routed.view(1, rows, -1) * float(routed_scale)
+        comb = routed if comb is None else comb + routed
+    if comb is None:
+        comb = q.new_zeros(1, rows, d)
+    return linear(comb, wo, cd).view(b, l, -1).to(h.dtype)

@@ -68,7 +68,7 @@ class MemoryCrossAttention(nn.Module):
         if token_routing_state is not None:
             if return_attn_weights:
                 raise ValueError("return_attn_weights=True is not supported for token_routing_state path.")
-            raise NotImplementedError("token-level routing is not wired into this module yet")
+            return self._forward_token_routed(hidden_states, token_routing_state), None
         if memory is None:
             raise ValueError("memory must be provided when token_routing_state is None.")
         if return_attn_weights:
@@ -77,6 +77,34 @@ class MemoryCrossAttention(nn.Module):
                                     self.v_proj.weight, self.o_proj.weight, self.num_heads, self.num_kv_heads,
                                     self._compute_dtype(hidden_states))
         return out, None
+
+    def _forward_token_routed(self, hidden_states: torch.Tensor, state: Dict[str, Any]) -> torch.Tensor:
+        """Token-level routing payload of the reference's model (model.py:592-606): dense attention over the
+        shared rows plus, per token, its selected chapters (memory_attention.py:480-716), then o_proj.  With
+        ``chapter_weights`` every chapter has its own softmax and the outputs are mixed by the weights; without,
+        the selected chapters share one softmax.  ``kernel_version`` / ``assume_sorted_topk`` select among the
+        reference's Triton variants and have nothing to choose between here."""
+        idx = state.get("token_chapter_indices", None)
+        if idx is None:
+            raise ValueError("token_routing_state must include token_chapter_indices.")
+        if idx.dim() != 3:
+            raise ValueError(f"token_chapter_indices must be rank-3 [B, T, topk], got shape {tuple(idx.shape)}.")
+        if idx.shape[0] != hidden_states.shape[0] or idx.shape[1] != hidden_states.shape[1]:
+            raise ValueError(
+                "token_chapter_indices shape prefix must match hidden_states [B, T, ...]. "
+                f"got hidden_states={tuple(hidden_states.shape)}, token_chapter_indices={tuple(idx.shape)}")
+        cd = self._compute_dtype(hidden_states)
+        args = dict(num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
+                    tokens_per_chapter=int(state.get("tokens_per_chapter", 0)),
+                    routed_scale=float(state.get("routed_scale", 1.0)), compute_dtype=cd)
+        w = (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, self.o_proj.weight)
+        shared, routed = state.get("shared_memory"), state.get("routed_memory")
+        if args["tokens_per_chapter"] <= 0:
+            routed = None
+        weights = state.get("chapter_weights", None)
+        if weights is not None:
+            return F_moc.token_routed_attention(hidden_states, shared, routed, idx, weights, *w, **args)
+        return F_moc.token_routed_attention_joint(hidden_states, shared, routed, idx, *w, **args)
 
     def _compute_dtype(self, hidden_states: torch.Tensor) -> torch.dtype:
         """Arithmetic type of the projections and the attention.  An explicit ``compute_dtype`` wins; otherwise

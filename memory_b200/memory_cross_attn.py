@@ -37,6 +37,30 @@ def memory_cross_attn_forward(q, k, v, block_indices, block_size: int,
     return ops.sparse_attn_fwd(q, k, v, block_indices.to(torch.int32).contiguous(), block_size, scale)
 
 
+def memory_cross_attn_preprocess_delta(o: torch.Tensor, do: torch.Tensor) -> torch.Tensor:
+    """delta[b, t, h] = <o, do> (kernels-final/memory_cross_attn.py:1369-1384); fp32 [B,TQ,HQ]."""
+    for name, t in (("o", o), ("do", do)):
+        if not t.is_cuda:
+            raise ValueError(f"{name} must be a CUDA tensor.")
+    assert o.shape == do.shape
+    return ops.row_dot(o, do)
+
+
+def memory_cross_attn_backward(q, k, v, o, lse, do, block_indices, block_size: int, scale: Optional[float] = None,
+                               dkv_strategy: str = "b", q_chunk_size: int = 1024, d_chunk_size: int = 256,
+                               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(dq, dk, dv) in the inputs' dtypes (kernels-final/memory_cross_attn.py:1387-1603).  One backward exists
+    here, so ``dkv_strategy`` and the chunk sizes are validated and otherwise unused."""
+    if dkv_strategy not in ("a", "b", "c", "d"):
+        raise ValueError(f"Unknown dkv_strategy={dkv_strategy}")
+    bi = block_indices.to(torch.int32).contiguous()
+    _check(q, k, v, bi, block_size)
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    dq, dk, dv = ops.sparse_attn_bwd(q, k, v, bi, o, lse, do.contiguous(), block_size, scale)
+    return dq, dk.to(k.dtype), dv.to(v.dtype)
+
+
 class MemoryCrossAttnFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, block_indices, block_size, scale):

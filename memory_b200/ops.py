@@ -76,10 +76,12 @@ def _router_fwd_launches(*a, **k):
 def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top_k: int,
                num_shared: int, routed_scale: float, with_losses: bool, parts: int = 3,
                out: Optional[Dict[str, torch.Tensor]] = None,
-               pooled: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
+               pooled: Optional[torch.Tensor] = None,
+               logits: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
     """``parts`` (1 = pooling, logits, selection; 2 = loss terms) runs a subset on the current stream; pass the dict
     returned by the first call as ``out`` to the second.  ``pooled`` ([B, d] fp32): pooled states computed by
-    another rule (see :func:`pool_weighted_fwd`); the mean-pool is then skipped."""
+    another rule (see :func:`pool_weighted_fwd`); the mean-pool is then skipped.  ``logits`` ([B, C] fp32, without
+    the bias): pooled x W^T already computed by a projection kernel; only the bias is added (in place)."""
     L.require_cuda(h, weight, bias)
     if h.dim() != 3:
         raise ValueError(f"hidden_states must be 3D (B, T, D), got shape {tuple(h.shape)}")
@@ -93,7 +95,10 @@ def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     s = _router_shape(h, c, top_k, num_shared, routed_scale)
     f32 = dict(dtype=torch.float32, device=dev)
     lib = L.lib()
-    ws_bytes = lib.moc_router_workspace_bytes(C.byref(s))
+    if pooled is not None and logits is not None:
+        ws_bytes = lib.moc_router_workspace_bytes_parts(C.byref(s), 1 | 2 | 8 | 16, 0)   # loss partials only
+    else:
+        ws_bytes = lib.moc_router_workspace_bytes(C.byref(s))
     if out is None:
         out = {
             "pooled": torch.empty(b, d, **f32), "logits": torch.empty(b, c, **f32), "probs": torch.empty(b, c, **f32),
@@ -104,9 +109,15 @@ def router_fwd(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
             "losses": torch.empty(4, **f32) if with_losses else None,
             "_ws": torch.empty(ws_bytes, dtype=torch.uint8, device=dev),
         }
+    ws_bytes = out["_ws"].numel()
     if pooled is not None:
         out["pooled"] = _contig(pooled.float())
         parts = int(parts) | 8
+    if logits is not None:
+        if logits.dtype != torch.float32 or tuple(logits.shape) != (b, c) or not logits.is_contiguous():
+            raise ValueError("logits must be a contiguous fp32 [rows, num_chapters] tensor")
+        out["logits"] = logits
+        parts = int(parts) | 16
     rc = lib.moc_router_fwd_parts(C.byref(s), L.ptr(h), L.ptr(weight), L.ptr(bias), L.ptr(out["pooled"]),
                                   L.ptr(out["logits"]), L.ptr(out["probs"]), L.ptr(out["idx"]), L.ptr(out["weights"]),
                                   L.ptr(out["comb_idx"]), L.ptr(out["comb_w"]), L.ptr(out["row_stats"]),
@@ -140,10 +151,19 @@ def router_bwd(h_shape, h_dtype, weight: torch.Tensor, saved: Dict[str, torch.Te
     f32 = dict(dtype=torch.float32, device=dev)
     weight = _contig(weight.float())
     lib = L.lib()
-    ws_bytes = lib.moc_router_workspace_bytes(C.byref(s))
     if out is None:
-        out = {"d_logits": torch.empty(b, c, **f32), "d_w": torch.empty(c, d, **f32), "d_bias": torch.empty(c, **f32),
-               "d_pooled": torch.empty(b, d, **f32), "d_h": None, "_ws": torch.empty(ws_bytes, dtype=torch.uint8, device=dev)}
+        if parts == 1:
+            # logit gradient only (the token-level path finishes with projection kernels): no batch-sized scratch
+            ws_bytes = max(16, lib.moc_router_workspace_bytes_parts(C.byref(s), 0, 1))
+            out = {"d_logits": torch.empty(b, c, **f32), "d_w": torch.empty(1, **f32), "d_bias": torch.empty(1, **f32),
+                   "d_pooled": torch.empty(1, **f32), "d_h": None,
+                   "_ws": torch.empty(ws_bytes, dtype=torch.uint8, device=dev)}
+        else:
+            ws_bytes = lib.moc_router_workspace_bytes(C.byref(s))
+            out = {"d_logits": torch.empty(b, c, **f32), "d_w": torch.empty(c, d, **f32),
+                   "d_bias": torch.empty(c, **f32), "d_pooled": torch.empty(b, d, **f32), "d_h": None,
+                   "_ws": torch.empty(ws_bytes, dtype=torch.uint8, device=dev)}
+    ws_bytes = out["_ws"].numel()
     accumulate = 0
     if want_dh and (parts & 4):
         if d_h_accum is not None:
@@ -446,6 +466,90 @@ def sparse_attn_bwd(q, k, v, block_indices, o, lse, d_o, block_size: int, scale:
                                      L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))
     L.check(rc, "moc_sparse_attn_bwd")
     return d_q, d_k, d_v
+
+
+@_instrument("sparse_attn_weighted_fwd", 1)
+def sparse_attn_weighted_fwd(q, k, v, block_indices, weights, block_size: int, scale: float,
+                             base: Optional[torch.Tensor] = None, out_scale: float = 1.0):
+    """Per-chapter softmax, outputs mixed by ``weights``: o = base + out_scale * sum_s w_s softmax(q K_s^T) V_s.
+    q [B,TQ,HQ,D]; k / v [B,TK,H,D] views whose rows may be strided (unit stride over (H, D));
+    block_indices int32 [B,TQ,H,S]; weights [B,TQ,S].  Returns (o like q, lse_slots fp32 [B,TQ,HQ,S])."""
+    L.require_cuda(q, k, v, block_indices, weights)
+    b, tq, hq, d = q.shape
+    _, tk, h, _ = k.shape
+    q = _contig(q)
+    ld = _kv_row_stride(k, v)
+    s = L.SparseAttnShape(b, tq, tk, hq, h, d, block_indices.shape[-1], int(block_size), float(scale),
+                          L.dtype_code(q.dtype))
+    o = torch.empty_like(q)
+    lse = torch.empty(b, tq, hq, block_indices.shape[-1], dtype=torch.float32, device=q.device)
+    rc = L.lib().moc_sparse_attn_weighted_fwd(C.byref(s), L.ptr(q), L.ptr(k), L.ptr(v), ld,
+                                              L.ptr(_contig(block_indices)), L.ptr(_contig(weights.float())),
+                                              L.ptr(_contig(base)), float(out_scale), L.ptr(o), L.ptr(lse),
+                                              L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))
+    L.check(rc, "moc_sparse_attn_weighted_fwd")
+    return o, lse
+
+
+@_instrument("sparse_attn_weighted_bwd", 1)
+def sparse_attn_weighted_bwd(q, k, v, block_indices, weights, lse_slots, d_o, block_size: int, scale: float,
+                             out_scale: float, d_k: torch.Tensor, d_v: torch.Tensor,
+                             d_q_accum: Optional[torch.Tensor] = None):
+    """Gradients of :func:`sparse_attn_weighted_fwd`.  ``d_k`` / ``d_v`` are zeroed fp32 accumulators shaped like
+    k / v (row-strided views allowed); returns (d_q, d_w [B,TQ,S])."""
+    b, tq, hq, d = q.shape
+    _, tk, h, _ = k.shape
+    q, d_o = _contig(q), _contig(d_o)
+    ld, ldg = _kv_row_stride(k, v), _kv_row_stride(d_k, d_v)
+    n_sel = block_indices.shape[-1]
+    s = L.SparseAttnShape(b, tq, tk, hq, h, d, n_sel, int(block_size), float(scale), L.dtype_code(q.dtype))
+    d_q = d_q_accum if d_q_accum is not None else torch.empty_like(q)
+    d_w_heads = torch.empty(b, tq, hq, n_sel, dtype=torch.float32, device=q.device)
+    rc = L.lib().moc_sparse_attn_weighted_bwd(C.byref(s), L.ptr(q), L.ptr(k), L.ptr(v), ld,
+                                              L.ptr(_contig(block_indices)), L.ptr(_contig(weights.float())),
+                                              float(out_scale), L.ptr(lse_slots), L.ptr(d_o), L.ptr(d_q),
+                                              1 if d_q_accum is not None else 0, L.ptr(d_k), L.ptr(d_v), ldg,
+                                              L.ptr(d_w_heads), L.ptr(L.status_word(q.device)),
+                                              L.stream_ptr(q.device))
+    L.check(rc, "moc_sparse_attn_weighted_bwd")
+    return d_q, d_w_heads.sum(dim=2)
+
+
+def _kv_row_stride(k: torch.Tensor, v: torch.Tensor) -> int:
+    """Elements between consecutive rows of a [B,TK,H,D] key / value view whose (H, D) part is dense."""
+    b, tk, h, d = k.shape
+    for t in (k, v):
+        if t.stride(3) != 1 or t.stride(2) != d or (b > 1 and t.stride(0) != tk * t.stride(1)):
+            raise ValueError("k / v must be dense over (heads, head_dim) with uniformly strided rows")
+    if k.stride(1) != v.stride(1):
+        raise ValueError("k and v must share a row stride")
+    return int(k.stride(1))
+
+
+@_instrument("row_dot", 1)
+def row_dot(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """<a[..., :], b[..., :]> over the last axis, fp32, shaped like ``a.shape[:-1]``."""
+    L.require_cuda(a, b)
+    if a.dtype != b.dtype or a.shape != b.shape:
+        raise ValueError("row_dot operands must share shape and dtype")
+    a, b = _contig(a), _contig(b)
+    dim = a.shape[-1]
+    out = torch.empty(a.shape[:-1], dtype=torch.float32, device=a.device)
+    rc = L.lib().moc_row_dot(L.ptr(a), L.ptr(b), L.dtype_code(a.dtype), L.ptr(out), a.numel() // dim, dim,
+                             L.stream_ptr(a.device))
+    L.check(rc, "moc_row_dot")
+    return out
+
+
+@_instrument("col_sum", 1)
+def col_sum(x: torch.Tensor) -> torch.Tensor:
+    """Sum over the rows of a contiguous fp32 [rows, cols] matrix."""
+    L.require_cuda(x)
+    x = _contig(x.float())
+    out = torch.empty(x.shape[1], dtype=torch.float32, device=x.device)
+    rc = L.lib().moc_col_sum(L.ptr(x), L.ptr(out), x.shape[0], x.shape[1], L.stream_ptr(x.device))
+    L.check(rc, "moc_col_sum")
+    return out
 
 
 def cast(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:

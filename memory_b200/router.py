@@ -66,6 +66,20 @@ class ChapterRouter(nn.Module):
             cache[key] = F_moc.ops.rolling_pool_coefficients(seq, window).to(device)
         return cache[key]
 
+    def route_token_level(self, hidden_states: torch.Tensor, return_losses: bool = True,
+                          exclude_prefix_chapters: int = 0
+                          ) -> Tuple[torch.Tensor, torch.Tensor, Dict[str, torch.Tensor]]:
+        """Every token selects its own chapters (router.py:262-340).  Returns (global chapter ids int64
+        [B, L, k'], weights [B, L, k'] renormalised over the selection, losses over all B*L routing rows);
+        k' = min(top_k, num_chapters - exclude_prefix_chapters), empty tensors when k' <= 0."""
+        if hidden_states.dim() != 3:
+            raise ValueError(f"hidden_states must be 3D (B, T, D), got shape {tuple(hidden_states.shape)}")
+        if exclude_prefix_chapters < 0 or exclude_prefix_chapters > self.num_chapters:
+            raise ValueError(
+                f"exclude_prefix_chapters must be in [0, {self.num_chapters}], got {exclude_prefix_chapters}")
+        return F_moc.route_tokens(hidden_states, self.router.weight, self.router.bias, self.top_k,
+                                  exclude_prefix_chapters, return_losses)
+
     def route_with_shared(self, hidden_states: torch.Tensor, num_shared_chapters: int,
                           routed_scaling_factor: float, return_losses: bool = True):
         """Router plus the model-side shared-prefix step (model.py:356-391) in one launch sequence.

@@ -167,9 +167,10 @@ def total_router_loss(losses: Dict[str, torch.Tensor], load_balance_coef: float 
 
 def route_token_level(
     hidden_states: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
-    top_k: int, exclude_prefix_chapters: int = 0,
-) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Per-token routing (router.py:262-340): global chapter ids and weights."""
+    top_k: int, exclude_prefix_chapters: int = 0, return_losses: bool = False,
+):
+    """Per-token routing (router.py:262-340): global chapter ids and weights; with ``return_losses`` also the
+    loss dict over all B*L routing rows (router.py:333-338)."""
     num_chapters = weight.shape[0]
     logits = hidden_states.float() @ weight.float().t() + bias.float()   # router.py:294
     probs = F.softmax(logits, dim=-1)                                    # router.py:295
@@ -178,7 +179,12 @@ def route_token_level(
     routed = routed / routed.sum(dim=-1, keepdim=True).clamp_min(1e-12)
     w, idx_local = topk_lower_index_first(routed, select_k)              # router.py:324-328
     w = w / w.sum(dim=-1, keepdim=True).clamp_min(1e-12)                 # router.py:329
-    return idx_local + int(exclude_prefix_chapters), w                   # router.py:330
+    idx = idx_local + int(exclude_prefix_chapters)                       # router.py:330
+    if not return_losses:
+        return idx, w
+    losses = router_losses(logits.reshape(-1, num_chapters), probs.reshape(-1, num_chapters),
+                           idx.reshape(-1, select_k))                    # router.py:333-338
+    return idx, w, losses
 
 
 # --------------------------------------------------------------------------
@@ -281,6 +287,118 @@ def sparse_chapter_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                 p = F.softmax(s, dim=-1)
                 out[b, :, qh, :] = (p.unsqueeze(-1) * vv).sum(1)
     return out.to(v.dtype)
+
+
+def attention_heads(hidden_states: torch.Tensor, memory: torch.Tensor, wq, wk, wv,
+                    num_heads: int, num_kv_heads: int) -> torch.Tensor:
+    """``MemoryCrossAttention._forward_attention`` (memory_attention.py:458-478): joint-softmax attention over the
+    given rows, heads concatenated, BEFORE the output projection."""
+    batch, seq, hidden = hidden_states.shape
+    if memory.dim() == 2:
+        memory = memory.unsqueeze(0).expand(batch, -1, -1)
+    head_dim = hidden // num_heads
+    q = F.linear(hidden_states, wq).view(batch, seq, num_heads, head_dim).transpose(1, 2)
+    k = F.linear(memory, wk).view(batch, -1, num_kv_heads, head_dim)
+    v = F.linear(memory, wv).view(batch, -1, num_kv_heads, head_dim)
+    g = num_heads // num_kv_heads
+    k = k.repeat_interleave(g, dim=2).transpose(1, 2)
+    v = v.repeat_interleave(g, dim=2).transpose(1, 2)
+    attn = F.softmax(torch.matmul(q, k.transpose(-2, -1)) * (head_dim ** -0.5), dim=-1)
+    return torch.matmul(attn, v).transpose(1, 2).reshape(batch, seq, hidden)
+
+
+def weighted_chapter_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_indices: torch.Tensor,
+                               weights: Optional[torch.Tensor], block_size: int, scale: Optional[float] = None,
+                               chunk: int = 256) -> torch.Tensor:
+    """The exact mixture rule (kernels-final/kernel_v4.py:298-407; memory_attention.py:667-686 with the emulated
+    per-chapter call :856-898): out[b,t] = sum_s w[b,t,s] * softmax(q K_s^T scale) V_s, one softmax per chapter.
+    q [B,TQ,HQ,D], k/v [B,TK,H,D], block_indices [B,TQ,H,S], weights [B,TQ,S] (None = all ones)."""
+    bsz, tq, hq, d = q.shape
+    h = k.shape[2]
+    g = hq // h
+    if scale is None:
+        scale = d ** -0.5
+    offs = torch.arange(block_size)
+    outs = []
+    for b in range(bsz):
+        per_b = []
+        for t0 in range(0, tq, chunk):
+            t1 = min(tq, t0 + chunk)
+            acc = []
+            for kh in range(h):
+                bi = block_indices[b, t0:t1, kh, :].long()                               # [n, S]
+                rows = bi.unsqueeze(-1) * block_size + offs                             # [n, S, T]
+                kk = k[b, :, kh, :].float()[rows]                                       # [n, S, T, D]
+                vv = v[b, :, kh, :].float()[rows]
+                qq = q[b, t0:t1, kh * g:(kh + 1) * g, :].float()                        # [n, g, D]
+                sc = torch.einsum("ngd,nstd->ngst", qq, kk) * scale
+                p = F.softmax(sc, dim=-1)                                               # per chapter
+                o = torch.einsum("ngst,nstd->ngsd", p, vv)                              # [n, g, S, D]
+                if weights is not None:
+                    o = o * weights[b, t0:t1].float().view(t1 - t0, 1, -1, 1)
+                acc.append(o.sum(dim=2))                                                # [n, g, D]
+            per_b.append(torch.cat(acc, dim=1))                                         # [n, HQ, D]
+        outs.append(torch.cat(per_b, dim=0))
+    return torch.stack(outs, dim=0)
+
+
+def token_routed_attention(hidden_states, shared_memory, routed_memory, idx_local, weights, tokens_per_chapter: int,
+                           routed_scale: float, wq, wk, wv, wo, num_heads: int, num_kv_heads: int) -> torch.Tensor:
+    """``MemoryCrossAttention.forward(token_routing_state=...)`` with chapter weights
+    (memory_attention.py:352-400, 480-716, 452-456): dense attention over the shared rows, plus routed_scale times
+    the weighted mixture of per-chapter attentions over each token's own chapters, then the output projection.
+    ``idx_local`` are chapter ids inside ``routed_memory`` (model.py:583-595)."""
+    batch, seq, hidden = hidden_states.shape
+    head_dim = hidden // num_heads
+    combined = hidden_states.new_zeros(batch, seq, hidden).float()
+    if shared_memory is not None and shared_memory.numel() > 0:                          # :550-551
+        combined = combined + attention_heads(hidden_states, shared_memory, wq, wk, wv, num_heads, num_kv_heads)
+    if routed_memory is not None and routed_memory.numel() > 0 and idx_local.shape[-1] > 0:
+        q = F.linear(hidden_states, wq).view(batch, seq, num_heads, head_dim)           # :560
+        rm = routed_memory.unsqueeze(0).expand(batch, -1, -1)
+        k = F.linear(rm, wk).view(batch, -1, num_kv_heads, head_dim)
+        v = F.linear(rm, wv).view(batch, -1, num_kv_heads, head_dim)
+        bi = idx_local.unsqueeze(2).expand(batch, seq, num_kv_heads, idx_local.shape[-1])
+        routed = weighted_chapter_attention(q, k, v, bi, weights, tokens_per_chapter, head_dim ** -0.5)
+        combined = combined + routed.reshape(batch, seq, hidden) * float(routed_scale)   # :707-714
+    return F.linear(combined, wo)                                                        # :456
+
+
+def token_memory_layer(shape: "LayerShape", h_router, h_attn, bank, router_w, router_b, wq, wk, wv, wo,
+                       return_losses: bool = True) -> Dict[str, torch.Tensor]:
+    """Token-level branch of the model's memory layer (model.py:544-606): per-token routing, bank split into
+    shared / routed rows (normalised over the whole bank when configured), token-routed attention."""
+    s, t = shape.num_shared_chapters, shape.tokens_per_chapter
+    r = route_token_level(h_router, router_w, router_b, shape.top_k, s, return_losses)
+    idx, w = r[0], r[1]
+    losses = r[2] if return_losses else {}
+    shared_tokens = s * t
+    shared = bank[:shared_tokens] if shared_tokens > 0 else None                         # model.py:551-563
+    routed = bank[shared_tokens:] if shared_tokens < bank.shape[0] else None
+    if shape.norm_type is not None and shared is not None and routed is not None:        # model.py:565-581
+        merged = normalize_memory_rows(torch.cat([shared, routed], dim=0).unsqueeze(0), s, t, shape.norm_type,
+                                       shape.norm_eps).squeeze(0)
+        shared, routed = merged[:shared_tokens], merged[shared_tokens:]
+    out = token_routed_attention(h_attn, shared, routed, idx - s, w, t, shape.routed_scaling_factor,
+                                 wq, wk, wv, wo, shape.num_heads, shape.num_kv_heads)
+    return {"out": out, "indices": idx, "weights": w, "losses": losses}
+
+
+def token_memory_layer_fwd_bwd(shape: "LayerShape", tensors: Dict[str, torch.Tensor], d_out: torch.Tensor,
+                               load_balance_coef: float = 0.01, z_loss_coef: float = 0.001) -> Dict[str, torch.Tensor]:
+    """Forward + autograd backward of ``(out * d_out).sum() + router loss`` for the token-level layer."""
+    names = ["h_router", "bank", "router_w", "router_b", "wq", "wk", "wv", "wo"]
+    leaves = {n: tensors[n].detach().clone().float().requires_grad_(True) for n in names}
+    res = token_memory_layer(shape, leaves["h_router"], leaves["h_router"], leaves["bank"], leaves["router_w"],
+                             leaves["router_b"], leaves["wq"], leaves["wk"], leaves["wv"], leaves["wo"])
+    loss = (res["out"].float() * d_out.float()).sum() + total_router_loss(res["losses"], load_balance_coef, 0.0,
+                                                                            z_loss_coef)
+    loss.backward()
+    out = {"out": res["out"].detach(), "indices": res["indices"], "weights": res["weights"].detach(),
+           "losses": {k: v.detach() for k, v in res["losses"].items()}, "loss": loss.detach()}
+    for n in names:
+        out["d_" + n] = leaves[n].grad.detach() if leaves[n].grad is not None else torch.zeros_like(leaves[n])
+    return out
 
 
 # --------------------------------------------------------------------------
@@ -406,6 +524,7 @@ def layer_flops(batch: int, seq: int, shape: LayerShape) -> float:
 __all__ = [
     "LayerShape", "topk_lower_index_first", "router_pool", "router_pool_rolling", "router_forward", "router_losses",
     "total_router_loss", "route_token_level", "prepend_shared_chapters", "gather_chapters",
-    "normalize_memory_rows", "scale_memory", "cross_attention", "sparse_chapter_attention",
+    "normalize_memory_rows", "scale_memory", "cross_attention", "sparse_chapter_attention", "attention_heads",
+    "weighted_chapter_attention", "token_routed_attention", "token_memory_layer", "token_memory_layer_fwd_bwd",
     "memory_layer", "memory_layer_fwd_bwd", "layer_flops",
 ]

@@ -99,3 +99,14 @@ def make_inputs(case: Case) -> Dict[str, np.ndarray]:
     out["d_out"] = np.random.Generator(np.random.PCG64(case.seed + 999)).standard_normal(
         (case.batch, case.seq, d), dtype=np.float32)
     return out
+
+
+# token-level routing (every token selects its own chapters; model.py:544-606, memory_attention.py:480-716)
+TOKEN_CASES = {
+    c.name: c for c in [
+        Case("token_t16", 2, 32, 128, 2, 2, 9, 16, 3, seed=1250,
+             notes="per-token top-3 of 8 routed chapters of 16 rows plus the shared chapter"),
+        Case("token_gqa_rms", 2, 32, 128, 2, 1, 9, 64, 3, norm_type="rms", seed=1251,
+             notes="64-row chapters, head_dim 64, grouped KV heads, whole-bank RMS normalisation"),
+    ]
+}

@@ -29,7 +29,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
-from cases import BF16_CASES, CASES, make_inputs  # noqa: E402
+from cases import BF16_CASES, CASES, TOKEN_CASES, make_inputs  # noqa: E402
 
 
 def import_reference(path: str):
@@ -135,6 +135,51 @@ def run_reference(ref, case, inputs, autocast_bf16=False):
     return res
 
 
+def run_reference_token(ref, case, inputs):
+    """Token-level routing exactly as the reference's model wires it (model.py:544-606): ``route_token_level``,
+    bank split into shared / routed rows (whole-bank normalisation when configured), the ``token_routing_state``
+    payload, ``MemoryCrossAttention.forward(token_routing_state=...)`` (on CPU: its emulated per-chapter path,
+    memory_attention.py:667-686, 856-898)."""
+    t = {k: torch.from_numpy(v.copy()) for k, v in inputs.items()}
+    d, T, S = case.hidden_dim, case.tokens_per_chapter, case.num_shared_chapters
+    router = ref["ChapterRouter"](d, case.num_chapters, top_k=case.top_k, routing_strategy="token")
+    base = ref["StandardMemoryBank"](case.num_chapters * T, d)
+    bank = ref["ChapteredMemoryBank"](base, case.num_chapters)
+    attn = ref["MemoryCrossAttention"](d, case.num_heads, num_kv_heads=case.num_kv_heads, wo_init_zero=False,
+                                       use_flash_attention=False)
+    with torch.no_grad():
+        router.router.weight.copy_(t["router_w"]); router.router.bias.copy_(t["router_b"])
+        base.memory.copy_(t["bank"])
+        attn.q_proj.weight.copy_(t["wq"]); attn.k_proj.weight.copy_(t["wk"])
+        attn.v_proj.weight.copy_(t["wv"]); attn.o_proj.weight.copy_(t["wo"])
+    router.train(); attn.train()
+    h = t["h_router"].clone().requires_grad_(True)
+    idx, w, losses = router.route_token_level(hidden_states=h, return_losses=True, exclude_prefix_chapters=S)
+    full = bank.get_memory()
+    shared, routed = full[:S * T].contiguous(), full[S * T:].contiguous()
+    if case.norm_type is not None:
+        merged = ref["MemoryTransformer"]._normalize_shared_routed_memory_vectors(
+            torch.cat([shared, routed], dim=0).unsqueeze(0), num_shared_chapters=S, tokens_per_chapter=T,
+            norm_type=case.norm_type, eps=case.norm_eps).squeeze(0)
+        shared, routed = merged[:S * T].contiguous(), merged[S * T:].contiguous()
+    state = {"shared_memory": shared, "routed_memory": routed,
+             "token_chapter_indices": (idx - S).to(torch.int32), "tokens_per_chapter": T,
+             "routed_scale": float(case.routed_scaling_factor), "kernel_version": "v2", "chapter_weights": w}
+    out, _ = attn(h, None, token_routing_state=state, token_routing_kernel_version="v2")
+    aux = ref["compute_total_router_loss"](losses, load_balance_coef=0.01, auxiliary_coef=0.0, z_loss_coef=0.001)
+    loss = (out.float() * t["d_out"]).sum() + aux
+    loss.backward()
+    res = {"indices": idx.numpy(), "weights": w.detach().numpy(), "out": out.detach().numpy(),
+           "loss": loss.detach().numpy(), "d_h_router": h.grad.numpy(),
+           "d_router_w": router.router.weight.grad.numpy(), "d_router_b": router.router.bias.grad.numpy(),
+           "d_wq": attn.q_proj.weight.grad.numpy(), "d_wk": attn.k_proj.weight.grad.numpy(),
+           "d_wv": attn.v_proj.weight.grad.numpy(), "d_wo": attn.o_proj.weight.grad.numpy(),
+           "d_bank": base.memory.grad.numpy()}
+    for k, v in losses.items():
+        res["loss_" + k] = v.detach().numpy()
+    return res
+
+
 ROLLING = dict(case="rms_norm", window=8, coef={"load_balance": 0.3, "auxiliary": 700.0, "z_loss": 0.2, "entropy": 0.1})
 
 
@@ -171,6 +216,12 @@ def main():
     if not args.only or args.only == "rolling":
         np.savez_compressed(os.path.join(HERE, "rolling.npz"), **run_reference_rolling(ref))
         print("rolling", os.path.getsize(os.path.join(HERE, "rolling.npz")))
+    for name, case in TOKEN_CASES.items():
+        if args.only and name != args.only:
+            continue
+        res = run_reference_token(ref, case, make_inputs(case))
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **res)
+        print(name, "loss", float(res["loss"]), "size", os.path.getsize(os.path.join(HERE, name + ".npz")))
     for name, case in CASES.items():
         if args.only and name != args.only:
             continue

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from cases import CASES, make_inputs
+from cases import CASES, TOKEN_CASES, make_inputs
 from oracle import moc_oracle as O
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
@@ -83,6 +83,34 @@ def test_oracle_rolling_pool_router_matches_reference():
         np.testing.assert_allclose(losses[k].item(), gold["loss_" + k], rtol=1e-5, atol=1e-8)
     np.testing.assert_allclose(h.grad.numpy(), gold["d_h"], rtol=1e-4, atol=1e-8)
     np.testing.assert_allclose(W.grad.numpy(), gold["d_router_w"], rtol=1e-4, atol=1e-8)
+
+
+@pytest.mark.parametrize("name", list(TOKEN_CASES))
+def test_oracle_token_level_layer_matches_reference(name):
+    """route_token_level + token_routing_state attention (model.py:544-606, memory_attention.py:480-716)."""
+    case = TOKEN_CASES[name]
+    gold = np.load(os.path.join(GOLDEN, name + ".npz"))
+    inp = {k: torch.from_numpy(v) for k, v in make_inputs(case).items()}
+    res = O.token_memory_layer_fwd_bwd(shape_of(case), inp, inp["d_out"])
+    assert np.array_equal(res["indices"].numpy(), gold["indices"])
+    np.testing.assert_allclose(res["weights"].numpy(), gold["weights"], rtol=1e-5, atol=1e-7)
+    np.testing.assert_allclose(res["out"].numpy(), gold["out"], rtol=1e-4, atol=1e-6)
+    for k in ("load_balance", "auxiliary", "z_loss", "entropy"):
+        np.testing.assert_allclose(res["losses"][k].numpy(), gold["loss_" + k], rtol=1e-5, atol=1e-7)
+    for k in ("d_h_router", "d_router_w", "d_router_b", "d_wq", "d_wk", "d_wv", "d_wo", "d_bank"):
+        np.testing.assert_allclose(res[k].numpy(), gold[k], rtol=1e-4, atol=2e-6, err_msg=k)
+
+
+def test_rank_gaps_of_token_cases_are_wide():
+    for name, case in TOKEN_CASES.items():
+        inp = make_inputs(case)
+        z = inp["h_router"].astype(np.float64) @ inp["router_w"].astype(np.float64).T + inp["router_b"]
+        p = np.exp(z - z.max(-1, keepdims=True)); p /= p.sum(-1, keepdims=True)
+        p = p[..., case.num_shared_chapters:]
+        srt = -np.sort(-p, axis=-1)
+        k = case.top_k
+        rel = ((srt[..., :k] - srt[..., 1:k + 1]) / srt[..., :k]).min()
+        assert rel > 64 * np.finfo(np.float32).eps, (name, rel)
 
 
 def test_topk_order_is_value_desc_then_index_asc():
