@@ -579,7 +579,7 @@ class _RouteTokens(torch.autograd.Function):
         g_w = None if g_w is None else g_w.reshape(rows, -1).float().contiguous()
         g_losses = None if g_losses is None else g_losses.float()
         r = ops.router_bwd((rows, 1, d), torch.float32, w32, saved, top_k, num_shared, 1.0, g_w, None, g_losses,
-                           want_dh=False, parts=1)
+                           want_dh=False, parts=1, logits_only=True)
         d_logits = r["d_logits"]
         h32 = saved["pooled"]
         d_h = d_w = d_b = None

@@ -139,11 +139,14 @@ def router_bwd(h_shape, h_dtype, weight: torch.Tensor, saved: Dict[str, torch.Te
                num_shared: int, routed_scale: float, d_weights: Optional[torch.Tensor],
                d_comb_w: Optional[torch.Tensor], d_losses: Optional[torch.Tensor],
                want_dh: bool, d_h_accum: Optional[torch.Tensor] = None, parts: int = 7,
-               out: Optional[Dict[str, torch.Tensor]] = None) -> Dict[str, torch.Tensor]:
+               out: Optional[Dict[str, torch.Tensor]] = None, logits_only: bool = False) -> Dict[str, torch.Tensor]:
     """``d_h_accum`` ([B, L, d] of the hidden-state dtype): the hidden-state gradient is added into it instead
     of being written to a fresh tensor (the attention branch's gradient of the same hidden states).
     ``parts`` (1 = d_logits, 2 = d_w / d_bias, 4 = d_pooled / d_h) runs a subset on the current stream; pass the
-    dict returned by the first call as ``out`` to the later ones so they share buffers."""
+    dict returned by the first call as ``out`` to the later ones so they share buffers.  ``logits_only`` (with
+    parts = 1): no later part will run on these buffers, so no batch-sized scratch is allocated."""
+    if logits_only and parts != 1:
+        raise ValueError("logits_only goes with parts=1")
     b, l, d = h_shape
     c = weight.shape[0]
     dev = weight.device
@@ -152,7 +155,7 @@ def router_bwd(h_shape, h_dtype, weight: torch.Tensor, saved: Dict[str, torch.Te
     weight = _contig(weight.float())
     lib = L.lib()
     if out is None:
-        if parts == 1:
+        if logits_only:
             # logit gradient only (the token-level path finishes with projection kernels): no batch-sized scratch
             ws_bytes = max(16, lib.moc_router_workspace_bytes_parts(C.byref(s), 0, 1))
             out = {"d_logits": torch.empty(b, c, **f32), "d_w": torch.empty(1, **f32), "d_bias": torch.empty(1, **f32),
