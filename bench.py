@@ -217,7 +217,7 @@ def workload_config(cfg, n_gpus):
 class LayerRunner:
     """One memory layer with its parameters; ``step`` = forward + backward (+ gradient reduction)."""
 
-    def __init__(self, cfg, device, world=1, group=None, use_graph=True, exchange="nccl"):
+    def __init__(self, cfg, device, world=1, group=None, use_graph=True, exchange="nccl", wire="bf16"):
         import memory_b200 as M
         from memory_b200.graph import GraphedStep
         self.M = M
@@ -230,13 +230,15 @@ class LayerRunner:
         self.reducer = None
         if world > 1:
             from memory_b200.distributed import GradReducer
+            self.wire_dtype = torch.bfloat16 if wire == "bf16" else torch.float32
             self.reducer = GradReducer(cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["hidden_dim"], device,
-                                       group=group, exchange=exchange)
+                                       group=group, exchange=exchange, wire_dtype=self.wire_dtype, merge=True,
+                                       record_timings=True)
         # With a reduction the step is captured twice and the two graphs are replayed alternately: the
         # gradients of step i stay untouched in their graph's buffers while step i+1 runs in the other graph, so
         # the exchange reads them in place (no staging copy on the compute stream).
         self.slots = 2 if (world > 1 and use_graph) else 1
-        self.sinks = [M.SparseBankGrad() for _ in range(self.slots)]
+        self.sinks = [M.SparseBankGrad(self.wire_dtype if world > 1 else None) for _ in range(self.slots)]
         self.sink = self.sinks[0]
         self.params["bank"].moc_sparse_grad = self.sink
         self.pending = [None] * self.slots
@@ -279,8 +281,8 @@ class LayerRunner:
         slot = self.step_index % self.slots
         self.step_index += 1
         if self.reducer is not None and self.pending[slot] is not None:
-            # the exchange that still reads this slot's gradient buffers (started two steps ago) must be over;
-            # an optimizer step would consume its result here
+            # the exchange that still reads this slot's gradient buffers (started two steps ago) must be over, and
+            # with it the union-sum that turned the ranks' rows into the mean gradient an optimizer step applies
             self.pending[slot].wait()
             self.pending[slot].release()
             self.pending[slot] = None
@@ -320,6 +322,41 @@ class LayerRunner:
             last.wait()
             last.release()
             self.prev_snap = None
+
+    def verify_exchange(self, h, d_out):
+        """Two consecutive steps (both receive-buffer parities): the exchanged + merged bank gradient and the dense
+        bucket against plain NCCL all-reduces of each rank's own gradients divided by the world size."""
+        import torch.distributed as dist
+        P = self.params
+        worst = {"bank": 0.0, "dense": 0.0}
+        for step in range(2):
+            slot = step % self.slots
+            if self.graphs:
+                self.graphs[slot](h, d_out)
+                dense = self.dense_by_slot[slot]
+            else:
+                self._fwd_bwd(h, d_out, slot)
+                dense = [P[k].grad for k in self.DENSE_KEYS]
+            copy = not (self.slots == 2)
+            snap = self.reducer.snapshot(dense, self.sinks[slot], copy=copy)
+            pend = self.reducer.reduce_snapshot_async(snap)
+            pend.wait()
+            dense_red, bank_red = pend.result()
+            got = bank_red.to_dense(P["bank"])
+            want = self.sinks[slot].to_dense(P["bank"])
+            dist.all_reduce(want)
+            want /= self.world
+            worst["bank"] = max(worst["bank"], float((got - want).abs().max() / (want.abs().max() + 1e-30)))
+            del got, want
+            for g_red, g_loc in zip(dense_red, dense):
+                ref = g_loc.detach().float().clone()
+                dist.all_reduce(ref)
+                ref /= self.world
+                worst["dense"] = max(worst["dense"], float((g_red - ref).abs().max() / (ref.abs().max() + 1e-30)))
+            pend.release()
+            torch.cuda.synchronize()
+        self.reducer.timings.clear()
+        return worst
 
     def launches_per_step(self):
         """Kernels of this library one step launches (counted on an eager pass)."""
@@ -504,7 +541,7 @@ def run_cuda_arm(args):
     L.lib()
 
     cfg = dict(PAPER)
-    runner = LayerRunner(cfg, device, world, use_graph=not args.no_graph, exchange=args.exchange)
+    runner = LayerRunner(cfg, device, world, use_graph=not args.no_graph, exchange=args.exchange, wire=args.wire)
     hs_cpu, gs_cpu = make_hidden(cfg, N_INPUT_SETS, 1234 + rank, torch.bfloat16)
     hs = [t.to(device).requires_grad_(True) for t in hs_cpu]
     gs = [t.to(device) for t in gs_cpu]
@@ -516,9 +553,17 @@ def run_cuda_arm(args):
         torch.cuda.synchronize()
 
     # ---- headline: inputs resident in HBM ----
+    exchange_check = None
+    if world > 1:
+        exchange_check = runner.verify_exchange(hs[0], gs[0])
+        barrier()
     for i in range(args.warmup):
         runner.step(hs[i % N_INPUT_SETS], gs[i % N_INPUT_SETS])
     barrier()
+    if runner.reducer is not None:
+        runner.finish()
+        torch.cuda.synchronize()
+        runner.reducer.timings.clear()
     L.check_device_status(device)
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
@@ -544,6 +589,13 @@ def run_cuda_arm(args):
         block_ms.append(ms / args.steps)
     launches = per_step_launches * args.steps
     L.check_device_status(device)
+    exchange_ms = None
+    if runner.reducer is not None and runner.reducer.timings:
+        tm = runner.reducer.timings
+        exchange_ms = {"exchange": sum(a.elapsed_time(b) for a, b, _ in tm) / len(tm),
+                       "union_sum": sum(b.elapsed_time(c) for _, b, c in tm) / len(tm), "samples": len(tm)}
+        runner.reducer.timings = []
+        runner.reducer.record_timings = False
     ms_per_step = statistics.median(block_ms)
     value = tokens_per_step / (ms_per_step * 1e-3)
 
@@ -669,10 +721,13 @@ def run_cuda_arm(args):
     }
     if world > 1:
         line["config"]["gradient_exchange"] = (
-            "dense bucket: one NCCL all-reduce; bank rows: sparse, " +
+            "dense bucket: one NCCL all-reduce; bank rows: sparse, " + args.wire + " on the wire, " +
             ("copy-engine pushes into symmetric-memory receive buffers" if runner.reducer.exchange == "peer"
              and runner.reducer._peer is not None else "three fixed-size NCCL all-gathers") +
-            ", one step behind the compute on a second stream")
+            ", then a union-sum kernel (fp32 accumulation) that leaves the mean gradient rows an optimizer step "
+            "applies; all of it one step behind the compute on a second stream, inside the timed region")
+        line["config"]["exchange_ms_per_step_rank0"] = exchange_ms
+        line["exchange_check"] = exchange_check
     sys.stdout.flush()
     os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
@@ -696,6 +751,9 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="N > 1: how the sparse bank-gradient rows travel (NCCL all-gathers, or copy-engine pushes "
                          "into symmetric-memory receive buffers; falls back to NCCL when those cannot be set up)")
+    ap.add_argument("--wire", default="bf16", choices=["bf16", "fp32"],
+                    help="N > 1: dtype of the bank-gradient rows between ranks (sums are formed in fp32 at the receiver; "
+                         "the reference's DDP sends fp32)")
     ap.add_argument("--kernels", action="store_true", help="time the hot kernels alone (small footprint) and exit")
     ap.add_argument("--only", default="", help="--kernels: comma-separated kernel names")
     ap.add_argument("--iters", type=int, default=5, help="--kernels: launches per kernel")

@@ -155,13 +155,28 @@ int moc_chapter_segments(const int32_t* comb_idx, int32_t n_pairs, int32_t num_c
  * (memory_bank.py:291) done only on touched rows.
  * d_mem [B*K*T, dim] (fp32 or bf16) is the gradient of the scaled rows.
  * d_comb_w [B,K] <- sum over the slot's rows of <d_mem, norm(bank row)>.
- * bank_grad [num_unique*T, dim] fp32, compact: block u holds the gradient of chapter uniq[u]. */
+ * bank_grad [num_unique*T, dim] fp32, compact: block u holds the gradient of chapter uniq[u];
+ * bank_grad_bf16 (may be NULL): the same rows once more in bf16, for a gradient exchange that sends half the bytes. */
 int moc_gather_rows_bwd(const void* d_mem, int32_t d_mem_dtype, const void* bank, int32_t bank_dtype,
                         int64_t bank_rows, int32_t dim, int32_t tokens_per_chapter, const int32_t* comb_idx,
                         const float* comb_w, int32_t batch, int32_t k_sel, int32_t norm_type, float eps,
                         const float* row_stats, const int32_t* uniq, const int32_t* seg_offsets,
                         const int32_t* seg_pairs, const int32_t* num_unique, float* d_comb_w,
-                        float* bank_grad, int32_t* status, void* stream);
+                        float* bank_grad, void* bank_grad_bf16, int32_t* status, void* stream);
+
+/* Consumer of a data-parallel gradient exchange: the ranks' compact bank-gradient rows summed over the UNION of
+ * their chapter lists (the sum DDP's dense all-reduce of the bank gradient produces, training/trainer.py:873, on
+ * the touched chapters only).  rank_rows: host array of `world` device pointers, rank r's rows [per_rank*T, dim]
+ * (fp32 or bf16); ids_all [world, per_rank] int32 chapter ids, of which the first counts[r] of rank r are filled.
+ * Outputs: uniq (ascending union) / num_unique, seg_offsets / seg_pairs / pair_to_uniq (scratch, world*per_rank (+1)
+ * ints each), rows_out fp32 [num_unique*T, dim] = scale * sum over the ranks holding each chapter, added in
+ * ascending (rank, slot) order, so every rank computes identical bits.  rows_out_capacity (rows) must cover
+ * min(world*per_rank, num_chapters) chapters. */
+int moc_bank_grad_merge(const void* const* rank_rows, int32_t rows_dtype, int32_t world, const int32_t* ids_all,
+                        const int32_t* counts, int32_t per_rank, int32_t tokens_per_chapter, int32_t dim,
+                        int32_t num_chapters, float scale, int32_t* uniq, int32_t* seg_offsets, int32_t* seg_pairs,
+                        int32_t* pair_to_uniq, int32_t* num_unique, float* rows_out, int64_t rows_out_capacity,
+                        int32_t* status, void* stream);
 
 /* bank_dense[uniq[u]*T + r, :] += bank_grad[u*T + r, :]  (fp32). */
 int moc_scatter_bank_grad(const float* bank_grad, const int32_t* uniq, const int32_t* num_unique,

@@ -108,7 +108,11 @@ __global__ void gather_rows_kernel(const TB* __restrict__ bank, long long bank_r
 __global__ void __launch_bounds__(1024)
 chapter_segments_kernel(const int* __restrict__ comb_idx, int n_pairs, int C, int* __restrict__ uniq,
                         int* __restrict__ seg_offsets, int* __restrict__ seg_pairs,
-                        int* __restrict__ pair_to_uniq, int* __restrict__ num_unique, int* __restrict__ status) {
+                        int* __restrict__ pair_to_uniq, int* __restrict__ num_unique, int* __restrict__ status,
+                        const int* __restrict__ list_counts, int per_list) {
+  // With `list_counts` the entries form lists of `per_list` slots of which only the first list_counts[list] are
+  // filled (the ranks' touched-chapter lists of a gradient exchange); the rest is skipped.
+#define MOC_SEG_VALID(i) (list_counts == nullptr || ((i) % per_list) < list_counts[(i) / per_list])
   extern __shared__ int sh[];          // count[C], then start[C], urank[C]
   int* count = sh;
   int* start = sh + C;
@@ -117,6 +121,7 @@ chapter_segments_kernel(const int* __restrict__ comb_idx, int n_pairs, int C, in
   for (int c = threadIdx.x; c < C; c += blockDim.x) count[c] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    if (!MOC_SEG_VALID(i)) continue;
     const int c = comb_idx[i];
     if (c < 0 || c >= C) atomicMax(status, MOC_DEV_BAD_INDEX);
     else atomicAdd(&count[c], 1);
@@ -157,12 +162,56 @@ chapter_segments_kernel(const int* __restrict__ comb_idx, int n_pairs, int C, in
   const int U = warp_tot[1][31];
   if (threadIdx.x == 0) { num_unique[0] = U; seg_offsets[U] = warp_tot[0][31]; }
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-    const int c = comb_idx[i];
+    const int c = MOC_SEG_VALID(i) ? comb_idx[i] : -1;
     if (c < 0 || c >= C) { pair_to_uniq[i] = -1; continue; }
     int pos = 0;
-    for (int j = 0; j < i; ++j) pos += (comb_idx[j] == c);
+    for (int j = 0; j < i; ++j) pos += (MOC_SEG_VALID(j) && comb_idx[j] == c);
     seg_pairs[start[c] + pos] = i;
     pair_to_uniq[i] = urank[c];
+  }
+#undef MOC_SEG_VALID
+}
+
+// Sum of the ranks' compact gradient rows over the union of their chapter lists: one warp per output row;
+// the contributions of a chapter are added in ascending (rank, slot) order, so every rank computes the same bits.
+struct RankRows { const void* p[16]; };
+template <typename TR>
+__global__ void union_sum_kernel(RankRows src, int per_list, int T, int dim, const int* __restrict__ seg_offsets,
+                                 const int* __restrict__ seg_pairs, const int* __restrict__ num_unique,
+                                 long long max_rows, float scale, float* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  if (r >= max_rows) return;
+  const int u = static_cast<int>(r / T);
+  if (u >= num_unique[0]) return;
+  const int within = static_cast<int>(r - static_cast<long long>(u) * T);
+  const int p0 = seg_offsets[u], p1 = seg_offsets[u + 1];
+  float* dst = out + r * dim;
+  if ((dim & 7) == 0) {
+    for (int c = lane * 8; c < dim; c += 256) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int q = p0; q < p1; ++q) {
+        const int pair = seg_pairs[q];
+        const TR* rows = static_cast<const TR*>(src.p[pair / per_list]);
+        float g[8];
+        ld8(rows + (static_cast<long long>(pair % per_list) * T + within) * dim + c, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += g[j];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] *= scale;
+      st8(dst + c, acc);
+    }
+    return;
+  }
+  for (int c = lane; c < dim; c += 32) {
+    float acc = 0.f;
+    for (int q = p0; q < p1; ++q) {
+      const int pair = seg_pairs[q];
+      const TR* rows = static_cast<const TR*>(src.p[pair / per_list]);
+      acc += ld(rows + (static_cast<long long>(pair % per_list) * T + within) * dim, c);
+    }
+    dst[c] = acc * scale;
   }
 }
 
@@ -222,7 +271,7 @@ __global__ void bank_grad_kernel(const TG* __restrict__ d_mem, const TB* __restr
                                  int norm_type, const int* __restrict__ uniq,
                                  const int* __restrict__ seg_offsets, const int* __restrict__ seg_pairs,
                                  const int* __restrict__ num_unique, long long max_rows,
-                                 float* __restrict__ bank_grad) {
+                                 float* __restrict__ bank_grad, __nv_bfloat16* __restrict__ bank_grad_wire) {
   const int lane = threadIdx.x & 31;
   const long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   if (r >= max_rows) return;
@@ -231,6 +280,8 @@ __global__ void bank_grad_kernel(const TG* __restrict__ d_mem, const TB* __restr
   const int within = static_cast<int>(r - static_cast<long long>(u) * T);
   const int p0 = seg_offsets[u], p1 = seg_offsets[u + 1];
   float* dst = bank_grad + r * dim;
+  // optional second copy in bf16: what travels between ranks when the exchange is asked to halve its volume
+  __nv_bfloat16* wire = bank_grad_wire ? bank_grad_wire + r * dim : nullptr;
   if (norm_type == MOC_NORM_NONE && (dim & 7) == 0) {
     for (int c = lane * 8; c < dim; c += 256) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -243,6 +294,7 @@ __global__ void bank_grad_kernel(const TG* __restrict__ d_mem, const TB* __restr
         for (int j = 0; j < 8; ++j) acc[j] = fmaf(w, g[j], acc[j]);
       }
       st8(dst + c, acc);
+      if (wire) st8(wire + c, acc);
     }
     return;
   }
@@ -254,6 +306,7 @@ __global__ void bank_grad_kernel(const TG* __restrict__ d_mem, const TB* __restr
         acc = fmaf(comb_w ? comb_w[pair] : 1.f, ld(d_mem + (pair * T + within) * dim, c), acc);
       }
       dst[c] = acc;
+      if (wire) wire[c] = __float2bfloat16(acc);
     }
     return;
   }
@@ -279,7 +332,9 @@ __global__ void bank_grad_kernel(const TG* __restrict__ d_mem, const TB* __restr
   __syncwarp();
   for (int c = lane; c < dim; c += 32) {
     const float y = (ld(row, c) - mean) * rinv;
-    dst[c] = rinv * (dst[c] - sg - y * sgy);
+    const float v = rinv * (dst[c] - sg - y * sgy);
+    dst[c] = v;
+    if (wire) wire[c] = __float2bfloat16(v);
   }
 }
 
@@ -398,7 +453,43 @@ extern "C" int moc_chapter_segments(const int32_t* comb_idx, int32_t n_pairs, in
   const size_t sm = static_cast<size_t>(num_chapters) * 12;
   MOC_CUDA_OK(cudaFuncSetAttribute(chapter_segments_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
   chapter_segments_kernel<<<1, 1024, sm, stream>>>(comb_idx, n_pairs, num_chapters, uniq, seg_offsets, seg_pairs,
-                                                   pair_to_uniq, num_unique, status);
+                                                   pair_to_uniq, num_unique, status, nullptr, 1);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+extern "C" int moc_bank_grad_merge(const void* const* rank_rows, int32_t rows_dtype, int32_t world,
+                                   const int32_t* ids_all, const int32_t* counts, int32_t per_rank, int32_t T,
+                                   int32_t dim, int32_t num_chapters, float scale, int32_t* uniq,
+                                   int32_t* seg_offsets, int32_t* seg_pairs, int32_t* pair_to_uniq,
+                                   int32_t* num_unique, float* rows_out, int64_t rows_out_capacity,
+                                   int32_t* status, void* stream_) {
+  MOC_REQUIRE(rank_rows && ids_all && counts && uniq && seg_offsets && seg_pairs && pair_to_uniq && num_unique &&
+              rows_out && status, "NULL buffer");
+  MOC_REQUIRE(world >= 1 && world <= 16, "world size must be in [1, 16]");
+  MOC_REQUIRE(per_rank > 0 && T > 0 && dim > 0, "empty lists");
+  MOC_REQUIRE(rows_dtype == MOC_F32 || rows_dtype == MOC_BF16, "bad rows_dtype");
+  const int n_pairs = world * per_rank;
+  MOC_REQUIRE(n_pairs <= 65536, "too many list entries");
+  MOC_REQUIRE(num_chapters > 0 && static_cast<size_t>(num_chapters) * 12 <= 200 * 1024, "num_chapters too large");
+  const long long cap = n_pairs < num_chapters ? n_pairs : num_chapters;     // the union cannot be larger
+  MOC_REQUIRE(rows_out_capacity >= cap * T, "rows_out too small for the largest possible union");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const size_t sm = static_cast<size_t>(num_chapters) * 12;
+  MOC_CUDA_OK(cudaFuncSetAttribute(chapter_segments_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
+  chapter_segments_kernel<<<1, 1024, sm, stream>>>(ids_all, n_pairs, num_chapters, uniq, seg_offsets, seg_pairs,
+                                                   pair_to_uniq, num_unique, status, counts, per_rank);
+  RankRows src;
+  for (int r = 0; r < 16; ++r) src.p[r] = r < world ? rank_rows[r] : nullptr;
+  for (int r = 0; r < world; ++r) MOC_REQUIRE(src.p[r] != nullptr, "NULL rank rows");
+  const long long max_rows = cap * T;
+  const int blocks = static_cast<int>((max_rows * 32 + 255) / 256);
+  if (rows_dtype == MOC_F32)
+    union_sum_kernel<float><<<blocks, 256, 0, stream>>>(src, per_rank, T, dim, seg_offsets, seg_pairs, num_unique,
+                                                        max_rows, scale, rows_out);
+  else
+    union_sum_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(src, per_rank, T, dim, seg_offsets, seg_pairs,
+                                                                num_unique, max_rows, scale, rows_out);
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
 }
@@ -409,7 +500,7 @@ extern "C" int moc_gather_rows_bwd(const void* d_mem, int32_t d_mem_dtype, const
                                    float eps, const float* row_stats, const int32_t* uniq,
                                    const int32_t* seg_offsets, const int32_t* seg_pairs,
                                    const int32_t* num_unique, float* d_comb_w, float* bank_grad,
-                                   int32_t* status, void* stream_) {
+                                   void* bank_grad_bf16, int32_t* status, void* stream_) {
   (void)eps; (void)status;
   MOC_REQUIRE(d_mem && bank && comb_idx && uniq && seg_offsets && seg_pairs && num_unique, "NULL buffer");
   MOC_REQUIRE(norm_type == MOC_NORM_NONE || row_stats != nullptr, "row_stats needed for normalised rows");
@@ -427,7 +518,8 @@ extern "C" int moc_gather_rows_bwd(const void* d_mem, int32_t d_mem_dtype, const
       bank_grad_kernel<TG, TB><<<blocks, 256, 0, stream>>>(static_cast<const TG*>(d_mem),                     \
                                                            static_cast<const TB*>(bank), dim, T, comb_w,      \
                                                            row_stats, norm_type, uniq, seg_offsets,           \
-                                                           seg_pairs, num_unique, max_rows, bank_grad);       \
+                                                           seg_pairs, num_unique, max_rows, bank_grad,        \
+                                                           static_cast<__nv_bfloat16*>(bank_grad_bf16));      \
   } while (0)
   if (d_mem_dtype == MOC_F32 && bank_dtype == MOC_F32) MOC_GBWD(float, float);
   else if (d_mem_dtype == MOC_F32 && bank_dtype == MOC_BF16) MOC_GBWD(float, __nv_bfloat16);

@@ -62,14 +62,19 @@ class _PeerPush:
     device-to-device: copy engines, no kernel), one-element all-reduce (every push has landed everywhere).
     """
 
-    def __init__(self, group, device, n_ids: int, rows_shape, parities: int = 2):
+    def __init__(self, group, device, n_ids: int, rows_shape, parities: int = 2,
+                 rows_dtype: torch.dtype = torch.float32):
         import torch.distributed._symmetric_memory as symm
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.n, self.m, self.d = int(n_ids), int(rows_shape[0]), int(rows_shape[1])
         self.parities = parities
+        self.rows_dtype = rows_dtype
         w = self.world
-        self.rows_words = w * self.m * self.d
+        per_word = 4 // torch.empty(0, dtype=rows_dtype).element_size()      # row elements per fp32 word
+        if (self.m * self.d) % per_word:
+            raise ValueError("row block must fill whole 32-bit words")
+        self.rows_words = w * self.m * self.d // per_word
         self.ids_words = -(-(w * self.n) // 4) * 4
         self.num_words = -(-w // 4) * 4
         self.per_parity = self.rows_words + self.ids_words + self.num_words
@@ -82,7 +87,7 @@ class _PeerPush:
 
     def _views(self, flat: torch.Tensor, parity: int):
         base = parity * self.per_parity
-        rows = flat[base:base + self.rows_words].view(self.world, self.m, self.d)
+        rows = flat[base:base + self.rows_words].view(self.rows_dtype).view(self.world, self.m, self.d)
         ids = flat[base + self.rows_words:base + self.rows_words + self.world * self.n].view(torch.int32)
         nums = flat[base + self.rows_words + self.ids_words:
                     base + self.rows_words + self.ids_words + self.world].view(torch.int32)
@@ -101,8 +106,12 @@ class _PeerPush:
             p_nums[self.rank:self.rank + 1].copy_(num_unique.view(torch.int32).reshape(1), non_blocking=True)
         work = dist.all_reduce(self.token, group=self.group, async_op=True)
         rows_all, ids_all, nums_all = self._views(self.buf, parity)
+        # the local list also goes into its own slot (a few KB), so that [world, n] is one table for the merge;
+        # the local rows stay where they are
+        ids_all[self.rank].copy_(uniq.view(torch.int32), non_blocking=True)
+        nums_all[self.rank:self.rank + 1].copy_(num_unique.view(torch.int32).reshape(1), non_blocking=True)
         return work, [(uniq, num_unique, rows) if r == self.rank else (ids_all[r], nums_all[r:r + 1], rows_all[r])
-                      for r in range(self.world)]
+                      for r in range(self.world)], (ids_all, nums_all)
 
     def release(self, parity: int) -> None:
         """The consumer of this parity's buffers is done (recorded on the current stream)."""
@@ -116,10 +125,24 @@ class GradReducer:
 
     def __init__(self, num_chapters: int, tokens_per_chapter: int, dim: int, device,
                  group: Optional[dist.ProcessGroup] = None, bank_dtype: torch.dtype = torch.float32,
-                 exchange: str = "nccl"):
+                 exchange: str = "nccl", wire_dtype: torch.dtype = torch.float32, merge: bool = False,
+                 record_timings: bool = False):
+        """``wire_dtype`` bf16: the pipelined exchange sends the bf16 copy of the rows that the backward pass
+        wrote next to the fp32 ones (the sink must be created with ``SparseBankGrad(torch.bfloat16)``); sums are
+        still formed in fp32 at the receiver.  The reference's DDP reduces fp32; bf16 halves the volume at a
+        rounding of 2^-9 relative per rank's contribution.  ``merge``: the exchange is followed, on the reducer's
+        stream, by the union-sum kernel, so ``PendingReduction.result()`` holds ONE entry: the mean gradient rows
+        over the union of all ranks' chapters (identical bits on every rank)."""
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
+        if wire_dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("wire_dtype must be float32 or bfloat16")
         self.exchange = exchange
+        self.wire_dtype = wire_dtype
+        self.merge = merge
+        self.record_timings = record_timings
+        self.timings = []          # (start, exchanged, merged) CUDA events on the reducer's stream, per exchange
+        self._merge_out = {}       # per parity: output buffers of the union-sum kernel
         self._peer = None
         self._parity = 0
         self.c, self.t, self.d = int(num_chapters), int(tokens_per_chapter), int(dim)
@@ -176,7 +199,7 @@ class GradReducer:
         if flat is not None and self.world > 1:
             works.append(dist.all_reduce(flat, group=self.group, async_op=True))
         bank = None
-        if sink is not None and sink.entries:
+        if sink is not None:       # entered by every rank, whatever its own sink holds: the collectives must match
             counts = torch.zeros(self.c, dtype=torch.int32, device=self.device)
             ids, rows = self._merge_local(sink)
             if ids.numel():
@@ -211,11 +234,18 @@ class GradReducer:
             if sink is not None:
                 for uniq, num_unique, rows, t in sink.entries:
                     staged = rows.float() * inv if self.world > 1 else rows.float().clone()
-                    entries.append((uniq.clone(), num_unique.clone(), staged, t))
+                    entries.append((uniq.clone(), num_unique.clone(), staged.to(self.wire_dtype), t))
         else:
             flat = None
             if sink is not None:
-                entries = [(u, n, r if r.dtype == torch.float32 else r.float(), t) for u, n, r, t in sink.entries]
+                for i, (u, n, r, t) in enumerate(sink.entries):
+                    if self.wire_dtype == torch.bfloat16:
+                        wire = sink.wire[i] if i < len(sink.wire) else None
+                        if wire is None:
+                            raise ValueError("bf16 exchange needs SparseBankGrad(wire_dtype=torch.bfloat16)")
+                        entries.append((u, n, wire, t))
+                    else:
+                        entries.append((u, n, r if r.dtype == torch.float32 else r.float(), t))
         ev = torch.cuda.Event() if self.device.type == "cuda" else None
         if ev is not None:
             ev.record(torch.cuda.current_stream(self.device))
@@ -241,6 +271,7 @@ class GradReducer:
         if snap.flat is not None and self.world > 1:
             works.append(dist.all_reduce(snap.flat, group=self.group, async_op=True))
         gathered = []
+        merge_inputs = None
         use_peer = (self.exchange == "peer" and self.world > 1 and self.device.type == "cuda"
                     and len(snap.entries) == 1)
         for uniq, num_unique, rows, t in snap.entries:
@@ -248,13 +279,14 @@ class GradReducer:
                 gathered.append((uniq, num_unique, rows, t))
                 continue
             if use_peer and self._peer is None:
-                use_peer = self._open_peer(uniq.numel(), rows.shape)
+                use_peer = self._open_peer(uniq.numel(), rows.shape, rows.dtype)
             if use_peer:
                 parity = self._parity
                 self._parity = (parity + 1) % self._peer.parities
-                work, triples = self._peer.exchange(parity, uniq, num_unique, rows)
+                work, triples, (ids_tab, num_tab) = self._peer.exchange(parity, uniq, num_unique, rows)
                 works.append(work)
                 gathered += [(i, c, r, t) for i, c, r in triples]
+                merge_inputs = ([r for _, _, r in triples], ids_tab, num_tab, t)
                 pending_parity = parity
                 continue
             n, m = uniq.numel(), rows.shape[0]
@@ -265,17 +297,21 @@ class GradReducer:
                       self._all_gather(rows_all, rows)]
             for r in range(self.world):
                 gathered.append((ids_all[r * n:(r + 1) * n], num_all[r:r + 1], rows_all[r * m:(r + 1) * m], t))
+            if len(snap.entries) == 1:
+                merge_inputs = ([rows_all[r * m:(r + 1) * m] for r in range(self.world)],
+                                ids_all.view(self.world, n), num_all, t)
         pending = PendingReduction(self, works, snap.flat, snap.shapes, None, snap.sink_type, gathered=gathered)
         pending.bank_scale = snap.bank_scale
+        pending.merge_inputs = merge_inputs
         if use_peer and self.world > 1 and snap.entries:
             pending.parity = pending_parity
         return pending
 
-    def _open_peer(self, n_ids: int, rows_shape) -> bool:
+    def _open_peer(self, n_ids: int, rows_shape, rows_dtype=torch.float32) -> bool:
         """Create the symmetric-memory receive buffers; every rank must succeed or all fall back to NCCL."""
         ok = 1
         try:
-            self._peer = _PeerPush(self.group, self.device, n_ids, rows_shape)
+            self._peer = _PeerPush(self.group, self.device, n_ids, rows_shape, rows_dtype=rows_dtype)
         except Exception:                      # symmetric memory unavailable in this process / on this node
             self._peer, ok = None, 0
         flag = torch.tensor([ok], dtype=torch.int32, device=self.device)
@@ -295,15 +331,36 @@ class GradReducer:
             self._stream = torch.cuda.Stream(self.device)
         with torch.cuda.stream(self._stream):
             self._stream.wait_event(snap.event)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if self.record_timings else None
+            if ev:
+                ev[0].record(self._stream)
             pending = self._gather_snapshot(snap)
             pending.stream = self._stream
             # completion of exactly this exchange (later exchanges queued on the same stream do not count)
             for w in pending.works:
                 w.wait()
             pending.works = []
+            if ev:
+                ev[1].record(self._stream)
+            if self.merge and pending.merge_inputs is not None:
+                self._merge(pending)
+            if ev:
+                ev[2].record(self._stream)
+                self.timings.append(tuple(ev))
             pending.done = torch.cuda.Event()
             pending.done.record(self._stream)
         return pending
+
+    def _merge(self, pending: "PendingReduction") -> None:
+        """Union-sum of the gathered rows on the current (reducer) stream.  The output buffers belong to the
+        receive-buffer parity (or rotate over two sets), so a result stays valid until the exchange after next."""
+        from . import ops
+        rank_rows, ids_tab, num_tab, t = pending.merge_inputs
+        slot = pending.parity if pending.parity is not None else (len(self.timings) & 1)
+        out = ops.bank_grad_merge(rank_rows, ids_tab, num_tab, t, self.c, pending.bank_scale,
+                                  out=self._merge_out.get(slot))
+        self._merge_out[slot] = out
+        pending.merged = (out["uniq"], out["num_unique"], out["rows"], t)
 
     @staticmethod
     def _split(flat, shapes):
@@ -321,12 +378,15 @@ class GradReducer:
     def reduce(self, dense_grads: Sequence[Optional[torch.Tensor]], sink):
         """All-reduce the dense gradients in place and return the reduced bank gradient (or None)."""
         self.reduce_dense(dense_grads)
-        if sink is not None and sink.entries:
+        if sink is not None:       # entered by every rank, whatever its own sink holds: the collectives must match
             return self.reduce_bank(sink)
         return None
 
     def _merge_local(self, sink):
         """Sum this rank's entries (several memory layers may share one bank) into one id list."""
+        if len(sink.entries) == 0:
+            return (torch.empty(0, dtype=torch.int32, device=self.device),
+                    torch.empty(0, self.d, dtype=torch.float32, device=self.device))
         if len(sink.entries) == 1:
             uniq, num_unique, rows, _ = sink.entries[0]
             n = int(num_unique.item())
@@ -366,6 +426,8 @@ class PendingReduction:
         self.gathered = gathered      # per-rank (ids, count, rows / world, T) of the pipelined form
         self.parity = None            # receive-buffer parity of the peer exchange, if that carried the rows
         self.bank_scale = 1.0
+        self.merge_inputs = None      # (per-rank rows, [world, n] id table, [world] counts, T) for the union-sum
+        self.merged = None            # (union ids, count, summed fp32 rows, T) once the union-sum has run
 
     def release(self) -> None:
         """Tell the reducer that the result's tensors are no longer read after the work queued so far on the
@@ -395,9 +457,12 @@ class PendingReduction:
             bank = None
             if self.sink_type is not None:
                 bank = self.sink_type()
-                for e in self.gathered:
-                    bank.add(*e)
-                bank.scale = self.bank_scale
+                if self.merged is not None:
+                    bank.add(*self.merged)        # one entry: the mean rows over the union (scale applied)
+                else:
+                    for e in self.gathered:
+                        bank.add(*e)
+                    bank.scale = self.bank_scale
             return GradReducer._split(self.flat, self.shapes), bank
         dense = []
         if self.flat is not None:

@@ -34,20 +34,25 @@ class SparseBankGrad:
     passes then append here and return no dense gradient for the bank.
     """
 
-    def __init__(self):
+    def __init__(self, wire_dtype: Optional[torch.dtype] = None):
         self.entries = []   # list of (uniq int32 [n_pairs], num_unique int32 [1], rows fp32 [n_pairs*T, d], T)
+        self.wire = []      # per entry: the same rows in ``wire_dtype`` (what a gradient exchange sends), or None
+        self.wire_dtype = wire_dtype   # torch.bfloat16: backward passes also produce the bf16 copy
         self.scale = 1.0    # factor the consumer applies to the summed rows (1 / world after a zero-copy reduction)
 
-    def add(self, uniq, num_unique, rows, tokens_per_chapter):
+    def add(self, uniq, num_unique, rows, tokens_per_chapter, wire=None):
         self.entries.append((uniq, num_unique, rows, int(tokens_per_chapter)))
+        self.wire.append(wire)
 
     def clear(self):
         self.entries.clear()
+        self.wire.clear()
 
     def to_dense(self, like: torch.Tensor) -> torch.Tensor:
         dense = torch.zeros(like.shape, dtype=torch.float32, device=like.device)
         for uniq, num_unique, rows, t in self.entries:
-            ops.scatter_bank_grad(rows, {"uniq": uniq, "num_unique": num_unique}, t, dense)
+            ops.scatter_bank_grad(rows if rows.dtype == torch.float32 else rows.float(),
+                                  {"uniq": uniq, "num_unique": num_unique}, t, dense)
         if self.scale != 1.0:
             dense.mul_(self.scale)
         return dense
@@ -114,12 +119,13 @@ def route(h: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], t
 # --------------------------------------------------------------------------------------------
 def _bank_backward(sink, d_mem, bank, t, comb_idx, comb_w, norm, eps, stats, num_chapters, want_dw, want_bank):
     seg = ops.chapter_segments(comb_idx, num_chapters)
+    wire = [] if (sink is not None and sink.wire_dtype == torch.bfloat16) else None
     d_cw, rows = ops.gather_rows_bwd(d_mem, bank, t, comb_idx, comb_w, norm, eps, stats, seg,
-                                     want_dw=want_dw, want_bank=want_bank)
+                                     want_dw=want_dw, want_bank=want_bank, wire_copy=wire)
     d_bank = None
     if want_bank:
         if sink is not None:
-            sink.add(seg["uniq"], seg["num_unique"], rows, t)
+            sink.add(seg["uniq"], seg["num_unique"], rows, t, wire=wire[0] if wire else None)
         else:
             d_bank = torch.zeros(bank.shape, dtype=torch.float32, device=bank.device)
             ops.scatter_bank_grad(rows, seg, t, d_bank)
@@ -457,12 +463,13 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
 
         d_mem = ops.gemm(d_kv2, wkv_t, tag="d_mem")
         want_bank = need[2]
+        wire = [] if (ctx.sink is not None and ctx.sink.wire_dtype == torch.bfloat16) else None
         d_cw, rows = ops.gather_rows_bwd(d_mem, bank, t, r["comb_idx"], r["comb_w"], ctx.norm_row, row_eps, stats_m,
-                                         seg, want_dw=True, want_bank=want_bank)
+                                         seg, want_dw=True, want_bank=want_bank, wire_copy=wire)
         d_bank = None
         if want_bank:
             if ctx.sink is not None:
-                ctx.sink.add(seg["uniq"], seg["num_unique"], rows, t)
+                ctx.sink.add(seg["uniq"], seg["num_unique"], rows, t, wire=wire[0] if wire else None)
             else:
                 d_bank = torch.zeros(bank.shape, dtype=f32, device=dev)
                 ops.scatter_bank_grad(rows, seg, t, d_bank)

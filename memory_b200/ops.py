@@ -283,7 +283,10 @@ def chapter_segments(comb_idx: torch.Tensor, num_chapters: int) -> Dict[str, tor
 def gather_rows_bwd(d_mem: torch.Tensor, bank: torch.Tensor, tokens_per_chapter: int, comb_idx: torch.Tensor,
                     comb_w: Optional[torch.Tensor], norm_type: Optional[str], eps: float,
                     row_stats: Optional[torch.Tensor], seg: Dict[str, torch.Tensor],
-                    want_dw: bool = True, want_bank: bool = True) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+                    want_dw: bool = True, want_bank: bool = True, wire_copy: Optional[list] = None
+                    ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """``wire_copy``: pass an empty list to also get the compact rows in bf16 (appended to it): the copy a
+    gradient exchange sends when it is asked to halve its volume."""
     bank = _contig(bank)
     d_mem = _contig(d_mem)
     comb_idx = _contig(comb_idx.to(torch.int32))
@@ -293,13 +296,51 @@ def gather_rows_bwd(d_mem: torch.Tensor, bank: torch.Tensor, tokens_per_chapter:
     dev = bank.device
     d_comb_w = torch.empty(b, k, dtype=torch.float32, device=dev) if want_dw else None
     bank_grad = torch.empty(b * k * t, d, dtype=torch.float32, device=dev) if want_bank else None
+    wire = None
+    if want_bank and wire_copy is not None:
+        wire = torch.empty(b * k * t, d, dtype=torch.bfloat16, device=dev)
+        wire_copy.append(wire)
     rc = L.lib().moc_gather_rows_bwd(L.ptr(d_mem), L.dtype_code(d_mem.dtype), L.ptr(bank), L.dtype_code(bank.dtype),
                                      n_rows, d, t, L.ptr(comb_idx), L.ptr(_contig(comb_w)), b, k,
                                      L.NORM_CODES[norm_type], float(eps), L.ptr(row_stats), L.ptr(seg["uniq"]),
                                      L.ptr(seg["seg_offsets"]), L.ptr(seg["seg_pairs"]), L.ptr(seg["num_unique"]),
-                                     L.ptr(d_comb_w), L.ptr(bank_grad), L.ptr(L.status_word(dev)), L.stream_ptr(dev))
+                                     L.ptr(d_comb_w), L.ptr(bank_grad), L.ptr(wire), L.ptr(L.status_word(dev)),
+                                     L.stream_ptr(dev))
     L.check(rc, "moc_gather_rows_bwd")
     return d_comb_w, bank_grad
+
+
+@_instrument("bank_grad_merge", 2)
+def bank_grad_merge(rank_rows, ids_all: torch.Tensor, counts: torch.Tensor, tokens_per_chapter: int,
+                    num_chapters: int, scale: float = 1.0, out: Optional[Dict[str, torch.Tensor]] = None
+                    ) -> Dict[str, torch.Tensor]:
+    """Sum of the ranks' compact gradient rows over the union of their chapter lists.
+
+    ``rank_rows``: one [per_rank*T, d] tensor per rank (all fp32 or all bf16); ``ids_all`` int32 [world, per_rank];
+    ``counts`` int32 [world].  Returns {"uniq", "num_unique", "rows" fp32 [cap*T, d], scratch...}; pass the dict
+    back as ``out`` to reuse its buffers."""
+    world, per_rank = ids_all.shape
+    t, d = int(tokens_per_chapter), rank_rows[0].shape[1]
+    dev = ids_all.device
+    L.require_cuda(ids_all, counts, *rank_rows)
+    if any(r.dtype != rank_rows[0].dtype or not r.is_contiguous() for r in rank_rows):
+        raise ValueError("rank_rows must be contiguous tensors of one dtype")
+    n = world * per_rank
+    cap = min(n, int(num_chapters))
+    if out is None:
+        i32 = dict(dtype=torch.int32, device=dev)
+        out = {"uniq": torch.empty(n, **i32), "seg_offsets": torch.empty(n + 1, **i32),
+               "seg_pairs": torch.empty(n, **i32), "pair_to_uniq": torch.empty(n, **i32),
+               "num_unique": torch.empty(1, **i32),
+               "rows": torch.empty(cap * t, d, dtype=torch.float32, device=dev)}
+    arr = (C.c_void_p * world)(*[r.data_ptr() for r in rank_rows])
+    rc = L.lib().moc_bank_grad_merge(arr, L.dtype_code(rank_rows[0].dtype), world, L.ptr(_contig(ids_all)),
+                                     L.ptr(_contig(counts)), per_rank, t, d, int(num_chapters), float(scale),
+                                     L.ptr(out["uniq"]), L.ptr(out["seg_offsets"]), L.ptr(out["seg_pairs"]),
+                                     L.ptr(out["pair_to_uniq"]), L.ptr(out["num_unique"]), L.ptr(out["rows"]),
+                                     out["rows"].shape[0], L.ptr(L.status_word(dev)), L.stream_ptr(dev))
+    L.check(rc, "moc_bank_grad_merge")
+    return out
 
 
 @_instrument("scatter_bank_grad", 1)

@@ -561,3 +561,33 @@ def test_bounded_device_wait_gives_up_and_reports(dev):
     y = ops.gemm(x, x, out_dtype=torch.float32)
     assert rel_err(y, x.float() @ x.float().t()) < 1e-5
     _status_ok(dev)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_bank_grad_union_sum_over_rank_lists(dtype, dev):
+    """Consumer of the gradient exchange: rows of several ranks summed over the union of their chapter lists,
+    lists only partly filled, chapters shared between ranks, sums in ascending (rank, slot) order."""
+    from memory_b200 import ops
+    W, n, T, d, C = 3, 7, 4, 24, 20
+    g = torch.Generator().manual_seed(9)
+    counts = torch.tensor([7, 4, 5], dtype=torch.int32)
+    ids = torch.stack([torch.sort(torch.randperm(C, generator=g)[:n]).values for _ in range(W)]).int()
+    rows = [torch.randn(n * T, d, generator=g).to(dtype) for _ in range(W)]
+    dense = torch.zeros(C * T, d)
+    for r in range(W):
+        for s_ in range(int(counts[r])):
+            c = int(ids[r, s_])
+            dense[c * T:(c + 1) * T] += rows[r][s_ * T:(s_ + 1) * T].float()
+    dense *= 0.5
+    out = ops.bank_grad_merge([x.to(dev) for x in rows], ids.to(dev), counts.to(dev), T, C, scale=0.5)
+    _status_ok(dev)
+    nu = int(out["num_unique"].item())
+    uniq = out["uniq"][:nu].cpu().long()
+    want_ids = torch.unique(torch.cat([ids[r, :counts[r]] for r in range(W)])).long()
+    assert torch.equal(uniq, want_ids)
+    got = out["rows"][:nu * T].cpu().view(nu, T, d)
+    ref = dense.view(C, T, d)[uniq]
+    assert rel_err(got, ref) < 1e-6
+    # the same buffers can be reused
+    out2 = ops.bank_grad_merge([x.to(dev) for x in rows], ids.to(dev), counts.to(dev), T, C, scale=0.5, out=out)
+    assert out2["rows"].data_ptr() == out["rows"].data_ptr()
