@@ -217,7 +217,7 @@ def workload_config(cfg, n_gpus):
 class LayerRunner:
     """One memory layer with its parameters; ``step`` = forward + backward (+ gradient reduction)."""
 
-    def __init__(self, cfg, device, world=1, group=None, use_graph=True, exchange="nccl", wire="bf16"):
+    def __init__(self, cfg, device, world=1, group=None, use_graph=True, exchange="nccl", wire="bf16", merge=True):
         import memory_b200 as M
         from memory_b200.graph import GraphedStep
         self.M = M
@@ -232,13 +232,17 @@ class LayerRunner:
             from memory_b200.distributed import GradReducer
             self.wire_dtype = torch.bfloat16 if wire == "bf16" else torch.float32
             self.reducer = GradReducer(cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["hidden_dim"], device,
-                                       group=group, exchange=exchange, wire_dtype=self.wire_dtype, merge=True,
+                                       group=group, exchange=exchange, wire_dtype=self.wire_dtype, merge=merge,
                                        record_timings=True)
         # With a reduction the step is captured twice and the two graphs are replayed alternately: the
         # gradients of step i stay untouched in their graph's buffers while step i+1 runs in the other graph, so
         # the exchange reads them in place (no staging copy on the compute stream).
-        self.slots = 2 if (world > 1 and use_graph) else 1
+        self.slots = 2 if ((world > 1 or os.environ.get("MOC_BENCH_TWO_SLOTS")) and use_graph) else 1
         self.sinks = [M.SparseBankGrad(self.wire_dtype if world > 1 else None) for _ in range(self.slots)]
+        if os.environ.get("MOC_BENCH_DEBUG"):
+            torch.cuda.synchronize()
+            from memory_b200 import _lib as _L
+            print(f"[dbg] before capture: status = {int(_L.status_word(device).item())}", file=sys.stderr)
         self.sink = self.sinks[0]
         self.params["bank"].moc_sparse_grad = self.sink
         self.pending = [None] * self.slots
@@ -254,6 +258,10 @@ class LayerRunner:
             for s in range(self.slots):
                 self.graphs.append(GraphedStep(lambda h, d, s=s: self._fwd_bwd(h, d, s), [h0, g0]))
                 self.dense_by_slot.append([self.params[k].grad for k in self.DENSE_KEYS])
+                if os.environ.get("MOC_BENCH_DEBUG"):
+                    torch.cuda.synchronize()
+                    from memory_b200 import _lib as _L
+                    print(f"[dbg] after capture of slot {s}: status = {int(_L.status_word(device).item())}", file=sys.stderr)
             self.graphed = self.graphs[0]
 
     DENSE_KEYS = ("router_w", "router_b", "wq", "wk", "wv", "wo")
@@ -329,11 +337,16 @@ class LayerRunner:
         import torch.distributed as dist
         P = self.params
         worst = {"bank": 0.0, "dense": 0.0}
+        from memory_b200 import _lib as L
+        dbg = os.environ.get("MOC_BENCH_DEBUG")
         for step in range(2):
             slot = step % self.slots
             if self.graphs:
                 self.graphs[slot](h, d_out)
                 dense = self.dense_by_slot[slot]
+                if dbg:
+                    torch.cuda.synchronize()
+                    print(f"[dbg] verify step {step}: status after replay = {int(L.status_word(self.device).item())}", file=sys.stderr)
             else:
                 self._fwd_bwd(h, d_out, slot)
                 dense = [P[k].grad for k in self.DENSE_KEYS]
@@ -359,14 +372,23 @@ class LayerRunner:
         return worst
 
     def launches_per_step(self):
-        """Kernels of this library one step launches (counted on an eager pass)."""
+        """Kernels of this library one step launches (counted on an eager pass into a scratch sink, so the sinks
+        that hold the captured steps' gradient buffers are left alone)."""
         from memory_b200 import ops
         shape = (self.cfg["batch"], self.cfg["seq"], self.cfg["hidden_dim"])
         h = torch.randn(shape, device=self.device).bfloat16().requires_grad_(True)
         g = torch.randn(shape, device=self.device).bfloat16()
         n0 = ops.LAUNCHES
-        self._fwd_bwd(h, g)
-        torch.cuda.synchronize()
+        saved_sinks, saved_grads = self.sinks, {k: v.grad for k, v in self.params.items()}
+        self.sinks = [self.M.SparseBankGrad(s.wire_dtype) for s in saved_sinks]
+        try:
+            self._fwd_bwd(h, g)
+            torch.cuda.synchronize()
+        finally:
+            self.sinks = saved_sinks
+            for k, v in self.params.items():
+                v.grad = saved_grads[k]
+            self.params["bank"].moc_sparse_grad = self.sinks[0]
         return ops.LAUNCHES - n0
 
 
@@ -541,7 +563,8 @@ def run_cuda_arm(args):
     L.lib()
 
     cfg = dict(PAPER)
-    runner = LayerRunner(cfg, device, world, use_graph=not args.no_graph, exchange=args.exchange, wire=args.wire)
+    runner = LayerRunner(cfg, device, world, use_graph=not args.no_graph, exchange=args.exchange, wire=args.wire,
+                         merge=not args.no_merge)
     hs_cpu, gs_cpu = make_hidden(cfg, N_INPUT_SETS, 1234 + rank, torch.bfloat16)
     hs = [t.to(device).requires_grad_(True) for t in hs_cpu]
     gs = [t.to(device) for t in gs_cpu]
@@ -552,11 +575,20 @@ def run_cuda_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if os.environ.get("MOC_BENCH_DEBUG"):
+        torch.cuda.synchronize()
+        print(f"[dbg] after runner init: status = {int(L.status_word(device).item())}", file=sys.stderr)
+    if runner.reducer is not None:
+        runner.reducer.prepare(runner.sinks[0])     # peer mappings and streams exist before anything is timed
+    if os.environ.get("MOC_BENCH_DEBUG"):
+        torch.cuda.synchronize()
+        print(f"[dbg] after prepare: status = {int(L.status_word(device).item())}", file=sys.stderr)
     # ---- headline: inputs resident in HBM ----
     exchange_check = None
-    if world > 1:
+    if world > 1 and not args.no_exchange_check:
         exchange_check = runner.verify_exchange(hs[0], gs[0])
         barrier()
+        L.check_device_status(device)
     for i in range(args.warmup):
         runner.step(hs[i % N_INPUT_SETS], gs[i % N_INPUT_SETS])
     barrier()
@@ -754,6 +786,8 @@ def main():
     ap.add_argument("--wire", default="bf16", choices=["bf16", "fp32"],
                     help="N > 1: dtype of the bank-gradient rows between ranks (sums are formed in fp32 at the receiver; "
                          "the reference's DDP sends fp32)")
+    ap.add_argument("--no-exchange-check", action="store_true", help="N > 1: skip the numerical check of the exchange")
+    ap.add_argument("--no-merge", action="store_true", help="N > 1: leave the ranks' rows unsummed (exchange only)")
     ap.add_argument("--kernels", action="store_true", help="time the hot kernels alone (small footprint) and exit")
     ap.add_argument("--only", default="", help="--kernels: comma-separated kernel names")
     ap.add_argument("--iters", type=int, default=5, help="--kernels: launches per kernel")

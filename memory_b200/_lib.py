@@ -17,6 +17,7 @@ MOC_F32, MOC_BF16 = 0, 1
 ATTN_BWD_STATIC_MAX_FLOATS = 1 << 20   # MOC_ATTN_BWD_STATIC_MAX_FLOATS in include/moc_b200.h
 NORM_NONE, NORM_RMS, NORM_LAYERNORM = 0, 1, 2
 NORM_CODES = {None: NORM_NONE, "none": NORM_NONE, "rms": NORM_RMS, "layernorm": NORM_LAYERNORM}
+KERNEL_TAGS = {1: "gemm_tc.cu", 2: "attn_tc_fwd.cu", 3: "attn_tc_bwd.cu", 4: "host_util.cu"}
 DEV_STATUS_TEXT = {1: "a bounded device wait timed out", 2: "a chapter index was out of range"}
 
 
@@ -161,7 +162,9 @@ def check_device_status(device, clear: bool = True) -> None:
     if clear and v != 0:
         t.zero_()
     if v != 0:
-        raise RuntimeError(f"device-side error {v}: {DEV_STATUS_TEXT.get(v, 'unknown')}")
+        code, tag, line = v & 0xFF, (v >> 8) & 0xF, v >> 12
+        where = f" ({KERNEL_TAGS.get(tag, 'kernel file %d' % tag)}, source line {line})" if (tag or line) else ""
+        raise RuntimeError(f"device-side error {code}: {DEV_STATUS_TEXT.get(code, 'unknown')}{where}")
 
 
 def dtype_code(dt: torch.dtype) -> int:

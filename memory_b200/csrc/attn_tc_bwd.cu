@@ -14,6 +14,7 @@
 //                                           columns S^T / dP^T occupied; B = dO / Q tiles MN-major)
 // Recomputing S in both kernels costs 2 extra MMAs per tile pair against a fused 5-MMA backward
 // but keeps every accumulator private to one CTA: results are deterministic.
+#define MOC_KERNEL_TAG 3
 #include "moc_common.cuh"
 
 namespace moc {

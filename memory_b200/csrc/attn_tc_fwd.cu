@@ -12,6 +12,7 @@
 // of the current ones; the second CTA fills what is left of the strictly ordered chain.  The
 // running maximum is only raised (and O rescaled) when it grows by more than 2^8, which keeps P
 // within bf16 range while skipping almost every rescale.
+#define MOC_KERNEL_TAG 2
 #include "moc_common.cuh"
 
 namespace moc {
@@ -85,7 +86,10 @@ __global__ void __launch_bounds__(kThreads, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
                    FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t q_bar, kv_full[kStages], kv_empty[kStages], s_full[2], p_full, pv_bar;
+  // p_full is one barrier per score buffer: S_{j+1} is issued before the MMA warp waits for P_j, so the row owners
+  // can finish tile j+1 (the other buffer) while that wait has not yet observed tile j's phase; with a single barrier
+  // two completed phases would look like none to a parity wait and the warp would wait forever.
+  __shared__ __align__(8) uint64_t q_bar, kv_full[kStages], kv_empty[kStages], s_full[2], p_full[2], pv_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -105,7 +109,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     for (int s = 0; s < kStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
-    mbar_init(&p_full, 128);
+    mbar_init(&p_full[0], 128);
+    mbar_init(&p_full[1], 128);
     mbar_init(&pv_bar, 1);
     fence_mbar_init();
     prefetch_tmap(&tmap_q);
@@ -168,7 +173,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           tc_commit_w(&s_full[(j + 1) & 1]);
         }
         const int s = j % kStages;
-        ok = mbar_wait_w(&p_full, j & 1, &abort_flag, p.status);
+        ok = mbar_wait_w(&p_full[j & 1], (j >> 1) & 1, &abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
         issue_ts_single(tmem + kColO, tmem + kColP + (j & 1) * 64, v_desc0 + s * kStageOff, idesc_o, j > 0 ? 1u : 0u);
@@ -248,7 +253,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       tmem_st32(tmem + lane_sel + kColP + (j & 1) * 64, pk);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&p_full);
+      mbar_arrive(&p_full[j & 1]);
     }
     if (ok) {
       ok = mbar_wait(&pv_bar, (n_tiles - 1) & 1, &abort_flag, p.status);

@@ -9,6 +9,7 @@
 // warp_id % 4).  Two accumulator buffers in tensor memory let the epilogue of one tile run under the
 // main loop of the next.  The A operand can be fetched through a row-block gather
 // list, which is how selected chapters are read straight out of the memory bank.
+#define MOC_KERNEL_TAG 1
 #include "moc_common.cuh"
 
 namespace moc {

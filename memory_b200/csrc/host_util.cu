@@ -1,6 +1,7 @@
 // Host-side utilities shared by the entry points: last-error text and TMA tensor-map creation.
 #include <string>
 
+#define MOC_KERNEL_TAG 4
 #include "moc_common.cuh"
 
 namespace moc {

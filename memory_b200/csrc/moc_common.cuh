@@ -53,7 +53,7 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_
 // ---------------------------------------------------------------------------
 // device helpers
 // ---------------------------------------------------------------------------
-constexpr uint32_t kWaitPollLimit = 1u << 22;   // polls before a wait gives up
+constexpr uint32_t kWaitPollLimit = 1u << 24;   // polls before a wait gives up (of the order of a second)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -88,22 +88,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait.  `abort_flag` lives in shared memory; `status` in global memory.  After `limit` polls the
-// waiter gives up: it raises the CTA's abort flag, records MOC_DEV_TIMEOUT and returns false.
+// waiter gives up: it raises the CTA's abort flag, records MOC_DEV_TIMEOUT and returns false.  The status word
+// keeps the code in its low byte; bits 8-11 name the kernel file (MOC_KERNEL_TAG) and bits 12+ the source line of
+// the wait that gave up, so a report says where the device stopped waiting.
+#ifndef MOC_KERNEL_TAG
+#define MOC_KERNEL_TAG 0
+#endif
 __device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                  int* status, uint32_t limit) {
+                                                  int* status, uint32_t limit, int where = 0) {
   if (*abort_flag) return false;
   for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u && *abort_flag) return false;
   }
   *abort_flag = 1;
-  atomicMax(status, MOC_DEV_TIMEOUT);
+  atomicMax(status, MOC_DEV_TIMEOUT | (MOC_KERNEL_TAG << 8) | (where << 12));
   return false;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status) {
-  return mbar_wait_limited(bar, parity, abort_flag, status, kWaitPollLimit);
-}
+#define mbar_wait(bar, parity, abort_flag, status) \
+  mbar_wait_limited(bar, parity, abort_flag, status, kWaitPollLimit, __LINE__)
 
 // TMA: 2-D tiled load global -> shared, completion on an mbarrier.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
@@ -282,9 +285,8 @@ __device__ __forceinline__ void tc_commit_w(uint64_t* bar) {
       : "memory");
 }
 // mbar_wait for a whole warp with a warp-uniform result
-__device__ __forceinline__ bool mbar_wait_w(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status));
-}
+#define mbar_wait_w(bar, parity, abort_flag, status) \
+  __all_sync(0xffffffffu, mbar_wait_limited(bar, parity, abort_flag, status, kWaitPollLimit, __LINE__))
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);   // .x = lo (low 16 bits), .y = hi

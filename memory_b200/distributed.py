@@ -322,6 +322,25 @@ class GradReducer:
             return False
         return True
 
+    def prepare(self, sink) -> None:
+        """Set up everything the pipelined exchange allocates or maps lazily -- the reducer's stream and, for
+        ``exchange="peer"``, the symmetric-memory receive buffers and their peer mappings -- while the device is
+        idle.  Mapping peer memory updates the GPU's page tables; done under running kernels it stalled their
+        memory traffic long enough for a bounded device wait to give up.  Call once, on every rank, after the
+        first backward pass has filled ``sink`` (its entry gives the block sizes) and before the timed loop."""
+        if self.device.type != "cuda" or self.world == 1:
+            return
+        torch.cuda.synchronize(self.device)
+        if getattr(self, "_stream", None) is None:
+            self._stream = torch.cuda.Stream(self.device)
+        if self.exchange == "peer" and self._peer is None and sink is not None and len(sink.entries) == 1:
+            uniq, _, rows, _ = sink.entries[0]
+            if self.wire_dtype == torch.bfloat16 and sink.wire and sink.wire[0] is not None:
+                rows = sink.wire[0]
+            self._open_peer(uniq.numel(), rows.shape, rows.dtype)
+        dist.barrier(group=self.group)
+        torch.cuda.synchronize(self.device)
+
     def reduce_snapshot_async(self, snap: "GradSnapshot") -> "PendingReduction":
         """Exchange a snapshot on the reducer's own stream: one all-reduce of the dense bucket and three
         all-gathers per bank entry, all of fixed size, so nothing here waits for the device."""
