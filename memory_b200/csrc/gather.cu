@@ -108,11 +108,7 @@ __global__ void gather_rows_kernel(const TB* __restrict__ bank, long long bank_r
 __global__ void __launch_bounds__(1024)
 chapter_segments_kernel(const int* __restrict__ comb_idx, int n_pairs, int C, int* __restrict__ uniq,
                         int* __restrict__ seg_offsets, int* __restrict__ seg_pairs,
-                        int* __restrict__ pair_to_uniq, int* __restrict__ num_unique, int* __restrict__ status,
-                        const int* __restrict__ list_counts, int per_list) {
-  // With `list_counts` the entries form lists of `per_list` slots of which only the first list_counts[list] are
-  // filled (the ranks' touched-chapter lists of a gradient exchange); the rest is skipped.
-#define MOC_SEG_VALID(i) (list_counts == nullptr || ((i) % per_list) < list_counts[(i) / per_list])
+                        int* __restrict__ pair_to_uniq, int* __restrict__ num_unique, int* __restrict__ status) {
   extern __shared__ int sh[];          // count[C], then start[C], urank[C]
   int* count = sh;
   int* start = sh + C;
@@ -121,7 +117,6 @@ chapter_segments_kernel(const int* __restrict__ comb_idx, int n_pairs, int C, in
   for (int c = threadIdx.x; c < C; c += blockDim.x) count[c] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-    if (!MOC_SEG_VALID(i)) continue;
     const int c = comb_idx[i];
     if (c < 0 || c >= C) atomicMax(status, MOC_DEV_BAD_INDEX);
     else atomicAdd(&count[c], 1);
@@ -162,14 +157,72 @@ chapter_segments_kernel(const int* __restrict__ comb_idx, int n_pairs, int C, in
   const int U = warp_tot[1][31];
   if (threadIdx.x == 0) { num_unique[0] = U; seg_offsets[U] = warp_tot[0][31]; }
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-    const int c = MOC_SEG_VALID(i) ? comb_idx[i] : -1;
+    const int c = comb_idx[i];
     if (c < 0 || c >= C) { pair_to_uniq[i] = -1; continue; }
     int pos = 0;
-    for (int j = 0; j < i; ++j) pos += (MOC_SEG_VALID(j) && comb_idx[j] == c);
+    for (int j = 0; j < i; ++j) pos += (comb_idx[j] == c);
     seg_pairs[start[c] + pos] = i;
     pair_to_uniq[i] = urank[c];
   }
-#undef MOC_SEG_VALID
+}
+
+// Union of the ranks' chapter lists (rank r holds counts[r] distinct ids in ids_all[r, :]).  One small CTA, linear
+// in the number of entries: a bit mask per chapter says which ranks hold it; a chapter's contributions are ordered
+// by rank, so an entry's place inside its chapter is the number of lower ranks holding the same chapter.
+// Shared memory: mask[C] (which ranks), then packed[C] = (first pair slot << 16) | union rank  (entries <= 65535).
+__global__ void __launch_bounds__(256)
+union_segments_kernel(const int* __restrict__ ids_all, const int* __restrict__ counts, int world, int per_rank,
+                      int C, int* __restrict__ uniq, int* __restrict__ seg_offsets, int* __restrict__ seg_pairs,
+                      int* __restrict__ pair_to_uniq, int* __restrict__ num_unique, int* __restrict__ status) {
+  extern __shared__ unsigned int ush[];
+  unsigned int* mask = ush;
+  unsigned int* packed = ush + C;
+  __shared__ int warp_tot[2][8];
+  const int n_pairs = world * per_rank;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) mask[c] = 0u;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int r = i / per_rank;
+    if (i - r * per_rank >= counts[r]) continue;
+    const int c = ids_all[i];
+    if (c < 0 || c >= C) atomicMax(status, MOC_DEV_BAD_INDEX);
+    else atomicOr(&mask[c], 1u << r);
+  }
+  __syncthreads();
+  const int per = (C + blockDim.x - 1) / blockDim.x;
+  const int lo = threadIdx.x * per, hi = min(C, lo + per);
+  int s0 = 0, s1 = 0;
+  for (int c = lo; c < hi; ++c) { s0 += __popc(mask[c]); s1 += (mask[c] != 0u); }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int i0 = s0, i1 = s1;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t0 = __shfl_up_sync(0xffffffffu, i0, o), t1 = __shfl_up_sync(0xffffffffu, i1, o);
+    if (lane >= o) { i0 += t0; i1 += t1; }
+  }
+  if (lane == 31) { warp_tot[0][warp] = i0; warp_tot[1][warp] = i1; }
+  __syncthreads();
+  int b0 = 0, b1 = 0, tot0 = 0, tot1 = 0;
+  for (int w = 0; w < 8; ++w) {
+    if (w < warp) { b0 += warp_tot[0][w]; b1 += warp_tot[1][w]; }
+    tot0 += warp_tot[0][w]; tot1 += warp_tot[1][w];
+  }
+  int e0 = i0 - s0 + b0, e1 = i1 - s1 + b1;
+  for (int c = lo; c < hi; ++c) {
+    packed[c] = (static_cast<unsigned int>(e0) << 16) | static_cast<unsigned int>(e1);
+    if (mask[c] != 0u) { uniq[e1] = c; seg_offsets[e1] = e0; }
+    e0 += __popc(mask[c]); e1 += (mask[c] != 0u);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) { num_unique[0] = tot1; seg_offsets[tot1] = tot0; }
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int r = i / per_rank;
+    const int c = (i - r * per_rank < counts[r]) ? ids_all[i] : -1;
+    if (c < 0 || c >= C) { pair_to_uniq[i] = -1; continue; }
+    const unsigned int pk = packed[c];
+    seg_pairs[(pk >> 16) + __popc(mask[c] & ((1u << r) - 1u))] = i;
+    pair_to_uniq[i] = static_cast<int>(pk & 0xFFFFu);
+  }
 }
 
 // Sum of the ranks' compact gradient rows over the union of their chapter lists: one warp per output row;
@@ -453,7 +506,7 @@ extern "C" int moc_chapter_segments(const int32_t* comb_idx, int32_t n_pairs, in
   const size_t sm = static_cast<size_t>(num_chapters) * 12;
   MOC_CUDA_OK(cudaFuncSetAttribute(chapter_segments_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
   chapter_segments_kernel<<<1, 1024, sm, stream>>>(comb_idx, n_pairs, num_chapters, uniq, seg_offsets, seg_pairs,
-                                                   pair_to_uniq, num_unique, status, nullptr, 1);
+                                                   pair_to_uniq, num_unique, status);
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
 }
@@ -470,15 +523,16 @@ extern "C" int moc_bank_grad_merge(const void* const* rank_rows, int32_t rows_dt
   MOC_REQUIRE(per_rank > 0 && T > 0 && dim > 0, "empty lists");
   MOC_REQUIRE(rows_dtype == MOC_F32 || rows_dtype == MOC_BF16, "bad rows_dtype");
   const int n_pairs = world * per_rank;
-  MOC_REQUIRE(n_pairs <= 65536, "too many list entries");
-  MOC_REQUIRE(num_chapters > 0 && static_cast<size_t>(num_chapters) * 12 <= 200 * 1024, "num_chapters too large");
+  MOC_REQUIRE(n_pairs <= 65535, "too many list entries");
+  MOC_REQUIRE(num_chapters > 0 && num_chapters <= 65535 && static_cast<size_t>(num_chapters) * 8 <= 200 * 1024,
+              "num_chapters too large");
   const long long cap = n_pairs < num_chapters ? n_pairs : num_chapters;     // the union cannot be larger
   MOC_REQUIRE(rows_out_capacity >= cap * T, "rows_out too small for the largest possible union");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  const size_t sm = static_cast<size_t>(num_chapters) * 12;
-  MOC_CUDA_OK(cudaFuncSetAttribute(chapter_segments_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
-  chapter_segments_kernel<<<1, 1024, sm, stream>>>(ids_all, n_pairs, num_chapters, uniq, seg_offsets, seg_pairs,
-                                                   pair_to_uniq, num_unique, status, counts, per_rank);
+  const size_t sm = static_cast<size_t>(num_chapters) * 8;
+  MOC_CUDA_OK(cudaFuncSetAttribute(union_segments_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
+  union_segments_kernel<<<1, 256, sm, stream>>>(ids_all, counts, world, per_rank, num_chapters, uniq, seg_offsets,
+                                                seg_pairs, pair_to_uniq, num_unique, status);
   RankRows src;
   for (int r = 0; r < 16; ++r) src.p[r] = r < world ? rank_rows[r] : nullptr;
   for (int r = 0; r < world; ++r) MOC_REQUIRE(src.p[r] != nullptr, "NULL rank rows");
