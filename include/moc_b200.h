@@ -342,6 +342,27 @@ int moc_sparse_attn_weighted_bwd(const moc_sparse_attn_shape* s, const void* q, 
                                  int32_t accumulate_dq, float* d_k, float* d_v, int64_t dkv_row_stride,
                                  float* d_w_heads, int32_t* status, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Optimizer step of the bank from a compact gradient.  Replaces torch.optim.AdamW over the bank parameter
+ * (training/trainer.py:372-378, param group "memory_bank" :338-347) fed by the dense gradient of torch.gather's
+ * backward: same update for EVERY row (rows of untouched chapters see a zero gradient: moments decay, decoupled
+ * weight decay and the remaining momentum still apply), computed in one pass without a dense gradient tensor.
+ *   param / exp_avg / exp_avg_sq fp32 [bank_rows, dim], updated in place; uniq / num_unique / grad_rows: the
+ *   compact gradient (block u of grad_rows = chapter uniq[u]); grad_scale multiplies the gradient first (1 / world,
+ *   a clipping coefficient); step counts from 1 (bias correction); shadow_bf16 (may be NULL) receives the updated
+ *   parameter as bf16 -- the working copy the TMA-gather projection reads.
+ *   workspace: moc_bank_adamw_workspace_bytes(num_chapters). */
+size_t moc_bank_adamw_workspace_bytes(int32_t num_chapters);
+int moc_bank_adamw_step(float* param, float* exp_avg, float* exp_avg_sq, int64_t bank_rows, int32_t dim,
+                        int32_t tokens_per_chapter, const int32_t* uniq, const int32_t* num_unique,
+                        int32_t max_unique, const float* grad_rows, float grad_scale, float lr, float beta1,
+                        float beta2, float eps, float weight_decay, int64_t step, void* shadow_bf16,
+                        void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+/* out[0] = sum of squares of the first num_unique*T rows of a compact gradient: the bank's share of the global
+ * gradient norm that the reference clips by (training/trainer.py:876-880).  workspace: 592 floats. */
+int moc_rows_sqnorm(const float* rows, const int32_t* num_unique, int32_t tokens_per_chapter, int32_t dim,
+                    float* out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Element-wise helpers used by the host layer (device pointers, n elements). */
 int moc_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream);
 int moc_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream);

@@ -12,11 +12,12 @@ from .memory_block import MemorySubBlock, RMSNorm
 from .memory_bank import ChapteredMemoryBank, StandardMemoryBank
 from .memory_cross_attn import (memory_cross_attn, memory_cross_attn_backward, memory_cross_attn_forward,
                                 memory_cross_attn_preprocess_delta)
+from .optim import SparseBankAdamW
 from .router import ChapterRouter, compute_total_router_loss
 
 __all__ = [
     "ChapterRouter", "compute_total_router_loss", "StandardMemoryBank", "ChapteredMemoryBank",
     "MemoryCrossAttention", "MemoryDecoder", "ProjectedBankCache", "RoutingWindow", "MemorySubBlock", "RMSNorm", "memory_cross_attn", "memory_cross_attn_forward", "memory_layer", "route",
-    "gather_chapters", "cross_attention", "SparseBankGrad", "route_tokens", "token_routed_attention",
+    "gather_chapters", "cross_attention", "SparseBankGrad", "SparseBankAdamW", "route_tokens", "token_routed_attention",
     "token_routed_attention_joint", "memory_cross_attn_backward", "memory_cross_attn_preprocess_delta",
 ]

@@ -86,6 +86,11 @@ _PROTOTYPES = {
                                                P, P, P, P]),
     "moc_sparse_attn_weighted_bwd": (C.c_int, [C.POINTER(SparseAttnShape), P, P, P, C.c_int64, P, P, C.c_float, P,
                                                P, P, C.c_int32, P, P, C.c_int64, P, P, P]),
+    "moc_bank_adamw_workspace_bytes": (C.c_size_t, [C.c_int32]),
+    "moc_bank_adamw_step": (C.c_int, [P, P, P, C.c_int64, C.c_int32, C.c_int32, P, P, C.c_int32, P, C.c_float,
+                                      C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int64, P, P,
+                                      C.c_size_t, P, P]),
+    "moc_rows_sqnorm": (C.c_int, [P, P, C.c_int32, C.c_int32, P, P, C.c_size_t, P]),
     "moc_row_dot": (C.c_int, [P, P, C.c_int32, P, C.c_int64, C.c_int32, P]),
     "moc_col_sum": (C.c_int, [P, P, C.c_int64, C.c_int32, P]),
     "moc_cast_f32_to_bf16": (C.c_int, [P, P, C.c_int64, P]),

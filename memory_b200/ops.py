@@ -343,6 +343,45 @@ def bank_grad_merge(rank_rows, ids_all: torch.Tensor, counts: torch.Tensor, toke
     return out
 
 
+@_instrument("bank_adamw_step", 2)
+def bank_adamw_step(param: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, uniq: torch.Tensor,
+                    num_unique: torch.Tensor, grad_rows: torch.Tensor, tokens_per_chapter: int, *, lr: float,
+                    betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01, step: int = 1,
+                    grad_scale: float = 1.0, shadow: Optional[torch.Tensor] = None,
+                    workspace: Optional[torch.Tensor] = None) -> None:
+    """In-place AdamW update of every bank row from a compact gradient (see ``moc_bank_adamw_step``)."""
+    L.require_cuda(param, exp_avg, exp_avg_sq, uniq, num_unique, grad_rows, shadow)
+    for t in (param, exp_avg, exp_avg_sq, grad_rows):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise TypeError("parameter, moments and gradient rows must be contiguous fp32 tensors")
+    if shadow is not None and (shadow.dtype != torch.bfloat16 or shadow.shape != param.shape or not shadow.is_contiguous()):
+        raise TypeError("shadow must be a contiguous bf16 tensor shaped like the parameter")
+    rows, d = param.shape
+    c = rows // int(tokens_per_chapter)
+    lib = L.lib()
+    need = lib.moc_bank_adamw_workspace_bytes(c)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=param.device)
+    rc = lib.moc_bank_adamw_step(L.ptr(param), L.ptr(exp_avg), L.ptr(exp_avg_sq), rows, d, int(tokens_per_chapter),
+                                 L.ptr(uniq), L.ptr(num_unique), uniq.numel(), L.ptr(grad_rows), float(grad_scale),
+                                 float(lr), float(betas[0]), float(betas[1]), float(eps), float(weight_decay),
+                                 int(step), L.ptr(shadow), L.ptr(workspace), workspace.numel(),
+                                 L.ptr(L.status_word(param.device)), L.stream_ptr(param.device))
+    L.check(rc, "moc_bank_adamw_step")
+
+
+@_instrument("rows_sqnorm", 2)
+def rows_sqnorm(rows: torch.Tensor, num_unique: torch.Tensor, tokens_per_chapter: int) -> torch.Tensor:
+    """Sum of squares of the valid part of a compact gradient ([1] fp32, no host synchronisation)."""
+    L.require_cuda(rows, num_unique)
+    out = torch.empty(1, dtype=torch.float32, device=rows.device)
+    ws = torch.empty(592, dtype=torch.float32, device=rows.device)
+    rc = L.lib().moc_rows_sqnorm(L.ptr(_contig(rows)), L.ptr(num_unique), int(tokens_per_chapter), rows.shape[1],
+                                 L.ptr(out), L.ptr(ws), ws.numel() * 4, L.stream_ptr(rows.device))
+    L.check(rc, "moc_rows_sqnorm")
+    return out
+
+
 @_instrument("scatter_bank_grad", 1)
 def scatter_bank_grad(bank_grad: torch.Tensor, seg: Dict[str, torch.Tensor], tokens_per_chapter: int,
                       dense: torch.Tensor) -> None:

@@ -591,3 +591,42 @@ def test_bank_grad_union_sum_over_rank_lists(dtype, dev):
     # the same buffers can be reused
     out2 = ops.bank_grad_merge([x.to(dev) for x in rows], ids.to(dev), counts.to(dev), T, C, scale=0.5, out=out)
     assert out2["rows"].data_ptr() == out["rows"].data_ptr()
+
+
+def test_bank_adamw_from_compact_gradient_matches_torch_adamw(dev):
+    """SparseBankAdamW against torch.optim.AdamW fed the dense form of the same gradients, three steps with
+    different touched chapters: parameter, both moments, the bf16 working copy, and the gradient norm."""
+    import memory_b200 as M
+    T, d, C = 8, 64, 40
+    g = torch.Generator().manual_seed(21)
+    p0 = torch.randn(C * T, d, generator=g) * 0.02
+    ref_p = torch.nn.Parameter(p0.clone())
+    ref = torch.optim.AdamW([ref_p], lr=3e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
+    p = p0.clone().to(dev)
+    shadow = torch.empty(C * T, d, dtype=torch.bfloat16, device=dev)
+    opt = M.SparseBankAdamW(p, T, lr=3e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01, shadow=shadow)
+    for step in range(3):
+        n = 12
+        touched = torch.sort(torch.randperm(C, generator=g)[:7 + step]).values.int()
+        nu = touched.numel()
+        uniq = torch.zeros(n, dtype=torch.int32)
+        uniq[:nu] = touched
+        rows = torch.randn(n * T, d, generator=g)
+        dense = torch.zeros(C * T, d)
+        for u in range(nu):
+            c = int(touched[u])
+            dense[c * T:(c + 1) * T] = rows[u * T:(u + 1) * T]
+        scale = 0.5
+        ref_p.grad = dense * scale
+        ref.step()
+        sg = M.SparseBankGrad()
+        sg.add(uniq.to(dev), torch.tensor([nu], dtype=torch.int32, device=dev), rows.to(dev), T)
+        sg.scale = scale
+        assert rel_err(opt.grad_sqnorm(sg), (dense * scale).pow(2).sum().reshape(1)) < 1e-5
+        opt.step(sg)
+        _status_ok(dev)
+        st = ref.state[ref_p]
+        assert rel_err(p, ref_p.detach()) < 1e-6
+        assert rel_err(opt.exp_avg, st["exp_avg"]) < 1e-6 and rel_err(opt.exp_avg_sq, st["exp_avg_sq"]) < 1e-6
+        assert torch.equal(shadow, p.bfloat16())
+    assert int(opt.state_dict()["step"]) == 3
