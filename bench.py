@@ -256,7 +256,8 @@ class LayerRunner:
             g0 = torch.zeros(shape, dtype=torch.bfloat16, device=device)
             h0.data.normal_()
             for s in range(self.slots):
-                self.graphs.append(GraphedStep(lambda h, d, s=s: self._fwd_bwd(h, d, s), [h0, g0]))
+                self.graphs.append(GraphedStep(lambda h, d, s=s: self._fwd_bwd(h, d, s), [h0, g0],
+                                               high_priority=world > 1 and not os.environ.get("MOC_BENCH_FLAT_PRIORITY")))
                 self.dense_by_slot.append([self.params[k].grad for k in self.DENSE_KEYS])
                 if os.environ.get("MOC_BENCH_DEBUG"):
                     torch.cuda.synchronize()

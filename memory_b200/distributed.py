@@ -93,18 +93,26 @@ class _PeerPush:
                     base + self.rows_words + self.ids_words + self.world].view(torch.int32)
         return rows, ids.view(self.world, self.n), nums
 
-    def exchange(self, parity: int, uniq: torch.Tensor, num_unique: torch.Tensor, rows: torch.Tensor):
+    def exchange(self, parity: int, uniq: torch.Tensor, num_unique: torch.Tensor, rows: torch.Tensor,
+                 handshake: bool = True):
+        """``handshake=False`` leaves both one-element all-reduces out.  That is safe when (a) the only reader of
+        a receive buffer is work queued on this same stream right after the exchange that filled it (the
+        union-sum), and (b) the caller issues one collective of its own after this call and treats its completion
+        as "every push has landed" (every rank enters it after its pushes, in stream order).  Then a rank can only
+        push into parity p again after all ranks entered the collective of the exchange in between, which they
+        do after their reader of parity p."""
         stream = torch.cuda.current_stream(self.buf.device)
         if self.consumed[parity] is not None:
             stream.wait_event(self.consumed[parity])
-        dist.all_reduce(self.token, group=self.group)
+        if handshake:
+            dist.all_reduce(self.token, group=self.group)
         for k in range(1, self.world):          # the local block is used where it is: no copy to self
             r = (self.rank + k) % self.world
             p_rows, p_ids, p_nums = self._views(self.peers[r], parity)
             p_rows[self.rank].copy_(rows.view(self.m, self.d), non_blocking=True)
             p_ids[self.rank].copy_(uniq.view(torch.int32), non_blocking=True)
             p_nums[self.rank:self.rank + 1].copy_(num_unique.view(torch.int32).reshape(1), non_blocking=True)
-        work = dist.all_reduce(self.token, group=self.group, async_op=True)
+        work = dist.all_reduce(self.token, group=self.group, async_op=True) if handshake else None
         rows_all, ids_all, nums_all = self._views(self.buf, parity)
         # the local list also goes into its own slot (a few KB), so that [world, n] is one table for the merge;
         # the local rows stay where they are
@@ -268,23 +276,33 @@ class GradReducer:
             snap.flat = torch.cat([g.reshape(-1).float() for g in snap.dense_refs])
             if self.world > 1:
                 snap.flat.mul_(1.0 / self.world)
-        if snap.flat is not None and self.world > 1:
-            works.append(dist.all_reduce(snap.flat, group=self.group, async_op=True))
         gathered = []
         merge_inputs = None
         use_peer = (self.exchange == "peer" and self.world > 1 and self.device.type == "cuda"
                     and len(snap.entries) == 1)
+        # With the union-sum as the only reader of the receive buffers, the dense bucket's all-reduce, issued
+        # after the pushes, is the one collective of the exchange (see _PeerPush.exchange).
+        light = use_peer and self.merge and snap.flat is not None
+        if snap.flat is not None and self.world > 1 and not light:
+            works.append(dist.all_reduce(snap.flat, group=self.group, async_op=True))
         for uniq, num_unique, rows, t in snap.entries:
             if self.world == 1:
                 gathered.append((uniq, num_unique, rows, t))
                 continue
             if use_peer and self._peer is None:
                 use_peer = self._open_peer(uniq.numel(), rows.shape, rows.dtype)
+                if not use_peer and light:        # fell back to NCCL: the dense bucket travels on its own after all
+                    light = False
+                    works.append(dist.all_reduce(snap.flat, group=self.group, async_op=True))
             if use_peer:
                 parity = self._parity
                 self._parity = (parity + 1) % self._peer.parities
-                work, triples, (ids_tab, num_tab) = self._peer.exchange(parity, uniq, num_unique, rows)
-                works.append(work)
+                work, triples, (ids_tab, num_tab) = self._peer.exchange(parity, uniq, num_unique, rows,
+                                                                         handshake=not light)
+                if work is not None:
+                    works.append(work)
+                else:
+                    works.append(dist.all_reduce(snap.flat, group=self.group, async_op=True))
                 gathered += [(i, c, r, t) for i, c, r in triples]
                 merge_inputs = ([r for _, _, r in triples], ids_tab, num_tab, t)
                 pending_parity = parity

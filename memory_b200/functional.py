@@ -308,14 +308,18 @@ def cross_attention(h: torch.Tensor, memory: torch.Tensor, wq, wk, wv, wo, num_h
 # --------------------------------------------------------------------------------------------
 # the whole layer as one node with two streams (bf16 path)
 # --------------------------------------------------------------------------------------------
-_side_streams: Dict[int, "torch.cuda.Stream"] = {}
+_side_streams: Dict[tuple, "torch.cuda.Stream"] = {}
 
 
 def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    """Second stream of the layer, with the priority of the stream it runs beside (a step captured on a
+    high-priority stream keeps both of its streams ahead of background work such as a gradient exchange)."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    if idx not in _side_streams:
-        _side_streams[idx] = torch.cuda.Stream(device=device)
-    return _side_streams[idx]
+    prio = torch.cuda.current_stream(device).priority
+    key = (idx, prio)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device, priority=prio)
+    return _side_streams[key]
 
 
 class _MemoryLayerTwoStream(torch.autograd.Function):

@@ -20,7 +20,10 @@ class GraphedStep:
     outputs -- the same tensor objects every time, valid until the next call.
     """
 
-    def __init__(self, fn: Callable, inputs: Sequence[torch.Tensor], warmup: int = 3):
+    def __init__(self, fn: Callable, inputs: Sequence[torch.Tensor], warmup: int = 3, high_priority: bool = False):
+        """``high_priority``: capture on a high-priority stream.  Kernel nodes keep the priority of the stream they
+        were captured on, so a replayed step is scheduled ahead of work on ordinary streams -- a gradient exchange
+        running beside the next step then fills the gaps instead of taking SM slots from it."""
         self.fn = fn
         self.static_inputs = []
         for t in inputs:
@@ -40,7 +43,8 @@ class GraphedStep:
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        capture_stream = torch.cuda.Stream(device, priority=-1) if high_priority else None
+        with torch.cuda.graph(self.graph, stream=capture_stream):
             self.outputs = fn(*self.static_inputs)
 
     def load(self, *inputs: torch.Tensor) -> None:
