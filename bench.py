@@ -205,7 +205,8 @@ def workload_config(cfg, n_gpus):
             "bank_rows": cfg["num_chapters"] * cfg["tokens_per_chapter"], "chapters": cfg["num_chapters"],
             "tokens_per_chapter": cfg["tokens_per_chapter"], "top_k": cfg["top_k"],
             "shared_chapters": cfg["num_shared_chapters"], "routed_scale": cfg["routed_scaling_factor"],
-            "row_norm": "off", "parallelism": f"dp{n_gpus} (batch sharded, bank replicated)",
+            "row_norm": "off", "gather": "fused into the K/V projection (TMA gather list over a bf16 copy of the bank)",
+            "parallelism": f"dp{n_gpus} (batch sharded, bank replicated)",
             "l2_policy": f"inputs larger than L2: {N_INPUT_SETS} rotating hidden-state batches, "
                          "per-step working set > 400 MB against a 126 MB L2",
             "launch": "one CUDA graph replay per step (forward + backward captured once)"}
@@ -217,7 +218,8 @@ def workload_config(cfg, n_gpus):
 class LayerRunner:
     """One memory layer with its parameters; ``step`` = forward + backward (+ gradient reduction)."""
 
-    def __init__(self, cfg, device, world=1, group=None, use_graph=True, exchange="nccl", wire="bf16", merge=True):
+    def __init__(self, cfg, device, world=1, group=None, use_graph=True, exchange="nccl", wire="bf16", merge=True,
+                 fused_gather=True):
         import memory_b200 as M
         from memory_b200.graph import GraphedStep
         self.M = M
@@ -226,6 +228,10 @@ class LayerRunner:
         self.world = world
         p = make_params(cfg, device)
         self.params = {k: v.requires_grad_(True) for k, v in p.items()}
+        # bf16 working copy of the bank: what the fused gather-and-project kernel reads (in training it is refreshed
+        # by the optimizer step's own pass over the bank)
+        from memory_b200 import ops as _ops
+        self.bank_shadow = _ops.cast(self.params["bank"].detach(), torch.bfloat16) if fused_gather else None
         self.g_losses = torch.tensor([0.01, 0.0, 0.001, 0.0], device=device)   # load_balance, auxiliary, z, entropy
         self.reducer = None
         if world > 1:
@@ -280,7 +286,7 @@ class LayerRunner:
             num_heads=cfg["num_heads"], num_kv_heads=cfg["num_kv_heads"],
             tokens_per_chapter=cfg["tokens_per_chapter"], top_k=cfg["top_k"],
             num_shared_chapters=cfg["num_shared_chapters"], routed_scaling_factor=cfg["routed_scaling_factor"],
-            compute_dtype=torch.bfloat16)
+            compute_dtype=torch.bfloat16, bank_shadow=self.bank_shadow)
         # d(loss)/d(out) = d_out, loss = <out, d_out> + 0.01 load_balance + 0.001 z_loss: seed the backward
         # directly instead of materialising the inner product on the device
         torch.autograd.backward([out, losses.vector], [d_out, self.g_losses])
@@ -565,7 +571,7 @@ def run_cuda_arm(args):
 
     cfg = dict(PAPER)
     runner = LayerRunner(cfg, device, world, use_graph=not args.no_graph, exchange=args.exchange, wire=args.wire,
-                         merge=not args.no_merge)
+                         merge=not args.no_merge, fused_gather=not args.two_pass_gather)
     hs_cpu, gs_cpu = make_hidden(cfg, N_INPUT_SETS, 1234 + rank, torch.bfloat16)
     hs = [t.to(device).requires_grad_(True) for t in hs_cpu]
     gs = [t.to(device) for t in gs_cpu]
@@ -752,6 +758,8 @@ def run_cuda_arm(args):
         "reference_eager_same_gpu": gpu_eager, "verify": verify,
         "pct_of_bf16_tc_roofline": 100.0 * roofline["layer"]["frac"],
     }
+    if args.two_pass_gather:
+        line["config"]["gather"] = "two-pass: gathered rows materialised, then the K/V projection"
     if world > 1:
         line["config"]["gradient_exchange"] = (
             "dense bucket: one NCCL all-reduce; bank rows: sparse, " + args.wire + " on the wire, " +
@@ -787,6 +795,9 @@ def main():
     ap.add_argument("--wire", default="bf16", choices=["bf16", "fp32"],
                     help="N > 1: dtype of the bank-gradient rows between ranks (sums are formed in fp32 at the receiver; "
                          "the reference's DDP sends fp32)")
+    ap.add_argument("--two-pass-gather", action="store_true",
+                    help="materialise the gathered rows before the K/V projection instead of reading the chapters "
+                         "through the projection kernel's TMA gather list")
     ap.add_argument("--no-exchange-check", action="store_true", help="N > 1: skip the numerical check of the exchange")
     ap.add_argument("--no-merge", action="store_true", help="N > 1: leave the ranks' rows unsummed (exchange only)")
     ap.add_argument("--kernels", action="store_true", help="time the hot kernels alone (small footprint) and exit")

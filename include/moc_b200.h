@@ -164,6 +164,30 @@ int moc_gather_rows_bwd(const void* d_mem, int32_t d_mem_dtype, const void* bank
                         const int32_t* seg_pairs, const int32_t* num_unique, float* d_comb_w,
                         float* bank_grad, void* bank_grad_bf16, int32_t* status, void* stream);
 
+/* ---- Fused gather-and-project path (no gathered rows are materialised) ----------------------------------------
+ * Forward: moc_gemm with the TMA gather list over a bf16 copy of the bank and row_scale[pair*T + r] = u~[pair]
+ * (times 1/rms of the bank row when the rows are RMS-normalised, model.py:423-425) -- get_chapters_batched, the
+ * normalisation, the weight multiply and k_proj / v_proj (memory_bank.py:263-293, model.py:393-432, 689-692,
+ * memory_attention.py:241-243) in one kernel.  Backward: moc_attn_bwd_scaled writes dK / dV already multiplied by
+ * the same row scale; g' = dKV' x [Wk; Wv] is then s_r * dM~_r, from which moc_gather_rows_bwd_prescaled derives the
+ * chapter-weight gradient and the compact bank gradient, and moc_gemm_gather_b forms the Wk / Wv gradient reading the
+ * bank rows through the same list.
+ * moc_row_inv_rms: out[row] = 1 / sqrt(mean(row^2) + eps) for every bank row (refresh after an update).
+ * moc_chapter_row_scale: scale [n_pairs*T]; inv_rms may be NULL (no normalisation). */
+int moc_row_inv_rms(const void* bank, int32_t bank_dtype, int64_t rows, int32_t dim, float eps, float* out,
+                    void* stream);
+int moc_chapter_row_scale(const int32_t* comb_idx, const float* comb_w, const float* inv_rms, int64_t bank_rows,
+                          int32_t n_pairs, int32_t tokens_per_chapter, float* scale, int32_t* status, void* stream);
+/* g [n_pairs*T, dim] = s_r * dM~_r (fp32 or bf16); bank: the rows the forward read (its bf16 copy, or fp32);
+ * inv_rms [bank_rows] or NULL.  d_comb_w [n_pairs] = (1/u~) sum_r <g_r, m_r>; bank_grad compact fp32 as in
+ * moc_gather_rows_bwd (bank_grad_bf16 optional second copy). */
+int moc_gather_rows_bwd_prescaled(const void* g, int32_t g_dtype, const void* bank, int32_t bank_dtype,
+                                  int64_t bank_rows, int32_t dim, int32_t tokens_per_chapter,
+                                  const int32_t* comb_idx, const float* comb_w, int32_t n_pairs,
+                                  const float* inv_rms, const int32_t* uniq, const int32_t* seg_offsets,
+                                  const int32_t* seg_pairs, const int32_t* num_unique, float* d_comb_w,
+                                  float* bank_grad, void* bank_grad_bf16, int32_t* status, void* stream);
+
 /* Consumer of a data-parallel gradient exchange: the ranks' compact bank-gradient rows summed over the UNION of
  * their chapter lists (the sum DDP's dense all-reduce of the bank gradient produces, training/trainer.py:873, on
  * the touched chapters only).  rank_rows: host array of `world` device pointers, rank r's rows [per_rank*T, dim]
@@ -217,6 +241,14 @@ typedef struct {
 int moc_gemm(const moc_gemm_desc* g, const void* a, const void* b, void* c, const float* row_scale,
              const int32_t* a_row_blocks, int32_t* status, void* stream);
 
+/* moc_gemm with a gather list over the K rows of an MN-major B ([K, N] row-major, g->b_kmajor = 0): logical K row
+ * j*b_block_rows + r is stored row b_row_blocks[j]*b_block_rows + r of a matrix with b_stored_rows rows.  This is
+ * how the Wk / Wv weight gradient dKV'^T x (selected bank rows) reads the bank without a gathered copy.  bf16 only;
+ * b_block_rows a multiple of 8 that divides 64 or is a multiple of 64. */
+int moc_gemm_gather_b(const moc_gemm_desc* g, const void* a, const void* b, void* c, const float* row_scale,
+                      const int32_t* b_row_blocks, int32_t b_block_rows, int64_t b_stored_rows, int32_t* status,
+                      void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Normalisation in front of the memory cross-attention.  Replaces `memory_layernorm` of
  * MemoryTransformerBlock (memory_block.py:475, 551, 578): RMSNorm (memory_block.py:18-28,
@@ -263,6 +295,12 @@ int moc_attn_bwd(const moc_attn_shape* s, const void* q, const void* kv, const v
 int moc_attn_bwd_parts(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
                        const void* d_o, void* d_q, void* d_kv, float* delta, int32_t parts, int32_t* status,
                        void* stream);
+
+/* moc_attn_bwd (bf16 only) whose dK / dV rows leave multiplied by kv_row_scale [B*n_sel]: the backward half of the
+ * fused gather-and-project path described at moc_row_inv_rms.  No counterpart in the reference. */
+int moc_attn_bwd_scaled(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
+                        const void* d_o, void* d_q, void* d_kv, float* delta, const float* kv_row_scale,
+                        int32_t* status, void* stream);
 
 /* moc_attn_bwd without caller-provided scratch and without any allocation.  It has no counterpart in the
  * reference.  It exists for callers that are not allowed to allocate device memory when they run the

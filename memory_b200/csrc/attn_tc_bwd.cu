@@ -374,6 +374,7 @@ constexpr int kDkvSmem = 2 * kKBytes + kStages * kStageB + kPtBytes + kStages * 
 constexpr uint32_t kColST = 0, kColDPT = 64, kColDV = 128, kColDK = 192;   // dS^T aliases dP^T
 
 struct DkvParams {
+  const float* row_scale;  // optional per-key-row factor applied to dK and dV when they are written, or nullptr
   __nv_bfloat16* d_kv;
   int dkv_tma;             // d_kv written through staging blocks and TMA stores (n_sel % 32 == 0)
   const uint4* statb;
@@ -606,7 +607,10 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           uint32_t r[32];
           tmem_ld32(tmem + lane_sel + (which ? kColDV : kColDK) + half * 32, r);
           tmem_wait_ld();
-          const float f = which ? 1.f : p.scale;
+          const int krow = key0 + quarter * 32 + lane;
+          const float rsf = (p.row_scale != nullptr && krow < p.n_sel)
+                                ? p.row_scale[static_cast<long long>(b) * p.n_sel + krow] : 1.f;
+          const float f = (which ? 1.f : p.scale) * rsf;
           const uint32_t row_addr = smem_u32(ring) + (quarter * 2 + which) * 4096 + lane * 128;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -638,7 +642,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         uint32_t r[32];
         tmem_ld32(tmem + lane_sel + (which ? kColDV : kColDK) + half * 32, r);
         tmem_wait_ld();
-        const float f = which ? 1.f : p.scale;
+        const float rsf = (p.row_scale != nullptr && key < p.n_sel)
+                              ? p.row_scale[static_cast<long long>(b) * p.n_sel + key] : 1.f;
+        const float f = (which ? 1.f : p.scale) * rsf;
         if (key < p.n_sel) {
           __nv_bfloat16* d2 = dst + (which ? p.HK * kD : 0);
 #pragma unroll
@@ -664,7 +670,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
 int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
                        const void* d_o, void* d_q, void* d_kv, float* scratch, int32_t* status,
-                       cudaStream_t stream, int parts) {
+                       cudaStream_t stream, int parts, const float* kv_row_scale) {
   MOC_REQUIRE(s->head_dim == kD, "bf16 attention needs head_dim 64");
   MOC_REQUIRE(s->seq % kQB == 0, "bf16 attention backward needs seq % 64 == 0");
   MOC_REQUIRE(s->num_heads % s->num_kv_heads == 0, "num_heads must be a multiple of num_kv_heads");
@@ -704,7 +710,7 @@ int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, c
     CUtensorMap tdkv = tkv;      // placeholder when the TMA-store epilogue is not used
     p.dkv_tma = (s->n_sel % 32 == 0 && (reinterpret_cast<uintptr_t>(d_kv) & 15) == 0) ? 1 : 0;
     if (p.dkv_tma && (rc = make_tmap_bf16_2d(&tdkv, d_kv, kvrows, kvcols, kvcols, 32, kD)) != MOC_OK) return rc;
-    p.d_kv = static_cast<__nv_bfloat16*>(d_kv); p.statb = statb;
+    p.d_kv = static_cast<__nv_bfloat16*>(d_kv); p.statb = statb; p.row_scale = kv_row_scale;
     p.L = L; p.n_sel = s->n_sel; p.H = H; p.HK = HK;
     p.scale = s->scale; p.scale_log2 = s->scale * kLog2e; p.status = status;
     dim3 grid(ceil_div(s->n_sel, kKeysB), HK, B);

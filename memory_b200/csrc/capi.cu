@@ -4,7 +4,8 @@
 
 namespace moc {
 int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c, const float* row_scale,
-                   const int32_t* a_row_blocks, int32_t* status, cudaStream_t stream);
+                   const int32_t* a_row_blocks, int32_t* status, cudaStream_t stream,
+                   const int32_t* b_row_blocks = nullptr, int32_t b_block_rows = 0, int64_t b_stored_rows = 0);
 int launch_sgemm(const moc_gemm_desc* g, const float* a, const float* b, float* c, const float* row_scale,
                  cudaStream_t stream);
 int launch_delta(int dtype, const void* o, const void* d_o, float* delta, int B, int L, int H, int D,
@@ -17,7 +18,7 @@ int launch_attn_tc_fwd(const moc_attn_shape* s, const void* q, const void* kv, v
                        int32_t* status, cudaStream_t stream);
 int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
                        const void* d_o, void* d_q, void* d_kv, float* scratch, int32_t* status,
-                       cudaStream_t stream, int parts);
+                       cudaStream_t stream, int parts, const float* kv_row_scale = nullptr);
 }  // namespace moc
 
 using namespace moc;
@@ -97,4 +98,26 @@ extern "C" int moc_row_dot(const void* a, const void* b, int32_t dtype, float* o
   MOC_REQUIRE(rows <= 0x7fffffffLL, "too many rows");
   // one (batch, head) with `rows` positions: delta[l] = <a[l, :], b[l, :]>
   return launch_delta(dtype, a, b, out, 1, static_cast<int>(rows), 1, dim, static_cast<cudaStream_t>(stream_));
+}
+
+
+extern "C" int moc_gemm_gather_b(const moc_gemm_desc* g, const void* a, const void* b, void* c,
+                                 const float* row_scale, const int32_t* b_row_blocks, int32_t b_block_rows,
+                                 int64_t b_stored_rows, int32_t* status, void* stream_) {
+  MOC_REQUIRE(g && a && b && c && status && b_row_blocks, "NULL projection argument");
+  MOC_REQUIRE(g->m > 0 && g->n > 0 && g->k > 0, "empty projection");
+  MOC_REQUIRE(g->dtype == MOC_BF16, "the gathered-B projection is a bf16 tensor-core kernel");
+  return launch_gemm_tc(g, a, b, c, row_scale, nullptr, status, static_cast<cudaStream_t>(stream_), b_row_blocks,
+                        b_block_rows, b_stored_rows);
+}
+
+extern "C" int moc_attn_bwd_scaled(const moc_attn_shape* s, const void* q, const void* kv, const void* o,
+                                   const float* lse, const void* d_o, void* d_q, void* d_kv, float* delta,
+                                   const float* kv_row_scale, int32_t* status, void* stream_) {
+  int rc = check_attn(s);
+  if (rc != MOC_OK) return rc;
+  MOC_REQUIRE(q && kv && o && lse && d_o && d_q && d_kv && delta && status && kv_row_scale, "NULL attention buffer");
+  MOC_REQUIRE(s->dtype == MOC_BF16, "the row-scaled backward exists for the bf16 kernels only");
+  return launch_attn_tc_bwd(s, q, kv, o, lse, d_o, d_q, d_kv, delta, status, static_cast<cudaStream_t>(stream_), 7,
+                            kv_row_scale);
 }

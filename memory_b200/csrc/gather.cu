@@ -391,6 +391,116 @@ __global__ void bank_grad_kernel(const TG* __restrict__ d_mem, const TB* __restr
   }
 }
 
+// ---- fused gather-and-project path: no gathered rows are materialised in the forward pass --------------------
+// K = s_r * (bank_row W^T) with s_r = u~[pair] (* 1/rms of the bank row): the forward reads the bank through the TMA
+// gather list and applies s_r in the projection epilogue.  Its backward works from g'_r = s_r * dM~_r (the dK/dV
+// kernel scales its output rows by s_r before the memory-row projection):
+//   d u~[pair] = (1 / u~[pair]) * sum_r <g'_r, m_r>            (both without and with the rms norm)
+//   d m_r      = G_r - m_r * inv_rms_r^2 * <G_r, m_r> / dim    with G_r = sum over the pairs of the chapter of g'_r
+//                (second term only with the rms norm)
+
+// inv_rms[row] = 1 / sqrt(mean(row^2) + eps) for every bank row; one warp per row
+template <typename TB>
+__global__ void row_inv_rms_kernel(const TB* __restrict__ bank, long long rows, int dim, float eps,
+                                   float* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  if (r >= rows) return;
+  const TB* row = bank + r * dim;
+  float acc = 0.f;
+  for (int c = lane; c < dim; c += 32) { const float x = ld(row, c); acc = fmaf(x, x, acc); }
+  acc = warp_sum(acc);
+  if (lane == 0) out[r] = rsqrtf(acc / static_cast<float>(dim) + eps);
+}
+// scale[pair * T + r] = comb_w[pair] * (inv_rms ? inv_rms[comb_idx[pair] * T + r] : 1)
+__global__ void row_scale_kernel(const int* __restrict__ comb_idx, const float* __restrict__ comb_w,
+                                 const float* __restrict__ inv_rms, long long bank_rows, int n_pairs, int T,
+                                 float* __restrict__ scale, int* __restrict__ status) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= static_cast<long long>(n_pairs) * T) return;
+  const int pair = static_cast<int>(i / T), r = static_cast<int>(i - static_cast<long long>(pair) * T);
+  const long long c = comb_idx[pair];
+  float v = comb_w ? comb_w[pair] : 1.f;
+  if (c < 0 || (c + 1) * T > bank_rows) { atomicMax(status, MOC_DEV_BAD_INDEX); v = 0.f; }
+  else if (inv_rms) v *= inv_rms[c * T + r];
+  scale[i] = v;
+}
+template <typename TG, typename TB>
+__global__ void dcombw_prescaled_kernel(const TG* __restrict__ g, const TB* __restrict__ bank, long long bank_rows,
+                                        int dim, int T, const int* __restrict__ comb_idx,
+                                        const float* __restrict__ comb_w, float* __restrict__ d_comb_w) {
+  __shared__ float red[32];
+  const long long pair = blockIdx.x;
+  const long long chapter = comb_idx[pair];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float acc = 0.f;
+  if (chapter >= 0 && (chapter + 1) * T <= bank_rows) {
+    if ((dim & 7) == 0) {
+      const int per_row = dim >> 3;
+      for (int i = threadIdx.x; i < T * per_row; i += blockDim.x) {
+        const int r = i / per_row, c = (i - r * per_row) << 3;
+        float gv[8], x[8];
+        ld8(g + (pair * T + r) * dim + c, gv);
+        ld8(bank + (chapter * T + r) * dim + c, x);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = fmaf(gv[j], x[j], acc);
+      }
+    } else {
+      for (int r = warp; r < T; r += nw)
+        for (int c = lane; c < dim; c += 32)
+          acc += ld(g + (pair * T + r) * dim, c) * ld(bank + (chapter * T + r) * dim, c);
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) red[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) {
+      const float u = comb_w ? comb_w[pair] : 1.f;
+      d_comb_w[pair] = (fabsf(u) > 1e-30f) ? t / u : 0.f;
+    }
+  }
+}
+template <typename TG, typename TB>
+__global__ void bank_grad_prescaled_kernel(const TG* __restrict__ g, const TB* __restrict__ bank, int dim, int T,
+                                           const float* __restrict__ inv_rms, const int* __restrict__ uniq,
+                                           const int* __restrict__ seg_offsets, const int* __restrict__ seg_pairs,
+                                           const int* __restrict__ num_unique, long long max_rows,
+                                           float* __restrict__ bank_grad, __nv_bfloat16* __restrict__ bank_grad_wire) {
+  const int lane = threadIdx.x & 31;
+  const long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  if (r >= max_rows) return;
+  const int u = static_cast<int>(r / T);
+  if (u >= num_unique[0]) return;
+  const int within = static_cast<int>(r - static_cast<long long>(u) * T);
+  const int p0 = seg_offsets[u], p1 = seg_offsets[u + 1];
+  float* dst = bank_grad + r * dim;
+  __nv_bfloat16* wire = bank_grad_wire ? bank_grad_wire + r * dim : nullptr;
+  const long long brow = static_cast<long long>(uniq[u]) * T + within;
+  const TB* row = bank + brow * dim;
+  float sgm = 0.f;
+  for (int c = lane; c < dim; c += 32) {
+    float acc = 0.f;
+    for (int q = p0; q < p1; ++q) acc += ld(g + (static_cast<long long>(seg_pairs[q]) * T + within) * dim, c);
+    dst[c] = acc;
+    if (inv_rms) sgm = fmaf(acc, ld(row, c), sgm);
+  }
+  if (inv_rms == nullptr) {
+    if (wire) { __syncwarp(); for (int c = lane; c < dim; c += 32) wire[c] = __float2bfloat16(dst[c]); }
+    return;
+  }
+  const float ir = inv_rms[brow];
+  const float k = warp_sum(sgm) * ir * ir / static_cast<float>(dim);
+  __syncwarp();
+  for (int c = lane; c < dim; c += 32) {
+    const float v = dst[c] - ld(row, c) * k;
+    dst[c] = v;
+    if (wire) wire[c] = __float2bfloat16(v);
+  }
+}
+
 __global__ void scatter_bank_grad_kernel(const float* __restrict__ bank_grad, const int* __restrict__ uniq,
                                          const int* __restrict__ num_unique, long long max_rows, int T, int dim,
                                          float* __restrict__ dense, long long bank_rows) {
@@ -652,6 +762,65 @@ extern "C" int moc_pack_weights(int32_t n, const void* const* src, int32_t src_d
   if (src_dtype == MOC_F32) pack_weights_kernel<float><<<grid, block, 0, stream>>>(jobs);
   else if (src_dtype == MOC_BF16) pack_weights_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(jobs);
   else MOC_REQUIRE(false, "bad dtype");
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+
+extern "C" int moc_row_inv_rms(const void* bank, int32_t bank_dtype, int64_t rows, int32_t dim, float eps,
+                               float* out, void* stream_) {
+  MOC_REQUIRE(bank && out && rows > 0 && dim > 0, "bad arguments");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int blocks = static_cast<int>((rows * 32 + 255) / 256);
+  if (bank_dtype == MOC_F32)
+    row_inv_rms_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(bank), rows, dim, eps, out);
+  else if (bank_dtype == MOC_BF16)
+    row_inv_rms_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(bank), rows, dim,
+                                                                  eps, out);
+  else MOC_REQUIRE(false, "bad dtype");
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+extern "C" int moc_chapter_row_scale(const int32_t* comb_idx, const float* comb_w, const float* inv_rms,
+                                     int64_t bank_rows, int32_t n_pairs, int32_t T, float* scale, int32_t* status,
+                                     void* stream_) {
+  MOC_REQUIRE(comb_idx && scale && status && n_pairs > 0 && T > 0, "bad arguments");
+  const long long total = static_cast<long long>(n_pairs) * T;
+  row_scale_kernel<<<static_cast<int>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      comb_idx, comb_w, inv_rms, bank_rows, n_pairs, T, scale, status);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
+extern "C" int moc_gather_rows_bwd_prescaled(const void* g, int32_t g_dtype, const void* bank, int32_t bank_dtype,
+                                             int64_t bank_rows, int32_t dim, int32_t T, const int32_t* comb_idx,
+                                             const float* comb_w, int32_t n_pairs, const float* inv_rms,
+                                             const int32_t* uniq, const int32_t* seg_offsets,
+                                             const int32_t* seg_pairs, const int32_t* num_unique, float* d_comb_w,
+                                             float* bank_grad, void* bank_grad_bf16, int32_t* status, void* stream_) {
+  (void)status;
+  MOC_REQUIRE(g && bank && comb_idx && uniq && seg_offsets && seg_pairs && num_unique, "NULL buffer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long max_rows = static_cast<long long>(n_pairs) * T;
+  const int blocks = static_cast<int>((max_rows * 32 + 255) / 256);
+#define MOC_GPRE(TG, TB)                                                                                          \
+  do {                                                                                                            \
+    if (d_comb_w != nullptr)                                                                                      \
+      dcombw_prescaled_kernel<TG, TB><<<n_pairs, 256, 0, stream>>>(static_cast<const TG*>(g),                     \
+                                                                   static_cast<const TB*>(bank), bank_rows, dim,  \
+                                                                   T, comb_idx, comb_w, d_comb_w);                \
+    if (bank_grad != nullptr)                                                                                     \
+      bank_grad_prescaled_kernel<TG, TB><<<blocks, 256, 0, stream>>>(                                             \
+          static_cast<const TG*>(g), static_cast<const TB*>(bank), dim, T, inv_rms, uniq, seg_offsets, seg_pairs, \
+          num_unique, max_rows, bank_grad, static_cast<__nv_bfloat16*>(bank_grad_bf16));                          \
+  } while (0)
+  if (g_dtype == MOC_F32 && bank_dtype == MOC_F32) MOC_GPRE(float, float);
+  else if (g_dtype == MOC_F32 && bank_dtype == MOC_BF16) MOC_GPRE(float, __nv_bfloat16);
+  else if (g_dtype == MOC_BF16 && bank_dtype == MOC_F32) MOC_GPRE(__nv_bfloat16, float);
+  else if (g_dtype == MOC_BF16 && bank_dtype == MOC_BF16) MOC_GPRE(__nv_bfloat16, __nv_bfloat16);
+  else MOC_REQUIRE(false, "bad dtype");
+#undef MOC_GPRE
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
 }

@@ -51,6 +51,11 @@ struct GemmTcParams {
   int a_box_rows;          // rows per A box when A is K-major
   int a_num_blocks;        // entries in the gather list
   long long a_stored_rows;
+  const int* b_row_blocks; // gather list over the K rows of an MN-major B ([K, N] row-major), or nullptr
+  int b_block_rows;        // rows per listed block (a chapter)
+  int b_box_rows;          // rows per TMA box of the gathered B: min(b_block_rows, 64)
+  int b_num_blocks;
+  long long b_stored_rows;
   int k_tiles_total;
   int k_tiles_per_split;
   int splits;
@@ -151,10 +156,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
             for (int j = 0; j < BN / 128; ++j)
               tma_load_2d(b_s + j * 16384, &tmap_b, &full_bar[s], k0, n0 + j * 128);
-          } else {
+          } else if (p.b_row_blocks == nullptr) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
               tma_load_2d(b_s + j * 8192, &tmap_b, &full_bar[s], n0 + j * 64, k0);
+          } else {
+            // the K rows of this stage are rows of listed blocks (chapters of the bank): one box per run of rows
+            // that is contiguous in the stored matrix
+            const int nsub = BK / p.b_box_rows;
+            for (int i = 0; i < nsub; ++i) {
+              const long long kg = static_cast<long long>(k0) + i * p.b_box_rows;
+              const long long blk = kg / p.b_block_rows;
+              long long row = p.b_stored_rows;      // fully out of range: the copy zero-fills
+              if (blk < p.b_num_blocks) {
+                const long long id = p.b_row_blocks[blk];
+                if (id < 0 || (id + 1) * p.b_block_rows > p.b_stored_rows) atomicMax(p.status, MOC_DEV_BAD_INDEX);
+                else row = id * p.b_block_rows + (kg - blk * p.b_block_rows);
+              }
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(b_s + j * 8192 + i * p.b_box_rows * 128, &tmap_b, &full_bar[s], n0 + j * 64,
+                            static_cast<int>(row));
+            }
           }
         }
       }
@@ -393,7 +416,8 @@ int sm_count() {
 }  // namespace
 
 int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c, const float* row_scale,
-                   const int32_t* a_row_blocks, int32_t* status, cudaStream_t stream) {
+                   const int32_t* a_row_blocks, int32_t* status, cudaStream_t stream,
+                   const int32_t* b_row_blocks, int32_t b_block_rows, int64_t b_stored_rows) {
   MOC_REQUIRE(g->k % 8 == 0, "bf16 projection needs K % 8 == 0");
   MOC_REQUIRE(g->lda % 8 == 0 && g->ldb % 8 == 0, "bf16 projection needs 16-byte aligned operand rows");
   MOC_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(b) & 15) == 0,
@@ -413,6 +437,16 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
     a_num_blocks = g->m / a_box_rows;
     a_stored_rows = g->a_stored_rows;
     MOC_REQUIRE(a_stored_rows > 0, "a_stored_rows missing");
+  }
+  int b_box_rows = 64, b_num_blocks = 0;
+  if (b_row_blocks != nullptr) {
+    MOC_REQUIRE(!g->b_kmajor, "the B gather list needs an MN-major B ([K, N] row-major)");
+    MOC_REQUIRE(b_block_rows >= 8 && (b_block_rows % 8) == 0 && ((64 % b_block_rows) == 0 || (b_block_rows % 64) == 0),
+                "b_block_rows must be a multiple of 8 that divides 64 or is a multiple of 64");
+    MOC_REQUIRE(g->k % b_block_rows == 0, "K must be a multiple of b_block_rows");
+    MOC_REQUIRE(b_stored_rows > 0, "b_stored_rows missing");
+    b_box_rows = b_block_rows < 64 ? b_block_rows : 64;
+    b_num_blocks = g->k / b_block_rows;
   }
 
   // Tile width.  The kernel is fed from L2 (~8.4 TB/s measured over all SMs), so a tile's time goes with the
@@ -447,6 +481,9 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
   if (g->b_kmajor) {
     rc = make_tmap_bf16_2d(&tmap_b, b, static_cast<uint64_t>(g->n), static_cast<uint64_t>(g->k),
                            static_cast<uint64_t>(g->ldb), 128, 64);
+  } else if (b_row_blocks != nullptr) {
+    rc = make_tmap_bf16_2d(&tmap_b, b, static_cast<uint64_t>(b_stored_rows), static_cast<uint64_t>(g->n),
+                           static_cast<uint64_t>(g->ldb), static_cast<uint32_t>(b_box_rows), 64);
   } else {
     rc = make_tmap_bf16_2d(&tmap_b, b, static_cast<uint64_t>(g->k), static_cast<uint64_t>(g->n),
                            static_cast<uint64_t>(g->ldb), 64, 64);
@@ -471,6 +508,8 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
   p.residual = g->residual; p.ldr = g->ldr;
   p.a_row_blocks = a_row_blocks; p.a_box_rows = a_box_rows; p.a_num_blocks = a_num_blocks;
   p.a_stored_rows = a_stored_rows;
+  p.b_row_blocks = b_row_blocks; p.b_block_rows = b_block_rows; p.b_box_rows = b_box_rows;
+  p.b_num_blocks = b_num_blocks; p.b_stored_rows = b_stored_rows;
   p.k_tiles_total = ceil_div(g->k, BK);
   p.k_tiles_per_split = ceil_div(p.k_tiles_total, split);
   p.splits = ceil_div(p.k_tiles_total, p.k_tiles_per_split);   // no empty splits

@@ -338,7 +338,8 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, h_router, h_attn, bank, router_w, router_b, wq, wk, wv, wo, norm_w, norm_b, cfg, sink):
+    def forward(ctx, h_router, h_attn, bank, router_w, router_b, wq, wk, wv, wo, norm_w, norm_b, cfg, sink,
+                fused=None):
         (num_heads, num_kv_heads, t, top_k, num_shared, routed_scale, row_norm, row_eps, with_losses,
          pre_norm, pre_eps, add_residual) = cfg
         cd = torch.bfloat16
@@ -381,10 +382,23 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
         k_sel = r["idx"].shape[1]
         # the reference only normalises when both a shared and a routed slice exist (model.py:413-418)
         norm = row_norm if (num_shared > 0 and k_sel > 0) else None
-        memory, stats_m = ops.gather_rows_fwd(bank, t, r["comb_idx"], r["comb_w"], norm, row_eps, cd)
-        n_sel = memory.shape[-2]
-        m2 = memory.reshape(-1, d)
-        kv = ops.gemm(m2, wkv_c, tag="kv_proj").view(b, n_sel, -1)
+        if fused is not None and (norm not in (None, "rms") or (norm == "rms" and fused.get("inv_rms") is None)):
+            fused = None                      # affine-free LayerNorm rows are not a row scale: two-pass route
+        row_scale = None
+        if fused is not None:
+            # Gather, normalisation, weight multiply and the K/V projection in one kernel: chapters are read from
+            # the bf16 copy of the bank through the TMA gather list, u~ (and 1/rms) is the epilogue row scale.
+            n_sel = r["comb_idx"].shape[1] * t
+            row_scale = ops.chapter_row_scale(r["comb_idx"], r["comb_w"], fused["inv_rms"] if norm == "rms" else None,
+                                              bank.shape[0], t)
+            kv = ops.gemm(fused["shadow"], wkv_c, a_row_blocks=r["comb_idx"].reshape(-1), a_block_rows=t,
+                          m=b * n_sel, row_scale=row_scale, scale_block_rows=1, tag="kv_proj").view(b, n_sel, -1)
+            m2 = stats_m = None
+        else:
+            memory, stats_m = ops.gather_rows_fwd(bank, t, r["comb_idx"], r["comb_w"], norm, row_eps, cd)
+            n_sel = memory.shape[-2]
+            m2 = memory.reshape(-1, d)
+            kv = ops.gemm(m2, wkv_c, tag="kv_proj").view(b, n_sel, -1)
         scale = (d // num_heads) ** -0.5
         o, lse = ops.attn_fwd(q.view(b, l, -1), kv, num_heads, num_kv_heads, scale)
         res = (x2 if x2.dtype == torch.float32 else x2.float()) if add_residual else None
@@ -394,6 +408,7 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
 
         ctx.cfg = cfg
         ctx.norm_row = norm
+        ctx.fused = None if fused is None else dict(fused, row_scale=row_scale)
         ctx.scale = scale
         # outputs of this node (weights, combined weights, losses) are saved through save_for_backward below:
         # kept as attributes they would tie the node to its own outputs in a reference cycle
@@ -440,8 +455,9 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
             d_wo = ops.gemm(g2, o.view(b * l, -1), a_kmajor=False, b_kmajor=False, out_dtype=f32,
                             split_k=splits(b * l, d, d), tag="d_wo")
         d_o = ops.gemm(g2, wo_t, tag="d_attn_out")
+        fused = ctx.fused
         d_q, d_kv = ops.attn_bwd(q.view(b, l, -1), kv, o, lse, d_o.view(b, l, -1), num_heads, num_kv_heads,
-                                 ctx.scale)
+                                 ctx.scale, kv_row_scale=None if fused is None else fused["row_scale"])
         d_q2 = d_q.view(b * l, -1)
         d_kv2 = d_kv.view(-1, d_kv.shape[-1])
 
@@ -462,14 +478,26 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
             elif add_residual:
                 d_h = d_h.float() + g_res.float()
             d_h = d_h.view(b, l, d).to(ha_dtype)
-            d_wkv = ops.gemm(d_kv2, m2, a_kmajor=False, b_kmajor=False, out_dtype=f32,
-                             split_k=splits(d_kv2.shape[0], wkv_c.shape[0], d), tag="d_wkv")
+            if fused is None:
+                d_wkv = ops.gemm(d_kv2, m2, a_kmajor=False, b_kmajor=False, out_dtype=f32,
+                                 split_k=splits(d_kv2.shape[0], wkv_c.shape[0], d), tag="d_wkv")
+            else:
+                # dKV' already carries the row scale, so the weight gradient reads the raw bank rows in place
+                d_wkv = ops.gemm(d_kv2, fused["shadow"], a_kmajor=False, b_kmajor=False, out_dtype=f32,
+                                 split_k=splits(d_kv2.shape[0], wkv_c.shape[0], d), tag="d_wkv",
+                                 b_row_blocks=r["comb_idx"].reshape(-1), b_block_rows=t, k=d_kv2.shape[0])
 
         d_mem = ops.gemm(d_kv2, wkv_t, tag="d_mem")
         want_bank = need[2]
         wire = [] if (ctx.sink is not None and ctx.sink.wire_dtype == torch.bfloat16) else None
-        d_cw, rows = ops.gather_rows_bwd(d_mem, bank, t, r["comb_idx"], r["comb_w"], ctx.norm_row, row_eps, stats_m,
-                                         seg, want_dw=True, want_bank=want_bank, wire_copy=wire)
+        if fused is None:
+            d_cw, rows = ops.gather_rows_bwd(d_mem, bank, t, r["comb_idx"], r["comb_w"], ctx.norm_row, row_eps,
+                                             stats_m, seg, want_dw=True, want_bank=want_bank, wire_copy=wire)
+        else:
+            d_cw, rows = ops.gather_rows_bwd_prescaled(
+                d_mem, fused["shadow"], t, r["comb_idx"], r["comb_w"],
+                fused["inv_rms"] if ctx.norm_row == "rms" else None, seg, want_dw=True, want_bank=want_bank,
+                wire_copy=wire)
         d_bank = None
         if want_bank:
             if ctx.sink is not None:
@@ -501,7 +529,7 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
         else:
             d_hr, d_ha = rb["d_h"], d_h
         return (d_hr, d_ha, d_bank, d_rw, d_rb, d_wq.to(wdt[0]), d_wkv[:dkv_dim].to(wdt[1]),
-                d_wkv[dkv_dim:].to(wdt[2]), d_wo.to(wdt[3]), d_nw, d_nb, None, None)
+                d_wkv[dkv_dim:].to(wdt[2]), d_wo.to(wdt[3]), d_nw, d_nb, None, None, None)
 
 
 # --------------------------------------------------------------------------------------------
@@ -515,7 +543,8 @@ def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tenso
                  compute_dtype: Optional[torch.dtype] = None, pre_norm: Optional[str] = None,
                  pre_norm_weight: Optional[torch.Tensor] = None, pre_norm_bias: Optional[torch.Tensor] = None,
                  pre_norm_eps: float = 1e-6, add_residual: bool = False,
-                 two_stream: bool = True) -> Tuple[torch.Tensor, Dict[str, torch.Tensor], Dict]:
+                 two_stream: bool = True, bank_shadow: Optional[torch.Tensor] = None,
+                 bank_inv_rms: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Dict[str, torch.Tensor], Dict]:
     """Sequence-level Mixture-of-Chapters memory layer on the GPU.
 
     Returns (out [B,L,d], router losses, info) with info = indices / weights of the routing.
@@ -523,6 +552,12 @@ def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tenso
     h_attn + attn(pre_norm(h_attn), memory) (see :func:`cross_attention`).  With bf16 compute the layer runs as
     one autograd node that overlaps its small kernels with the tensor-core kernels on a second stream
     (``two_stream=False`` chains the three separate nodes instead; results are the same).
+
+    ``bank_shadow`` (bf16 copy of ``bank``, e.g. ``ChapteredMemoryBank.bf16_shadow()`` or the copy
+    ``SparseBankAdamW`` refreshes) switches the bf16 layer to the fused gather-and-project route: the K/V projection
+    reads the selected chapters straight from that copy and no gathered rows are materialised, forward or
+    backward.  With ``norm_type="rms"`` it also needs ``bank_inv_rms`` (``ops.row_inv_rms`` of the bank with
+    ``norm_eps``); ``norm_type="layernorm"`` keeps the two-pass route.
     """
     cd = compute_dtype or h_attn.dtype
     if (cd == torch.bfloat16 and two_stream and wq.dtype == wk.dtype == wv.dtype == wo.dtype
@@ -537,7 +572,8 @@ def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tenso
         out, idx, w, cidx, cw, lv = _MemoryLayerTwoStream.apply(
             h_router, h_attn, bank, router_weight, router_bias, wq, wk, wv, wo,
             pre_norm_weight if pre_norm else None, pre_norm_bias if pre_norm else None, cfg,
-            getattr(bank, "moc_sparse_grad", None))
+            getattr(bank, "moc_sparse_grad", None),
+            None if bank_shadow is None else {"shadow": bank_shadow, "inv_rms": bank_inv_rms})
         losses = {}
         if with_losses:
             losses = _LossDict({k: lv[i] for i, k in enumerate(LOSS_KEYS)})

@@ -44,6 +44,8 @@ class ChapteredMemoryBank(nn.Module):
         self.tokens_per_chapter = base_bank.num_tokens // num_chapters
         self._bf16_shadow: Optional[torch.Tensor] = None
         self._bf16_version = -1
+        self._inv_rms: Optional[torch.Tensor] = None
+        self._inv_rms_key = None
 
     def get_memory(self) -> torch.Tensor:
         return self.base_bank.get_memory()
@@ -71,3 +73,14 @@ class ChapteredMemoryBank(nn.Module):
             self._bf16_shadow = ops.cast(memory.detach(), torch.bfloat16)
             self._bf16_version = memory._version
         return self._bf16_shadow
+
+    def row_inv_rms(self, eps: float) -> torch.Tensor:
+        """1 / sqrt(mean(row^2) + eps) of every bank row (model.py:423-425 applied to the whole bank), the second
+        operand of the fused gather-and-project route under RMS row normalisation; refreshed when the parameter
+        changed."""
+        memory = self.get_memory()
+        key = (memory._version, float(eps))
+        if self._inv_rms is None or self._inv_rms_key != key:
+            self._inv_rms = ops.row_inv_rms(memory.detach(), eps)
+            self._inv_rms_key = key
+        return self._inv_rms

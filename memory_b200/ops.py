@@ -310,6 +310,61 @@ def gather_rows_bwd(d_mem: torch.Tensor, bank: torch.Tensor, tokens_per_chapter:
     return d_comb_w, bank_grad
 
 
+@_instrument("row_inv_rms", 1)
+def row_inv_rms(bank: torch.Tensor, eps: float) -> torch.Tensor:
+    """1 / sqrt(mean(row^2) + eps) of every bank row (fp32 [rows])."""
+    L.require_cuda(bank)
+    bank = _contig(bank)
+    out = torch.empty(bank.shape[0], dtype=torch.float32, device=bank.device)
+    rc = L.lib().moc_row_inv_rms(L.ptr(bank), L.dtype_code(bank.dtype), bank.shape[0], bank.shape[1], float(eps),
+                                 L.ptr(out), L.stream_ptr(bank.device))
+    L.check(rc, "moc_row_inv_rms")
+    return out
+
+
+@_instrument("chapter_row_scale", 1)
+def chapter_row_scale(comb_idx: torch.Tensor, comb_w: Optional[torch.Tensor], inv_rms: Optional[torch.Tensor],
+                      bank_rows: int, tokens_per_chapter: int) -> torch.Tensor:
+    """scale[pair*T + r] = comb_w[pair] * inv_rms[row] (inv_rms None: no normalisation); fp32 [n_pairs*T]."""
+    comb_idx = _contig(comb_idx.to(torch.int32))
+    n = comb_idx.numel()
+    t = int(tokens_per_chapter)
+    out = torch.empty(n * t, dtype=torch.float32, device=comb_idx.device)
+    rc = L.lib().moc_chapter_row_scale(L.ptr(comb_idx), L.ptr(_contig(comb_w)), L.ptr(_contig(inv_rms)), int(bank_rows),
+                                       n, t, L.ptr(out), L.ptr(L.status_word(comb_idx.device)),
+                                       L.stream_ptr(comb_idx.device))
+    L.check(rc, "moc_chapter_row_scale")
+    return out
+
+
+@_instrument("gather_rows_bwd_prescaled", 2)
+def gather_rows_bwd_prescaled(g: torch.Tensor, bank: torch.Tensor, tokens_per_chapter: int, comb_idx: torch.Tensor,
+                              comb_w: Optional[torch.Tensor], inv_rms: Optional[torch.Tensor],
+                              seg: Dict[str, torch.Tensor], want_dw: bool = True, want_bank: bool = True,
+                              wire_copy: Optional[list] = None):
+    """Chapter-weight gradient and compact bank gradient from g = (row scale) * dM~ (see ``moc_row_inv_rms``)."""
+    bank, g = _contig(bank), _contig(g)
+    comb_idx = _contig(comb_idx.to(torch.int32))
+    n = comb_idx.numel()
+    n_rows, d = bank.shape
+    t = int(tokens_per_chapter)
+    dev = bank.device
+    d_comb_w = torch.empty(comb_idx.shape, dtype=torch.float32, device=dev) if want_dw else None
+    bank_grad = torch.empty(n * t, d, dtype=torch.float32, device=dev) if want_bank else None
+    wire = None
+    if want_bank and wire_copy is not None:
+        wire = torch.empty(n * t, d, dtype=torch.bfloat16, device=dev)
+        wire_copy.append(wire)
+    rc = L.lib().moc_gather_rows_bwd_prescaled(L.ptr(g), L.dtype_code(g.dtype), L.ptr(bank), L.dtype_code(bank.dtype),
+                                               n_rows, d, t, L.ptr(comb_idx), L.ptr(_contig(comb_w)), n,
+                                               L.ptr(_contig(inv_rms)), L.ptr(seg["uniq"]), L.ptr(seg["seg_offsets"]),
+                                               L.ptr(seg["seg_pairs"]), L.ptr(seg["num_unique"]), L.ptr(d_comb_w),
+                                               L.ptr(bank_grad), L.ptr(wire), L.ptr(L.status_word(dev)),
+                                               L.stream_ptr(dev))
+    L.check(rc, "moc_gather_rows_bwd_prescaled")
+    return d_comb_w, bank_grad
+
+
 @_instrument("bank_grad_merge", 2)
 def bank_grad_merge(rank_rows, ids_all: torch.Tensor, counts: torch.Tensor, tokens_per_chapter: int,
                     num_chapters: int, scale: float = 1.0, out: Optional[Dict[str, torch.Tensor]] = None
@@ -406,9 +461,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_kmajor: bool = True, b_kmajor: b
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, accumulate: bool = False,
          split_k: int = 1, row_scale: Optional[torch.Tensor] = None, scale_block_rows: int = 1,
          a_row_blocks: Optional[torch.Tensor] = None, a_block_rows: int = 0, m: Optional[int] = None,
-         residual: Optional[torch.Tensor] = None, tag: Optional[str] = None) -> torch.Tensor:
+         residual: Optional[torch.Tensor] = None, tag: Optional[str] = None,
+         b_row_blocks: Optional[torch.Tensor] = None, b_block_rows: int = 0, k: Optional[int] = None) -> torch.Tensor:
     """C[M,N] (+)= op(A) op(B) (+ residual).  a_kmajor: A stored [M,K] else [K,M]; b_kmajor: B stored [N,K]
-    else [K,N]; residual: fp32 [M,N] added in the epilogue."""
+    else [K,N]; residual: fp32 [M,N] added in the epilogue.  ``a_row_blocks`` / ``b_row_blocks``: gather lists over
+    the rows of a K-major A / the K rows of an MN-major B (blocks of ``*_block_rows`` rows, e.g. chapters of the
+    bank); ``m`` / ``k`` give the gathered extent."""
     L.require_cuda(a, b)
     if a.dtype != b.dtype:
         raise TypeError("projection operands must share a dtype")
@@ -423,6 +481,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_kmajor: bool = True, b_kmajor: b
         nn, kb = b.shape
     else:
         kb, nn = b.shape
+    if b_row_blocks is not None:
+        if b_kmajor or a_row_blocks is not None or k is None:
+            raise ValueError("b_row_blocks needs b_kmajor=False, no a_row_blocks and the gathered extent k")
+        kb = int(k)
     if kk != kb:
         raise ValueError(f"inner dimensions differ: {kk} vs {kb}")
     if out_dtype is None:
@@ -437,6 +499,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_kmajor: bool = True, b_kmajor: b
             raise ValueError("residual must be fp32 [M, N] with unit column stride")
         L.require_cuda(residual)
         g.residual, g.ldr = L.ptr(residual), residual.stride(0)
+    if b_row_blocks is not None:
+        rc = L.lib().moc_gemm_gather_b(C.byref(g), L.ptr(a), L.ptr(b), L.ptr(out), L.ptr(_contig(row_scale)),
+                                       L.ptr(_contig(b_row_blocks)), int(b_block_rows), b.shape[0],
+                                       L.ptr(L.status_word(a.device)), L.stream_ptr(a.device))
+        L.check(rc, "moc_gemm_gather_b")
+        return out
     rc = L.lib().moc_gemm(C.byref(g), L.ptr(a), L.ptr(b), L.ptr(out), L.ptr(_contig(row_scale)),
                           L.ptr(_contig(a_row_blocks)), L.ptr(L.status_word(a.device)), L.stream_ptr(a.device))
     L.check(rc, "moc_gemm")
@@ -480,9 +548,10 @@ def _attn_bwd_launches(*a, **k):
              _attn_bwd_launches)
 def attn_bwd(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tensor, d_o: torch.Tensor,
              num_heads: int, num_kv_heads: int, scale: float, parts: Optional[int] = None,
-             buffers=None) -> Tuple[torch.Tensor, torch.Tensor]:
+             buffers=None, kv_row_scale: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """dQ and dKV.  ``parts`` (bf16 only) restricts the call to some of its kernels for timing;
-    ``buffers`` = (d_q, d_kv, scratch) reuses outputs between such calls."""
+    ``buffers`` = (d_q, d_kv, scratch) reuses outputs between such calls.  ``kv_row_scale`` [B*n_sel] fp32 (bf16
+    only): dK / dV rows leave multiplied by it (the fused gather-and-project path)."""
     q, kv, o, d_o = _contig(q), _contig(kv), _contig(o), _contig(d_o)
     s = _attn_shape(q, kv, num_heads, num_kv_heads, scale)
     if buffers is None:
@@ -491,7 +560,13 @@ def attn_bwd(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tens
         scratch = torch.empty(6, s.batch, num_heads, s.seq, dtype=torch.float32, device=q.device)
     else:
         d_q, d_kv, scratch = buffers
-    if parts is None:
+    if kv_row_scale is not None:
+        if parts is not None:
+            raise ValueError("kv_row_scale goes with the whole backward (parts=None)")
+        rc = L.lib().moc_attn_bwd_scaled(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse), L.ptr(d_o),
+                                         L.ptr(d_q), L.ptr(d_kv), L.ptr(scratch), L.ptr(_contig(kv_row_scale)),
+                                         L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))
+    elif parts is None:
         rc = L.lib().moc_attn_bwd(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse), L.ptr(d_o), L.ptr(d_q),
                                   L.ptr(d_kv), L.ptr(scratch), L.ptr(L.status_word(q.device)),
                                   L.stream_ptr(q.device))

@@ -39,7 +39,8 @@ def paper_inputs(case):
     """Seeded tensors of the case with the hidden states rounded to bf16 (what the layer is fed)."""
     key = (case.seed, case.router_scale)
     if key not in _cache:
-        _cache.clear()
+        for k_ in [k_ for k_ in _cache if not (isinstance(k_, tuple) and k_[-1] == "ref")]:
+            del _cache[k_]
         inp = {k: torch.from_numpy(v) for k, v in make_inputs(case).items()}
         inp["h_router"] = inp["h_router"].bfloat16().float()
         inp["h_attn"] = inp["h_router"]
@@ -121,18 +122,22 @@ def test_router_flat_logits_selection_is_exact_up_to_ulp_ties(dev):
     assert rel_err(gw, w64) < 1e-5
 
 
+@pytest.mark.parametrize("fused", [False, True], ids=["two_pass", "fused_gather"])
 @pytest.mark.parametrize("case", [PAPER, PAPER_RMS], ids=["norm_off", "norm_rms"])
-def test_layer_paper_shape_bf16_against_fp32_oracle(case, dev):
+def test_layer_paper_shape_bf16_against_fp32_oracle(case, fused, dev):
     """The whole bf16 layer, forward and backward, against the fp32 oracle: output, every parameter and input
     gradient, bank gradient on the touched rows and exactly zero elsewhere."""
     from memory_b200 import _lib as L
     inp = paper_inputs(case)
     tensors = {k: inp[k] for k in ("h_router", "h_attn", "bank", "router_w", "router_b", "wq", "wk", "wv", "wo")}
-    ref = O.memory_layer_fwd_bwd(shape_of(case), tensors, inp["d_out"], 0.01, 0.001)
+    key = (case.name, "ref")
+    if key not in _cache:
+        _cache[key] = O.memory_layer_fwd_bwd(shape_of(case), tensors, inp["d_out"], 0.01, 0.001)
+    ref = _cache[key]
     gpu_in = dict(inp)
     gpu_in["h_router"] = inp["h_router"].bfloat16()
     gpu_in["h_attn"] = gpu_in["h_router"]
-    out, losses, info, P = run_layer_gpu(case, torch.bfloat16, dev, inputs=gpu_in)
+    out, losses, info, P = run_layer_gpu(case, torch.bfloat16, dev, inputs=gpu_in, fused=fused)
     L.check_device_status(dev)
     assert out.dtype == torch.bfloat16
     assert torch.equal(info["indices"].cpu(), ref["indices"])

@@ -55,13 +55,23 @@ def test_layer_fp32_matches_reference_golden(name, dev):
     assert not bg[mask].any(), "bank gradient must be zero outside the touched chapters"
 
 
+@pytest.mark.parametrize("fused", [False, True], ids=["two_pass", "fused_gather"])
 @pytest.mark.parametrize("name", list(BF16_CASES))
-def test_layer_bf16_matches_reference_golden(name, dev):
+def test_layer_bf16_matches_reference_golden(name, fused, dev):
     """bf16 tensor-core path, with and without row normalisation of the gathered chapters (the paper's
-    setting is ``rms``), against the fp32 reference and against the reference under bf16 autocast."""
+    setting is ``rms``), against the fp32 reference and against the reference under bf16 autocast; both with the
+    gathered rows materialised and with the fused gather-and-project route."""
     case = CASES[name]
     gold = load_gold(name)
-    out, losses, info, P = run_layer_gpu(case, torch.bfloat16, dev)
+    seen = []
+    from memory_b200 import ops
+    ops.LAUNCH_HOOK = seen.append
+    try:
+        out, losses, info, P = run_layer_gpu(case, torch.bfloat16, dev, fused=fused)
+    finally:
+        ops.LAUNCH_HOOK = None
+    # affine-free LayerNorm rows cannot be a row scale: that case keeps the two-pass route even when asked
+    assert ("gather_rows_fwd:f32" in seen) == (not fused or case.norm_type == "layernorm"), sorted(set(seen))
     _status_ok(dev)
     assert np.array_equal(info["indices"].cpu().numpy(), gold["indices"])
     for prefix in ("", "bf16_"):

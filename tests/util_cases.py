@@ -56,8 +56,11 @@ def assert_close_all_forms(a, b, tol, what=""):
     return s
 
 
-def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001):
+def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001, fused=False):
+    """``fused``: the bf16 layer reads the chapters from a bf16 copy of the bank inside the K/V projection (no
+    gathered rows), forward and backward."""
     import memory_b200 as M
+    from memory_b200 import ops
     inp = inputs or {k: torch.from_numpy(v) for k, v in make_inputs(case).items()}
     inp = {k: v.to(dev) for k, v in inp.items()}
     names = ("h_router", "bank", "router_w", "router_b", "wq", "wk", "wv", "wo")
@@ -70,6 +73,9 @@ def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001):
             P["pre_norm_b"] = inp["pre_norm_b"].clone().requires_grad_(True)
         extra = dict(pre_norm=case.pre_norm, pre_norm_weight=P["pre_norm_w"], pre_norm_bias=P.get("pre_norm_b"),
                      pre_norm_eps=case.pre_norm_eps, add_residual=True)
+    if fused:
+        extra = dict(extra, bank_shadow=ops.cast(inp["bank"].contiguous(), torch.bfloat16),
+                     bank_inv_rms=ops.row_inv_rms(inp["bank"].contiguous(), case.norm_eps))
     out, losses, info = M.memory_layer(
         P["h_router"], P["h_attn"], P["bank"], P["router_w"], P["router_b"], P["wq"], P["wk"], P["wv"], P["wo"],
         num_heads=case.num_heads, num_kv_heads=case.num_kv_heads, tokens_per_chapter=case.tokens_per_chapter,
