@@ -297,10 +297,14 @@ int moc_attn_bwd_parts(const moc_attn_shape* s, const void* q, const void* kv, c
                        void* stream);
 
 /* moc_attn_bwd (bf16 only) whose dK / dV rows leave multiplied by kv_row_scale [B*n_sel]: the backward half of the
- * fused gather-and-project path described at moc_row_inv_rms.  No counterpart in the reference. */
+ * fused gather-and-project path described at moc_row_inv_rms.  kv_dot (may be NULL; needs n_sel % 64 == 0):
+ * [B, n_sel/64, HK] fp32, per 64-key block and KV head the sum over its rows of <dK, K> + <dV, V> with the unscaled
+ * dK / dV -- for 64-row chapters, summed over the heads and divided by the chapter weight, this is the chapter-weight
+ * gradient (d u~ = sum_r <dM~_r, M~_r> / u~ and <dM~_r, M~_r> = <dKV_r, KV_r>), taken while the K / V tile is
+ * still in shared memory.  No counterpart in the reference. */
 int moc_attn_bwd_scaled(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
                         const void* d_o, void* d_q, void* d_kv, float* delta, const float* kv_row_scale,
-                        int32_t* status, void* stream);
+                        float* kv_dot, int32_t* status, void* stream);
 
 /* moc_attn_bwd without caller-provided scratch and without any allocation.  It has no counterpart in the
  * reference.  It exists for callers that are not allowed to allocate device memory when they run the

@@ -22,7 +22,7 @@ int launch_attn_f32_bwd(const moc_attn_shape* s, const float* q, const float* kv
                         const float* lse, const float* delta, float* d_q, float* d_kv, cudaStream_t stream);
 int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
                        const void* d_o, void* d_q, void* d_kv, float* scratch, int32_t* status,
-                       cudaStream_t stream, int parts, const float* kv_row_scale = nullptr);
+                       cudaStream_t stream, int parts, const float* kv_row_scale = nullptr, float* kv_dot = nullptr);
 }  // namespace moc
 
 namespace {

@@ -375,6 +375,8 @@ constexpr uint32_t kColST = 0, kColDPT = 64, kColDV = 128, kColDK = 192;   // dS
 
 struct DkvParams {
   const float* row_scale;  // optional per-key-row factor applied to dK and dV when they are written, or nullptr
+  float* kv_dot;           // optional [B, n_sel / 64, HK]: per 64-key block and KV head, sum over its rows of
+                           // <dK, K> + <dV, V> (the chapter-weight gradient up to 1 / weight), or nullptr
   __nv_bfloat16* d_kv;
   int dkv_tma;             // d_kv written through staging blocks and TMA stores (n_sel % 32 == 0)
   const uint4* statb;
@@ -595,6 +597,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       ok = mbar_wait(&acc_bar, 0, &abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
     }
+    float kv_dot_part = 0.f;        // this thread's share of sum_rows (<dK, K> + <dV, V>) for its key row and column half
     if (p.dkv_tma) {
       // One thread owns one key row, so direct stores would scatter 16-byte pieces over 32 rows per instruction.
       // The tile ring is idle now: each (lane quarter, dK | dV) gets a 32-row x 128-byte swizzled block there,
@@ -611,6 +614,23 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           const float rsf = (p.row_scale != nullptr && krow < p.n_sel)
                                 ? p.row_scale[static_cast<long long>(b) * p.n_sel + krow] : 1.f;
           const float f = (which ? 1.f : p.scale) * rsf;
+          if (p.kv_dot != nullptr && krow < p.n_sel) {
+            // the stationary K / V tile is still in shared memory (two 64-row boxes, 128-byte rows, swizzled)
+            const int rr = quarter * 32 + lane;
+            const uint8_t* tile = (which ? v_s : k_s) + (rr >> 6) * (kKBytes / 2) + (rr & 63) * 128;
+            float acc = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const uint4 kvv = *reinterpret_cast<const uint4*>(tile + ((static_cast<uint32_t>(half * 4 + c) ^ (rr & 7)) << 4));
+              const uint32_t w4[4] = {kvv.x, kvv.y, kvv.z, kvv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                acc = fmaf(__uint_as_float(r[8 * c + 2 * e]), __uint_as_float(w4[e] << 16), acc);
+                acc = fmaf(__uint_as_float(r[8 * c + 2 * e + 1]), __uint_as_float(w4[e] & 0xFFFF0000u), acc);
+              }
+            }
+            kv_dot_part = fmaf(acc, which ? 1.f : p.scale, kv_dot_part);
+          }
           const uint32_t row_addr = smem_u32(ring) + (quarter * 2 + which) * 4096 + lane * 128;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -624,6 +644,21 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           }
         }
         fence_proxy_async();
+      }
+      if (p.kv_dot != nullptr) {
+        // 64-key block c of this tile = lane quarters 2c, 2c+1 and both column halves: four warps; the sum is
+        // formed in a fixed order (warp shuffle tree, then the four partials in warp order)
+        const float wsum = warp_sum(ok ? kv_dot_part : 0.f);
+        float* part = reinterpret_cast<float*>(stats);         // the constant rows are no longer read
+        if (lane == 0) part[warp] = wsum;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (ok && warp < 2 && lane == 0) {
+          const int blk = key0 / 64 + warp;
+          if (blk * 64 < p.n_sel) {
+            const float t = part[2 * warp] + part[2 * warp + 1] + part[4 + 2 * warp] + part[4 + 2 * warp + 1];
+            p.kv_dot[(static_cast<long long>(b) * (p.n_sel / 64) + blk) * p.HK + kh] = t;
+          }
+        }
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight row-owning warps, whatever `ok` is
       if (ok && half == 0 && lane == 0 && key0 + quarter * 32 < p.n_sel) {
@@ -670,7 +705,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
 int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
                        const void* d_o, void* d_q, void* d_kv, float* scratch, int32_t* status,
-                       cudaStream_t stream, int parts, const float* kv_row_scale) {
+                       cudaStream_t stream, int parts, const float* kv_row_scale, float* kv_dot) {
   MOC_REQUIRE(s->head_dim == kD, "bf16 attention needs head_dim 64");
   MOC_REQUIRE(s->seq % kQB == 0, "bf16 attention backward needs seq % 64 == 0");
   MOC_REQUIRE(s->num_heads % s->num_kv_heads == 0, "num_heads must be a multiple of num_kv_heads");
@@ -711,6 +746,9 @@ int launch_attn_tc_bwd(const moc_attn_shape* s, const void* q, const void* kv, c
     p.dkv_tma = (s->n_sel % 32 == 0 && (reinterpret_cast<uintptr_t>(d_kv) & 15) == 0) ? 1 : 0;
     if (p.dkv_tma && (rc = make_tmap_bf16_2d(&tdkv, d_kv, kvrows, kvcols, kvcols, 32, kD)) != MOC_OK) return rc;
     p.d_kv = static_cast<__nv_bfloat16*>(d_kv); p.statb = statb; p.row_scale = kv_row_scale;
+    p.kv_dot = kv_dot;
+    if (kv_dot != nullptr)
+      MOC_REQUIRE(p.dkv_tma && s->n_sel % 64 == 0, "the per-block <dKV, KV> sums need n_sel % 64 == 0 and an aligned d_kv");
     p.L = L; p.n_sel = s->n_sel; p.H = H; p.HK = HK;
     p.scale = s->scale; p.scale_log2 = s->scale * kLog2e; p.status = status;
     dim3 grid(ceil_div(s->n_sel, kKeysB), HK, B);

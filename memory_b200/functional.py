@@ -456,8 +456,14 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
                             split_k=splits(b * l, d, d), tag="d_wo")
         d_o = ops.gemm(g2, wo_t, tag="d_attn_out")
         fused = ctx.fused
+        # 64-row chapters: the chapter-weight gradient is taken in the dK/dV epilogue, where K and V are still in
+        # shared memory, instead of by a pass over the memory-row gradient and the bank rows
+        kv_dot = None
+        if fused is not None and t == 64:
+            kv_dot = torch.empty(b, kv.shape[1] // 64, num_kv_heads, dtype=f32, device=dev)
         d_q, d_kv = ops.attn_bwd(q.view(b, l, -1), kv, o, lse, d_o.view(b, l, -1), num_heads, num_kv_heads,
-                                 ctx.scale, kv_row_scale=None if fused is None else fused["row_scale"])
+                                 ctx.scale, kv_row_scale=None if fused is None else fused["row_scale"],
+                                 kv_dot=kv_dot)
         d_q2 = d_q.view(b * l, -1)
         d_kv2 = d_kv.view(-1, d_kv.shape[-1])
 
@@ -496,8 +502,10 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
         else:
             d_cw, rows = ops.gather_rows_bwd_prescaled(
                 d_mem, fused["shadow"], t, r["comb_idx"], r["comb_w"],
-                fused["inv_rms"] if ctx.norm_row == "rms" else None, seg, want_dw=True, want_bank=want_bank,
-                wire_copy=wire)
+                fused["inv_rms"] if ctx.norm_row == "rms" else None, seg, want_dw=kv_dot is None,
+                want_bank=want_bank, wire_copy=wire)
+            if kv_dot is not None:
+                d_cw = kv_dot.sum(dim=2) / r["comb_w"].clamp_min(1e-30)
         d_bank = None
         if want_bank:
             if ctx.sink is not None:

@@ -548,10 +548,12 @@ def _attn_bwd_launches(*a, **k):
              _attn_bwd_launches)
 def attn_bwd(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tensor, d_o: torch.Tensor,
              num_heads: int, num_kv_heads: int, scale: float, parts: Optional[int] = None,
-             buffers=None, kv_row_scale: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+             buffers=None, kv_row_scale: Optional[torch.Tensor] = None,
+             kv_dot: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """dQ and dKV.  ``parts`` (bf16 only) restricts the call to some of its kernels for timing;
     ``buffers`` = (d_q, d_kv, scratch) reuses outputs between such calls.  ``kv_row_scale`` [B*n_sel] fp32 (bf16
-    only): dK / dV rows leave multiplied by it (the fused gather-and-project path)."""
+    only): dK / dV rows leave multiplied by it (the fused gather-and-project path); ``kv_dot`` fp32
+    [B, n_sel/64, HK] then receives per 64-key block and KV head sum_rows(<dK, K> + <dV, V>)."""
     q, kv, o, d_o = _contig(q), _contig(kv), _contig(o), _contig(d_o)
     s = _attn_shape(q, kv, num_heads, num_kv_heads, scale)
     if buffers is None:
@@ -565,7 +567,7 @@ def attn_bwd(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tens
             raise ValueError("kv_row_scale goes with the whole backward (parts=None)")
         rc = L.lib().moc_attn_bwd_scaled(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse), L.ptr(d_o),
                                          L.ptr(d_q), L.ptr(d_kv), L.ptr(scratch), L.ptr(_contig(kv_row_scale)),
-                                         L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))
+                                         L.ptr(kv_dot), L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))
     elif parts is None:
         rc = L.lib().moc_attn_bwd(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse), L.ptr(d_o), L.ptr(d_q),
                                   L.ptr(d_kv), L.ptr(scratch), L.ptr(L.status_word(q.device)),
