@@ -480,6 +480,51 @@ __global__ void bank_grad_prescaled_kernel(const TG* __restrict__ g, const TB* _
   __nv_bfloat16* wire = bank_grad_wire ? bank_grad_wire + r * dim : nullptr;
   const long long brow = static_cast<long long>(uniq[u]) * T + within;
   const TB* row = bank + brow * dim;
+  if ((dim & 7) == 0 && dim <= 8 * 32 * 4) {
+    // 16-byte accesses: lane l owns columns [8 l + 256 n, +8); the sums stay in registers for the norm term
+    float acc[4][8];
+    float sgm = 0.f;
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int c = lane * 8 + n * 256;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[n][j] = 0.f;
+      if (c < dim) {
+        for (int q = p0; q < p1; ++q) {
+          float gv[8];
+          ld8(g + (static_cast<long long>(seg_pairs[q]) * T + within) * dim + c, gv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[n][j] += gv[j];
+        }
+        if (inv_rms) {
+          float x[8];
+          ld8(row + c, x);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sgm = fmaf(acc[n][j], x[j], sgm);
+        }
+      }
+    }
+    float k = 0.f;
+    if (inv_rms) {
+      const float ir = inv_rms[brow];
+      k = warp_sum(sgm) * ir * ir / static_cast<float>(dim);
+    }
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int c = lane * 8 + n * 256;
+      if (c < dim) {
+        if (inv_rms) {
+          float x[8];
+          ld8(row + c, x);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[n][j] -= x[j] * k;
+        }
+        st8(dst + c, acc[n]);
+        if (wire) st8(wire + c, acc[n]);
+      }
+    }
+    return;
+  }
   float sgm = 0.f;
   for (int c = lane; c < dim; c += 32) {
     float acc = 0.f;

@@ -122,9 +122,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int kt_begin = split * p.k_tiles_per_split;
         int kt_count = p.k_tiles_total - kt_begin;
         if (kt_count > p.k_tiles_per_split) kt_count = p.k_tiles_per_split;
+        // Gathered A: the stored rows of this tile's boxes depend on the tile only, so the list is read once per
+        // item (up to 32 boxes: 256 rows of 8), not once per K step -- a dependent global load in front of every
+        // copy would pace the whole pipeline.
+        int a_rows[32];
+        const int nbox_a = p.a_kmajor ? BM * MT / p.a_box_rows : 0;
+        if (p.a_kmajor && p.a_row_blocks != nullptr) {
+#pragma unroll 1
+          for (int i = 0; i < nbox_a; ++i) {
+            const int blk = m0 / p.a_box_rows + i;
+            long long row = (blk < p.a_num_blocks) ? static_cast<long long>(p.a_row_blocks[blk]) * p.a_box_rows
+                                                   : p.a_stored_rows;
+            if (row < 0 || row > p.a_stored_rows) {
+              atomicMax(p.status, MOC_DEV_BAD_INDEX);
+              row = p.a_stored_rows;   // fully out of range: the copy zero-fills
+            }
+            a_rows[i] = static_cast<int>(row);
+          }
+        }
+        // Gathered B: block ids are requested kIdAhead K steps before they are needed (a register ring), so the
+        // latency of the list read (a dependent global load) is hidden behind the copies of the steps in between.
+        constexpr int kIdAhead = 8;
+        const int nsub_b = (p.b_row_blocks != nullptr) ? BK / p.b_box_rows : 0;
+        auto blk_of = [&](long long kg) { return kg / p.b_block_rows; };
+        auto ld_id = [&](long long kg) -> long long {
+          const long long blk = blk_of(kg);
+          return (blk < p.b_num_blocks) ? static_cast<long long>(p.b_row_blocks[blk]) : -1;
+        };
+        long long ring[kIdAhead];
+        if (nsub_b == 1) {
+#pragma unroll
+          for (int i = 0; i < kIdAhead; ++i)
+            ring[i] = (i < kt_count) ? ld_id(static_cast<long long>(kt_begin + i) * BK) : -1;
+        }
         for (int kt = 0; kt < kt_count; ++kt, ++it) {
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
+          long long b_rows[8];
+          if (nsub_b > 0) {
+#pragma unroll 1
+            for (int i = 0; i < nsub_b; ++i) {
+              const long long kg = static_cast<long long>(kt_begin + kt) * BK + i * p.b_box_rows;
+              const long long blk = blk_of(kg);
+              const long long id = (nsub_b == 1) ? ring[0] : ld_id(kg);
+              long long row = p.b_stored_rows;      // fully out of range: the copy zero-fills
+              if (blk < p.b_num_blocks) {
+                if (id < 0 || (id + 1) * p.b_block_rows > p.b_stored_rows) atomicMax(p.status, MOC_DEV_BAD_INDEX);
+                else row = id * p.b_block_rows + (kg - blk * p.b_block_rows);
+              }
+              b_rows[i] = row;
+            }
+            if (nsub_b == 1) {
+#pragma unroll
+              for (int i = 0; i + 1 < kIdAhead; ++i) ring[i] = ring[i + 1];
+              ring[kIdAhead - 1] = (kt + kIdAhead < kt_count)
+                                       ? ld_id(static_cast<long long>(kt_begin + kt + kIdAhead) * BK) : -1;
+            }
+          }
           ok = mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, p.status);
           if (!ok) break;
           mbar_arrive_expect_tx(&full_bar[s], C::kStageBytes);
@@ -132,21 +186,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           uint8_t* b_s = a_s + C::kABytes;
           const int k0 = (kt_begin + kt) * BK;
           if (p.a_kmajor) {
-            const int nbox = BM * MT / p.a_box_rows;
-            for (int i = 0; i < nbox; ++i) {
-              long long row;
-              if (p.a_row_blocks != nullptr) {
-                const int blk = m0 / p.a_box_rows + i;
-                row = (blk < p.a_num_blocks) ? static_cast<long long>(p.a_row_blocks[blk]) * p.a_box_rows
-                                             : p.a_stored_rows;
-                if (row < 0 || row > p.a_stored_rows) {
-                  atomicMax(p.status, MOC_DEV_BAD_INDEX);
-                  row = p.a_stored_rows;   // fully out of range: the copy zero-fills
-                }
-              } else {
-                row = m0 + i * p.a_box_rows;
-              }
-              tma_load_2d(a_s + i * p.a_box_rows * 128, &tmap_a, &full_bar[s], k0, static_cast<int>(row));
+            for (int i = 0; i < nbox_a; ++i) {
+              const int row = (p.a_row_blocks != nullptr) ? a_rows[i] : m0 + i * p.a_box_rows;
+              tma_load_2d(a_s + i * p.a_box_rows * 128, &tmap_a, &full_bar[s], k0, row);
             }
           } else {
 #pragma unroll
@@ -163,20 +205,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           } else {
             // the K rows of this stage are rows of listed blocks (chapters of the bank): one box per run of rows
             // that is contiguous in the stored matrix
-            const int nsub = BK / p.b_box_rows;
-            for (int i = 0; i < nsub; ++i) {
-              const long long kg = static_cast<long long>(k0) + i * p.b_box_rows;
-              const long long blk = kg / p.b_block_rows;
-              long long row = p.b_stored_rows;      // fully out of range: the copy zero-fills
-              if (blk < p.b_num_blocks) {
-                const long long id = p.b_row_blocks[blk];
-                if (id < 0 || (id + 1) * p.b_block_rows > p.b_stored_rows) atomicMax(p.status, MOC_DEV_BAD_INDEX);
-                else row = id * p.b_block_rows + (kg - blk * p.b_block_rows);
-              }
+            for (int i = 0; i < nsub_b; ++i) {
 #pragma unroll
               for (int j = 0; j < BN / 64; ++j)
                 tma_load_2d(b_s + j * 8192 + i * p.b_box_rows * 128, &tmap_b, &full_bar[s], n0 + j * 64,
-                            static_cast<int>(row));
+                            static_cast<int>(b_rows[i]));
             }
           }
         }
@@ -433,6 +466,7 @@ int launch_gemm_tc(const moc_gemm_desc* g, const void* a, const void* b, void* c
     a_box_rows = g->a_block_rows;
     MOC_REQUIRE(a_box_rows >= 8 && a_box_rows <= 128 && (128 % a_box_rows) == 0 && (a_box_rows % 8) == 0,
                 "a_block_rows must be a multiple of 8 that divides 128");
+    // (up to 256 / 8 = 32 boxes per tile, the size of the per-item row table in the producer)
     MOC_REQUIRE(g->m % a_box_rows == 0, "M must be a multiple of a_block_rows");
     a_num_blocks = g->m / a_box_rows;
     a_stored_rows = g->a_stored_rows;

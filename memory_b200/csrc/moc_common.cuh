@@ -116,6 +116,12 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(col), "r"(row)
       : "memory");
 }
+// TMA: 2-D tiled prefetch of a box into L2 (no shared-memory destination, no completion tracking).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int32_t col, int32_t row) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(col), "r"(row)
+               : "memory");
+}
 // TMA: 2-D tiled store shared -> global (clipped at the tensor's edges), tracked by bulk groups.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int32_t col, int32_t row) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"

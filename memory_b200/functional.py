@@ -487,11 +487,20 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
             if fused is None:
                 d_wkv = ops.gemm(d_kv2, m2, a_kmajor=False, b_kmajor=False, out_dtype=f32,
                                  split_k=splits(d_kv2.shape[0], wkv_c.shape[0], d), tag="d_wkv")
-            else:
-                # dKV' already carries the row scale, so the weight gradient reads the raw bank rows in place
+            elif fused.get("wkv_grad_in_place"):
+                # dKV' already carries the row scale, so the weight gradient can read the raw bank rows in place
+                # through the gather list on its B operand
                 d_wkv = ops.gemm(d_kv2, fused["shadow"], a_kmajor=False, b_kmajor=False, out_dtype=f32,
                                  split_k=splits(d_kv2.shape[0], wkv_c.shape[0], d), tag="d_wkv",
                                  b_row_blocks=r["comb_idx"].reshape(-1), b_block_rows=t, k=d_kv2.shape[0])
+            else:
+                # ... but with the contraction running over chapters, every K step of that projection lands in
+                # another chapter of the 403 MB copy and it measured twice as slow as over contiguous rows.  This
+                # stream has slack, so the raw selected rows (no norm, no weight: dKV' carries both) are copied out
+                # once here, off the critical path, and the projection runs over the contiguous copy.
+                m_raw, _ = ops.gather_rows_fwd(fused["shadow"], t, r["comb_idx"], None, None, row_eps, cd)
+                d_wkv = ops.gemm(d_kv2, m_raw.view(-1, d), a_kmajor=False, b_kmajor=False, out_dtype=f32,
+                                 split_k=splits(d_kv2.shape[0], wkv_c.shape[0], d), tag="d_wkv")
 
         d_mem = ops.gemm(d_kv2, wkv_t, tag="d_mem")
         want_bank = need[2]
@@ -552,7 +561,8 @@ def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tenso
                  pre_norm_weight: Optional[torch.Tensor] = None, pre_norm_bias: Optional[torch.Tensor] = None,
                  pre_norm_eps: float = 1e-6, add_residual: bool = False,
                  two_stream: bool = True, bank_shadow: Optional[torch.Tensor] = None,
-                 bank_inv_rms: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Dict[str, torch.Tensor], Dict]:
+                 bank_inv_rms: Optional[torch.Tensor] = None,
+                 wkv_grad_in_place: bool = False) -> Tuple[torch.Tensor, Dict[str, torch.Tensor], Dict]:
     """Sequence-level Mixture-of-Chapters memory layer on the GPU.
 
     Returns (out [B,L,d], router losses, info) with info = indices / weights of the routing.
@@ -565,7 +575,9 @@ def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tenso
     ``SparseBankAdamW`` refreshes) switches the bf16 layer to the fused gather-and-project route: the K/V projection
     reads the selected chapters straight from that copy and no gathered rows are materialised, forward or
     backward.  With ``norm_type="rms"`` it also needs ``bank_inv_rms`` (``ops.row_inv_rms`` of the bank with
-    ``norm_eps``); ``norm_type="layernorm"`` keeps the two-pass route.
+    ``norm_eps``); ``norm_type="layernorm"`` keeps the two-pass route.  ``wkv_grad_in_place`` lets the Wk / Wv
+    gradient read the bank through a gather list as well instead of copying the raw selected rows out on the side
+    stream first (no gathered copy at all, but slower at the paper shape).
     """
     cd = compute_dtype or h_attn.dtype
     if (cd == torch.bfloat16 and two_stream and wq.dtype == wk.dtype == wv.dtype == wo.dtype
@@ -581,7 +593,8 @@ def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tenso
             h_router, h_attn, bank, router_weight, router_bias, wq, wk, wv, wo,
             pre_norm_weight if pre_norm else None, pre_norm_bias if pre_norm else None, cfg,
             getattr(bank, "moc_sparse_grad", None),
-            None if bank_shadow is None else {"shadow": bank_shadow, "inv_rms": bank_inv_rms})
+            None if bank_shadow is None else {"shadow": bank_shadow, "inv_rms": bank_inv_rms,
+                                              "wkv_grad_in_place": wkv_grad_in_place})
         losses = {}
         if with_losses:
             losses = _LossDict({k: lv[i] for i, k in enumerate(LOSS_KEYS)})

@@ -55,7 +55,7 @@ def test_layer_fp32_matches_reference_golden(name, dev):
     assert not bg[mask].any(), "bank gradient must be zero outside the touched chapters"
 
 
-@pytest.mark.parametrize("fused", [False, True], ids=["two_pass", "fused_gather"])
+@pytest.mark.parametrize("fused", [False, True, "in_place"], ids=["two_pass", "fused_gather", "fused_in_place"])
 @pytest.mark.parametrize("name", list(BF16_CASES))
 def test_layer_bf16_matches_reference_golden(name, fused, dev):
     """bf16 tensor-core path, with and without row normalisation of the gathered chapters (the paper's
@@ -67,11 +67,13 @@ def test_layer_bf16_matches_reference_golden(name, fused, dev):
     from memory_b200 import ops
     ops.LAUNCH_HOOK = seen.append
     try:
-        out, losses, info, P = run_layer_gpu(case, torch.bfloat16, dev, fused=fused)
+        out, losses, info, P = run_layer_gpu(case, torch.bfloat16, dev, fused=bool(fused), in_place=fused == "in_place")
     finally:
         ops.LAUNCH_HOOK = None
     # affine-free LayerNorm rows cannot be a row scale: that case keeps the two-pass route even when asked
     assert ("gather_rows_fwd:f32" in seen) == (not fused or case.norm_type == "layernorm"), sorted(set(seen))
+    if fused == "in_place" and case.norm_type != "layernorm":
+        assert not any(s_.startswith("gather_rows_fwd") for s_ in seen), sorted(set(seen))
     _status_ok(dev)
     assert np.array_equal(info["indices"].cpu().numpy(), gold["indices"])
     for prefix in ("", "bf16_"):

@@ -56,7 +56,7 @@ def assert_close_all_forms(a, b, tol, what=""):
     return s
 
 
-def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001, fused=False):
+def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001, fused=False, in_place=False):
     """``fused``: the bf16 layer reads the chapters from a bf16 copy of the bank inside the K/V projection (no
     gathered rows), forward and backward."""
     import memory_b200 as M
@@ -75,7 +75,8 @@ def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001, fused
                      pre_norm_eps=case.pre_norm_eps, add_residual=True)
     if fused:
         extra = dict(extra, bank_shadow=ops.cast(inp["bank"].contiguous(), torch.bfloat16),
-                     bank_inv_rms=ops.row_inv_rms(inp["bank"].contiguous(), case.norm_eps))
+                     bank_inv_rms=ops.row_inv_rms(inp["bank"].contiguous(), case.norm_eps),
+                     wkv_grad_in_place=in_place)
     out, losses, info = M.memory_layer(
         P["h_router"], P["h_attn"], P["bank"], P["router_w"], P["router_b"], P["wq"], P["wk"], P["wv"], P["wo"],
         num_heads=case.num_heads, num_kv_heads=case.num_kv_heads, tokens_per_chapter=case.tokens_per_chapter,
