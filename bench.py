@@ -30,7 +30,7 @@ METRIC = "memory-xattn fwd+bwd tokens/sec/GPU at L=1024,k=64; % of bf16 TC roofl
 N_INPUT_SETS = 4       # distinct hidden-state batches rotated between steps
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at this shape, from the ncu captures summarised under
 # profiles/ (bytes); kernels without a capture report null
-DOMINANT_KERNEL_DRAM_BYTES = {"attn_bwd_dkv": 193.9e6}
+DOMINANT_KERNEL_DRAM_BYTES = {"attn_bwd_dkv": 193.2e6, "attn_bwd_dq": 136.2e6, "attn_fwd": 123.0e6}
 
 
 def layer_flops(cfg) -> float:
