@@ -384,6 +384,30 @@ int moc_sparse_attn_weighted_bwd(const moc_sparse_attn_shape* s, const void* q, 
                                  int32_t accumulate_dq, float* d_k, float* d_v, int64_t dkv_row_stride,
                                  float* d_w_heads, int32_t* status, void* stream);
 
+/* The same weighted mixture on the tensor cores (bf16, head_dim 64, block_size 64 only): an inverted index
+ * chapter -> (token, slot) pairs is built on the device and each chapter's K / V tile stays in shared memory while
+ * the query rows that selected it are gathered against it (tcgen05 products, accumulators in tensor memory).
+ *   index_heads: 1 when block_indices is [B,TQ,1,S] (one chapter list per token, every head uses it -- the module
+ *   path, memory_transformer/memory_attention.py:596-714) or H for [B,TQ,H,S] (kernels-final/kernel_v4.py:972-1027).
+ *   workspace: moc_token_mix_workspace_bytes() bytes; moc_token_mix_index fills it, forward and backward read it.
+ *   partial / dq_partial: bf16 scratch [B,TQ,S,HQ,D].  Chapter ids outside [0, TK/64) raise MOC_DEV_BAD_INDEX in
+ *   the status word and contribute nothing. */
+size_t moc_token_mix_workspace_bytes(const moc_sparse_attn_shape* s, int32_t index_heads);
+int moc_token_mix_index(const moc_sparse_attn_shape* s, int32_t index_heads, const int32_t* block_indices,
+                        void* workspace, int32_t* status, void* stream);
+int moc_token_mix_fwd(const moc_sparse_attn_shape* s, int32_t index_heads, const void* q, const void* k, const void* v,
+                      int64_t kv_row_stride, const int32_t* block_indices, const float* weights, const void* base,
+                      float out_scale, const void* workspace, void* partial, void* o, float* lse_slots,
+                      int32_t* status, void* stream);
+/* d_q = d_q_base (or 0 when NULL) + the routed branch's gradient; d_k / d_v are bf16 with row stride
+ * dkv_row_stride: the 64 rows of every selected chapter are WRITTEN (each chapter by one CTA, pairs in ascending
+ * order), rows of chapters nobody selected are left as the caller set them (zero them). */
+int moc_token_mix_bwd(const moc_sparse_attn_shape* s, int32_t index_heads, const void* q, const void* k, const void* v,
+                      int64_t kv_row_stride, const int32_t* block_indices, const float* weights, float out_scale,
+                      const float* lse_slots, const void* d_o, const void* workspace, void* dq_partial,
+                      const void* d_q_base, void* d_q, void* d_k, void* d_v, int64_t dkv_row_stride,
+                      float* d_w_heads, int32_t* status, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Optimizer step of the bank from a compact gradient.  Replaces torch.optim.AdamW over the bank parameter
  * (training/trainer.py:372-378, param group "memory_bank" :338-347) fed by the dense gradient of torch.gather's

@@ -17,7 +17,8 @@ MOC_F32, MOC_BF16 = 0, 1
 ATTN_BWD_STATIC_MAX_FLOATS = 1 << 20   # MOC_ATTN_BWD_STATIC_MAX_FLOATS in include/moc_b200.h
 NORM_NONE, NORM_RMS, NORM_LAYERNORM = 0, 1, 2
 NORM_CODES = {None: NORM_NONE, "none": NORM_NONE, "rms": NORM_RMS, "layernorm": NORM_LAYERNORM}
-KERNEL_TAGS = {1: "gemm_tc.cu", 2: "attn_tc_fwd.cu", 3: "attn_tc_bwd.cu", 4: "host_util.cu"}
+KERNEL_TAGS = {1: "gemm_tc.cu", 2: "attn_tc_fwd.cu", 3: "attn_tc_bwd.cu", 4: "host_util.cu",
+               5: "token_mix_tc.cu"}
 DEV_STATUS_TEXT = {1: "a bounded device wait timed out", 2: "a chapter index was out of range"}
 
 
@@ -92,6 +93,12 @@ _PROTOTYPES = {
                                                P, P, P, P]),
     "moc_sparse_attn_weighted_bwd": (C.c_int, [C.POINTER(SparseAttnShape), P, P, P, C.c_int64, P, P, C.c_float, P,
                                                P, P, C.c_int32, P, P, C.c_int64, P, P, P]),
+    "moc_token_mix_workspace_bytes": (C.c_size_t, [C.POINTER(SparseAttnShape), C.c_int32]),
+    "moc_token_mix_index": (C.c_int, [C.POINTER(SparseAttnShape), C.c_int32, P, P, P, P]),
+    "moc_token_mix_fwd": (C.c_int, [C.POINTER(SparseAttnShape), C.c_int32, P, P, P, C.c_int64, P, P, P, C.c_float,
+                                    P, P, P, P, P, P]),
+    "moc_token_mix_bwd": (C.c_int, [C.POINTER(SparseAttnShape), C.c_int32, P, P, P, C.c_int64, P, P, C.c_float, P, P,
+                                    P, P, P, P, P, P, C.c_int64, P, P, P]),
     "moc_bank_adamw_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "moc_bank_adamw_step": (C.c_int, [P, P, P, C.c_int64, C.c_int32, C.c_int32, P, P, C.c_int32, P, C.c_float,
                                       C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int64, P, P,

@@ -18,7 +18,8 @@ OUT_DIR = os.path.join(HERE, "_lib")
 LIB_PATH = os.path.join(OUT_DIR, "libmoc_b200.so")
 
 SOURCES = ["host_util.cu", "capi.cu", "router.cu", "gather.cu", "simt_f32.cu", "gemm_tc.cu",
-           "attn_tc_fwd.cu", "attn_tc_bwd.cu", "sparse_attn.cu", "attn_bwd_static.cu", "norm.cu", "decode_attn.cu", "optim.cu"]
+           "attn_tc_fwd.cu", "attn_tc_bwd.cu", "sparse_attn.cu", "attn_bwd_static.cu", "norm.cu", "decode_attn.cu", "optim.cu",
+           "token_mix_tc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC"]
 

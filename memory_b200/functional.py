@@ -712,13 +712,20 @@ class _TokenRoutedAttention(torch.autograd.Function):
             n_rt = kv_rt.shape[0]
             k4 = kv_rt[:, :dkv].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
             v4 = kv_rt[:, dkv:].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
-            bidx = idx_local.reshape(1, rows, 1, k_sel).expand(1, rows, num_kv_heads, k_sel).to(torch.int32).contiguous()
             w2 = weights.reshape(1, rows, k_sel).float().contiguous()
             q4 = q.view(1, rows, num_heads, head_dim)
             base = None if comb is None else comb.contiguous().view(1, rows, num_heads, head_dim)
-            comb4, lse_slots = ops.sparse_attn_weighted_fwd(q4, k4, v4, bidx, w2, t, scale, base=base, out_scale=rho)
+            mix_ws = None
+            if ops.token_mix_supported(q4, k4, t, 1):
+                # tensor cores: every chapter's K / V tile stationary under the tokens that selected it
+                bidx = idx_local.reshape(1, rows, 1, k_sel).to(torch.int32).contiguous()
+                comb4, lse_slots, mix_ws = ops.token_mix_fwd(q4, k4, v4, bidx, w2, scale, base=base, out_scale=rho)
+            else:
+                bidx = idx_local.reshape(1, rows, 1, k_sel).expand(1, rows, num_kv_heads, k_sel).to(torch.int32).contiguous()
+                comb4, lse_slots = ops.sparse_attn_weighted_fwd(q4, k4, v4, bidx, w2, t, scale, base=base,
+                                                                out_scale=rho)
             comb = comb4.view(rows, -1)
-            rt = (rm2, kv_rt, bidx, w2, lse_slots, n_rt)
+            rt = (rm2, kv_rt, bidx, w2, lse_slots, n_rt, mix_ws)
         if comb is None:
             comb = q.new_zeros(rows, d)
         out = ops.gemm(comb.contiguous(), wo_c, out_dtype=h.dtype if h.dtype in (torch.float32, cd) else cd, tag="o_proj")
@@ -754,19 +761,24 @@ class _TokenRoutedAttention(torch.autograd.Function):
             d_shared = ops.gemm(d_kv_sh2, wkv_c, b_kmajor=False, tag="d_shared_mem").to(sh_dtype)
             d_wkv = ops.gemm(d_kv_sh2, sm2, a_kmajor=False, b_kmajor=False, out_dtype=f32, tag="d_wkv_shared")
         if ctx.rt is not None:
-            rm2, kv_rt, bidx, w2, lse_slots, n_rt = ctx.rt
+            rm2, kv_rt, bidx, w2, lse_slots, n_rt, mix_ws = ctx.rt
             k4 = kv_rt[:, :dkv].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
             v4 = kv_rt[:, dkv:].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
-            d_kv_rt = torch.zeros(n_rt, 2 * dkv, dtype=f32, device=q.device)
+            d_kv_rt = torch.zeros(n_rt, 2 * dkv, dtype=f32 if mix_ws is None else cd, device=q.device)
             dk4 = d_kv_rt[:, :dkv].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
             dv4 = d_kv_rt[:, dkv:].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
-            d_q, d_w = ops.sparse_attn_weighted_bwd(
-                q.view(1, rows, num_heads, head_dim), k4, v4, bidx, w2, lse_slots,
-                d_comb.view(1, rows, num_heads, head_dim), t, scale, rho, dk4, dv4,
-                d_q_accum=None if d_q is None else d_q.view(1, rows, num_heads, head_dim))
+            q4, dc4 = q.view(1, rows, num_heads, head_dim), d_comb.view(1, rows, num_heads, head_dim)
+            d_q4 = None if d_q is None else d_q.view(1, rows, num_heads, head_dim)
+            if mix_ws is not None:
+                d_q, d_w = ops.token_mix_bwd(q4, k4, v4, bidx, w2, lse_slots, dc4, scale, rho, mix_ws, dk4, dv4,
+                                             d_q_base=d_q4)
+                d_kv_c = d_kv_rt
+            else:
+                d_q, d_w = ops.sparse_attn_weighted_bwd(q4, k4, v4, bidx, w2, lse_slots, dc4, t, scale, rho, dk4, dv4,
+                                                        d_q_accum=d_q4)
+                d_kv_c = ops.cast(d_kv_rt, cd)
             d_q = d_q.view(rows, -1)
             d_weights = d_w.view(b, l, -1).to(w_dtype)
-            d_kv_c = ops.cast(d_kv_rt, cd)
             d_routed = ops.gemm(d_kv_c, wkv_c, b_kmajor=False, tag="d_routed_mem").to(rt_dtype)
             g_wkv = ops.gemm(d_kv_c, rm2, a_kmajor=False, b_kmajor=False, out_dtype=f32, tag="d_wkv_routed")
             d_wkv = g_wkv if d_wkv is None else d_wkv + g_wkv

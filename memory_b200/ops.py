@@ -675,6 +675,70 @@ def sparse_attn_weighted_bwd(q, k, v, block_indices, weights, lse_slots, d_o, bl
     return d_q, d_w_heads.sum(dim=2)
 
 
+def token_mix_supported(q: torch.Tensor, k: torch.Tensor, block_size: int, index_heads: int) -> bool:
+    """Whether the tensor-core chapter-stationary mixture takes this problem: bf16, head_dim 64, 64-row chapters,
+    whole chapters, and one chapter list per token (``index_heads`` 1) or per KV head."""
+    return (q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and q.shape[-1] == 64 and int(block_size) == 64
+            and k.shape[1] % 64 == 0 and index_heads in (1, k.shape[2]) and q.shape[2] % k.shape[2] == 0)
+
+
+def _token_mix_shape(q, k, block_indices, scale):
+    b, tq, hq, d = q.shape
+    _, tk, h, _ = k.shape
+    return L.SparseAttnShape(b, tq, tk, hq, h, d, block_indices.shape[-1], 64, float(scale), L.dtype_code(q.dtype))
+
+
+@_instrument("token_mix_fwd", 7)
+def token_mix_fwd(q, k, v, block_indices, weights, scale: float, base: Optional[torch.Tensor] = None,
+                  out_scale: float = 1.0):
+    """o = base + out_scale * sum_s w_s softmax(q K_s^T) V_s with every chapter's K / V tile stationary under the
+    query rows that selected it.  q [B,TQ,HQ,64] bf16; k / v [B,TK,H,64] (row-strided views allowed);
+    block_indices int32 [B,TQ,1 or H,S]; weights [B,TQ,S].
+    Returns (o, lse_slots fp32 [B,TQ,HQ,S], index workspace for :func:`token_mix_bwd`)."""
+    L.require_cuda(q, k, v, block_indices, weights)
+    b, tq, hq, d = q.shape
+    hi, n_sel = block_indices.shape[2], block_indices.shape[3]
+    q = _contig(q)
+    bi = _contig(block_indices)
+    ld = _kv_row_stride(k, v)
+    s = _token_mix_shape(q, k, bi, scale)
+    ws = torch.empty(L.lib().moc_token_mix_workspace_bytes(C.byref(s), hi) // 4, dtype=torch.int32, device=q.device)
+    status, stream = L.ptr(L.status_word(q.device)), L.stream_ptr(q.device)
+    L.check(L.lib().moc_token_mix_index(C.byref(s), hi, L.ptr(bi), L.ptr(ws), status, stream), "moc_token_mix_index")
+    partial = torch.empty(b * tq * n_sel * hq * d, dtype=q.dtype, device=q.device)
+    o = torch.empty_like(q)
+    lse = torch.empty(b, tq, hq, n_sel, dtype=torch.float32, device=q.device)
+    rc = L.lib().moc_token_mix_fwd(C.byref(s), hi, L.ptr(q), L.ptr(k), L.ptr(v), ld, L.ptr(bi),
+                                   L.ptr(_contig(weights.float())), L.ptr(_contig(base)), float(out_scale), L.ptr(ws),
+                                   L.ptr(partial), L.ptr(o), L.ptr(lse), status, stream)
+    L.check(rc, "moc_token_mix_fwd")
+    return o, lse, ws
+
+
+@_instrument("token_mix_bwd", 2)
+def token_mix_bwd(q, k, v, block_indices, weights, lse_slots, d_o, scale: float, out_scale: float,
+                  workspace: torch.Tensor, d_k: torch.Tensor, d_v: torch.Tensor,
+                  d_q_base: Optional[torch.Tensor] = None):
+    """Gradients of :func:`token_mix_fwd`.  ``d_k`` / ``d_v`` are zeroed bf16 tensors shaped like k / v (row-strided
+    views allowed) whose selected chapters are written; returns (d_q = d_q_base + routed part, d_w [B,TQ,S])."""
+    b, tq, hq, d = q.shape
+    hi, n_sel = block_indices.shape[2], block_indices.shape[3]
+    q, d_o = _contig(q), _contig(d_o)
+    bi = _contig(block_indices)
+    ld, ldg = _kv_row_stride(k, v), _kv_row_stride(d_k, d_v)
+    s = _token_mix_shape(q, k, bi, scale)
+    partial = torch.empty(b * tq * n_sel * hq * d, dtype=q.dtype, device=q.device)
+    d_q = torch.empty_like(q)
+    d_w_heads = torch.zeros(b, tq, hq, n_sel, dtype=torch.float32, device=q.device)
+    rc = L.lib().moc_token_mix_bwd(C.byref(s), hi, L.ptr(q), L.ptr(k), L.ptr(v), ld, L.ptr(bi),
+                                   L.ptr(_contig(weights.float())), float(out_scale), L.ptr(lse_slots), L.ptr(d_o),
+                                   L.ptr(workspace), L.ptr(partial), L.ptr(_contig(d_q_base)), L.ptr(d_q), L.ptr(d_k),
+                                   L.ptr(d_v), ldg, L.ptr(d_w_heads), L.ptr(L.status_word(q.device)),
+                                   L.stream_ptr(q.device))
+    L.check(rc, "moc_token_mix_bwd")
+    return d_q, d_w_heads.sum(dim=2)
+
+
 def _kv_row_stride(k: torch.Tensor, v: torch.Tensor) -> int:
     """Elements between consecutive rows of a [B,TK,H,D] key / value view whose (H, D) part is dense."""
     b, tk, h, d = k.shape

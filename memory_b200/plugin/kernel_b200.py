@@ -68,15 +68,23 @@ class _WeightedSparseAttention(torch.autograd.Function):
     def forward(ctx, q, k, v, bi, weights, block_size, scale):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         w32 = weights.float().contiguous()
-        o, lse_slots = ops.sparse_attn_weighted_fwd(q, k, v, bi, w32, block_size, scale)
+        mix_ws = None
+        if ops.token_mix_supported(q, k, block_size, bi.shape[2]):
+            o, lse_slots, mix_ws = ops.token_mix_fwd(q, k, v, bi, w32, scale)      # tcgen05, chapter-stationary
+        else:
+            o, lse_slots = ops.sparse_attn_weighted_fwd(q, k, v, bi, w32, block_size, scale)
         ctx.save_for_backward(q, k, v, bi, w32, lse_slots)
-        ctx.cfg = (block_size, scale, weights.dtype)
+        ctx.cfg = (block_size, scale, weights.dtype, mix_ws)
         return o
 
     @staticmethod
     def backward(ctx, g):
         q, k, v, bi, w32, lse_slots = ctx.saved_tensors
-        block_size, scale, w_dtype = ctx.cfg
+        block_size, scale, w_dtype, mix_ws = ctx.cfg
+        if mix_ws is not None:
+            d_k, d_v = torch.zeros_like(k), torch.zeros_like(v)
+            d_q, d_w = ops.token_mix_bwd(q, k, v, bi, w32, lse_slots, g.contiguous(), scale, 1.0, mix_ws, d_k, d_v)
+            return d_q, d_k, d_v, None, d_w.to(w_dtype), None, None
         d_k = torch.zeros(k.shape, dtype=torch.float32, device=k.device)
         d_v = torch.zeros(v.shape, dtype=torch.float32, device=v.device)
         d_q, d_w = ops.sparse_attn_weighted_bwd(q, k, v, bi, w32, lse_slots, g.contiguous(), block_size, scale, 1.0,

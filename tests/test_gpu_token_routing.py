@@ -155,6 +155,96 @@ def test_plugin_weighted_entry_point_values_and_gradients(dtype, dev):
         fn(qg, kg, vg, bi.to(dev), wg[:, :, :2], BS, disable_causal_mask=True)
 
 
+TC_SHAPES = {
+    "per_head_lists_multi_tile": dict(B=2, TQ=300, TK=512, HQ=4, H=2, S=3),
+    "small_ragged": dict(B=1, TQ=70, TK=256, HQ=2, H=2, S=4),
+    "gqa6_three_tiles_per_chapter": dict(B=1, TQ=520, TK=192, HQ=6, H=1, S=2),
+}
+
+
+@pytest.mark.parametrize("shape", list(TC_SHAPES))
+def test_plugin_weighted_entry_point_tensor_core_path(shape, dev):
+    """bf16, head_dim 64, 64-row chapters: the chapter-stationary tcgen05 kernels (inverted index, gathered query
+    tiles, per-pair partial outputs summed in slot order).  Chapters hold fewer than, exactly and several times
+    128 (token, slot) pairs."""
+    from memory_b200 import _lib as L
+    from memory_b200 import ops
+    from memory_b200.plugin import FSA_topk_sparse_attention_weighted_bthd as fn
+    q, k, v, bi, w, do, BS = _plugin_problem(dev, torch.bfloat16, BS=64, seed=11, **TC_SHAPES[shape])
+    assert ops.token_mix_supported(q, k, BS, bi.shape[2])
+    qc, kc, vc, wc = (t.float().clone().requires_grad_(True) for t in (q, k, v, w))
+    ref = O.weighted_chapter_attention(qc, kc, vc, bi, wc, BS)
+    ref.backward(do.float())
+    qg, kg, vg, wg = (t.to(dev).clone().requires_grad_(True) for t in (q, k, v, w))
+    seen = []
+    ops.LAUNCH_HOOK = seen.append
+    try:
+        o = fn(q_bthd=qg, k_bthd=kg, v_bthd=vg, block_indices_bths=bi.to(dev), chapter_weights_bts=wg, block_size=BS,
+               disable_causal_mask=True)
+        o.backward(do.to(dev))
+    finally:
+        ops.LAUNCH_HOOK = None
+    L.check_device_status(dev)
+    assert any(n.startswith("token_mix_fwd") for n in seen) and any(n.startswith("token_mix_bwd") for n in seen)
+    assert_close_all_forms(o, ref, BF16_FWD, "o")
+    assert_close_all_forms(qg.grad, qc.grad, BF16_BWD, "dq")
+    assert_close_all_forms(kg.grad, kc.grad, BF16_BWD, "dk")
+    assert_close_all_forms(vg.grad, vc.grad, BF16_BWD, "dv")
+    assert_close_all_forms(wg.grad, wc.grad, BF16_BWD, "dw")
+
+
+def test_token_mix_shared_lists_base_scale_and_reproducibility(dev):
+    """One chapter list per token for all heads (the module path): a base term, an output scale, a chapter that every
+    token selects (several tiles), one nobody selects (its gradient rows stay zero), bit-identical repeats, and an
+    out-of-range chapter id reported through the status word."""
+    from memory_b200 import _lib as L
+    from memory_b200 import ops
+    g = torch.Generator().manual_seed(21)
+    B, TQ, HQ, H, D, M_, S = 1, 333, 4, 2, 64, 6, 3
+    q = torch.randn(B, TQ, HQ, D, generator=g).bfloat16()
+    kv = torch.randn(B, M_ * 64, 2 * H * D, generator=g).bfloat16()            # K and V of a row share a projected row
+    bi = torch.stack([torch.cat([torch.zeros(1, dtype=torch.long), 1 + torch.randperm(M_ - 2, generator=g)[:S - 1]])
+                      for _ in range(B * TQ)]).view(B, TQ, 1, S).int()          # chapter 0 always, chapter 5 never
+    w = torch.rand(B, TQ, S, generator=g) + 0.1
+    base = torch.randn(B, TQ, HQ, D, generator=g).bfloat16()
+    do = torch.randn(B, TQ, HQ, D, generator=g).bfloat16()
+    rho = 2.5
+    k4 = kv[..., :H * D].unflatten(-1, (H, D))
+    v4 = kv[..., H * D:].unflatten(-1, (H, D))
+    qc, kc, vc, wc = (t.float().clone().requires_grad_(True) for t in (q, k4, v4, w))
+    ref = base.float() + rho * O.weighted_chapter_attention(qc, kc, vc, bi.expand(B, TQ, H, S), wc, 64)
+    ref.backward(do.float())
+    kvd = kv.to(dev)
+    k4d, v4d = kvd[..., :H * D].unflatten(-1, (H, D)), kvd[..., H * D:].unflatten(-1, (H, D))
+    scale = D ** -0.5
+
+    def run():
+        o, lse, ws = ops.token_mix_fwd(q.to(dev), k4d, v4d, bi.to(dev), w.to(dev), scale, base=base.to(dev),
+                                       out_scale=rho)
+        d_kv = torch.zeros_like(kvd)
+        dk4, dv4 = d_kv[..., :H * D].unflatten(-1, (H, D)), d_kv[..., H * D:].unflatten(-1, (H, D))
+        dq0 = torch.full_like(q, 0.5).to(dev)
+        dq, dw = ops.token_mix_bwd(q.to(dev), k4d, v4d, bi.to(dev), w.to(dev), lse, do.to(dev), scale, rho, ws, dk4,
+                                   dv4, d_q_base=dq0)
+        return o, dq, dw, d_kv
+
+    o, dq, dw, d_kv = run()
+    L.check_device_status(dev)
+    assert_close_all_forms(o, ref, BF16_FWD, "o")
+    assert_close_all_forms(dq.float() - 0.5, qc.grad, BF16_BWD, "dq")
+    assert_close_all_forms(dw, wc.grad, BF16_BWD, "dw")
+    assert_close_all_forms(d_kv[..., :H * D].unflatten(-1, (H, D)), kc.grad, BF16_BWD, "dk")
+    assert_close_all_forms(d_kv[..., H * D:].unflatten(-1, (H, D)), vc.grad, BF16_BWD, "dv")
+    assert not d_kv[:, 5 * 64:].any(), "rows of a chapter nobody selected must stay zero"
+    o2, dq2, dw2, d_kv2 = run()
+    assert torch.equal(o, o2) and torch.equal(dq, dq2) and torch.equal(dw, dw2) and torch.equal(d_kv, d_kv2)
+    bad = bi.clone()
+    bad[0, 7, 0, 1] = M_
+    ops.token_mix_fwd(q.to(dev), k4d, v4d, bad.to(dev), w.to(dev), scale)
+    with pytest.raises(RuntimeError, match="out of range"):
+        L.check_device_status(dev)
+
+
 def test_plugin_joint_entry_point_and_backward_exports(dev):
     """FSA_topk_sparse_attention_bthd (one softmax over the selected chapters) and the stand-alone
     memory_cross_attn_backward / _preprocess_delta surfaces."""
@@ -219,7 +309,7 @@ def test_reference_attention_module_runs_on_the_plugin_file(dev):
                           token_routing_kernel_version="v4")
     finally:
         ops.LAUNCH_HOOK = None
-    assert "sparse_attn_weighted_fwd:bf16" in seen, sorted(set(seen))
+    assert "token_mix_fwd:bf16" in seen, sorted(set(seen))        # 64-row chapters, head_dim 64: tensor-core mixture
     ref = O.token_routed_attention(inp["h_router"], shared, routed, idx - s, w, t, case.routed_scaling_factor,
                                    inp["wq"], inp["wk"], inp["wv"], inp["wo"], case.num_heads, case.num_kv_heads)
     assert rel_err(out, ref) < 3e-2     # the reference's own bf16 projections and output rounding are in this path
