@@ -432,6 +432,15 @@ int moc_rows_sqnorm(const float* rows, const int32_t* num_unique, int32_t tokens
 /* Element-wise helpers used by the host layer (device pointers, n elements). */
 int moc_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream);
 int moc_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream);
+/* dst bf16 [terms, n]: term t is the bf16 rounding of what terms 0..t-1 left of src (terms <= 3; three terms carry
+ * 24 mantissa bits).  Lets an fp32 projection run as sums of exact bf16 tensor-core products -- the per-token
+ * router projection nn.Linear(hidden, num_chapters) of ChapterRouter.route_token_level
+ * (memory_transformer/router.py:262-340) at [B*L, hidden] x [hidden, C]. */
+int moc_split_bf16(const float* src, void* dst, int64_t n, int32_t terms, void* stream);
+/* dst[r, c] = bias[c] + sum_t src[r, t * ld + c] (bias may be NULL): folds the column blocks that one product against
+ * the stacked terms of a split weight leaves side by side, and adds the router's bias (router.py:294). */
+int moc_sum_terms(const float* src, const float* bias, float* dst, int64_t rows, int32_t cols, int32_t ld,
+                  int32_t terms, void* stream);
 /* dst[c, r] = src[r, c] for a row-major [rows, cols] matrix, converting between the dtype codes.  Used to
  * keep the nn.Linear weights (memory_attention.py:140-143) in the K-major layout the input-gradient
  * projections want. */

@@ -108,6 +108,8 @@ _PROTOTYPES = {
     "moc_col_sum": (C.c_int, [P, P, C.c_int64, C.c_int32, P]),
     "moc_cast_f32_to_bf16": (C.c_int, [P, P, C.c_int64, P]),
     "moc_cast_bf16_to_f32": (C.c_int, [P, P, C.c_int64, P]),
+    "moc_split_bf16": (C.c_int, [P, P, C.c_int64, C.c_int32, P]),
+    "moc_sum_terms": (C.c_int, [P, P, P, C.c_int64, C.c_int32, C.c_int32, C.c_int32, P]),
     "moc_transpose": (C.c_int, [P, C.c_int32, P, C.c_int32, C.c_int32, C.c_int32, P]),
     "moc_pack_weights": (C.c_int, [C.c_int32, P, C.c_int32, P, P, P, P, P, P]),
     "moc_decode_attn": (C.c_int, [P, P, P, C.c_int64, P, P, P, P, P, P]),

@@ -771,6 +771,28 @@ extern "C" int moc_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void
   return MOC_OK;
 }
 
+// x = t0 + t1 + t2 (+ rounding below 2^-24 |x|): successive bf16 roundings of the residual.  Products of the terms
+// with bf16 operands are exact in fp32, so sums of tensor-core products over the terms reach fp32-grade accuracy.
+__global__ void split_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n,
+                                  int terms) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  float r = src[i];
+  for (int t = 0; t < terms; ++t) {
+    const __nv_bfloat16 b = __float2bfloat16_rn(r);
+    dst[t * n + i] = b;
+    r -= __bfloat162float(b);
+  }
+}
+extern "C" int moc_split_bf16(const float* src, void* dst, int64_t n, int32_t terms, void* stream_) {
+  MOC_REQUIRE(src && dst && n >= 0 && terms >= 1 && terms <= 3, "bad split arguments");
+  if (n == 0) return MOC_OK;
+  split_bf16_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      src, static_cast<__nv_bfloat16*>(dst), n, terms);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
+
 extern "C" int moc_transpose(const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, int32_t rows,
                              int32_t cols, void* stream_) {
   MOC_REQUIRE(src && dst && rows > 0 && cols > 0, "bad transpose arguments");

@@ -449,6 +449,64 @@ __global__ void loss_partial_kernel(const float* __restrict__ probs, const long 
     partial[blockIdx.x * 3 + 2] = ent;
   }
 }
+// The same statistics for many routing rows (token-level routing: B = batch * seq): the rows are cut into `splits`
+// ranges, every (chapter chunk, range) CTA leaves {sum p, sum p^2, sum p log p, count} per chapter, and a second kernel
+// adds the ranges in order before the non-linear terms are formed.
+__global__ void loss_rows_partial_kernel(const float* __restrict__ probs, const long long* __restrict__ idx,
+                                         float* __restrict__ part, int B, int C, int k_sel, int rows_per_split) {
+  __shared__ int cnt[kLossChunk];
+  const int c0 = blockIdx.x * kLossChunk;
+  const int r0 = blockIdx.y * rows_per_split, r1 = min(B, r0 + rows_per_split);
+  cnt[threadIdx.x] = 0;
+  __syncthreads();
+  for (long long i = static_cast<long long>(r0) * k_sel + threadIdx.x; i < static_cast<long long>(r1) * k_sel;
+       i += blockDim.x) {
+    const int c = static_cast<int>(idx[i]) - c0;
+    if (c >= 0 && c < kLossChunk) atomicAdd(&cnt[c], 1);
+  }
+  __syncthreads();
+  const int c = c0 + threadIdx.x;
+  if (c >= C) return;
+  float ps = 0.f, p2 = 0.f, e = 0.f;
+  for (int b = r0; b < r1; ++b) {
+    const float pv = probs[static_cast<long long>(b) * C + c];
+    ps += pv;
+    p2 += pv * pv;
+    e += pv * logf(fmaxf(pv, 1e-12f));
+  }
+  float4* dst = reinterpret_cast<float4*>(part) + static_cast<long long>(blockIdx.y) * C + c;
+  *dst = make_float4(ps, p2, e, static_cast<float>(cnt[threadIdx.x]));
+}
+__global__ void loss_rows_finish_kernel(const float* __restrict__ part, float* __restrict__ chapter_stats,
+                                        float* __restrict__ partial, int B, int C, int splits) {
+  __shared__ float red[33];
+  const int c = blockIdx.x * kLossChunk + threadIdx.x;
+  float lb = 0.f, aux = 0.f, ent = 0.f;
+  if (c < C) {
+    float ps = 0.f, p2 = 0.f, e = 0.f, n = 0.f;
+    for (int sp = 0; sp < splits; ++sp) {
+      const float4 v = reinterpret_cast<const float4*>(part)[static_cast<long long>(sp) * C + c];
+      ps += v.x; p2 += v.y; e += v.z; n += v.w;
+    }
+    const float f = n / static_cast<float>(B);
+    const float P = ps / static_cast<float>(B);
+    const float q = p2 / static_cast<float>(B);
+    chapter_stats[c] = f;
+    chapter_stats[C + c] = q;
+    lb = f * P;
+    const float dv = q - 1.f / static_cast<float>(C);
+    aux = dv * dv;
+    ent = e;
+  }
+  lb = block_sum(lb, red);
+  aux = block_sum(aux, red);
+  ent = block_sum(ent, red);
+  if (threadIdx.x == 0) {
+    partial[blockIdx.x * 3 + 0] = lb;
+    partial[blockIdx.x * 3 + 1] = aux;
+    partial[blockIdx.x * 3 + 2] = ent;
+  }
+}
 __global__ void loss_finish_kernel(const float* __restrict__ partial, const float* __restrict__ row_stats,
                                    float* __restrict__ losses, int nblk, int B, int C) {
   // one warp; every lane sums a strided share in a fixed order, then a fixed-order shuffle tree
@@ -471,6 +529,20 @@ __global__ void add_bias_kernel(float* __restrict__ logits, const float* __restr
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
     logits[i] += bias[static_cast<int>(i % C)];
+}
+// dst[r, c] = bias[c] + sum_t src[r, t * ld + c], smallest term (highest t) first
+__global__ void sum_terms_kernel(const float* __restrict__ src, const float* __restrict__ bias,
+                                 float* __restrict__ dst, long long rows, int cols, int ld, int terms) {
+  const long long total = rows * cols;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols;
+    const int c = static_cast<int>(i - r * cols);
+    const float* p = src + r * static_cast<long long>(ld) * terms + c;
+    float acc = 0.f;
+    for (int t = terms - 1; t >= 0; --t) acc += p[static_cast<long long>(t) * ld];
+    dst[i] = bias != nullptr ? acc + bias[c] : acc;
+  }
 }
 // out[c] = sum_r x[r, c]: one CTA per 32 columns, 8 row groups, fixed-order sums
 __global__ void col_sum_kernel(const float* __restrict__ x, float* __restrict__ out, long long rows, int cols) {
@@ -713,8 +785,15 @@ inline size_t ws_floats(const moc_router_shape* s, bool pool, bool dpooled) {
   const size_t dp = dpooled ? static_cast<size_t>(ceil_div(s->num_chapters, kDpChunk)) * s->batch * s->hidden_dim : 0;
   return p > dp ? p : dp;
 }
+// row ranges of the loss statistics: one for the handful of rows of sequence-level routing, ~128 rows each otherwise
+inline int loss_row_splits(const moc_router_shape* s) {
+  return s->batch <= 256 ? 1 : (ceil_div(s->batch, 128) < 64 ? ceil_div(s->batch, 128) : 64);
+}
 inline size_t loss_floats(const moc_router_shape* s) {
-  return static_cast<size_t>(ceil_div(s->num_chapters, kLossChunk)) * 3;
+  const int splits = loss_row_splits(s);
+  // (the per-range records are float4: four floats of slack let the block start on a 16-byte boundary)
+  const size_t rows_part = splits > 1 ? static_cast<size_t>(splits) * s->num_chapters * 4 + 4 : 0;
+  return static_cast<size_t>(ceil_div(s->num_chapters, kLossChunk)) * 3 + rows_part;
 }
 inline size_t ws_bytes(const moc_router_shape* s) { return (ws_floats(s, true, true) + loss_floats(s)) * sizeof(float); }
 inline int check_shape(const moc_router_shape* s) {
@@ -793,8 +872,18 @@ extern "C" int moc_router_fwd_parts(const moc_router_shape* s, const void* h, co
   if ((parts & 2) && losses != nullptr) {
     MOC_REQUIRE(chapter_stats != nullptr, "chapter_stats is NULL");
     const int nblk = ceil_div(C, kLossChunk);
-    loss_partial_kernel<<<nblk, kLossChunk, 0, stream>>>(probs, reinterpret_cast<const long long*>(idx),
-                                                         chapter_stats, loss_partial, B, C, k_sel);
+    const int splits = loss_row_splits(s);
+    if (splits > 1) {
+      float* rows_part = reinterpret_cast<float*>(
+          (reinterpret_cast<uintptr_t>(loss_partial + static_cast<size_t>(nblk) * 3) + 15) & ~uintptr_t(15));
+      const int rows_per_split = ceil_div(B, splits);
+      loss_rows_partial_kernel<<<dim3(nblk, splits), kLossChunk, 0, stream>>>(
+          probs, reinterpret_cast<const long long*>(idx), rows_part, B, C, k_sel, rows_per_split);
+      loss_rows_finish_kernel<<<nblk, kLossChunk, 0, stream>>>(rows_part, chapter_stats, loss_partial, B, C, splits);
+    } else {
+      loss_partial_kernel<<<nblk, kLossChunk, 0, stream>>>(probs, reinterpret_cast<const long long*>(idx),
+                                                           chapter_stats, loss_partial, B, C, k_sel);
+    }
     loss_finish_kernel<<<1, 32, 0, stream>>>(loss_partial, row_stats, losses, nblk, B, C);
   }
   MOC_CUDA_OK(cudaGetLastError());
@@ -911,6 +1000,18 @@ extern "C" int moc_pool_weighted_bwd(const float* d_pooled, const float* pos_wei
   return MOC_OK;
 }
 
+
+extern "C" int moc_sum_terms(const float* src, const float* bias, float* dst, int64_t rows, int32_t cols, int32_t ld,
+                             int32_t terms, void* stream_) {
+  MOC_REQUIRE(src && dst && rows >= 0 && cols > 0 && ld >= cols && terms >= 1, "bad sum_terms arguments");
+  if (rows == 0) return MOC_OK;
+  long long blocks = (rows * cols + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  sum_terms_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream_)>>>(src, bias, dst, rows, cols,
+                                                                                             ld, terms);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
 
 extern "C" int moc_col_sum(const float* x, float* out, int64_t rows, int32_t cols, void* stream_) {
   MOC_REQUIRE(x && out && rows > 0 && cols > 0, "bad column-sum arguments");

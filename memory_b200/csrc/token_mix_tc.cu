@@ -416,14 +416,40 @@ struct MixBwdParams {
   MixShape x;
   int* status;
 };
-constexpr int kBwdSmem = 4 * kTileQ + 2 * kTileKV + 1024;
+constexpr int kBwdSmem = 4 * kTileQ + 4 * kTileKV + 1024;
 constexpr uint32_t kColS = 0, kColDP = 64, kColD = 128;      // dQ reuses S's columns
+
+// The (chapter bucket, KV head) groups a CTA works through: buckets blockIdx.x, + gridDim.x, ... that hold pairs,
+// and for each the KV heads that read its index list.  The control warp and the row warps walk the same sequence.
+struct GroupIter {
+  int bkt, kh, kh_hi, first, n, kv_row;
+  __device__ __forceinline__ void seek(const MixBwdParams& p) {      // first non-empty bucket at or after bkt
+    for (; bkt < p.n_buckets; bkt += gridDim.x) {
+      first = p.bucket_off[bkt];
+      n = p.bucket_off[bkt + 1] - first;
+      if (n > 0) break;
+    }
+    if (bkt >= p.n_buckets) return;
+    const MixShape& x = p.x;
+    const int c = bkt % x.M, bh = bkt / x.M, hi = bh % x.HI, b = bh / x.HI;
+    kh = x.HI == 1 ? 0 : hi;
+    kh_hi = x.HI == 1 ? x.HK : hi + 1;
+    kv_row = b * x.TK + c * kKeys;
+  }
+  __device__ __forceinline__ void start(const MixBwdParams& p) { bkt = blockIdx.x; seek(p); }
+  __device__ __forceinline__ bool done(const MixBwdParams& p) const { return bkt >= p.n_buckets; }
+  __device__ __forceinline__ void next(const MixBwdParams& p) {
+    if (++kh < kh_hi) return;
+    bkt += gridDim.x;
+    seek(p);
+  }
+};
 
 __global__ void __launch_bounds__(kMixThreads, 2)
 token_mix_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                         MixBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t kv_bar, in_ready, sdp_bar, ds_ready, done_bar, d_read;
+  __shared__ __align__(8) uint64_t kv_bar[2], in_ready, sdp_bar, ds_ready, done_bar, d_read;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -432,14 +458,14 @@ token_mix_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
   uint8_t* q_s = base + kTileQ;
   uint8_t* pw_s = base + 2 * kTileQ;     // [Pw | dS]: the two 64-row blocks of the MN-major A operand of D
   uint8_t* ds_s = base + 3 * kTileQ;
-  uint8_t* k_s = base + 4 * kTileQ;
-  uint8_t* v_s = k_s + kTileKV;
+  uint8_t* kv_s = base + 4 * kTileQ;     // two (K, V) tile pairs: the next group's pair arrives under this group's work
   const MixShape& x = p.x;
   const int G = x.HQ / x.HK;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    mbar_init(&kv_bar, 1); mbar_init(&in_ready, kTok); mbar_init(&sdp_bar, 1); mbar_init(&ds_ready, kTok);
+    mbar_init(&kv_bar[0], 1); mbar_init(&kv_bar[1], 1);
+    mbar_init(&in_ready, kTok); mbar_init(&sdp_bar, 1); mbar_init(&ds_ready, kTok);
     mbar_init(&done_bar, 1); mbar_init(&d_read, kTok);
     fence_mbar_init();
     prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
@@ -450,165 +476,188 @@ token_mix_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
   const uint32_t tmem = tmem_slot;
   uint32_t it = 0, kvn = 0;      // tile iterations and (bucket, KV head) groups this CTA has run
   bool ok = true;
+  GroupIter gi;
+  gi.start(p);
 
-  for (int bkt = blockIdx.x; bkt < p.n_buckets && ok; bkt += gridDim.x) {
-    const int first = p.bucket_off[bkt], n = p.bucket_off[bkt + 1] - first;
-    if (n == 0) continue;
-    const int c = bkt % x.M, bh = bkt / x.M, hi = bh % x.HI, b = bh / x.HI;
-    const int kh_lo = x.HI == 1 ? 0 : hi, kh_hi = x.HI == 1 ? x.HK : hi + 1;
-    const int kv_row = b * x.TK + c * kKeys;
-    const int tiles = (n + kTok - 1) / kTok;
-    for (int kh = kh_lo; kh < kh_hi && ok; ++kh, ++kvn) {
-      if (warp == 4) {
-        const uint32_t idesc_kk = umma_idesc_bf16(kTok, kKeys, 0, 0);     // S, dP: both operands K-major
-        const uint32_t idesc_dq = umma_idesc_bf16(kTok, kD, 0, 1);        // dQ = dS K: B = K tile, MN-major
-        const uint32_t idesc_d = umma_idesc_bf16(128, 128, 1, 1);         // D = [Pw|dS]^T [dO|Q]
-        const uint64_t q_desc = umma_desc_sw128(smem_u32(q_s), 16, 1024);
-        const uint64_t do_desc = umma_desc_sw128(smem_u32(do_s), 16, 1024);
-        const uint64_t ds_desc = umma_desc_sw128(smem_u32(ds_s), 16, 1024);
-        const uint64_t k_desc = umma_desc_sw128(smem_u32(k_s), 16, 1024);
-        const uint64_t v_desc = umma_desc_sw128(smem_u32(v_s), 16, 1024);
-        const uint64_t kmn_desc = umma_desc_sw128(smem_u32(k_s), 8192, 1024);
-        const uint64_t a_d = umma_desc_sw128(smem_u32(pw_s), kTileQ, 1024);
-        const uint64_t b_d = umma_desc_sw128(smem_u32(do_s), kTileQ, 1024);
-        // K/V tiles are free once every product of the previous group has completed; D once it has been read
-        if (it > 0) ok = mbar_wait_w(&done_bar, (it - 1) & 1, &abort_flag, p.status);
-        if (ok && kvn > 0) ok = mbar_wait_w(&d_read, (kvn - 1) & 1, &abort_flag, p.status);
+  if (warp == 4) {
+    const uint32_t idesc_kk = umma_idesc_bf16(kTok, kKeys, 0, 0);     // S, dP: both operands K-major
+    const uint32_t idesc_dq = umma_idesc_bf16(kTok, kD, 0, 1);        // dQ = dS K: B = K tile, MN-major
+    const uint32_t idesc_d = umma_idesc_bf16(128, 128, 1, 1);         // D = [Pw|dS]^T [dO|Q]
+    const uint64_t q_desc = umma_desc_sw128(smem_u32(q_s), 16, 1024);
+    const uint64_t do_desc = umma_desc_sw128(smem_u32(do_s), 16, 1024);
+    const uint64_t ds_desc = umma_desc_sw128(smem_u32(ds_s), 16, 1024);
+    const uint64_t k_desc0 = umma_desc_sw128(smem_u32(kv_s), 16, 1024);
+    const uint64_t v_desc0 = umma_desc_sw128(smem_u32(kv_s) + kTileKV, 16, 1024);
+    const uint64_t kmn_desc0 = umma_desc_sw128(smem_u32(kv_s), 8192, 1024);
+    const uint64_t a_d = umma_desc_sw128(smem_u32(pw_s), kTileQ, 1024);
+    const uint64_t b_d = umma_desc_sw128(smem_u32(do_s), kTileQ, 1024);
+    constexpr uint64_t kBufOff = (2 * kTileKV) >> 4;
+    auto load_kv = [&](const GroupIter& g, uint32_t n) {
+      if (lane == 0) {
+        uint8_t* dst = kv_s + (n & 1) * 2 * kTileKV;
+        mbar_arrive_expect_tx(&kv_bar[n & 1], 2 * kTileKV);
+        tma_load_2d(dst, &tmap_k, &kv_bar[n & 1], g.kh * kD, g.kv_row);
+        tma_load_2d(dst + kTileKV, &tmap_v, &kv_bar[n & 1], g.kh * kD, g.kv_row);
+      }
+      __syncwarp();
+    };
+    if (!gi.done(p)) load_kv(gi, 0);
+    for (; !gi.done(p) && ok; ++kvn) {
+      const int iters = G * ((gi.n + kTok - 1) / kTok);
+      GroupIter nxt = gi;
+      nxt.next(p);
+      // the other K/V buffer is free once every product of the previous group has completed
+      if (it > 0) ok = mbar_wait_w(&done_bar, (it - 1) & 1, &abort_flag, p.status);
+      if (!ok) break;
+      if (!nxt.done(p)) load_kv(nxt, kvn + 1);
+      ok = mbar_wait_w(&kv_bar[kvn & 1], (kvn >> 1) & 1, &abort_flag, p.status);
+      const uint64_t boff = (kvn & 1) * kBufOff;
+      for (int u = 0; u < iters && ok; ++u, ++it) {
+        ok = mbar_wait_w(&in_ready, it & 1, &abort_flag, p.status);
         if (!ok) break;
-        if (lane == 0) {
-          mbar_arrive_expect_tx(&kv_bar, 2 * kTileKV);
-          tma_load_2d(k_s, &tmap_k, &kv_bar, kh * kD, kv_row);
-          tma_load_2d(v_s, &tmap_v, &kv_bar, kh * kD, kv_row);
-        }
-        __syncwarp();
-        ok = mbar_wait_w(&kv_bar, kvn & 1, &abort_flag, p.status);
-        for (int u = 0; u < G * tiles && ok; ++u, ++it) {
-          ok = mbar_wait_w(&in_ready, it & 1, &abort_flag, p.status);
-          if (!ok) break;
-          tc_fence_after();
-          issue_ss_one<2>(tmem + kColS, q_desc, k_desc, idesc_kk, 0u);
-          issue_ss_one<2>(tmem + kColDP, do_desc, v_desc, idesc_kk, 0u);
-          tc_commit_w(&sdp_bar);
-          ok = mbar_wait_w(&ds_ready, it & 1, &abort_flag, p.status);
-          if (!ok) break;
-          tc_fence_after();
-          issue_ss_one<128>(tmem + kColS, ds_desc, kmn_desc, idesc_dq, 0u);
-          issue_ss_mn128(tmem + kColD, a_d, b_d, idesc_d, u > 0 ? 1u : 0u);
-          tc_commit_w(&done_bar);
-        }
-      } else {
-        const int r = threadIdx.x;
-        const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
-        for (int u = 0; u < G * tiles && ok; ++u, ++it) {
-          const int hq = kh * G + u / tiles, tl = u % tiles;
-          const bool valid = tl * kTok + r < n;
-          const int pair = valid ? p.entries[first + tl * kTok + r] : 0;
-          const int s = pair % x.S;
-          const long long tokrow = (pair / x.S) / x.HI;
-          // the tiles are free: this thread has seen done_bar of the previous iteration
-          gather_row(do_s, r, p.d_o + tokrow * (x.HQ * kD) + hq * kD, valid);
-          gather_row(q_s, r, p.q + tokrow * (x.HQ * kD) + hq * kD, valid);
-          const float wv = valid ? p.w[tokrow * x.S + s] * x.out_scale : 0.f;
-          const float nl2 = valid ? -p.lse_slots[(tokrow * x.HQ + hq) * x.S + s] * kLog2e : 0.f;
-          fence_proxy_async();
-          mbar_arrive(&in_ready);
-          ok = mbar_wait(&sdp_bar, it & 1, &abort_flag, p.status);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          float pr[64];
-          float delta = 0.f;
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t rs[32], rd[32];
-            tmem_ld32(tmem + lane_sel + kColS + half * 32, rs);
-            tmem_ld32(tmem + lane_sel + kColDP + half * 32, rd);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float pj = ex2(fmaf(__uint_as_float(rs[i]), x.scale_log2, nl2));
-              delta = fmaf(pj, __uint_as_float(rd[i]), delta);
-              pr[half * 32 + i] = pj;
-            }
-          }
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t rd[32];
-            tmem_ld32(tmem + lane_sel + kColDP + half * 32, rd);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint32_t a[4], d[4];
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int e = j * 8 + 2 * i;
-                const float p0 = wv * pr[half * 32 + e], p1 = wv * pr[half * 32 + e + 1];
-                a[i] = pack_bf16x2(p0, p1);
-                d[i] = pack_bf16x2(p0 * (__uint_as_float(rd[e]) - delta), p1 * (__uint_as_float(rd[e + 1]) - delta));
-              }
-              const int chunk = ((half * 4 + j) ^ (r & 7)) << 4;
-              *reinterpret_cast<uint4*>(pw_s + r * 128 + chunk) = valid ? make_uint4(a[0], a[1], a[2], a[3])
-                                                                        : make_uint4(0u, 0u, 0u, 0u);
-              *reinterpret_cast<uint4*>(ds_s + r * 128 + chunk) = valid ? make_uint4(d[0], d[1], d[2], d[3])
-                                                                        : make_uint4(0u, 0u, 0u, 0u);
-            }
-          }
-          if (valid) p.d_w_heads[(tokrow * x.HQ + hq) * x.S + s] = x.out_scale * delta;
-          tc_fence_before();
-          fence_proxy_async();
-          mbar_arrive(&ds_ready);
-          ok = mbar_wait(&done_bar, it & 1, &abort_flag, p.status);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          __nv_bfloat16* dst = p.dq_partial + ((tokrow * x.S + s) * x.HQ + hq) * kD;
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t o[32];
-            tmem_ld32(tmem + lane_sel + kColS + half * 32, o);
-            tmem_wait_ld();
-            if (valid) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 v;
-                v.x = pack_bf16x2(__uint_as_float(o[8 * j + 0]) * x.scale, __uint_as_float(o[8 * j + 1]) * x.scale);
-                v.y = pack_bf16x2(__uint_as_float(o[8 * j + 2]) * x.scale, __uint_as_float(o[8 * j + 3]) * x.scale);
-                v.z = pack_bf16x2(__uint_as_float(o[8 * j + 4]) * x.scale, __uint_as_float(o[8 * j + 5]) * x.scale);
-                v.w = pack_bf16x2(__uint_as_float(o[8 * j + 6]) * x.scale, __uint_as_float(o[8 * j + 7]) * x.scale);
-                *reinterpret_cast<uint4*>(dst + half * 32 + j * 8) = v;
-              }
-            }
-          }
-          tc_fence_before();
-        }
+        tc_fence_after();
+        issue_ss_one<2>(tmem + kColS, q_desc, k_desc0 + boff, idesc_kk, 0u);
+        issue_ss_one<2>(tmem + kColDP, do_desc, v_desc0 + boff, idesc_kk, 0u);
+        tc_commit_w(&sdp_bar);
+        ok = mbar_wait_w(&ds_ready, it & 1, &abort_flag, p.status);
         if (!ok) break;
-        // D is complete (done_bar of the last iteration): rows 0..63 x columns 0..63 = dV_c, rows 64..127 x columns
-        // 64..127 = dK_c (before the softmax scale)
-        {
-          const int key = r & 63;
-          const bool is_k = r >= 64;
-          const float f = is_k ? x.scale : 1.f;
-          __nv_bfloat16* dst = (is_k ? p.d_k : p.d_v) + (static_cast<long long>(kv_row) + key) * p.dkv_ld + kh * kD;
+        tc_fence_after();
+        issue_ss_one<128>(tmem + kColS, ds_desc, kmn_desc0 + boff, idesc_dq, 0u);
+        if (u == 0 && kvn > 0) {        // D of the previous group has been read out
+          ok = mbar_wait_w(&d_read, (kvn - 1) & 1, &abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        issue_ss_mn128(tmem + kColD, a_d, b_d, idesc_d, u > 0 ? 1u : 0u);
+        tc_commit_w(&done_bar);
+      }
+      gi = nxt;
+    }
+  } else {
+    const int r = threadIdx.x;
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    // D of a finished group is read out after this thread has handed over the inputs of the next iteration, so
+    // that the read runs beside that iteration's S / dP products: rows 0..63 x columns 0..63 = dV_c, rows
+    // 64..127 x columns 64..127 = dK_c (before the softmax scale)
+    bool pending = false;
+    long long pend_row = 0;
+    int pend_kh = 0;
+    auto flush_d = [&]() {
+      const int key = r & 63;
+      const bool is_k = r >= 64;
+      const float f = is_k ? x.scale : 1.f;
+      __nv_bfloat16* dst = (is_k ? p.d_k : p.d_v) + (pend_row + key) * p.dkv_ld + pend_kh * kD;
+      tc_fence_after();
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t o[32];
-            tmem_ld32(tmem + lane_sel + kColD + (is_k ? 64 : 0) + half * 32, o);
-            tmem_wait_ld();
+      for (int half = 0; half < 2; ++half) {
+        uint32_t o[32];
+        tmem_ld32(tmem + lane_sel + kColD + (is_k ? 64 : 0) + half * 32, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(o[8 * j + 0]) * f, __uint_as_float(o[8 * j + 1]) * f);
+          v.y = pack_bf16x2(__uint_as_float(o[8 * j + 2]) * f, __uint_as_float(o[8 * j + 3]) * f);
+          v.z = pack_bf16x2(__uint_as_float(o[8 * j + 4]) * f, __uint_as_float(o[8 * j + 5]) * f);
+          v.w = pack_bf16x2(__uint_as_float(o[8 * j + 6]) * f, __uint_as_float(o[8 * j + 7]) * f);
+          *reinterpret_cast<uint4*>(dst + half * 32 + j * 8) = v;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&d_read);
+      pending = false;
+    };
+    for (; !gi.done(p) && ok; gi.next(p), ++kvn) {
+      const int tiles = (gi.n + kTok - 1) / kTok;
+      for (int u = 0; u < G * tiles && ok; ++u, ++it) {
+        const int hq = gi.kh * G + u / tiles, tl = u % tiles;
+        const bool valid = tl * kTok + r < gi.n;
+        const int pair = valid ? p.entries[gi.first + tl * kTok + r] : 0;
+        const int s = pair % x.S;
+        const long long tokrow = (pair / x.S) / x.HI;
+        // the tiles are free: this thread has seen done_bar of the previous iteration
+        gather_row(do_s, r, p.d_o + tokrow * (x.HQ * kD) + hq * kD, valid);
+        gather_row(q_s, r, p.q + tokrow * (x.HQ * kD) + hq * kD, valid);
+        const float wv = valid ? p.w[tokrow * x.S + s] * x.out_scale : 0.f;
+        const float nl2 = valid ? -p.lse_slots[(tokrow * x.HQ + hq) * x.S + s] * kLog2e : 0.f;
+        fence_proxy_async();
+        mbar_arrive(&in_ready);
+        if (pending) flush_d();
+        ok = mbar_wait(&sdp_bar, it & 1, &abort_flag, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        float pr[64];
+        float delta = 0.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t rs[32], rd[32];
+          tmem_ld32(tmem + lane_sel + kColS + half * 32, rs);
+          tmem_ld32(tmem + lane_sel + kColDP + half * 32, rd);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float pj = ex2(fmaf(__uint_as_float(rs[i]), x.scale_log2, nl2));
+            delta = fmaf(pj, __uint_as_float(rd[i]), delta);
+            pr[half * 32 + i] = pj;
+          }
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t rd[32];
+          tmem_ld32(tmem + lane_sel + kColDP + half * 32, rd);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t a[4], d[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int e = j * 8 + 2 * i;
+              const float p0 = wv * pr[half * 32 + e], p1 = wv * pr[half * 32 + e + 1];
+              a[i] = pack_bf16x2(p0, p1);
+              d[i] = pack_bf16x2(p0 * (__uint_as_float(rd[e]) - delta), p1 * (__uint_as_float(rd[e + 1]) - delta));
+            }
+            const int chunk = ((half * 4 + j) ^ (r & 7)) << 4;
+            *reinterpret_cast<uint4*>(pw_s + r * 128 + chunk) = valid ? make_uint4(a[0], a[1], a[2], a[3])
+                                                                      : make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(ds_s + r * 128 + chunk) = valid ? make_uint4(d[0], d[1], d[2], d[3])
+                                                                      : make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+        if (valid) p.d_w_heads[(tokrow * x.HQ + hq) * x.S + s] = x.out_scale * delta;
+        tc_fence_before();
+        fence_proxy_async();
+        mbar_arrive(&ds_ready);
+        ok = mbar_wait(&done_bar, it & 1, &abort_flag, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        __nv_bfloat16* dst = p.dq_partial + ((tokrow * x.S + s) * x.HQ + hq) * kD;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t o[32];
+          tmem_ld32(tmem + lane_sel + kColS + half * 32, o);
+          tmem_wait_ld();
+          if (valid) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(o[8 * j + 0]) * f, __uint_as_float(o[8 * j + 1]) * f);
-              v.y = pack_bf16x2(__uint_as_float(o[8 * j + 2]) * f, __uint_as_float(o[8 * j + 3]) * f);
-              v.z = pack_bf16x2(__uint_as_float(o[8 * j + 4]) * f, __uint_as_float(o[8 * j + 5]) * f);
-              v.w = pack_bf16x2(__uint_as_float(o[8 * j + 6]) * f, __uint_as_float(o[8 * j + 7]) * f);
+              v.x = pack_bf16x2(__uint_as_float(o[8 * j + 0]) * x.scale, __uint_as_float(o[8 * j + 1]) * x.scale);
+              v.y = pack_bf16x2(__uint_as_float(o[8 * j + 2]) * x.scale, __uint_as_float(o[8 * j + 3]) * x.scale);
+              v.z = pack_bf16x2(__uint_as_float(o[8 * j + 4]) * x.scale, __uint_as_float(o[8 * j + 5]) * x.scale);
+              v.w = pack_bf16x2(__uint_as_float(o[8 * j + 6]) * x.scale, __uint_as_float(o[8 * j + 7]) * x.scale);
               *reinterpret_cast<uint4*>(dst + half * 32 + j * 8) = v;
             }
           }
-          tc_fence_before();
-          mbar_arrive(&d_read);
         }
+        tc_fence_before();
       }
+      if (!ok) break;
+      pending = true;        // D of this group is complete: done_bar of its last iteration has been seen
+      pend_row = gi.kv_row;
+      pend_kh = gi.kh;
     }
+    if (ok && pending) flush_d();
   }
   tc_fence_before();
   __syncthreads();

@@ -615,6 +615,19 @@ def memory_layer(h_router: torch.Tensor, h_attn: torch.Tensor, bank: torch.Tenso
 # --------------------------------------------------------------------------------------------
 # token-level routing (every token selects its own chapters)
 # --------------------------------------------------------------------------------------------
+def _weight_grad_splits(cd, rows: int, out_rows: int, out_cols: int) -> int:
+    """K-splits of a weight-gradient projection dW[out_rows, out_cols] = dY^T X over ``rows``: enough (tile, split)
+    items to fill the SMs once (tensor-core kernel only; the splits add into a zeroed fp32 output)."""
+    if cd != torch.bfloat16:
+        return 1
+    tiles = -(-out_rows // 128) * -(-out_cols // 256)
+    return max(1, min(148 // max(tiles, 1), rows // 512))
+
+
+# rows * chapters * hidden above which a bf16 model's token router projects on the tensor cores (split fp32 weight)
+_SPLIT_ROUTER_MIN_WORK = 1 << 27
+
+
 class _RouteTokens(torch.autograd.Function):
     """ChapterRouter.route_token_level (router.py:262-340): logits of every token by an fp32 projection, then the
     same softmax / prefix mask / top-k / renormalisation / loss kernels as the sequence router with one routing
@@ -624,11 +637,25 @@ class _RouteTokens(torch.autograd.Function):
     def forward(ctx, h, weight, bias, top_k, num_shared, with_losses):
         b, l, d = h.shape
         rows = b * l
-        h32 = ops.cast(h.reshape(rows, d).contiguous(), torch.float32)
+        h2 = h.reshape(rows, d).contiguous()
+        h32 = ops.cast(h2, torch.float32)
         w32 = weight.float().contiguous()
-        logits = ops.gemm(h32, w32, tag="token_router_logits")                     # [rows, C] fp32, no bias yet
-        r = ops.router_fwd(h32.view(rows, 1, d), w32, bias, top_k, num_shared, 1.0, with_losses, pooled=h32,
-                           logits=logits)
+        c = w32.shape[0]
+        split = None
+        if h.dtype == torch.bfloat16 and d % 8 == 0 and rows * c * d >= _SPLIT_ROUTER_MIN_WORK:
+            # bf16 activations are exact bf16 numbers: logits = h (w0 + w1 + w2)^T as three tensor-core products
+            # accumulated in fp32 (smallest term first) carry the fp32 weight's 24 mantissa bits
+            cp = -(-c // 8) * 8
+            w_terms = ops.split_bf16(w32 if cp == c else torch.nn.functional.pad(w32, (0, 0, 0, cp - c)), 3)
+            parts = ops.gemm(h2, w_terms.view(3 * cp, d), out_dtype=torch.float32, tag="token_router_logits")
+            logits = ops.sum_terms(parts, c, 3, bias=None if bias is None else bias.float())
+            del parts
+            split = (h2, w_terms, cp)
+        else:
+            logits = ops.gemm(h32, w32, tag="token_router_logits")                 # [rows, C] fp32, no bias yet
+        ctx.split = split
+        r = ops.router_fwd(h32.view(rows, 1, d), w32, None if split is not None else bias, top_k, num_shared, 1.0,
+                           with_losses, pooled=h32, logits=logits)      # (the split path has added the bias)
         k = r["idx"].shape[1]
         ctx.cfg = ((b, l, d), h.dtype, int(top_k), int(num_shared), bias is not None)
         ctx.internals = {n: r[n] for n in ("pooled", "probs", "idx", "row_stats", "chapter_stats", "_ws", "comb_w")}
@@ -651,10 +678,24 @@ class _RouteTokens(torch.autograd.Function):
         d_logits = r["d_logits"]
         h32 = saved["pooled"]
         d_h = d_w = d_b = None
-        if ctx.needs_input_grad[0]:
-            d_h = ops.gemm(d_logits, w32, b_kmajor=False, tag="token_router_dh").view(b, l, d).to(h_dtype)
-        if ctx.needs_input_grad[1]:
-            d_w = ops.gemm(d_logits, h32, a_kmajor=False, b_kmajor=False, tag="token_router_dw")
+        if ctx.split is not None:
+            h2, w_terms, cp = ctx.split
+            c = w32.shape[0]
+            dl = d_logits if cp == c else torch.nn.functional.pad(d_logits, (0, cp - c))
+            dl_terms = ops.split_bf16(dl, 3)                                       # [3, rows, cp]
+            if ctx.needs_input_grad[0]:
+                # the gradient leaves in bf16: one product of the leading terms
+                d_h = ops.gemm(dl_terms[0], w_terms[0], b_kmajor=False, tag="token_router_dh").view(b, l, d)
+            if ctx.needs_input_grad[1]:
+                for t in (2, 1, 0):
+                    d_w = ops.gemm(dl_terms[t], h2, a_kmajor=False, b_kmajor=False, out=d_w, out_dtype=torch.float32,
+                                   accumulate=d_w is not None, tag="token_router_dw")
+                d_w = d_w[:c]
+        else:
+            if ctx.needs_input_grad[0]:
+                d_h = ops.gemm(d_logits, w32, b_kmajor=False, tag="token_router_dh").view(b, l, d).to(h_dtype)
+            if ctx.needs_input_grad[1]:
+                d_w = ops.gemm(d_logits, h32, a_kmajor=False, b_kmajor=False, tag="token_router_dw")
         if has_bias and ctx.needs_input_grad[2]:
             d_b = ops.col_sum(d_logits)
         return d_h, d_w, d_b, None, None, None
@@ -747,7 +788,8 @@ class _TokenRoutedAttention(torch.autograd.Function):
         f32 = torch.float32
         g2 = ops.cast(g.reshape(rows, -1).contiguous(), cd)
         d_comb = ops.gemm(g2, wo_c, b_kmajor=False, tag="d_attn_out")                   # [rows, H*D]
-        d_wo = ops.gemm(g2, comb, a_kmajor=False, b_kmajor=False, out_dtype=f32, tag="d_wo")
+        d_wo = ops.gemm(g2, comb, a_kmajor=False, b_kmajor=False, out_dtype=f32,
+                        split_k=_weight_grad_splits(cd, rows, wo_c.shape[0], wo_c.shape[1]), tag="d_wo")
         d_q = None
         d_wkv = None
         d_shared = d_routed = d_weights = None
@@ -759,7 +801,8 @@ class _TokenRoutedAttention(torch.autograd.Function):
             d_q = d_q_sh.view(rows + pad, -1)[:rows].contiguous()
             d_kv_sh2 = d_kv_sh.view(kv_sh.shape[0], -1)
             d_shared = ops.gemm(d_kv_sh2, wkv_c, b_kmajor=False, tag="d_shared_mem").to(sh_dtype)
-            d_wkv = ops.gemm(d_kv_sh2, sm2, a_kmajor=False, b_kmajor=False, out_dtype=f32, tag="d_wkv_shared")
+            d_wkv = ops.gemm(d_kv_sh2, sm2, a_kmajor=False, b_kmajor=False, out_dtype=f32,
+                             split_k=_weight_grad_splits(cd, sm2.shape[0], 2 * dkv, d), tag="d_wkv_shared")
         if ctx.rt is not None:
             rm2, kv_rt, bidx, w2, lse_slots, n_rt, mix_ws = ctx.rt
             k4 = kv_rt[:, :dkv].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
@@ -780,12 +823,14 @@ class _TokenRoutedAttention(torch.autograd.Function):
             d_q = d_q.view(rows, -1)
             d_weights = d_w.view(b, l, -1).to(w_dtype)
             d_routed = ops.gemm(d_kv_c, wkv_c, b_kmajor=False, tag="d_routed_mem").to(rt_dtype)
-            g_wkv = ops.gemm(d_kv_c, rm2, a_kmajor=False, b_kmajor=False, out_dtype=f32, tag="d_wkv_routed")
+            g_wkv = ops.gemm(d_kv_c, rm2, a_kmajor=False, b_kmajor=False, out_dtype=f32,
+                             split_k=_weight_grad_splits(cd, n_rt, 2 * dkv, d), tag="d_wkv_routed")
             d_wkv = g_wkv if d_wkv is None else d_wkv + g_wkv
         if d_q is None:
             d_q = q.new_zeros(rows, d)
         d_h = ops.gemm(d_q, wq_c, b_kmajor=False, tag="d_h").view(b, l, d).to(h_dtype)
-        d_wq = ops.gemm(d_q, h2, a_kmajor=False, b_kmajor=False, out_dtype=f32, tag="d_wq")
+        d_wq = ops.gemm(d_q, h2, a_kmajor=False, b_kmajor=False, out_dtype=f32,
+                        split_k=_weight_grad_splits(cd, rows, d, d), tag="d_wq")
         if d_wkv is None:
             d_wkv = torch.zeros(2 * dkv, d, dtype=f32, device=q.device)
         return (d_h, d_shared, d_routed, None, d_weights, d_wq.to(wdt[0]), d_wkv[:dkv].to(wdt[1]),

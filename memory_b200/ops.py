@@ -783,6 +783,49 @@ def cast(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return _cast(t, dtype)
 
 
+@_instrument("split_bf16", 1)
+def split_bf16(t: torch.Tensor, terms: int = 3) -> torch.Tensor:
+    """bf16 [terms, *t.shape] with t == sum of the terms to 2^-24 relative (terms = 3): successive roundings of the
+    residual.  Sums of bf16 tensor-core products over the terms reproduce an fp32 product to fp32-grade accuracy."""
+    L.require_cuda(t)
+    if t.dtype != torch.float32:
+        raise TypeError("split_bf16 takes an fp32 tensor")
+    t = _contig(t)
+    out = torch.empty((terms,) + tuple(t.shape), dtype=torch.bfloat16, device=t.device)
+    L.check(L.lib().moc_split_bf16(L.ptr(t), L.ptr(out), t.numel(), int(terms), L.stream_ptr(t.device)),
+            "moc_split_bf16")
+    return out
+
+
+@_instrument("sum_terms", 1)
+def sum_terms(src: torch.Tensor, cols: int, terms: int, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dst[r, c] = bias[c] + sum_t src[r, t * ld + c] for fp32 src [rows, terms * ld] (smallest term, highest t,
+    first)."""
+    L.require_cuda(src)
+    src = _contig(src)
+    rows, ld = src.shape[0], src.shape[1] // terms
+    out = torch.empty(rows, cols, dtype=torch.float32, device=src.device)
+    L.check(L.lib().moc_sum_terms(L.ptr(src), L.ptr(_contig(bias)), L.ptr(out), rows, int(cols), ld, int(terms),
+                                  L.stream_ptr(src.device)), "moc_sum_terms")
+    return out
+
+
+def gemm_split(a: torch.Tensor, b: torch.Tensor, *, a_kmajor: bool = True, b_kmajor: bool = True,
+               out_dtype: torch.dtype = torch.float32, tag: Optional[str] = None) -> torch.Tensor:
+    """fp32-grade C = op(A) op(B) on the tensor cores: an fp32 operand is split into three bf16 terms, a bf16 operand
+    is taken as it is, and the partial products (smallest first) accumulate in one fp32 output.  Pairs of terms whose
+    product lies below 2^-24 of the leading one are left out."""
+    ta = split_bf16(a, 3) if a.dtype == torch.float32 else a.unsqueeze(0)
+    tb = split_bf16(b, 3) if b.dtype == torch.float32 else b.unsqueeze(0)
+    pairs = sorted(((i, j) for i in range(ta.shape[0]) for j in range(tb.shape[0]) if i + j <= 2),
+                   key=lambda ij: -(ij[0] + ij[1]))
+    out = None
+    for i, j in pairs:
+        out = gemm(ta[i], tb[j], a_kmajor=a_kmajor, b_kmajor=b_kmajor, out=out, out_dtype=torch.float32,
+                   accumulate=out is not None, tag=tag)
+    return out if out_dtype == torch.float32 else cast(out, out_dtype)
+
+
 @_instrument("cast", 1)
 def _cast(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     L.require_cuda(t)

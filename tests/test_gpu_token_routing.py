@@ -94,6 +94,56 @@ def test_token_layer_bf16_matches_reference_golden(dev):
         assert_close_all_forms(g, torch.from_numpy(gold[k]), BF16_BWD, k)
 
 
+def test_token_router_split_weight_projection_on_the_tensor_cores(dev):
+    """bf16 activations, fp32 router, large enough for the split-weight tensor-core projection (4,097-style odd
+    chapter count: padded operands).  Selection is held to fp64 (exact top-k up to 16-ulp ties), weights and losses
+    to fp32 tolerances, the weight gradient to 1e-4 and the bf16 hidden-state gradient to 1e-2."""
+    import memory_b200 as M
+    from memory_b200 import _lib as L
+    from memory_b200 import ops
+    g = torch.Generator().manual_seed(77)
+    B, Lq, d, C, k, S = 2, 512, 256, 1025, 8, 1
+    h = torch.randn(B, Lq, d, generator=g).bfloat16()
+    W = torch.randn(C, d, generator=g) * 0.05
+    bias = torch.randn(C, generator=g) * 0.1
+    hc, wc, bc = h.float().clone().requires_grad_(True), W.clone().requires_grad_(True), bias.clone().requires_grad_(True)
+    idx, w, losses = O.route_token_level(hc, wc, bc, k, S, True)
+    g_w = torch.randn(w.shape, generator=g)
+    coef = {"load_balance": 0.3, "auxiliary": 50.0, "z_loss": 0.2, "entropy": 0.1}
+    (sum(coef[n] * losses[n] for n in coef) + (w * g_w).sum()).backward()
+
+    hg = h.to(dev).requires_grad_(True)
+    wg, bg = W.to(dev).requires_grad_(True), bias.to(dev).requires_grad_(True)
+    seen = []
+    ops.LAUNCH_HOOK = seen.append
+    try:
+        gi, gw, gl = M.route_tokens(hg, wg, bg, k, S, True)
+        (sum(coef[n] * gl[n] for n in coef) + (gw * g_w.to(dev)).sum()).backward()
+    finally:
+        ops.LAUNCH_HOOK = None
+    L.check_device_status(dev)
+    assert "split_bf16:f32" in seen and "gemm:bf16" in seen and "gemm:f32" not in seen, sorted(set(seen))
+    # selection against fp64
+    z = h.double().reshape(-1, d) @ W.double().t() + bias.double()
+    p = torch.softmax(z, -1)
+    p[:, :S] = 0
+    gi2 = gi.reshape(-1, k).cpu()
+    sel = torch.gather(p, 1, gi2)
+    tau = 16 * float(np.finfo(np.float32).eps)
+    assert (sel[:, :-1] >= sel[:, 1:] * (1 - tau)).all()
+    rest = p.clone()
+    rest.scatter_(1, gi2, 0.0)
+    assert (rest.max(-1).values <= sel[:, -1] * (1 + tau)).all(), "an unselected chapter outranks a selected one"
+    same = (gi.cpu() == idx).all(-1).reshape(-1)
+    assert same.float().mean() > 0.999, "ids differ from the fp32 oracle beyond rare ulp-level ties"
+    assert rel_err(gw.reshape(-1, k)[same.to(dev)], w.reshape(-1, k)[same]) < 1e-5
+    for n in coef:
+        np.testing.assert_allclose(gl[n].item(), losses[n].item(), rtol=2e-5, atol=1e-8, err_msg=n)
+    assert_close_all_forms(wg.grad, wc.grad, 1e-4, "d_router_w")
+    assert_close_all_forms(bg.grad, bc.grad, 1e-4, "d_router_b")
+    assert rel_err(hg.grad, hc.grad) < 1e-2
+
+
 def test_token_router_empty_selection_and_errors(dev):
     import memory_b200 as M
     router = M.ChapterRouter(32, 4, top_k=2).to(dev)
