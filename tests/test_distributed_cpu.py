@@ -76,8 +76,9 @@ def _worker(rank, world, port, q):
         torch.testing.assert_close(_dense_of(bank_async.entries), _dense_of(reduced.entries))
         uniq, n, rows, t = reduced.entries[0]
         got = _dense_of(reduced.entries)
-        q.put((rank, got, [d for d in dense if d is not None], uniq[:int(n)].tolist(), red.last_union_size,
-               [d for d in want_dense if d is not None]))
+        # numpy arrays travel by value; a tensor would travel as a file descriptor that dies with this process
+        q.put((rank, got.numpy(), [d.numpy() for d in dense if d is not None], uniq[:int(n)].tolist(),
+               red.last_union_size, [d.numpy() for d in want_dense if d is not None]))
     finally:
         dist.destroy_process_group()
 
@@ -90,6 +91,8 @@ def test_sparse_bank_gradient_reduction_world2():
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in range(world)]
+    results = [(r, torch.from_numpy(got), [torch.from_numpy(d) for d in dense], uniq, usize,
+                [torch.from_numpy(d) for d in want]) for r, got, dense, uniq, usize, want in results]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
