@@ -495,6 +495,87 @@ def run_kernels_mode(args):
     print(json.dumps({"kernels": res, "batch": b, "shape": "L 1024, 12 x 64 heads, 4160 keys per sequence, bf16"}))
 
 
+TOKEN_LEVEL = dict(batch=4, seq=2048, hidden_dim=768, num_heads=12, num_kv_heads=12, num_chapters=4097,
+                   tokens_per_chapter=64, top_k=16, num_shared_chapters=1, routed_scaling_factor=2.5)
+
+
+def run_token_mode(args):
+    """``--token-level``: the token-level routing variant of the layer (every token selects its own top-16 of 4,096
+    routed chapters plus the shared one; B 4, L 2048, d 768, 12 x 64 heads, bf16 activations, fp32 router and bank)
+    through the module API -- ``ChapterRouter.route_token_level`` + ``MemoryCrossAttention(token_routing_state=...)``,
+    forward and backward.  CUDA-event timed; prints one JSON object (a measurement of that variant, not the
+    benchmark line): step time, tokens/s, per-operator device time, and the HBM roofline of the two mixture
+    kernels.  ``--token-batch`` shrinks the batch (a profiler capture wants a small footprint)."""
+    import memory_b200 as M
+    from memory_b200 import _lib as L, ops
+    from memory_b200.build import build
+    build()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    cfg = dict(TOKEN_LEVEL, batch=args.token_batch)
+    b, l, d, h = cfg["batch"], cfg["seq"], cfg["hidden_dim"], cfg["num_heads"]
+    c, t, k, s = cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["top_k"], cfg["num_shared_chapters"]
+    torch.manual_seed(0)
+    bank_shared = (torch.randn(s * t, d, device=dev) * 0.02).requires_grad_(True)
+    bank_routed = (torch.randn((c - s) * t, d, device=dev) * 0.02).requires_grad_(True)
+    router = M.ChapterRouter(d, c, top_k=k, routing_strategy="token").to(dev)
+    attn = M.MemoryCrossAttention(d, h, wo_init_zero=False, compute_dtype=torch.bfloat16).to(dev)
+    params = [bank_shared, bank_routed] + list(router.parameters()) + list(attn.parameters())
+    hs = [torch.randn(b, l, d, device=dev).bfloat16().requires_grad_(True) for _ in range(2)]
+    gs = [torch.randn(b, l, d, device=dev).bfloat16() for _ in range(2)]
+
+    def step(i):
+        for p_ in params:
+            p_.grad = None
+        hs[i % 2].grad = None
+        idx, w, losses = router.route_token_level(hs[i % 2], return_losses=True, exclude_prefix_chapters=s)
+        state = {"shared_memory": bank_shared, "routed_memory": bank_routed,
+                 "token_chapter_indices": (idx - s).to(torch.int32), "tokens_per_chapter": t,
+                 "routed_scale": cfg["routed_scaling_factor"], "chapter_weights": w}
+        out, _ = attn(hs[i % 2], None, token_routing_state=state)
+        torch.autograd.backward([out, losses["load_balance"]], [gs[i % 2], torch.full_like(losses["load_balance"], 0.01)])
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    L.check_device_status(dev)
+    steps = min(args.steps, 20)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    ops.TIMER = {}
+    step(0)
+    torch.cuda.synchronize()
+    table = {n: round(sum(a.elapsed_time(z) for a, z in v), 4) for n, v in ops.TIMER.items()}
+    ops.TIMER = None
+    L.check_device_status(dev)
+    peaks = measured_peaks()
+    pairs = b * l * k
+    kv_bytes = (c - s) * t * 2 * d * 2            # the projected routed bank, bf16 K and V rows
+    act = b * l * d * 2
+    # compulsory traffic: forward reads every K/V tile once (each chapter is selected), Q once, writes the output;
+    # backward reads K/V, Q, dO and writes dK/dV of every selected chapter and dQ
+    alg = {"token_mix_fwd": kv_bytes + 2 * act + pairs * 8, "token_mix_bwd": 2 * kv_bytes + 3 * act + pairs * 12}
+    roof = {}
+    for n, by in alg.items():
+        if n in table:
+            gbs = by / (table[n] * 1e-3) / 1e9
+            roof[n] = {"bound": "hbm", "algorithmic_bytes": by, "ms": table[n], "achieved": round(gbs, 1),
+                       "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
+                       "peak_source": peaks["source"],
+                       "what": "index build + chapter-stationary tcgen05 kernel + slot sum" if n.endswith("fwd")
+                               else "chapter-stationary tcgen05 kernel + slot sum of the dQ partials"}
+    print(json.dumps({"workload": "token-level routing variant of the memory layer, forward + backward", "config": cfg,
+                      "ms_per_step": round(ms, 4), "tokens_per_s": round(b * l / (ms * 1e-3), 1), "steps": steps,
+                      "dtype": "bf16", "data": "synthetic", "pairs_per_step": pairs,
+                      "operator_ms": dict(sorted(table.items(), key=lambda kv: -kv[1])),
+                      "roofline": roof, "max_memory_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2)}))
+
+
 def verify_against_oracle(runner, cfg, h, device):
     """One-shot check, outside every timed region, of the very tensors the timed steps use: the CUDA layer's
     forward on ``h`` against the CPU oracle's (fp32, eager).  The benchmark draws its router weight from N(0, 0.02),
@@ -804,9 +885,15 @@ def main():
     ap.add_argument("--only", default="", help="--kernels: comma-separated kernel names")
     ap.add_argument("--iters", type=int, default=5, help="--kernels: launches per kernel")
     ap.add_argument("--kernels-batch", type=int, default=8)
+    ap.add_argument("--token-level", action="store_true",
+                    help="measure the token-level routing variant (top-16 chapters per token) and exit")
+    ap.add_argument("--token-batch", type=int, default=4, help="--token-level: sequences of 2,048 tokens")
     args = ap.parse_args()
     if args.kernels:
         run_kernels_mode(args)
+        return
+    if args.token_level:
+        run_token_mode(args)
         return
     if args.warmup < 3 and args.impl == "cuda":
         args.warmup = 3

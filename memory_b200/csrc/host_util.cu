@@ -2,6 +2,8 @@
 #include <string>
 
 #define MOC_KERNEL_TAG 4
+#include <cstdio>
+
 #include "moc_common.cuh"
 
 namespace moc {
@@ -45,11 +47,28 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_
   cuuint64_t strides[1] = {row_stride_elems * 2};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
+  // The encoder is a driver-API call and needs a context current on the calling thread.  A thread that has made no
+  // runtime call yet has none -- e.g. an autograd worker thread whose first operation of a backward pass is one of
+  // these projections on device 0 (the framework then has no reason to switch devices): bind the primary context of
+  // the thread's current device once per thread.
+  thread_local bool context_bound = false;
+  if (!context_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) cudaFree(nullptr);
+    context_bound = true;
+  }
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    set_last_error("cuTensorMapEncodeTiled", "encode failed");
+    // say what was asked for, and whether an earlier asynchronous error is what the driver is reporting
+    char msg[320];
+    const cudaError_t pending = cudaPeekAtLastError();
+    snprintf(msg, sizeof(msg), "encode failed (CUresult %d; base %p, rows %llu, cols %llu, row stride %llu, box %u x %u; "
+             "pending runtime error: %s)", static_cast<int>(r), base, static_cast<unsigned long long>(rows),
+             static_cast<unsigned long long>(cols), static_cast<unsigned long long>(row_stride_elems), box_rows,
+             box_cols, cudaGetErrorString(pending));
+    set_last_error("cuTensorMapEncodeTiled", msg);
     return MOC_ERR_CUDA;
   }
   return MOC_OK;

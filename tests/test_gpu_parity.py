@@ -1,6 +1,8 @@
 """GPU parity: the CUDA path (through the C ABI) against the reference's outputs stored as golden
 fixtures and against the CPU oracle.  Bars: chapter indices bit-exact, fp32 within 1e-4 relative
 (5e-4 for gradients, the reference harness's own fp32 bar), bf16 within 2e-2 relative."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -642,3 +644,27 @@ def test_bank_adamw_from_compact_gradient_matches_torch_adamw(dev):
         assert rel_err(opt.exp_avg, st["exp_avg"]) < 1e-6 and rel_err(opt.exp_avg_sq, st["exp_avg_sq"]) < 1e-6
         assert torch.equal(shadow, p.bfloat16())
     assert int(opt.state_dict()["step"]) == 3
+
+
+def test_backward_entered_first_on_a_fresh_autograd_thread():
+    """out.backward(g) with nothing else in the graph: the first device call an autograd worker thread makes is then
+    the tensor-map encoder of a projection (a driver-API call), which must find a context on that thread.  Run in a
+    child process: the worker threads of this one have long made runtime calls."""
+    import subprocess
+    import sys
+    code = (
+        "import torch, memory_b200 as M\n"
+        "from memory_b200 import functional as F, _lib as L\n"
+        "dev = torch.device('cuda:0')\n"
+        "x = torch.randn(256, 128, device=dev).bfloat16().requires_grad_(True)\n"
+        "w = (torch.randn(64, 128, device=dev) * 0.1).bfloat16().requires_grad_(True)\n"
+        "y = F.linear(x, w)\n"
+        "g = torch.randn(256, 64, device=dev).bfloat16()\n"
+        "y.backward(g)\n"
+        "torch.cuda.synchronize(); L.check_device_status(dev)\n"
+        "ref = g.float() @ w.float()\n"
+        "assert (x.grad.float() - ref).abs().max() <= 2e-2 * ref.abs().max()\n"
+        "print('ok')\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
