@@ -305,6 +305,11 @@ int moc_attn_bwd_parts(const moc_attn_shape* s, const void* q, const void* kv, c
 int moc_attn_bwd_scaled(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
                         const void* d_o, void* d_q, void* d_kv, float* delta, const float* kv_row_scale,
                         float* kv_dot, int32_t* status, void* stream);
+/* The same in pieces (parts as in moc_attn_bwd_parts: 1 = per-row constants, 2 = dQ, 4 = dK/dV; kv_row_scale may be
+ * NULL): lets a caller run the dQ kernel and the dK/dV kernel on different streams once the constants are there. */
+int moc_attn_bwd_scaled_parts(const moc_attn_shape* s, const void* q, const void* kv, const void* o, const float* lse,
+                              const void* d_o, void* d_q, void* d_kv, float* delta, const float* kv_row_scale,
+                              float* kv_dot, int32_t parts, int32_t* status, void* stream);
 
 /* moc_attn_bwd without caller-provided scratch and without any allocation.  It has no counterpart in the
  * reference.  It exists for callers that are not allowed to allocate device memory when they run the

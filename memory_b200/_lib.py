@@ -81,6 +81,7 @@ _PROTOTYPES = {
     "moc_attn_bwd": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P, P, P, P, P]),
     "moc_attn_bwd_parts": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P, P, P, C.c_int32, P, P]),
     "moc_attn_bwd_scaled": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P, P, P, P, P, P, P]),
+    "moc_attn_bwd_scaled_parts": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P, P, P, P, P, C.c_int32, P, P]),
     "moc_gemm_gather_b": (C.c_int, [C.POINTER(GemmDesc), P, P, P, P, P, C.c_int32, C.c_int64, P, P]),
     "moc_row_inv_rms": (C.c_int, [P, C.c_int32, C.c_int64, C.c_int32, C.c_float, P, P]),
     "moc_chapter_row_scale": (C.c_int, [P, P, P, C.c_int64, C.c_int32, C.c_int32, P, P, P]),

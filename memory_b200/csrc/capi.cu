@@ -111,6 +111,18 @@ extern "C" int moc_gemm_gather_b(const moc_gemm_desc* g, const void* a, const vo
                         b_block_rows, b_stored_rows);
 }
 
+extern "C" int moc_attn_bwd_scaled_parts(const moc_attn_shape* s, const void* q, const void* kv, const void* o,
+                                         const float* lse, const void* d_o, void* d_q, void* d_kv, float* delta,
+                                         const float* kv_row_scale, float* kv_dot, int32_t parts, int32_t* status,
+                                         void* stream_) {
+  int rc = check_attn(s);
+  if (rc != MOC_OK) return rc;
+  MOC_REQUIRE(q && kv && o && lse && d_o && d_q && d_kv && delta && status, "NULL attention buffer");
+  MOC_REQUIRE(s->dtype == MOC_BF16, "the row-scaled backward exists for the bf16 kernels only");
+  return launch_attn_tc_bwd(s, q, kv, o, lse, d_o, d_q, d_kv, delta, status, static_cast<cudaStream_t>(stream_),
+                            parts, kv_row_scale, kv_dot);
+}
+
 extern "C" int moc_attn_bwd_scaled(const moc_attn_shape* s, const void* q, const void* kv, const void* o,
                                    const float* lse, const void* d_o, void* d_q, void* d_kv, float* delta,
                                    const float* kv_row_scale, float* kv_dot, int32_t* status, void* stream_) {

@@ -13,6 +13,7 @@ Three differentiable pieces mirror the reference's sequence-level memory layer
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -322,6 +323,10 @@ def _side_stream(device: torch.device) -> "torch.cuda.Stream":
     return _side_streams[key]
 
 
+# experiment switch: run the dQ kernel on the side stream beside the dK/dV kernel (fused route only)
+_DQ_ON_SIDE_STREAM = os.environ.get("MOC_DQ_ON_SIDE_STREAM", "0") == "1"
+
+
 class _MemoryLayerTwoStream(torch.autograd.Function):
     """Router, gather, projections and attention of one layer as a single autograd node, so that the
     bandwidth- and latency-bound kernels (router, chapter bookkeeping, gather backward) run on a second
@@ -461,13 +466,29 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
         kv_dot = None
         if fused is not None and t == 64:
             kv_dot = torch.empty(b, kv.shape[1] // 64, num_kv_heads, dtype=f32, device=dev)
-        d_q, d_kv = ops.attn_bwd(q.view(b, l, -1), kv, o, lse, d_o.view(b, l, -1), num_heads, num_kv_heads,
-                                 ctx.scale, kv_row_scale=None if fused is None else fused["row_scale"],
-                                 kv_dot=kv_dot)
+        split_bwd = _DQ_ON_SIDE_STREAM and fused is not None
+        if split_bwd:
+            # per-row constants here, then the dQ kernel on the side stream (its consumers follow it there) beside
+            # the dK/dV kernel on this one: each fills the tail of the other's last round of CTAs
+            q3, do3 = q.view(b, l, -1), d_o.view(b, l, -1)
+            bufs = (torch.empty_like(q3), torch.empty_like(kv),
+                    torch.empty(6, b, num_heads, l, dtype=f32, device=dev))
+            akw = dict(buffers=bufs, kv_row_scale=fused["row_scale"], kv_dot=kv_dot)
+            ops.attn_bwd(q3, kv, o, lse, do3, num_heads, num_kv_heads, ctx.scale, parts=1, **akw)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                ops.attn_bwd(q3, kv, o, lse, do3, num_heads, num_kv_heads, ctx.scale, parts=2, **akw)
+            ops.attn_bwd(q3, kv, o, lse, do3, num_heads, num_kv_heads, ctx.scale, parts=4, **akw)
+            d_q, d_kv = bufs[0], bufs[1]
+        else:
+            d_q, d_kv = ops.attn_bwd(q.view(b, l, -1), kv, o, lse, d_o.view(b, l, -1), num_heads, num_kv_heads,
+                                     ctx.scale, kv_row_scale=None if fused is None else fused["row_scale"],
+                                     kv_dot=kv_dot)
         d_q2 = d_q.view(b * l, -1)
         d_kv2 = d_kv.view(-1, d_kv.shape[-1])
 
-        side.wait_stream(main)
+        if not split_bwd:
+            side.wait_stream(main)
         with torch.cuda.stream(side):
             d_wq = ops.gemm(d_q2, h2, a_kmajor=False, b_kmajor=False, out_dtype=f32, split_k=splits(b * l, d, d),
                             tag="d_wq")
@@ -484,6 +505,8 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
             elif add_residual:
                 d_h = d_h.float() + g_res.float()
             d_h = d_h.view(b, l, d).to(ha_dtype)
+            if split_bwd:
+                side.wait_stream(main)      # dK/dV was issued on the main stream
             if fused is None:
                 d_wkv = ops.gemm(d_kv2, m2, a_kmajor=False, b_kmajor=False, out_dtype=f32,
                                  split_k=splits(d_kv2.shape[0], wkv_c.shape[0], d), tag="d_wkv")

@@ -562,9 +562,12 @@ def attn_bwd(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, lse: torch.Tens
         scratch = torch.empty(6, s.batch, num_heads, s.seq, dtype=torch.float32, device=q.device)
     else:
         d_q, d_kv, scratch = buffers
-    if kv_row_scale is not None:
-        if parts is not None:
-            raise ValueError("kv_row_scale goes with the whole backward (parts=None)")
+    if kv_row_scale is not None and parts is not None:
+        rc = L.lib().moc_attn_bwd_scaled_parts(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse), L.ptr(d_o),
+                                               L.ptr(d_q), L.ptr(d_kv), L.ptr(scratch), L.ptr(_contig(kv_row_scale)),
+                                               L.ptr(kv_dot), int(parts), L.ptr(L.status_word(q.device)),
+                                               L.stream_ptr(q.device))
+    elif kv_row_scale is not None:
         rc = L.lib().moc_attn_bwd_scaled(C.byref(s), L.ptr(q), L.ptr(kv), L.ptr(o), L.ptr(lse), L.ptr(d_o),
                                          L.ptr(d_q), L.ptr(d_kv), L.ptr(scratch), L.ptr(_contig(kv_row_scale)),
                                          L.ptr(kv_dot), L.ptr(L.status_word(q.device)), L.stream_ptr(q.device))

@@ -209,6 +209,7 @@ TC_SHAPES = {
     "per_head_lists_multi_tile": dict(B=2, TQ=300, TK=512, HQ=4, H=2, S=3),
     "small_ragged": dict(B=1, TQ=70, TK=256, HQ=2, H=2, S=4),
     "gqa6_three_tiles_per_chapter": dict(B=1, TQ=520, TK=192, HQ=6, H=1, S=2),
+    "two_sequences_one_kv_head": dict(B=2, TQ=100, TK=256, HQ=2, H=1, S=2),
 }
 
 
