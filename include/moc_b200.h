@@ -405,8 +405,8 @@ int moc_token_mix_fwd(const moc_sparse_attn_shape* s, int32_t index_heads, const
                       float out_scale, const void* workspace, void* partial, void* o, float* lse_slots,
                       int32_t* status, void* stream);
 /* d_q = d_q_base (or 0 when NULL) + the routed branch's gradient; d_k / d_v are bf16 with row stride
- * dkv_row_stride: the 64 rows of every selected chapter are WRITTEN (each chapter by one CTA, pairs in ascending
- * order), rows of chapters nobody selected are left as the caller set them (zero them). */
+ * dkv_row_stride and are WRITTEN in full: the 64 rows of every selected chapter by the one CTA that owns the chapter
+ * (pairs in ascending order), zeros for chapters nobody selected -- the caller need not clear them. */
 int moc_token_mix_bwd(const moc_sparse_attn_shape* s, int32_t index_heads, const void* q, const void* k, const void* v,
                       int64_t kv_row_stride, const int32_t* block_indices, const float* weights, float out_scale,
                       const float* lse_slots, const void* d_o, const void* workspace, void* dq_partial,

@@ -423,11 +423,21 @@ constexpr uint32_t kColS = 0, kColDP = 64, kColD = 128;      // dQ reuses S's co
 // and for each the KV heads that read its index list.  The control warp and the row warps walk the same sequence.
 struct GroupIter {
   int bkt, kh, kh_hi, first, n, kv_row;
-  __device__ __forceinline__ void seek(const MixBwdParams& p) {      // first non-empty bucket at or after bkt
+  // first non-empty bucket at or after bkt; with zero_row >= 0 (thread index of a row-owning thread) the dK / dV rows
+  // of the empty buckets passed on the way are zero-filled, so the caller need not clear the buffers
+  __device__ __forceinline__ void seek(const MixBwdParams& p, int zero_row = -1) {
     for (; bkt < p.n_buckets; bkt += gridDim.x) {
       first = p.bucket_off[bkt];
       n = p.bucket_off[bkt + 1] - first;
       if (n > 0) break;
+      if (zero_row >= 0) {
+        const MixShape& x = p.x;
+        const int c = bkt % x.M, bh = bkt / x.M, hi = bh % x.HI, b = bh / x.HI;
+        const int h0 = x.HI == 1 ? 0 : hi, h1 = x.HI == 1 ? x.HK : hi + 1;
+        __nv_bfloat16* dst = (zero_row >= 64 ? p.d_k : p.d_v) +
+                             (static_cast<long long>(b) * x.TK + c * kKeys + (zero_row & 63)) * p.dkv_ld;
+        for (int e = h0 * (kD / 8); e < h1 * (kD / 8); ++e) reinterpret_cast<uint4*>(dst)[e] = make_uint4(0u, 0u, 0u, 0u);
+      }
     }
     if (bkt >= p.n_buckets) return;
     const MixShape& x = p.x;
@@ -436,12 +446,12 @@ struct GroupIter {
     kh_hi = x.HI == 1 ? x.HK : hi + 1;
     kv_row = b * x.TK + c * kKeys;
   }
-  __device__ __forceinline__ void start(const MixBwdParams& p) { bkt = blockIdx.x; seek(p); }
+  __device__ __forceinline__ void start(const MixBwdParams& p, int zero_row = -1) { bkt = blockIdx.x; seek(p, zero_row); }
   __device__ __forceinline__ bool done(const MixBwdParams& p) const { return bkt >= p.n_buckets; }
-  __device__ __forceinline__ void next(const MixBwdParams& p) {
+  __device__ __forceinline__ void next(const MixBwdParams& p, int zero_row = -1) {
     if (++kh < kh_hi) return;
     bkt += gridDim.x;
-    seek(p);
+    seek(p, zero_row);
   }
 };
 
@@ -477,7 +487,7 @@ token_mix_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
   uint32_t it = 0, kvn = 0;      // tile iterations and (bucket, KV head) groups this CTA has run
   bool ok = true;
   GroupIter gi;
-  gi.start(p);
+  gi.start(p, warp < 4 ? static_cast<int>(threadIdx.x) : -1);
 
   if (warp == 4) {
     const uint32_t idesc_kk = umma_idesc_bf16(kTok, kKeys, 0, 0);     // S, dP: both operands K-major
@@ -567,7 +577,7 @@ token_mix_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
       mbar_arrive(&d_read);
       pending = false;
     };
-    for (; !gi.done(p) && ok; gi.next(p), ++kvn) {
+    for (; !gi.done(p) && ok; gi.next(p, r), ++kvn) {
       const int tiles = (gi.n + kTok - 1) / kTok;
       for (int u = 0; u < G * tiles && ok; ++u, ++it) {
         const int hq = gi.kh * G + u / tiles, tl = u % tiles;

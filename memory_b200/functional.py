@@ -323,8 +323,10 @@ def _side_stream(device: torch.device) -> "torch.cuda.Stream":
     return _side_streams[key]
 
 
-# experiment switch: run the dQ kernel on the side stream beside the dK/dV kernel (fused route only)
-_DQ_ON_SIDE_STREAM = os.environ.get("MOC_DQ_ON_SIDE_STREAM", "0") == "1"
+# The dQ kernel runs on the side stream beside the dK/dV kernel (fused route): 768 CTAs over 296 slots leave the last
+# of dQ's three rounds 59 % full, and the other kernel's CTAs take the free slots (measured 1.189 -> 1.177 ms per
+# step).  MOC_DQ_ON_SIDE_STREAM=0 puts both back on the main stream.
+_DQ_ON_SIDE_STREAM = os.environ.get("MOC_DQ_ON_SIDE_STREAM", "1") != "0"
 
 
 class _MemoryLayerTwoStream(torch.autograd.Function):
@@ -823,14 +825,17 @@ class _TokenRoutedAttention(torch.autograd.Function):
                                            dc.view(1, rows + pad, -1), num_heads, num_kv_heads, scale)
             d_q = d_q_sh.view(rows + pad, -1)[:rows].contiguous()
             d_kv_sh2 = d_kv_sh.view(kv_sh.shape[0], -1)
-            d_shared = ops.gemm(d_kv_sh2, wkv_c, b_kmajor=False, tag="d_shared_mem").to(sh_dtype)
+            d_shared = ops.gemm(d_kv_sh2, wkv_c, b_kmajor=False, out_dtype=sh_dtype if sh_dtype in (f32, cd) else cd,
+                                tag="d_shared_mem").to(sh_dtype)
             d_wkv = ops.gemm(d_kv_sh2, sm2, a_kmajor=False, b_kmajor=False, out_dtype=f32,
                              split_k=_weight_grad_splits(cd, sm2.shape[0], 2 * dkv, d), tag="d_wkv_shared")
         if ctx.rt is not None:
             rm2, kv_rt, bidx, w2, lse_slots, n_rt, mix_ws = ctx.rt
             k4 = kv_rt[:, :dkv].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
             v4 = kv_rt[:, dkv:].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
-            d_kv_rt = torch.zeros(n_rt, 2 * dkv, dtype=f32 if mix_ws is None else cd, device=q.device)
+            # (the tensor-core mixture writes every row itself; the CUDA-core one adds into zeros)
+            d_kv_rt = (torch.zeros(n_rt, 2 * dkv, dtype=f32, device=q.device) if mix_ws is None
+                       else torch.empty(n_rt, 2 * dkv, dtype=cd, device=q.device))
             dk4 = d_kv_rt[:, :dkv].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
             dv4 = d_kv_rt[:, dkv:].unflatten(1, (num_kv_heads, head_dim)).unsqueeze(0)
             q4, dc4 = q.view(1, rows, num_heads, head_dim), d_comb.view(1, rows, num_heads, head_dim)
@@ -845,7 +850,10 @@ class _TokenRoutedAttention(torch.autograd.Function):
                 d_kv_c = ops.cast(d_kv_rt, cd)
             d_q = d_q.view(rows, -1)
             d_weights = d_w.view(b, l, -1).to(w_dtype)
-            d_routed = ops.gemm(d_kv_c, wkv_c, b_kmajor=False, tag="d_routed_mem").to(rt_dtype)
+            # written in the bank's dtype by the projection's epilogue (an fp32 master bank: no conversion pass
+            # over 805 MB afterwards)
+            d_routed = ops.gemm(d_kv_c, wkv_c, b_kmajor=False, out_dtype=rt_dtype if rt_dtype in (f32, cd) else cd,
+                                tag="d_routed_mem").to(rt_dtype)
             g_wkv = ops.gemm(d_kv_c, rm2, a_kmajor=False, b_kmajor=False, out_dtype=f32,
                              split_k=_weight_grad_splits(cd, n_rt, 2 * dkv, d), tag="d_wkv_routed")
             d_wkv = g_wkv if d_wkv is None else d_wkv + g_wkv

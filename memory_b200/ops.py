@@ -722,8 +722,9 @@ def token_mix_fwd(q, k, v, block_indices, weights, scale: float, base: Optional[
 def token_mix_bwd(q, k, v, block_indices, weights, lse_slots, d_o, scale: float, out_scale: float,
                   workspace: torch.Tensor, d_k: torch.Tensor, d_v: torch.Tensor,
                   d_q_base: Optional[torch.Tensor] = None):
-    """Gradients of :func:`token_mix_fwd`.  ``d_k`` / ``d_v`` are zeroed bf16 tensors shaped like k / v (row-strided
-    views allowed) whose selected chapters are written; returns (d_q = d_q_base + routed part, d_w [B,TQ,S])."""
+    """Gradients of :func:`token_mix_fwd`.  ``d_k`` / ``d_v`` are bf16 tensors shaped like k / v (row-strided views
+    allowed, uninitialised is fine) that the call writes in full -- zeros for chapters nobody selected; returns
+    (d_q = d_q_base + routed part, d_w [B,TQ,S])."""
     b, tq, hq, d = q.shape
     hi, n_sel = block_indices.shape[2], block_indices.shape[3]
     q, d_o = _contig(q), _contig(d_o)

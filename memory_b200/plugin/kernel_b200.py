@@ -82,7 +82,7 @@ class _WeightedSparseAttention(torch.autograd.Function):
         q, k, v, bi, w32, lse_slots = ctx.saved_tensors
         block_size, scale, w_dtype, mix_ws = ctx.cfg
         if mix_ws is not None:
-            d_k, d_v = torch.zeros_like(k), torch.zeros_like(v)
+            d_k, d_v = torch.empty_like(k), torch.empty_like(v)      # written in full by the kernel
             d_q, d_w = ops.token_mix_bwd(q, k, v, bi, w32, lse_slots, g.contiguous(), scale, 1.0, mix_ws, d_k, d_v)
             return d_q, d_k, d_v, None, d_w.to(w_dtype), None, None
         d_k = torch.zeros(k.shape, dtype=torch.float32, device=k.device)

@@ -272,7 +272,7 @@ def test_token_mix_shared_lists_base_scale_and_reproducibility(dev):
     def run():
         o, lse, ws = ops.token_mix_fwd(q.to(dev), k4d, v4d, bi.to(dev), w.to(dev), scale, base=base.to(dev),
                                        out_scale=rho)
-        d_kv = torch.zeros_like(kvd)
+        d_kv = torch.full_like(kvd, float("nan"))           # the call must write every row, zeros where nobody selected
         dk4, dv4 = d_kv[..., :H * D].unflatten(-1, (H, D)), d_kv[..., H * D:].unflatten(-1, (H, D))
         dq0 = torch.full_like(q, 0.5).to(dev)
         dq, dw = ops.token_mix_bwd(q.to(dev), k4d, v4d, bi.to(dev), w.to(dev), lse, do.to(dev), scale, rho, ws, dk4,
