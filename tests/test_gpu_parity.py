@@ -607,6 +607,34 @@ def test_bank_grad_union_sum_over_rank_lists(dtype, dev):
     assert out2["rows"].data_ptr() == out["rows"].data_ptr()
 
 
+def test_bank_grad_union_sum_eight_ranks_at_the_paper_chapter_count(dev):
+    """Eight ranks x 520 chapter slots (8 sequences x 65 selections, ascending lists partly filled) over 4,097
+    chapters: the union (about 2,500 chapters) and the sums against a dense scatter-add."""
+    from memory_b200 import ops
+    W, n, T, d, C = 8, 520, 8, 64, 4097
+    g = torch.Generator().manual_seed(19)
+    counts = torch.tensor([483, 470, 520, 455, 501, 478, 466, 490], dtype=torch.int32)
+    ids = torch.zeros(W, n, dtype=torch.int32)
+    rows = []
+    dense = torch.zeros(C, T, d, device=dev)
+    for r in range(W):
+        mine = torch.sort(torch.cat([torch.zeros(1, dtype=torch.long),
+                                     1 + torch.randperm(C - 1, generator=g)[:int(counts[r]) - 1]])).values
+        ids[r, :int(counts[r])] = mine.int()
+        x = torch.randn(n * T, d, generator=g).bfloat16()
+        rows.append(x.to(dev))
+        dense.index_add_(0, mine.to(dev), x.to(dev).float().view(n, T, d)[:int(counts[r])])
+    dense *= 0.125
+    out = ops.bank_grad_merge(rows, ids.to(dev), counts.to(dev), T, C, scale=0.125)
+    _status_ok(dev)
+    nu = int(out["num_unique"].item())
+    uniq = out["uniq"][:nu].long()
+    want_ids = torch.unique(torch.cat([ids[r, :int(counts[r])] for r in range(W)])).long().to(dev)
+    assert torch.equal(uniq, want_ids) and 2000 < nu < 3200
+    got = out["rows"][:nu * T].view(nu, T, d)
+    assert rel_err(got, dense[uniq]) < 1e-6
+
+
 def test_bank_adamw_from_compact_gradient_matches_torch_adamw(dev):
     """SparseBankAdamW against torch.optim.AdamW fed the dense form of the same gradients, three steps with
     different touched chapters: parameter, both moments, the bf16 working copy, and the gradient norm."""
