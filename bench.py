@@ -234,7 +234,7 @@ class LayerRunner:
         self.bank_shadow = _ops.cast(self.params["bank"].detach(), torch.bfloat16) if fused_gather else None
         self.g_losses = torch.tensor([0.01, 0.0, 0.001, 0.0], device=device)   # load_balance, auxiliary, z, entropy
         self.reducer = None
-        if world > 1:
+        if world > 1 and not os.environ.get("MOC_BENCH_NO_REDUCER"):      # (debug: independent replicas, no exchange)
             from memory_b200.distributed import GradReducer
             self.wire_dtype = torch.bfloat16 if wire == "bf16" else torch.float32
             self.reducer = GradReducer(cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["hidden_dim"], device,
@@ -244,7 +244,7 @@ class LayerRunner:
         # gradients of step i stay untouched in their graph's buffers while step i+1 runs in the other graph, so
         # the exchange reads them in place (no staging copy on the compute stream).
         self.slots = 2 if ((world > 1 or os.environ.get("MOC_BENCH_TWO_SLOTS")) and use_graph) else 1
-        self.sinks = [M.SparseBankGrad(self.wire_dtype if world > 1 else None) for _ in range(self.slots)]
+        self.sinks = [M.SparseBankGrad(self.wire_dtype if self.reducer is not None else None) for _ in range(self.slots)]
         if os.environ.get("MOC_BENCH_DEBUG"):
             torch.cuda.synchronize()
             from memory_b200 import _lib as _L
@@ -673,7 +673,7 @@ def run_cuda_arm(args):
         print(f"[dbg] after prepare: status = {int(L.status_word(device).item())}", file=sys.stderr)
     # ---- headline: inputs resident in HBM ----
     exchange_check = None
-    if world > 1 and not args.no_exchange_check:
+    if world > 1 and not args.no_exchange_check and runner.reducer is not None:
         exchange_check = runner.verify_exchange(hs[0], gs[0])
         barrier()
         L.check_device_status(device)
@@ -841,7 +841,9 @@ def run_cuda_arm(args):
     }
     if args.two_pass_gather:
         line["config"]["gather"] = "two-pass: gathered rows materialised, then the K/V projection"
-    if world > 1:
+    if world > 1 and runner.reducer is None:
+        line["config"]["gradient_exchange"] = "none (debug: independent replicas)"
+    elif world > 1:
         line["config"]["gradient_exchange"] = (
             "dense bucket: one NCCL all-reduce; bank rows: sparse, " + args.wire + " on the wire, " +
             ("copy-engine pushes into symmetric-memory receive buffers" if runner.reducer.exchange == "peer"

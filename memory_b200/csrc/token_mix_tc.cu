@@ -577,21 +577,43 @@ token_mix_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
       mbar_arrive(&d_read);
       pending = false;
     };
-    for (; !gi.done(p) && ok; gi.next(p, r), ++kvn) {
-      const int tiles = (gi.n + kTok - 1) / kTok;
-      for (int u = 0; u < G * tiles && ok; ++u, ++it) {
-        const int hq = gi.kh * G + u / tiles, tl = u % tiles;
-        const bool valid = tl * kTok + r < gi.n;
-        const int pair = valid ? p.entries[gi.first + tl * kTok + r] : 0;
-        const int s = pair % x.S;
-        const long long tokrow = (pair / x.S) / x.HI;
+    // pair ids and per-pair constants of an iteration; fetched one iteration ahead, so that the two dependent global
+    // loads (bucket offsets -> pair id -> weight / log-sum-exp) run under the previous iteration's products
+    struct Meta { long long tokrow; int s, hq; float wv, nl2; bool valid; };
+    auto fetch_meta = [&](const GroupIter& g, int u) {
+      Meta m;
+      const int tiles = (g.n + kTok - 1) / kTok;
+      const int tl = u % tiles;
+      m.hq = g.kh * G + u / tiles;
+      m.valid = tl * kTok + r < g.n;
+      const int pair = m.valid ? p.entries[g.first + tl * kTok + r] : 0;
+      m.s = pair % x.S;
+      m.tokrow = (pair / x.S) / x.HI;
+      m.wv = m.valid ? p.w[m.tokrow * x.S + m.s] * x.out_scale : 0.f;
+      m.nl2 = m.valid ? -p.lse_slots[(m.tokrow * x.HQ + m.hq) * x.S + m.s] * kLog2e : 0.f;
+      return m;
+    };
+    int u = 0;
+    Meta next_m = {0, 0, 0, 0.f, 0.f, false};
+    if (!gi.done(p)) next_m = fetch_meta(gi, 0);
+    while (!gi.done(p) && ok) {
+      {
+        const int iters = G * ((gi.n + kTok - 1) / kTok);
+        const Meta m = next_m;
+        const int hq = m.hq, s = m.s;
+        const bool valid = m.valid;
+        const long long tokrow = m.tokrow;
+        const float wv = m.wv, nl2 = m.nl2;
         // the tiles are free: this thread has seen done_bar of the previous iteration
         gather_row(do_s, r, p.d_o + tokrow * (x.HQ * kD) + hq * kD, valid);
         gather_row(q_s, r, p.q + tokrow * (x.HQ * kD) + hq * kD, valid);
-        const float wv = valid ? p.w[tokrow * x.S + s] * x.out_scale : 0.f;
-        const float nl2 = valid ? -p.lse_slots[(tokrow * x.HQ + hq) * x.S + s] * kLog2e : 0.f;
         fence_proxy_async();
         mbar_arrive(&in_ready);
+        GroupIter ngi = gi;
+        int nu = u + 1;
+        const bool last = nu == iters;
+        if (last) { ngi.next(p, r); nu = 0; }
+        if (!ngi.done(p)) next_m = fetch_meta(ngi, nu);
         if (pending) flush_d();
         ok = mbar_wait(&sdp_bar, it & 1, &abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
@@ -661,11 +683,15 @@ token_mix_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
           }
         }
         tc_fence_before();
+        ++it;
+        if (last) {            // D of this group is complete: done_bar of its last iteration has been seen
+          pending = true;
+          pend_row = gi.kv_row;
+          pend_kh = gi.kh;
+        }
+        gi = ngi;
+        u = nu;
       }
-      if (!ok) break;
-      pending = true;        // D of this group is complete: done_bar of its last iteration has been seen
-      pend_row = gi.kv_row;
-      pend_kh = gi.kh;
     }
     if (ok && pending) flush_d();
   }
