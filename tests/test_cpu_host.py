@@ -87,3 +87,22 @@ def test_rolling_pool_coefficients_reproduce_the_window_means():
         assert abs(float(c.sum()) - 1.0) < 1e-6
     with pytest.raises(ValueError):
         rolling_pool_coefficients(8, 0)
+
+
+def test_token_mixture_dispatch_and_split_k_rules():
+    """Host-side rules that need no device: which problems the tensor-core token mixture takes, and the K-splits of
+    the weight-gradient projections."""
+    import torch
+    from memory_b200 import functional as F, ops
+    q = torch.empty(1, 8, 4, 64, dtype=torch.bfloat16)
+    k = torch.empty(1, 256, 2, 64, dtype=torch.bfloat16)
+    assert ops.token_mix_supported(q, k, 64, 1) and ops.token_mix_supported(q, k, 64, 2)
+    assert not ops.token_mix_supported(q, k, 64, 4)                       # lists per query head are not taken
+    assert not ops.token_mix_supported(q, k, 32, 1)                       # 64-row chapters only
+    assert not ops.token_mix_supported(q.float(), k.float(), 64, 1)       # bf16 only
+    assert not ops.token_mix_supported(q, k[:, :200], 64, 1)              # whole chapters only
+    assert not ops.token_mix_supported(q[..., :32], k[..., :32], 64, 1)   # head_dim 64 only
+    assert F._weight_grad_splits(torch.float32, 1 << 20, 768, 768) == 1
+    assert F._weight_grad_splits(torch.bfloat16, 8192, 768, 768) == 8      # 18 tiles -> 148 // 18
+    assert F._weight_grad_splits(torch.bfloat16, 262144, 1536, 768) == 4   # 36 tiles
+    assert F._weight_grad_splits(torch.bfloat16, 256, 768, 768) == 1       # too few rows to split
