@@ -308,7 +308,7 @@ class LayerRunner:
             loss = self._fwd_bwd(h, d_out, slot)
             dense = [self.params[k].grad for k in self.DENSE_KEYS]
         if self.reducer is not None:
-            if self.slots == 2 and not eager:
+            if self.slots >= 2 and not eager:
                 # zero-copy: the exchange of step i runs on the reducer's stream under the compute of step i+1
                 snap = self.reducer.snapshot(dense, self.sinks[slot], copy=False)
                 self.pending[slot] = self.reducer.reduce_snapshot_async(snap)
@@ -357,7 +357,7 @@ class LayerRunner:
             else:
                 self._fwd_bwd(h, d_out, slot)
                 dense = [P[k].grad for k in self.DENSE_KEYS]
-            copy = not (self.slots == 2)
+            copy = not (self.slots >= 2)
             snap = self.reducer.snapshot(dense, self.sinks[slot], copy=copy)
             pend = self.reducer.reduce_snapshot_async(snap)
             pend.wait()
