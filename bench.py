@@ -219,7 +219,7 @@ class LayerRunner:
     """One memory layer with its parameters; ``step`` = forward + backward (+ gradient reduction)."""
 
     def __init__(self, cfg, device, world=1, group=None, use_graph=True, exchange="nccl", wire="bf16", merge=True,
-                 fused_gather=True):
+                 fused_gather=True, merged="fp32"):
         import memory_b200 as M
         from memory_b200.graph import GraphedStep
         self.M = M
@@ -239,7 +239,8 @@ class LayerRunner:
             self.wire_dtype = torch.bfloat16 if wire == "bf16" else torch.float32
             self.reducer = GradReducer(cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["hidden_dim"], device,
                                        group=group, exchange=exchange, wire_dtype=self.wire_dtype, merge=merge,
-                                       record_timings=True)
+                                       record_timings=True,
+                                       merge_dtype=torch.bfloat16 if merged == "bf16" else torch.float32)
         # With a reduction the step is captured twice and the two graphs are replayed alternately: the
         # gradients of step i stay untouched in their graph's buffers while step i+1 runs in the other graph, so
         # the exchange reads them in place (no staging copy on the compute stream).
@@ -652,7 +653,7 @@ def run_cuda_arm(args):
 
     cfg = dict(PAPER)
     runner = LayerRunner(cfg, device, world, use_graph=not args.no_graph, exchange=args.exchange, wire=args.wire,
-                         merge=not args.no_merge, fused_gather=not args.two_pass_gather)
+                         merge=not args.no_merge, fused_gather=not args.two_pass_gather, merged=args.merged)
     hs_cpu, gs_cpu = make_hidden(cfg, N_INPUT_SETS, 1234 + rank, torch.bfloat16)
     hs = [t.to(device).requires_grad_(True) for t in hs_cpu]
     gs = [t.to(device) for t in gs_cpu]
@@ -848,7 +849,7 @@ def run_cuda_arm(args):
             "dense bucket: one NCCL all-reduce; bank rows: sparse, " + args.wire + " on the wire, " +
             ("copy-engine pushes into symmetric-memory receive buffers" if runner.reducer.exchange == "peer"
              and runner.reducer._peer is not None else "three fixed-size NCCL all-gathers") +
-            ", then a union-sum kernel (fp32 accumulation) that leaves the mean gradient rows an optimizer step "
+            ", then a union-sum kernel (fp32 accumulation, " + args.merged + " result) that leaves the mean gradient rows an optimizer step "
             "applies; all of it one step behind the compute on a second stream, inside the timed region")
         line["config"]["exchange_ms_per_step_rank0"] = exchange_ms
         line["exchange_check"] = exchange_check
@@ -878,6 +879,8 @@ def main():
     ap.add_argument("--wire", default="bf16", choices=["bf16", "fp32"],
                     help="N > 1: dtype of the bank-gradient rows between ranks (sums are formed in fp32 at the receiver; "
                          "the reference's DDP sends fp32)")
+    ap.add_argument("--merged", default="fp32", choices=["fp32", "bf16"],
+                    help="N > 1: dtype of the mean gradient rows the union-sum leaves (sums are formed in fp32)")
     ap.add_argument("--two-pass-gather", action="store_true",
                     help="materialise the gathered rows before the K/V projection instead of reading the chapters "
                          "through the projection kernel's TMA gather list")

@@ -201,6 +201,13 @@ int moc_bank_grad_merge(const void* const* rank_rows, int32_t rows_dtype, int32_
                         int32_t num_chapters, float scale, int32_t* uniq, int32_t* seg_offsets, int32_t* seg_pairs,
                         int32_t* pair_to_uniq, int32_t* num_unique, float* rows_out, int64_t rows_out_capacity,
                         int32_t* status, void* stream);
+/* The same with the output dtype chosen by the caller (MOC_F32 or MOC_BF16; sums are formed in fp32 either way):
+ * bf16 mean rows halve what the consumer of an exchange writes at a rounding of 2^-9 relative. */
+int moc_bank_grad_merge_to(const void* const* rank_rows, int32_t rows_dtype, int32_t world, const int32_t* ids_all,
+                           const int32_t* counts, int32_t per_rank, int32_t T, int32_t dim, int32_t num_chapters,
+                           float scale, int32_t* uniq, int32_t* seg_offsets, int32_t* seg_pairs,
+                           int32_t* pair_to_uniq, int32_t* num_unique, void* rows_out, int32_t rows_out_dtype,
+                           int64_t rows_out_capacity, int32_t* status, void* stream);
 
 /* bank_dense[uniq[u]*T + r, :] += bank_grad[u*T + r, :]  (fp32). */
 int moc_scatter_bank_grad(const float* bank_grad, const int32_t* uniq, const int32_t* num_unique,

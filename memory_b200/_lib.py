@@ -75,6 +75,8 @@ _PROTOTYPES = {
                                       C.c_int32, C.c_int32, C.c_int32, C.c_float, P, P, P, P, P, P, P, P, P, P]),
     "moc_bank_grad_merge": (C.c_int, [P, C.c_int32, C.c_int32, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                       C.c_float, P, P, P, P, P, P, C.c_int64, P, P]),
+    "moc_bank_grad_merge_to": (C.c_int, [P, C.c_int32, C.c_int32, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                         C.c_float, P, P, P, P, P, P, C.c_int32, C.c_int64, P, P]),
     "moc_scatter_bank_grad": (C.c_int, [P, P, P, C.c_int32, C.c_int32, C.c_int32, P, C.c_int64, P, P]),
     "moc_gemm": (C.c_int, [C.POINTER(GemmDesc), P, P, P, P, P, P, P]),
     "moc_attn_fwd": (C.c_int, [C.POINTER(AttnShape), P, P, P, P, P, P]),

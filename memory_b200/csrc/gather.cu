@@ -228,10 +228,10 @@ union_segments_kernel(const int* __restrict__ ids_all, const int* __restrict__ c
 // Sum of the ranks' compact gradient rows over the union of their chapter lists: one warp per output row;
 // the contributions of a chapter are added in ascending (rank, slot) order, so every rank computes the same bits.
 struct RankRows { const void* p[16]; };
-template <typename TR>
+template <typename TR, typename TO>
 __global__ void union_sum_kernel(RankRows src, int per_list, int T, int dim, const int* __restrict__ seg_offsets,
                                  const int* __restrict__ seg_pairs, const int* __restrict__ num_unique,
-                                 long long max_rows, float scale, float* __restrict__ out) {
+                                 long long max_rows, float scale, TO* __restrict__ out) {
   // grid-stride over the output rows, one warp per row
   const int lane = threadIdx.x & 31;
   const long long n_rows = min(max_rows, static_cast<long long>(num_unique[0]) * T);
@@ -240,7 +240,7 @@ __global__ void union_sum_kernel(RankRows src, int per_list, int T, int dim, con
     const int u = static_cast<int>(r / T);
     const int within = static_cast<int>(r - static_cast<long long>(u) * T);
     const int p0 = seg_offsets[u], p1 = seg_offsets[u + 1];
-    float* dst = out + r * dim;
+    TO* dst = out + r * dim;
     if ((dim & 7) == 0) {
       for (int c = lane * 8; c < dim; c += 256) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -265,7 +265,7 @@ __global__ void union_sum_kernel(RankRows src, int per_list, int T, int dim, con
         const TR* rows = static_cast<const TR*>(src.p[pair / per_list]);
         acc += ld(rows + (static_cast<long long>(pair % per_list) * T + within) * dim, c);
       }
-      dst[c] = acc * scale;
+      st(dst, c, acc * scale);
     }
   }
 }
@@ -668,12 +668,13 @@ extern "C" int moc_chapter_segments(const int32_t* comb_idx, int32_t n_pairs, in
   return MOC_OK;
 }
 
-extern "C" int moc_bank_grad_merge(const void* const* rank_rows, int32_t rows_dtype, int32_t world,
-                                   const int32_t* ids_all, const int32_t* counts, int32_t per_rank, int32_t T,
-                                   int32_t dim, int32_t num_chapters, float scale, int32_t* uniq,
-                                   int32_t* seg_offsets, int32_t* seg_pairs, int32_t* pair_to_uniq,
-                                   int32_t* num_unique, float* rows_out, int64_t rows_out_capacity,
-                                   int32_t* status, void* stream_) {
+extern "C" int moc_bank_grad_merge_to(const void* const* rank_rows, int32_t rows_dtype, int32_t world,
+                                      const int32_t* ids_all, const int32_t* counts, int32_t per_rank, int32_t T,
+                                      int32_t dim, int32_t num_chapters, float scale, int32_t* uniq,
+                                      int32_t* seg_offsets, int32_t* seg_pairs, int32_t* pair_to_uniq,
+                                      int32_t* num_unique, void* rows_out, int32_t rows_out_dtype,
+                                      int64_t rows_out_capacity, int32_t* status, void* stream_) {
+  MOC_REQUIRE(rows_out_dtype == MOC_F32 || rows_out_dtype == MOC_BF16, "bad rows_out_dtype");
   MOC_REQUIRE(rank_rows && ids_all && counts && uniq && seg_offsets && seg_pairs && pair_to_uniq && num_unique &&
               rows_out && status, "NULL buffer");
   MOC_REQUIRE(world >= 1 && world <= 16, "world size must be in [1, 16]");
@@ -697,14 +698,28 @@ extern "C" int moc_bank_grad_merge(const void* const* rank_rows, int32_t rows_dt
   // one warp per output row over the whole grid: capping the grid at 1-4 CTAs per SM (a smaller footprint beside
   // the next step's compute) measured no better at two GPUs (1.246 ms per step uncapped, 1.259-1.267 capped)
   const long long blocks = (max_rows * 32 + 255) / 256;
-  if (rows_dtype == MOC_F32)
-    union_sum_kernel<float><<<static_cast<int>(blocks), 256, 0, stream>>>(src, per_rank, T, dim, seg_offsets, seg_pairs, num_unique,
-                                                        max_rows, scale, rows_out);
-  else
-    union_sum_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, stream>>>(src, per_rank, T, dim, seg_offsets, seg_pairs,
-                                                                num_unique, max_rows, scale, rows_out);
+#define MOC_USUM(TR, TO)                                                                                     \
+  union_sum_kernel<TR, TO><<<static_cast<int>(blocks), 256, 0, stream>>>(src, per_rank, T, dim, seg_offsets,   \
+                                                                         seg_pairs, num_unique, max_rows, scale, \
+                                                                         static_cast<TO*>(rows_out))
+  if (rows_dtype == MOC_F32 && rows_out_dtype == MOC_F32) MOC_USUM(float, float);
+  else if (rows_dtype == MOC_F32) MOC_USUM(float, __nv_bfloat16);
+  else if (rows_out_dtype == MOC_F32) MOC_USUM(__nv_bfloat16, float);
+  else MOC_USUM(__nv_bfloat16, __nv_bfloat16);
+#undef MOC_USUM
   MOC_CUDA_OK(cudaGetLastError());
   return MOC_OK;
+}
+
+extern "C" int moc_bank_grad_merge(const void* const* rank_rows, int32_t rows_dtype, int32_t world,
+                                   const int32_t* ids_all, const int32_t* counts, int32_t per_rank, int32_t T,
+                                   int32_t dim, int32_t num_chapters, float scale, int32_t* uniq,
+                                   int32_t* seg_offsets, int32_t* seg_pairs, int32_t* pair_to_uniq,
+                                   int32_t* num_unique, float* rows_out, int64_t rows_out_capacity,
+                                   int32_t* status, void* stream_) {
+  return moc_bank_grad_merge_to(rank_rows, rows_dtype, world, ids_all, counts, per_rank, T, dim, num_chapters, scale,
+                                uniq, seg_offsets, seg_pairs, pair_to_uniq, num_unique, rows_out, MOC_F32,
+                                rows_out_capacity, status, stream_);
 }
 
 extern "C" int moc_gather_rows_bwd(const void* d_mem, int32_t d_mem_dtype, const void* bank, int32_t bank_dtype,

@@ -134,13 +134,14 @@ class GradReducer:
     def __init__(self, num_chapters: int, tokens_per_chapter: int, dim: int, device,
                  group: Optional[dist.ProcessGroup] = None, bank_dtype: torch.dtype = torch.float32,
                  exchange: str = "nccl", wire_dtype: torch.dtype = torch.float32, merge: bool = False,
-                 record_timings: bool = False):
+                 record_timings: bool = False, merge_dtype: torch.dtype = torch.float32):
         """``wire_dtype`` bf16: the pipelined exchange sends the bf16 copy of the rows that the backward pass
         wrote next to the fp32 ones (the sink must be created with ``SparseBankGrad(torch.bfloat16)``); sums are
         still formed in fp32 at the receiver.  The reference's DDP reduces fp32; bf16 halves the volume at a
         rounding of 2^-9 relative per rank's contribution.  ``merge``: the exchange is followed, on the reducer's
         stream, by the union-sum kernel, so ``PendingReduction.result()`` holds ONE entry: the mean gradient rows
-        over the union of all ranks' chapters (identical bits on every rank)."""
+        over the union of all ranks' chapters (identical bits on every rank).  ``merge_dtype`` bf16 stores those
+        mean rows in bf16 (sums still in fp32): half the bytes the union-sum writes, one more rounding of 2^-9."""
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
         if wire_dtype not in (torch.float32, torch.bfloat16):
@@ -148,6 +149,9 @@ class GradReducer:
         self.exchange = exchange
         self.wire_dtype = wire_dtype
         self.merge = merge
+        if merge_dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("merge_dtype must be float32 or bfloat16")
+        self.merge_dtype = merge_dtype
         self.record_timings = record_timings
         self.timings = []          # (start, exchanged, merged) CUDA events on the reducer's stream, per exchange
         self._merge_out = {}       # per parity: output buffers of the union-sum kernel
@@ -395,7 +399,7 @@ class GradReducer:
         rank_rows, ids_tab, num_tab, t = pending.merge_inputs
         slot = pending.parity if pending.parity is not None else (len(self.timings) & 1)
         out = ops.bank_grad_merge(rank_rows, ids_tab, num_tab, t, self.c, pending.bank_scale,
-                                  out=self._merge_out.get(slot))
+                                  out=self._merge_out.get(slot), out_dtype=self.merge_dtype)
         self._merge_out[slot] = out
         pending.merged = (out["uniq"], out["num_unique"], out["rows"], t)
 

@@ -367,13 +367,13 @@ def gather_rows_bwd_prescaled(g: torch.Tensor, bank: torch.Tensor, tokens_per_ch
 
 @_instrument("bank_grad_merge", 2)
 def bank_grad_merge(rank_rows, ids_all: torch.Tensor, counts: torch.Tensor, tokens_per_chapter: int,
-                    num_chapters: int, scale: float = 1.0, out: Optional[Dict[str, torch.Tensor]] = None
-                    ) -> Dict[str, torch.Tensor]:
+                    num_chapters: int, scale: float = 1.0, out: Optional[Dict[str, torch.Tensor]] = None,
+                    out_dtype: torch.dtype = torch.float32) -> Dict[str, torch.Tensor]:
     """Sum of the ranks' compact gradient rows over the union of their chapter lists.
 
     ``rank_rows``: one [per_rank*T, d] tensor per rank (all fp32 or all bf16); ``ids_all`` int32 [world, per_rank];
-    ``counts`` int32 [world].  Returns {"uniq", "num_unique", "rows" fp32 [cap*T, d], scratch...}; pass the dict
-    back as ``out`` to reuse its buffers."""
+    ``counts`` int32 [world].  Returns {"uniq", "num_unique", "rows" [cap*T, d] in ``out_dtype`` (sums are formed in
+    fp32), scratch...}; pass the dict back as ``out`` to reuse its buffers."""
     world, per_rank = ids_all.shape
     t, d = int(tokens_per_chapter), rank_rows[0].shape[1]
     dev = ids_all.device
@@ -387,14 +387,15 @@ def bank_grad_merge(rank_rows, ids_all: torch.Tensor, counts: torch.Tensor, toke
         out = {"uniq": torch.empty(n, **i32), "seg_offsets": torch.empty(n + 1, **i32),
                "seg_pairs": torch.empty(n, **i32), "pair_to_uniq": torch.empty(n, **i32),
                "num_unique": torch.empty(1, **i32),
-               "rows": torch.empty(cap * t, d, dtype=torch.float32, device=dev)}
+               "rows": torch.empty(cap * t, d, dtype=out_dtype, device=dev)}
     arr = (C.c_void_p * world)(*[r.data_ptr() for r in rank_rows])
-    rc = L.lib().moc_bank_grad_merge(arr, L.dtype_code(rank_rows[0].dtype), world, L.ptr(_contig(ids_all)),
-                                     L.ptr(_contig(counts)), per_rank, t, d, int(num_chapters), float(scale),
-                                     L.ptr(out["uniq"]), L.ptr(out["seg_offsets"]), L.ptr(out["seg_pairs"]),
-                                     L.ptr(out["pair_to_uniq"]), L.ptr(out["num_unique"]), L.ptr(out["rows"]),
-                                     out["rows"].shape[0], L.ptr(L.status_word(dev)), L.stream_ptr(dev))
-    L.check(rc, "moc_bank_grad_merge")
+    rc = L.lib().moc_bank_grad_merge_to(arr, L.dtype_code(rank_rows[0].dtype), world, L.ptr(_contig(ids_all)),
+                                        L.ptr(_contig(counts)), per_rank, t, d, int(num_chapters), float(scale),
+                                        L.ptr(out["uniq"]), L.ptr(out["seg_offsets"]), L.ptr(out["seg_pairs"]),
+                                        L.ptr(out["pair_to_uniq"]), L.ptr(out["num_unique"]), L.ptr(out["rows"]),
+                                        L.dtype_code(out["rows"].dtype), out["rows"].shape[0],
+                                        L.ptr(L.status_word(dev)), L.stream_ptr(dev))
+    L.check(rc, "moc_bank_grad_merge_to")
     return out
 
 

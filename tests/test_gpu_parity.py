@@ -605,6 +605,11 @@ def test_bank_grad_union_sum_over_rank_lists(dtype, dev):
     # the same buffers can be reused
     out2 = ops.bank_grad_merge([x.to(dev) for x in rows], ids.to(dev), counts.to(dev), T, C, scale=0.5, out=out)
     assert out2["rows"].data_ptr() == out["rows"].data_ptr()
+    # bf16 mean rows: the same sums, rounded once
+    out3 = ops.bank_grad_merge([x.to(dev) for x in rows], ids.to(dev), counts.to(dev), T, C, scale=0.5,
+                               out_dtype=torch.bfloat16)
+    assert out3["rows"].dtype == torch.bfloat16 and torch.equal(out3["uniq"][:nu].cpu().long(), want_ids)
+    assert torch.equal(out3["rows"][:nu * T].cpu(), out["rows"][:nu * T].cpu().bfloat16())
 
 
 def test_bank_grad_union_sum_eight_ranks_at_the_paper_chapter_count(dev):
