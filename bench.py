@@ -686,6 +686,17 @@ def run_cuda_arm(args):
         torch.cuda.synchronize()
         runner.reducer.timings.clear()
     L.check_device_status(device)
+    # host time to issue one step (eight steps from an idle device, nothing blocks): a step cannot be shorter
+    torch.cuda.synchronize()
+    t_issue = time.perf_counter()
+    for i in range(8):
+        runner.step(hs[i % N_INPUT_SETS], gs[i % N_INPUT_SETS])
+    host_issue_ms = (time.perf_counter() - t_issue) / 8 * 1e3
+    if runner.reducer is not None:
+        runner.finish()
+    torch.cuda.synchronize()
+    if runner.reducer is not None:
+        runner.reducer.timings.clear()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
@@ -836,7 +847,8 @@ def run_cuda_arm(args):
                 "ms_per_step_min_max": [min(e2e_blocks), max(e2e_blocks)]},
         "timed_blocks": {"blocks": args.blocks, "steps_per_block": args.steps, "statistic": "median",
                          "ms_per_step_min_max": [min(block_ms), max(block_ms)]},
-        "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu_baseline,
+        "gpu_launches": launches, "host_issue_ms_per_step": round(host_issue_ms, 4), "roofline": roofline,
+        "cpu_baseline": cpu_baseline,
         "reference_eager_same_gpu": gpu_eager, "verify": verify,
         "pct_of_bf16_tc_roofline": 100.0 * roofline["layer"]["frac"],
     }

@@ -44,6 +44,32 @@ __device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&v)[8]) {
   *reinterpret_cast<uint4*>(p) = o;
 }
 
+// Streaming forms (evict-first in L2) for data that is read or written exactly once -- the exchange's consumer runs
+// beside the next step's attention kernels, whose K/V tiles live on L2 hits.
+__device__ __forceinline__ void ld8_stream(const float* p, float (&v)[8]) {
+  const float4 a = __ldcs(reinterpret_cast<const float4*>(p)), b = __ldcs(reinterpret_cast<const float4*>(p + 4));
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void ld8_stream(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void st8_stream(float* p, const float (&v)[8]) {
+  __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));
+  __stcs(reinterpret_cast<float4*>(p + 4), make_float4(v[4], v[5], v[6], v[7]));
+}
+__device__ __forceinline__ void st8_stream(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+  __stcs(reinterpret_cast<uint4*>(p), o);
+}
+
 // statistics of one bank row as the normalisation needs them: {mean, 1/sqrt(var or meansq + eps)}
 template <typename TB>
 __device__ __forceinline__ void row_norm_stats(const TB* row, int dim, int norm_type, float eps, int lane,
@@ -248,13 +274,13 @@ __global__ void union_sum_kernel(RankRows src, int per_list, int T, int dim, con
           const int pair = seg_pairs[q];
           const TR* rows = static_cast<const TR*>(src.p[pair / per_list]);
           float g[8];
-          ld8(rows + (static_cast<long long>(pair % per_list) * T + within) * dim + c, g);
+          ld8_stream(rows + (static_cast<long long>(pair % per_list) * T + within) * dim + c, g);
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[j] += g[j];
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] *= scale;
-        st8(dst + c, acc);
+        st8_stream(dst + c, acc);
       }
       continue;
     }

@@ -84,6 +84,8 @@ class _PeerPush:
         self.handle = handle
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
         self.consumed = [None] * parities
+        # one stream per peer: the pushes to different peers run on different copy engines / links at once
+        self.push_streams = [torch.cuda.Stream(device) for _ in range(w - 1)]
 
     def _views(self, flat: torch.Tensor, parity: int):
         base = parity * self.per_parity
@@ -106,12 +108,19 @@ class _PeerPush:
             stream.wait_event(self.consumed[parity])
         if handshake:
             dist.all_reduce(self.token, group=self.group)
+        start = torch.cuda.Event()
+        start.record(stream)
         for k in range(1, self.world):          # the local block is used where it is: no copy to self
             r = (self.rank + k) % self.world
             p_rows, p_ids, p_nums = self._views(self.peers[r], parity)
-            p_rows[self.rank].copy_(rows.view(self.m, self.d), non_blocking=True)
-            p_ids[self.rank].copy_(uniq.view(torch.int32), non_blocking=True)
-            p_nums[self.rank:self.rank + 1].copy_(num_unique.view(torch.int32).reshape(1), non_blocking=True)
+            side = self.push_streams[k - 1]
+            side.wait_event(start)
+            with torch.cuda.stream(side):
+                p_rows[self.rank].copy_(rows.view(self.m, self.d), non_blocking=True)
+                p_ids[self.rank].copy_(uniq.view(torch.int32), non_blocking=True)
+                p_nums[self.rank:self.rank + 1].copy_(num_unique.view(torch.int32).reshape(1), non_blocking=True)
+        for side in self.push_streams:          # what follows on the calling stream is behind every push
+            stream.wait_stream(side)
         work = dist.all_reduce(self.token, group=self.group, async_op=True) if handshake else None
         rows_all, ids_all, nums_all = self._views(self.buf, parity)
         # the local list also goes into its own slot (a few KB), so that [world, n] is one table for the merge;
@@ -306,6 +315,10 @@ class GradReducer:
                 if work is not None:
                     works.append(work)
                 else:
+                    # the reader of the previous exchange's receive buffers (the union-sum, on its own stream) must
+                    # be over before this rank enters the collective that licenses its peers to overwrite them
+                    if getattr(self, "_merge_done", None) is not None:
+                        torch.cuda.current_stream(self.device).wait_event(self._merge_done)
                     works.append(dist.all_reduce(snap.flat, group=self.group, async_op=True))
                 gathered += [(i, c, r, t) for i, c, r in triples]
                 merge_inputs = ([r for _, _, r in triples], ids_tab, num_tab, t)
@@ -355,6 +368,8 @@ class GradReducer:
         torch.cuda.synchronize(self.device)
         if getattr(self, "_stream", None) is None:
             self._stream = torch.cuda.Stream(self.device)
+        if self.merge and getattr(self, "_merge_stream", None) is None:
+            self._merge_stream = torch.cuda.Stream(self.device)
         if self.exchange == "peer" and self._peer is None and sink is not None and len(sink.entries) == 1:
             uniq, _, rows, _ = sink.entries[0]
             if self.wire_dtype == torch.bfloat16 and sink.wire and sink.wire[0] is not None:
@@ -384,12 +399,29 @@ class GradReducer:
             if ev:
                 ev[1].record(self._stream)
             if self.merge and pending.merge_inputs is not None:
-                self._merge(pending)
-            if ev:
-                ev[2].record(self._stream)
-                self.timings.append(tuple(ev))
-            pending.done = torch.cuda.Event()
-            pending.done.record(self._stream)
+                # The union-sum runs on a stream of its own, so the pushes of the next exchange (other parity) go
+                # out beside it; that exchange's collective waits for it (see _gather_snapshot): every rank still
+                # enters the collective after its reader of the parity before, which is what lets a peer overwrite
+                # that parity afterwards.
+                if getattr(self, "_merge_stream", None) is None:
+                    self._merge_stream = torch.cuda.Stream(self.device)
+                self._merge_stream.wait_stream(self._stream)
+                with torch.cuda.stream(self._merge_stream):
+                    self._merge(pending)
+                    if ev:
+                        ev[2].record(self._merge_stream)
+                    self._merge_done = torch.cuda.Event()
+                    self._merge_done.record(self._merge_stream)
+                    pending.done = self._merge_done
+                pending.stream = self._merge_stream
+                if ev:
+                    self.timings.append(tuple(ev))
+            else:
+                if ev:
+                    ev[2].record(self._stream)
+                    self.timings.append(tuple(ev))
+                pending.done = torch.cuda.Event()
+                pending.done.record(self._stream)
         return pending
 
     def _merge(self, pending: "PendingReduction") -> None:
@@ -397,6 +429,10 @@ class GradReducer:
         receive-buffer parity (or rotate over two sets), so a result stays valid until the exchange after next."""
         from . import ops
         rank_rows, ids_tab, num_tab, t = pending.merge_inputs
+        if self.device.type == "cuda":      # allocated on the exchange stream, read on this one
+            cur = torch.cuda.current_stream(self.device)
+            for x in (*rank_rows, ids_tab, num_tab):
+                x.record_stream(cur)
         slot = pending.parity if pending.parity is not None else (len(self.timings) & 1)
         out = ops.bank_grad_merge(rank_rows, ids_tab, num_tab, t, self.c, pending.bank_scale,
                                   out=self._merge_out.get(slot), out_dtype=self.merge_dtype)
