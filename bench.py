@@ -219,7 +219,7 @@ class LayerRunner:
     """One memory layer with its parameters; ``step`` = forward + backward (+ gradient reduction)."""
 
     def __init__(self, cfg, device, world=1, group=None, use_graph=True, exchange="nccl", wire="bf16", merge=True,
-                 fused_gather=True, merged="fp32"):
+                 fused_gather=True, merged="fp32", sync="collective"):
         import memory_b200 as M
         from memory_b200.graph import GraphedStep
         self.M = M
@@ -240,7 +240,8 @@ class LayerRunner:
             self.reducer = GradReducer(cfg["num_chapters"], cfg["tokens_per_chapter"], cfg["hidden_dim"], device,
                                        group=group, exchange=exchange, wire_dtype=self.wire_dtype, merge=merge,
                                        record_timings=True,
-                                       merge_dtype=torch.bfloat16 if merged == "bf16" else torch.float32)
+                                       merge_dtype=torch.bfloat16 if merged == "bf16" else torch.float32,
+                                       sync=sync)
         # With a reduction the step is captured twice and the two graphs are replayed alternately: the
         # gradients of step i stay untouched in their graph's buffers while step i+1 runs in the other graph, so
         # the exchange reads them in place (no staging copy on the compute stream).
@@ -653,7 +654,7 @@ def run_cuda_arm(args):
 
     cfg = dict(PAPER)
     runner = LayerRunner(cfg, device, world, use_graph=not args.no_graph, exchange=args.exchange, wire=args.wire,
-                         merge=not args.no_merge, fused_gather=not args.two_pass_gather, merged=args.merged)
+                         merge=not args.no_merge, fused_gather=not args.two_pass_gather, merged=args.merged, sync=args.sync)
     hs_cpu, gs_cpu = make_hidden(cfg, N_INPUT_SETS, 1234 + rank, torch.bfloat16)
     hs = [t.to(device).requires_grad_(True) for t in hs_cpu]
     gs = [t.to(device) for t in gs_cpu]
@@ -668,7 +669,8 @@ def run_cuda_arm(args):
         torch.cuda.synchronize()
         print(f"[dbg] after runner init: status = {int(L.status_word(device).item())}", file=sys.stderr)
     if runner.reducer is not None:
-        runner.reducer.prepare(runner.sinks[0])     # peer mappings and streams exist before anything is timed
+        # peer mappings and streams exist before anything is timed
+        runner.reducer.prepare(runner.sinks[0], [runner.params[k].grad for k in runner.DENSE_KEYS])
     if os.environ.get("MOC_BENCH_DEBUG"):
         torch.cuda.synchronize()
         print(f"[dbg] after prepare: status = {int(L.status_word(device).item())}", file=sys.stderr)
@@ -858,7 +860,10 @@ def run_cuda_arm(args):
         line["config"]["gradient_exchange"] = "none (debug: independent replicas)"
     elif world > 1:
         line["config"]["gradient_exchange"] = (
-            "dense bucket: one NCCL all-reduce; bank rows: sparse, " + args.wire + " on the wire, " +
+            ("dense bucket: one NCCL all-reduce; " if args.sync == "collective" or runner.reducer._peer is None
+             or not runner.reducer._peer.n_dense else
+             "dense bucket: pushed by copy engine and summed locally, a flag barrier over peer memory synchronises; ") +
+            "bank rows: sparse, " + args.wire + " on the wire, " +
             ("copy-engine pushes into symmetric-memory receive buffers" if runner.reducer.exchange == "peer"
              and runner.reducer._peer is not None else "three fixed-size NCCL all-gathers") +
             ", then a union-sum kernel (fp32 accumulation, " + args.merged + " result) that leaves the mean gradient rows an optimizer step "
@@ -891,6 +896,10 @@ def main():
     ap.add_argument("--wire", default="bf16", choices=["bf16", "fp32"],
                     help="N > 1: dtype of the bank-gradient rows between ranks (sums are formed in fp32 at the receiver; "
                          "the reference's DDP sends fp32)")
+    ap.add_argument("--sync", default="collective", choices=["collective", "flags"],
+                    help="N > 1, peer exchange: 'collective' = the dense bucket's NCCL all-reduce also synchronises the "
+                         "exchange; 'flags' = the dense bucket is pushed like the rows and a flag barrier over peer "
+                         "memory synchronises (no NCCL kernel in the steady state)")
     ap.add_argument("--merged", default="fp32", choices=["fp32", "bf16"],
                     help="N > 1: dtype of the mean gradient rows the union-sum leaves (sums are formed in fp32)")
     ap.add_argument("--two-pass-gather", action="store_true",

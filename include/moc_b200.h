@@ -51,6 +51,17 @@ int moc_abi_version(void);
 int moc_wait_probe(int32_t expected, int32_t arrivals, uint32_t poll_limit, int32_t* status, int32_t* out,
                    void* stream);
 
+/* Barrier between the ranks of one node through flag words in each other's memory (peer-mapped device pointers,
+ * e.g. views of one symmetric-memory allocation): flag_arrays[r] points at rank r's array of `world` uint32 words,
+ * zero before the first use; `epoch` must grow by one per call (the same on every rank).  The kernel stores the epoch
+ * into every peer's array (release, system scope: work this stream did before -- copy-engine pushes into the peers'
+ * buffers -- is visible first) and waits, at most poll_limit polls per peer, for the peers' stores into its own;
+ * a wait that runs out raises MOC_DEV_TIMEOUT in `status` and the kernel returns.  Replaces the collective a DDP
+ * bucket all-reduce provides as a side effect (the reference syncs gradients with torch DDP, training/trainer.py)
+ * where the data itself travels by copy engine. */
+int moc_peer_barrier(const void* const* flag_arrays, int32_t rank, int32_t world, uint32_t epoch, uint32_t poll_limit,
+                     int32_t* status, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Router.  Replaces ChapterRouter.forward / _compute_losses (memory_transformer/router.py:94-156,
  * 197-260) and MemoryTransformer._prepend_shared_chapters (memory_transformer/model.py:356-391).

@@ -59,6 +59,7 @@ P = C.c_void_p
 _PROTOTYPES = {
     "moc_last_error": (C.c_char_p, []),
     "moc_abi_version": (C.c_int, []),
+    "moc_peer_barrier": (C.c_int, [P, C.c_int32, C.c_int32, C.c_uint32, C.c_uint32, P, P]),
     "moc_router_workspace_bytes": (C.c_size_t, [C.POINTER(RouterShape)]),
     "moc_router_workspace_bytes_parts": (C.c_size_t, [C.POINTER(RouterShape), C.c_int32, C.c_int32]),
     "moc_router_fwd": (C.c_int, [C.POINTER(RouterShape)] + [P] * 13 + [P, C.c_size_t, P, P]),

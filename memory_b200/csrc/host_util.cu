@@ -95,7 +95,44 @@ __global__ void wait_probe_kernel(int expected, int arrivals, uint32_t poll_limi
   }
 }
 
+// Barrier between the ranks of one node over flag words in each other's memory (plain peer stores and loads, one
+// thread per peer, no SM held while nothing is due).  Rank r's flag array lives in r's own memory; word q of it is
+// written by rank q only.  An arrival stores the epoch (a counter that only grows) with release semantics at system
+// scope -- whatever this stream did before, e.g. copy-engine pushes into the peer's buffers, is complete and visible
+// first -- and then polls its own word of that peer with acquire loads until it holds at least this epoch.  The
+// poll is bounded: after `poll_limit` rounds the thread records MOC_DEV_TIMEOUT and returns.
+struct PeerFlags { uint32_t* p[16]; };
+__global__ void peer_barrier_kernel(PeerFlags flags, int rank, int world, uint32_t epoch, uint32_t poll_limit,
+                                    int* status) {
+  const int r = threadIdx.x;
+  if (r >= world || r == rank) return;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[r] + rank), "r"(epoch) : "memory");
+  const uint32_t* mine = flags.p[rank] + r;
+  for (uint32_t it = 0; it < poll_limit; ++it) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (static_cast<int32_t>(v - epoch) >= 0) return;
+    __nanosleep(100);
+  }
+  atomicMax(status, MOC_DEV_TIMEOUT | (MOC_KERNEL_TAG << 8) | (__LINE__ << 12));
+}
+
 }  // namespace moc
+
+extern "C" int moc_peer_barrier(const void* const* flag_arrays, int32_t rank, int32_t world, uint32_t epoch,
+                                uint32_t poll_limit, int32_t* status, void* stream_) {
+  using namespace moc;
+  MOC_REQUIRE(flag_arrays && status, "NULL buffer");
+  MOC_REQUIRE(world >= 1 && world <= 16 && rank >= 0 && rank < world, "bad rank / world size");
+  MOC_REQUIRE(poll_limit >= 1, "poll_limit must be positive");
+  PeerFlags f;
+  for (int r = 0; r < 16; ++r) f.p[r] = r < world ? static_cast<uint32_t*>(const_cast<void*>(flag_arrays[r])) : nullptr;
+  for (int r = 0; r < world; ++r) MOC_REQUIRE(f.p[r] != nullptr, "NULL flag array");
+  if (world == 1) return MOC_OK;
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(f, rank, world, epoch, poll_limit, status);
+  MOC_CUDA_OK(cudaGetLastError());
+  return MOC_OK;
+}
 
 extern "C" int moc_wait_probe(int32_t expected, int32_t arrivals, uint32_t poll_limit, int32_t* status,
                               int32_t* out, void* stream_) {

@@ -63,7 +63,7 @@ class _PeerPush:
     """
 
     def __init__(self, group, device, n_ids: int, rows_shape, parities: int = 2,
-                 rows_dtype: torch.dtype = torch.float32):
+                 rows_dtype: torch.dtype = torch.float32, n_dense: int = 0):
         import torch.distributed._symmetric_memory as symm
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
@@ -77,10 +77,20 @@ class _PeerPush:
         self.rows_words = w * self.m * self.d // per_word
         self.ids_words = -(-(w * self.n) // 4) * 4
         self.num_words = -(-w // 4) * 4
-        self.per_parity = self.rows_words + self.ids_words + self.num_words
-        self.buf = symm.empty(parities * self.per_parity, dtype=torch.float32, device=device)
+        # optional slots for a dense bucket of n_dense fp32 values per rank, and one flag word per rank for the
+        # flag barrier (behind the parities)
+        self.n_dense = int(n_dense)
+        self.dense_ld = -(-self.n_dense // 4) * 4
+        self.dense_words = w * self.dense_ld
+        self.per_parity = self.rows_words + self.ids_words + self.num_words + self.dense_words
+        total = parities * self.per_parity + 16
+        self.buf = symm.empty(total, dtype=torch.float32, device=device)
+        self.buf[parities * self.per_parity:].zero_()       # the flag words start at epoch 0
+        torch.cuda.synchronize(device)
         handle = symm.rendezvous(self.buf, self.group)
-        self.peers = [handle.get_buffer(r, (parities * self.per_parity,), torch.float32) for r in range(w)]
+        self.peers = [handle.get_buffer(r, (total,), torch.float32) for r in range(w)]
+        self.flags = [p_[parities * self.per_parity:].view(torch.int32) for p_ in self.peers]
+        self.epoch = 0
         self.handle = handle
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
         self.consumed = [None] * parities
@@ -95,8 +105,20 @@ class _PeerPush:
                     base + self.rows_words + self.ids_words + self.world].view(torch.int32)
         return rows, ids.view(self.world, self.n), nums
 
+    def _dense(self, flat: torch.Tensor, parity: int) -> torch.Tensor:
+        """[world, dense_ld] fp32: the ranks' dense buckets of this parity."""
+        base = parity * self.per_parity + self.rows_words + self.ids_words + self.num_words
+        return flat[base:base + self.dense_words].view(self.world, self.dense_ld)
+
+    def barrier(self) -> None:
+        """Flag barrier on the current stream (see ``ops.peer_barrier``): every rank's earlier work on this stream,
+        its pushes included, is complete and visible once it returns."""
+        from . import ops
+        self.epoch += 1
+        ops.peer_barrier(self.flags, self.rank, self.epoch)
+
     def exchange(self, parity: int, uniq: torch.Tensor, num_unique: torch.Tensor, rows: torch.Tensor,
-                 handshake: bool = True):
+                 handshake: bool = True, dense: Optional[torch.Tensor] = None):
         """``handshake=False`` leaves both one-element all-reduces out.  That is safe when (a) the only reader of
         a receive buffer is work queued on this same stream right after the exchange that filled it (the
         union-sum), and (b) the caller issues one collective of its own after this call and treats its completion
@@ -119,6 +141,10 @@ class _PeerPush:
                 p_rows[self.rank].copy_(rows.view(self.m, self.d), non_blocking=True)
                 p_ids[self.rank].copy_(uniq.view(torch.int32), non_blocking=True)
                 p_nums[self.rank:self.rank + 1].copy_(num_unique.view(torch.int32).reshape(1), non_blocking=True)
+                if dense is not None:           # the dense bucket travels the same way, into this rank's slot
+                    self._dense(self.peers[r], parity)[self.rank, :self.n_dense].copy_(dense, non_blocking=True)
+        if dense is not None:
+            self._dense(self.buf, parity)[self.rank, :self.n_dense].copy_(dense, non_blocking=True)
         for side in self.push_streams:          # what follows on the calling stream is behind every push
             stream.wait_stream(side)
         work = dist.all_reduce(self.token, group=self.group, async_op=True) if handshake else None
@@ -143,14 +169,21 @@ class GradReducer:
     def __init__(self, num_chapters: int, tokens_per_chapter: int, dim: int, device,
                  group: Optional[dist.ProcessGroup] = None, bank_dtype: torch.dtype = torch.float32,
                  exchange: str = "nccl", wire_dtype: torch.dtype = torch.float32, merge: bool = False,
-                 record_timings: bool = False, merge_dtype: torch.dtype = torch.float32):
+                 record_timings: bool = False, merge_dtype: torch.dtype = torch.float32, sync: str = "collective"):
         """``wire_dtype`` bf16: the pipelined exchange sends the bf16 copy of the rows that the backward pass
         wrote next to the fp32 ones (the sink must be created with ``SparseBankGrad(torch.bfloat16)``); sums are
         still formed in fp32 at the receiver.  The reference's DDP reduces fp32; bf16 halves the volume at a
         rounding of 2^-9 relative per rank's contribution.  ``merge``: the exchange is followed, on the reducer's
         stream, by the union-sum kernel, so ``PendingReduction.result()`` holds ONE entry: the mean gradient rows
         over the union of all ranks' chapters (identical bits on every rank).  ``merge_dtype`` bf16 stores those
-        mean rows in bf16 (sums still in fp32): half the bytes the union-sum writes, one more rounding of 2^-9."""
+        mean rows in bf16 (sums still in fp32): half the bytes the union-sum writes, one more rounding of 2^-9.
+        ``sync`` (peer exchange with ``merge``): "collective" -- the dense bucket is all-reduced by NCCL and that
+        collective doubles as the exchange's synchronisation; "flags" -- the dense bucket is pushed like the rows,
+        summed locally (rank order, identical bits everywhere), and a flag barrier over peer memory synchronises:
+        no NCCL kernel holds SMs beside the compute of the next step."""
+        if sync not in ("collective", "flags"):
+            raise ValueError("sync must be 'collective' or 'flags'")
+        self.sync = sync
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
         if wire_dtype not in (torch.float32, torch.bfloat16):
@@ -303,17 +336,29 @@ class GradReducer:
                 gathered.append((uniq, num_unique, rows, t))
                 continue
             if use_peer and self._peer is None:
-                use_peer = self._open_peer(uniq.numel(), rows.shape, rows.dtype)
+                use_peer = self._open_peer(uniq.numel(), rows.shape, rows.dtype,
+                                           snap.flat.numel() if snap.flat is not None else 0)
                 if not use_peer and light:        # fell back to NCCL: the dense bucket travels on its own after all
                     light = False
                     works.append(dist.all_reduce(snap.flat, group=self.group, async_op=True))
             if use_peer:
                 parity = self._parity
                 self._parity = (parity + 1) % self._peer.parities
+                flags = light and self.sync == "flags" and self._peer.n_dense == snap.flat.numel()
                 work, triples, (ids_tab, num_tab) = self._peer.exchange(parity, uniq, num_unique, rows,
-                                                                         handshake=not light)
+                                                                         handshake=not light,
+                                                                         dense=snap.flat if flags else None)
                 if work is not None:
                     works.append(work)
+                elif flags:
+                    # as below: this rank's reader of the previous exchange's buffers is over before it tells its
+                    # peers (by arriving at the barrier) that they may overwrite them
+                    if getattr(self, "_merge_done", None) is not None:
+                        torch.cuda.current_stream(self.device).wait_event(self._merge_done)
+                    self._peer.barrier()
+                    from . import ops
+                    dense_all = self._peer._dense(self._peer.buf, parity)
+                    snap.flat = ops.sum_terms(dense_all.view(1, -1), snap.flat.numel(), self.world).view(-1)
                 else:
                     # the reader of the previous exchange's receive buffers (the union-sum, on its own stream) must
                     # be over before this rank enters the collective that licenses its peers to overwrite them
@@ -342,11 +387,12 @@ class GradReducer:
             pending.parity = pending_parity
         return pending
 
-    def _open_peer(self, n_ids: int, rows_shape, rows_dtype=torch.float32) -> bool:
+    def _open_peer(self, n_ids: int, rows_shape, rows_dtype=torch.float32, n_dense: int = 0) -> bool:
         """Create the symmetric-memory receive buffers; every rank must succeed or all fall back to NCCL."""
         ok = 1
         try:
-            self._peer = _PeerPush(self.group, self.device, n_ids, rows_shape, rows_dtype=rows_dtype)
+            self._peer = _PeerPush(self.group, self.device, n_ids, rows_shape, rows_dtype=rows_dtype,
+                                   n_dense=n_dense if self.sync == "flags" else 0)
         except Exception:                      # symmetric memory unavailable in this process / on this node
             self._peer, ok = None, 0
         flag = torch.tensor([ok], dtype=torch.int32, device=self.device)
@@ -357,12 +403,13 @@ class GradReducer:
             return False
         return True
 
-    def prepare(self, sink) -> None:
+    def prepare(self, sink, dense_grads: Optional[Sequence[Optional[torch.Tensor]]] = None) -> None:
         """Set up everything the pipelined exchange allocates or maps lazily -- the reducer's stream and, for
         ``exchange="peer"``, the symmetric-memory receive buffers and their peer mappings -- while the device is
         idle.  Mapping peer memory updates the GPU's page tables; done under running kernels it stalled their
         memory traffic long enough for a bounded device wait to give up.  Call once, on every rank, after the
-        first backward pass has filled ``sink`` (its entry gives the block sizes) and before the timed loop."""
+        first backward pass has filled ``sink`` (its entry gives the block sizes) and before the timed loop.
+        ``dense_grads`` (needed for ``sync="flags"``): the dense gradients of a step, for the size of their bucket."""
         if self.device.type != "cuda" or self.world == 1:
             return
         torch.cuda.synchronize(self.device)
@@ -374,7 +421,8 @@ class GradReducer:
             uniq, _, rows, _ = sink.entries[0]
             if self.wire_dtype == torch.bfloat16 and sink.wire and sink.wire[0] is not None:
                 rows = sink.wire[0]
-            self._open_peer(uniq.numel(), rows.shape, rows.dtype)
+            n_dense = sum(g.numel() for g in dense_grads if g is not None) if dense_grads is not None else 0
+            self._open_peer(uniq.numel(), rows.shape, rows.dtype, n_dense)
         dist.barrier(group=self.group)
         torch.cuda.synchronize(self.device)
 

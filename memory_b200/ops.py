@@ -229,6 +229,18 @@ def pool_weighted_bwd(d_pooled: torch.Tensor, pos_weight: torch.Tensor, h_shape,
     return d_h
 
 
+def peer_barrier(flag_arrays, rank: int, epoch: int, poll_limit: int = 1 << 22) -> None:
+    """Barrier over flag words in the ranks' (peer-mapped) memory on the current stream; ``flag_arrays[r]`` is rank
+    r's uint32/int32 [world] array, ``epoch`` grows by one per call.  Bounded: a peer that never arrives leaves
+    MOC_DEV_TIMEOUT in the status word instead of a hung kernel."""
+    world = len(flag_arrays)
+    dev = flag_arrays[rank].device
+    arr = (C.c_void_p * world)(*[t.data_ptr() for t in flag_arrays])
+    rc = L.lib().moc_peer_barrier(arr, int(rank), world, int(epoch) & 0xFFFFFFFF, int(poll_limit),
+                                  L.ptr(L.status_word(dev)), L.stream_ptr(dev))
+    L.check(rc, "moc_peer_barrier")
+
+
 def wait_probe(device, expected: int, arrivals: int, poll_limit: int):
     """Runs the bounded-wait self-test kernel; returns (wait succeeded, second wait result, abort flag)."""
     out = torch.zeros(3, dtype=torch.int32, device=device)

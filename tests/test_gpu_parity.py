@@ -640,6 +640,26 @@ def test_bank_grad_union_sum_eight_ranks_at_the_paper_chapter_count(dev):
     assert rel_err(got, dense[uniq]) < 1e-6
 
 
+def test_peer_flag_barrier_arrives_and_gives_up(dev):
+    """The flag barrier of the gradient exchange on one GPU, one launch at a time (no kernel waits for another):
+    with the peers' words already at the epoch the kernel stores its own arrival into their arrays and returns; with
+    a peer that never arrives the bounded wait runs out, the status word says so and the kernel returns."""
+    from memory_b200 import _lib as L, ops
+    L.check_device_status(dev)
+    world, rank = 3, 1
+    flags = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(world)]
+    flags[rank][0] = 5          # ranks 0 and 2 have arrived at epoch 5 (they write word `their rank` of my array)
+    flags[rank][2] = 6          # ... rank 2 is already one exchange ahead
+    ops.peer_barrier(flags, rank, 5, poll_limit=1000)
+    L.check_device_status(dev)
+    assert int(flags[0][rank]) == 5 and int(flags[2][rank]) == 5 and int(flags[rank][rank]) == 0
+    ops.peer_barrier(flags, rank, 6, poll_limit=200)          # rank 0 never reaches epoch 6
+    with pytest.raises(RuntimeError, match="timed out"):
+        L.check_device_status(dev)
+    assert int(flags[0][rank]) == 6                           # my own arrival was still published
+    L.check_device_status(dev)
+
+
 def test_bank_adamw_from_compact_gradient_matches_torch_adamw(dev):
     """SparseBankAdamW against torch.optim.AdamW fed the dense form of the same gradients, three steps with
     different touched chapters: parameter, both moments, the bf16 working copy, and the gradient norm."""
