@@ -504,7 +504,9 @@ __global__ void bank_grad_prescaled_kernel(const TG* __restrict__ g, const TB* _
   if (u >= num_unique[0]) return;
   const int within = static_cast<int>(r - static_cast<long long>(u) * T);
   const int p0 = seg_offsets[u], p1 = seg_offsets[u + 1];
-  float* dst = bank_grad + r * dim;
+  // bank_grad may be NULL when only the bf16 rows are wanted (a data-parallel step whose mean gradient is formed
+  // from the ranks' bf16 rows): the vector path below then skips the fp32 store
+  float* dst = bank_grad ? bank_grad + r * dim : nullptr;
   __nv_bfloat16* wire = bank_grad_wire ? bank_grad_wire + r * dim : nullptr;
   const long long brow = static_cast<long long>(uniq[u]) * T + within;
   const TB* row = bank + brow * dim;
@@ -547,7 +549,7 @@ __global__ void bank_grad_prescaled_kernel(const TG* __restrict__ g, const TB* _
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[n][j] -= x[j] * k;
         }
-        st8(dst + c, acc[n]);
+        if (dst) st8(dst + c, acc[n]);
         if (wire) st8(wire + c, acc[n]);
       }
     }
@@ -913,6 +915,8 @@ extern "C" int moc_gather_rows_bwd_prescaled(const void* g, int32_t g_dtype, con
                                              float* bank_grad, void* bank_grad_bf16, int32_t* status, void* stream_) {
   (void)status;
   MOC_REQUIRE(g && bank && comb_idx && uniq && seg_offsets && seg_pairs && num_unique, "NULL buffer");
+  MOC_REQUIRE(bank_grad != nullptr || bank_grad_bf16 == nullptr || ((dim & 7) == 0 && dim <= 1024),
+              "bf16 rows without the fp32 rows need dim % 8 == 0 and dim <= 1024");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const long long max_rows = static_cast<long long>(n_pairs) * T;
   const int blocks = static_cast<int>((max_rows * 32 + 255) / 256);
@@ -922,7 +926,7 @@ extern "C" int moc_gather_rows_bwd_prescaled(const void* g, int32_t g_dtype, con
       dcombw_prescaled_kernel<TG, TB><<<n_pairs, 256, 0, stream>>>(static_cast<const TG*>(g),                     \
                                                                    static_cast<const TB*>(bank), bank_rows, dim,  \
                                                                    T, comb_idx, comb_w, d_comb_w);                \
-    if (bank_grad != nullptr)                                                                                     \
+    if (bank_grad != nullptr || bank_grad_bf16 != nullptr)                                                        \
       bank_grad_prescaled_kernel<TG, TB><<<blocks, 256, 0, stream>>>(                                             \
           static_cast<const TG*>(g), static_cast<const TB*>(bank), dim, T, inv_rms, uniq, seg_offsets, seg_pairs, \
           num_unique, max_rows, bank_grad, static_cast<__nv_bfloat16*>(bank_grad_bf16));                          \

@@ -35,10 +35,13 @@ class SparseBankGrad:
     passes then append here and return no dense gradient for the bank.
     """
 
-    def __init__(self, wire_dtype: Optional[torch.dtype] = None):
+    def __init__(self, wire_dtype: Optional[torch.dtype] = None, wire_only: bool = False):
         self.entries = []   # list of (uniq int32 [n_pairs], num_unique int32 [1], rows fp32 [n_pairs*T, d], T)
         self.wire = []      # per entry: the same rows in ``wire_dtype`` (what a gradient exchange sends), or None
         self.wire_dtype = wire_dtype   # torch.bfloat16: backward passes also produce the bf16 copy
+        # the fused layer then writes ONLY the bf16 rows (they become the entry's rows): for data-parallel steps whose
+        # mean gradient is formed from the ranks' bf16 rows anyway, the local fp32 rows would be written for nobody
+        self.wire_only = bool(wire_only and wire_dtype == torch.bfloat16)
         self.scale = 1.0    # factor the consumer applies to the summed rows (1 / world after a zero-copy reduction)
 
     def add(self, uniq, num_unique, rows, tokens_per_chapter, wire=None):
@@ -537,7 +540,10 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
             d_cw, rows = ops.gather_rows_bwd_prescaled(
                 d_mem, fused["shadow"], t, r["comb_idx"], r["comb_w"],
                 fused["inv_rms"] if ctx.norm_row == "rms" else None, seg, want_dw=kv_dot is None,
-                want_bank=want_bank, wire_copy=wire)
+                want_bank=want_bank, wire_copy=wire,
+                wire_only=ctx.sink is not None and getattr(ctx.sink, "wire_only", False))
+            if rows is None and wire:
+                rows = wire[0]          # bf16 rows only: they are the entry
             if kv_dot is not None:
                 d_cw = kv_dot.sum(dim=2) / r["comb_w"].clamp_min(1e-30)
         d_bank = None

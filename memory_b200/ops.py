@@ -353,8 +353,10 @@ def chapter_row_scale(comb_idx: torch.Tensor, comb_w: Optional[torch.Tensor], in
 def gather_rows_bwd_prescaled(g: torch.Tensor, bank: torch.Tensor, tokens_per_chapter: int, comb_idx: torch.Tensor,
                               comb_w: Optional[torch.Tensor], inv_rms: Optional[torch.Tensor],
                               seg: Dict[str, torch.Tensor], want_dw: bool = True, want_bank: bool = True,
-                              wire_copy: Optional[list] = None):
-    """Chapter-weight gradient and compact bank gradient from g = (row scale) * dM~ (see ``moc_row_inv_rms``)."""
+                              wire_copy: Optional[list] = None, wire_only: bool = False):
+    """Chapter-weight gradient and compact bank gradient from g = (row scale) * dM~ (see ``moc_row_inv_rms``).
+    ``wire_copy`` (a list) receives the same rows in bf16; with ``wire_only`` the fp32 rows are not written at all
+    (returned as None): a data-parallel step forms its mean gradient from the ranks' bf16 rows."""
     bank, g = _contig(bank), _contig(g)
     comb_idx = _contig(comb_idx.to(torch.int32))
     n = comb_idx.numel()
@@ -362,7 +364,8 @@ def gather_rows_bwd_prescaled(g: torch.Tensor, bank: torch.Tensor, tokens_per_ch
     t = int(tokens_per_chapter)
     dev = bank.device
     d_comb_w = torch.empty(comb_idx.shape, dtype=torch.float32, device=dev) if want_dw else None
-    bank_grad = torch.empty(n * t, d, dtype=torch.float32, device=dev) if want_bank else None
+    wire_only = bool(wire_only and want_bank and wire_copy is not None and d % 8 == 0 and d <= 1024)
+    bank_grad = torch.empty(n * t, d, dtype=torch.float32, device=dev) if (want_bank and not wire_only) else None
     wire = None
     if want_bank and wire_copy is not None:
         wire = torch.empty(n * t, d, dtype=torch.bfloat16, device=dev)

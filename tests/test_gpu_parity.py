@@ -660,6 +660,22 @@ def test_peer_flag_barrier_arrives_and_gives_up(dev):
     L.check_device_status(dev)
 
 
+def test_fused_layer_bank_gradient_as_bf16_rows_only(dev):
+    """A sink that wants the bank gradient in bf16 rows only (a data-parallel step: the mean gradient is formed from
+    the ranks' bf16 rows): the entry holds exactly the bf16 rounding of the fp32 rows a plain sink receives."""
+    import memory_b200 as M
+    case = CASES["head64_t64_rms"]
+    plain, lean = M.SparseBankGrad(), M.SparseBankGrad(torch.bfloat16, wire_only=True)
+    run_layer_gpu(case, torch.bfloat16, dev, fused=True, sink=plain)
+    run_layer_gpu(case, torch.bfloat16, dev, fused=True, sink=lean)
+    _status_ok(dev)
+    (u0, n0, r0, t0), (u1, n1, r1, t1) = plain.entries[0], lean.entries[0]
+    assert r0.dtype == torch.float32 and r1.dtype == torch.bfloat16 and lean.wire[0] is r1
+    nu = int(n0.item())
+    assert int(n1.item()) == nu and torch.equal(u0[:nu], u1[:nu]) and t0 == t1
+    assert torch.equal(r1[:nu * t0], r0[:nu * t0].bfloat16())
+
+
 def test_bank_adamw_from_compact_gradient_matches_torch_adamw(dev):
     """SparseBankAdamW against torch.optim.AdamW fed the dense form of the same gradients, three steps with
     different touched chapters: parameter, both moments, the bf16 working copy, and the gradient norm."""

@@ -56,7 +56,7 @@ def assert_close_all_forms(a, b, tol, what=""):
     return s
 
 
-def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001, fused=False, in_place=False):
+def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001, fused=False, in_place=False, sink=None):
     """``fused``: the bf16 layer reads the chapters from a bf16 copy of the bank inside the K/V projection (no
     gathered rows), forward and backward."""
     import memory_b200 as M
@@ -65,6 +65,8 @@ def run_layer_gpu(case, compute_dtype, dev, inputs=None, lb=0.01, z=0.001, fused
     inp = {k: v.to(dev) for k, v in inp.items()}
     names = ("h_router", "bank", "router_w", "router_b", "wq", "wk", "wv", "wo")
     P = {k: inp[k].clone().requires_grad_(True) for k in names}
+    if sink is not None:
+        P["bank"].moc_sparse_grad = sink
     P["h_attn"] = inp["h_attn"].clone().requires_grad_(True) if case.separate_router_input else P["h_router"]
     extra = {}
     if case.pre_norm is not None:
