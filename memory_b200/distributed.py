@@ -53,6 +53,13 @@ def compact_to_union(local_ids: torch.Tensor, local_rows: torch.Tensor, union_id
     return out.view(-1, d)
 
 
+# The exchange proper is a handful of small kernels, copy-engine pushes and one collective that completes only when the
+# slowest rank has entered it: on a low-priority stream each of them waits for an SM slot under the next step's
+# compute, and the wait of the slowest rank becomes everyone's (1.4 ms per exchange at eight GPUs).  It therefore
+# runs at the compute stream's priority; the union-sum, the one large kernel, keeps a low-priority stream of its own.
+_EXCHANGE_PRIORITY = -1
+
+
 class _PeerPush:
     """Fixed-size all-gather of one (ids, count, rows) triple by peer-to-peer copies.
 
@@ -95,7 +102,7 @@ class _PeerPush:
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
         self.consumed = [None] * parities
         # one stream per peer: the pushes to different peers run on different copy engines / links at once
-        self.push_streams = [torch.cuda.Stream(device) for _ in range(w - 1)]
+        self.push_streams = [torch.cuda.Stream(device, priority=-1) for _ in range(w - 1)]
 
     def _views(self, flat: torch.Tensor, parity: int):
         base = parity * self.per_parity
@@ -169,7 +176,8 @@ class GradReducer:
     def __init__(self, num_chapters: int, tokens_per_chapter: int, dim: int, device,
                  group: Optional[dist.ProcessGroup] = None, bank_dtype: torch.dtype = torch.float32,
                  exchange: str = "nccl", wire_dtype: torch.dtype = torch.float32, merge: bool = False,
-                 record_timings: bool = False, merge_dtype: torch.dtype = torch.float32, sync: str = "collective"):
+                 record_timings: bool = False, merge_dtype: torch.dtype = torch.float32, sync: str = "collective",
+                 parities: int = 2):
         """``wire_dtype`` bf16: the pipelined exchange sends the bf16 copy of the rows that the backward pass
         wrote next to the fp32 ones (the sink must be created with ``SparseBankGrad(torch.bfloat16)``); sums are
         still formed in fp32 at the receiver.  The reference's DDP reduces fp32; bf16 halves the volume at a
@@ -184,6 +192,9 @@ class GradReducer:
         if sync not in ("collective", "flags"):
             raise ValueError("sync must be 'collective' or 'flags'")
         self.sync = sync
+        # receive-buffer sets of the peer exchange (and of the union-sum's output): a result stays valid until
+        # `parities` exchanges later, so a caller that keeps k results in flight needs k + 1 ... at least 2
+        self.parities = max(2, int(parities))
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
         if wire_dtype not in (torch.float32, torch.bfloat16):
@@ -391,8 +402,8 @@ class GradReducer:
         """Create the symmetric-memory receive buffers; every rank must succeed or all fall back to NCCL."""
         ok = 1
         try:
-            self._peer = _PeerPush(self.group, self.device, n_ids, rows_shape, rows_dtype=rows_dtype,
-                                   n_dense=n_dense if self.sync == "flags" else 0)
+            self._peer = _PeerPush(self.group, self.device, n_ids, rows_shape, parities=self.parities,
+                                   rows_dtype=rows_dtype, n_dense=n_dense if self.sync == "flags" else 0)
         except Exception:                      # symmetric memory unavailable in this process / on this node
             self._peer, ok = None, 0
         flag = torch.tensor([ok], dtype=torch.int32, device=self.device)
@@ -413,8 +424,8 @@ class GradReducer:
         if self.device.type != "cuda" or self.world == 1:
             return
         torch.cuda.synchronize(self.device)
-        if getattr(self, "_stream", None) is None:
-            self._stream = torch.cuda.Stream(self.device)
+        if getattr(self, "_streams", None) is None:
+            self._streams = [torch.cuda.Stream(self.device, priority=_EXCHANGE_PRIORITY) for _ in range(2)]
         if self.merge and getattr(self, "_merge_stream", None) is None:
             self._merge_stream = torch.cuda.Stream(self.device)
         if self.exchange == "peer" and self._peer is None and sink is not None and len(sink.entries) == 1:
@@ -431,8 +442,13 @@ class GradReducer:
         all-gathers per bank entry, all of fixed size, so nothing here waits for the device."""
         if self.device.type != "cuda":
             return self._gather_snapshot(snap)
-        if getattr(self, "_stream", None) is None:
-            self._stream = torch.cuda.Stream(self.device)
+        if getattr(self, "_streams", None) is None:
+            self._streams = [torch.cuda.Stream(self.device, priority=_EXCHANGE_PRIORITY) for _ in range(2)]
+        # consecutive exchanges alternate between two streams (as they alternate between the receive-buffer parities):
+        # the pushes of one go out while the collective and the union-sum of the one before are still under way, so an
+        # exchange may take longer than a step without holding the steps back
+        self._xcount = getattr(self, "_xcount", 0) + 1
+        self._stream = self._streams[self._xcount & 1]
         with torch.cuda.stream(self._stream):
             self._stream.wait_event(snap.event)
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if self.record_timings else None

@@ -510,6 +510,8 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
             elif add_residual:
                 d_h = d_h.float() + g_res.float()
             d_h = d_h.view(b, l, d).to(ha_dtype)
+            ev_dh = torch.cuda.Event()
+            ev_dh.record(side)              # the router's hidden-state gradient is added into d_h later
             if split_bwd:
                 side.wait_stream(main)      # dK/dV was issued on the main stream
             if fused is None:
@@ -533,32 +535,46 @@ class _MemoryLayerTwoStream(torch.autograd.Function):
         d_mem = ops.gemm(d_kv2, wkv_t, tag="d_mem")
         want_bank = need[2]
         wire = [] if (ctx.sink is not None and ctx.sink.wire_dtype == torch.bfloat16) else None
-        if fused is None:
-            d_cw, rows = ops.gather_rows_bwd(d_mem, bank, t, r["comb_idx"], r["comb_w"], ctx.norm_row, row_eps,
-                                             stats_m, seg, want_dw=True, want_bank=want_bank, wire_copy=wire)
-        else:
-            d_cw, rows = ops.gather_rows_bwd_prescaled(
-                d_mem, fused["shadow"], t, r["comb_idx"], r["comb_w"],
-                fused["inv_rms"] if ctx.norm_row == "rms" else None, seg, want_dw=kv_dot is None,
-                want_bank=want_bank, wire_copy=wire,
-                wire_only=ctx.sink is not None and getattr(ctx.sink, "wire_only", False))
-            if rows is None and wire:
-                rows = wire[0]          # bf16 rows only: they are the entry
-            if kv_dot is not None:
-                d_cw = kv_dot.sum(dim=2) / r["comb_w"].clamp_min(1e-30)
         d_bank = None
-        if want_bank:
+
+        def emit_bank(rows):
+            nonlocal d_bank
+            if not want_bank:
+                return
             if ctx.sink is not None:
                 ctx.sink.add(seg["uniq"], seg["num_unique"], rows, t, wire=wire[0] if wire else None)
             else:
                 d_bank = torch.zeros(bank.shape, dtype=f32, device=dev)
                 ops.scatter_bank_grad(rows, seg, t, d_bank)
                 d_bank = d_bank.to(bank.dtype)
+
+        if fused is None:
+            d_cw, rows = ops.gather_rows_bwd(d_mem, bank, t, r["comb_idx"], r["comb_w"], ctx.norm_row, row_eps,
+                                             stats_m, seg, want_dw=True, want_bank=want_bank, wire_copy=wire)
+            emit_bank(rows)
+        else:
+            pre = dict(want_bank=want_bank, wire_copy=wire,
+                       wire_only=ctx.sink is not None and getattr(ctx.sink, "wire_only", False))
+            pargs = (d_mem, fused["shadow"], t, r["comb_idx"], r["comb_w"],
+                     fused["inv_rms"] if ctx.norm_row == "rms" else None, seg)
+            if kv_dot is not None:
+                # the chapter-weight gradient came out of the dK/dV epilogue, so nothing downstream reads the bank
+                # gradient: its kernel runs on the side stream, off the path to the router's backward
+                d_cw = kv_dot.sum(dim=2) / r["comb_w"].clamp_min(1e-30)
+                ev_mem = torch.cuda.Event()
+                ev_mem.record(main)
+                with torch.cuda.stream(side):
+                    side.wait_event(ev_mem)
+                    _, rows = ops.gather_rows_bwd_prescaled(*pargs, want_dw=False, **pre)
+                    emit_bank(rows if rows is not None else (wire[0] if wire else None))
+            else:
+                d_cw, rows = ops.gather_rows_bwd_prescaled(*pargs, want_dw=True, **pre)
+                emit_bank(rows if rows is not None else (wire[0] if wire else None))
         if g_cw is not None:
             d_cw = d_cw + g_cw.float()
         fuse_dh = ctx.same_h and need[0] and hr_dtype == ha_dtype
         if fuse_dh:
-            main.wait_stream(side)      # the attention branch's d_h must be complete before the router adds to it
+            main.wait_event(ev_dh)      # the attention branch's d_h must be complete before the router adds to it
         # logit gradient on the main stream; the router-weight gradient (nothing downstream reads it) on the side
         # stream beside the pooled / hidden-state gradient
         rargs = (hr_shape, hr_dtype, router_w, r, top_k, num_shared, routed_scale,
