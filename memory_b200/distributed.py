@@ -53,11 +53,11 @@ def compact_to_union(local_ids: torch.Tensor, local_rows: torch.Tensor, union_id
     return out.view(-1, d)
 
 
-# The exchange proper is a handful of small kernels, copy-engine pushes and one collective that completes only when the
-# slowest rank has entered it: on a low-priority stream each of them waits for an SM slot under the next step's
-# compute, and the wait of the slowest rank becomes everyone's (1.4 ms per exchange at eight GPUs).  It therefore
-# runs at the compute stream's priority; the union-sum, the one large kernel, keeps a low-priority stream of its own.
-_EXCHANGE_PRIORITY = -1
+# Priority of the exchange streams (the compute graph of a data-parallel step is captured on a high-priority stream).
+# Measured at eight GPUs: exchanges at the compute stream's priority, alternating between two streams, with a third
+# set of step buffers, made the step longer (1.71 ms against 1.56) -- two exchanges in flight share the same links and
+# each takes twice as long -- so the exchange keeps one default-priority stream.
+_EXCHANGE_PRIORITY = 0
 
 
 class _PeerPush:
@@ -102,7 +102,7 @@ class _PeerPush:
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
         self.consumed = [None] * parities
         # one stream per peer: the pushes to different peers run on different copy engines / links at once
-        self.push_streams = [torch.cuda.Stream(device, priority=-1) for _ in range(w - 1)]
+        self.push_streams = [torch.cuda.Stream(device, priority=_EXCHANGE_PRIORITY) for _ in range(w - 1)]
 
     def _views(self, flat: torch.Tensor, parity: int):
         base = parity * self.per_parity
@@ -444,11 +444,7 @@ class GradReducer:
             return self._gather_snapshot(snap)
         if getattr(self, "_streams", None) is None:
             self._streams = [torch.cuda.Stream(self.device, priority=_EXCHANGE_PRIORITY) for _ in range(2)]
-        # consecutive exchanges alternate between two streams (as they alternate between the receive-buffer parities):
-        # the pushes of one go out while the collective and the union-sum of the one before are still under way, so an
-        # exchange may take longer than a step without holding the steps back
-        self._xcount = getattr(self, "_xcount", 0) + 1
-        self._stream = self._streams[self._xcount & 1]
+        self._stream = self._streams[0]      # one exchange at a time (see _EXCHANGE_PRIORITY)
         with torch.cuda.stream(self._stream):
             self._stream.wait_event(snap.event)
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if self.record_timings else None
