@@ -234,7 +234,9 @@ class LayerRunner:
         self.bank_shadow = _ops.cast(self.params["bank"].detach(), torch.bfloat16) if fused_gather else None
         self.g_losses = torch.tensor([0.01, 0.0, 0.001, 0.0], device=device)   # load_balance, auxiliary, z, entropy
         self.reducer = None
-        n_slots = 2 if use_graph else 1
+        # sets of captured step buffers: step i waits for the exchange (and union-sum) of step i - n_slots.  From four
+        # GPUs on those two together outlast a step, so a third set pays (eight GPUs: 1.50 ms per step against 1.56)
+        n_slots = max(2, int(os.environ.get("MOC_BENCH_SLOTS", "3" if world >= 4 else "2"))) if use_graph else 1
         if world > 1 and not os.environ.get("MOC_BENCH_NO_REDUCER"):      # (debug: independent replicas, no exchange)
             from memory_b200.distributed import GradReducer
             self.wire_dtype = torch.bfloat16 if wire == "bf16" else torch.float32
@@ -246,7 +248,7 @@ class LayerRunner:
         # With a reduction the step is captured twice and the two graphs are replayed alternately: the
         # gradients of step i stay untouched in their graph's buffers while step i+1 runs in the other graph, so
         # the exchange reads them in place (no staging copy on the compute stream).
-        self.slots = 2 if ((world > 1 or os.environ.get("MOC_BENCH_TWO_SLOTS")) and use_graph) else 1
+        self.slots = n_slots if ((world > 1 or os.environ.get("MOC_BENCH_TWO_SLOTS")) and use_graph) else 1
         # with a bf16 wire the mean gradient comes out of the union-sum over every rank's bf16 rows, this rank's
         # included: the backward then writes no fp32 rows at all
         self.sinks = [M.SparseBankGrad(self.wire_dtype if self.reducer is not None else None,
