@@ -8,6 +8,12 @@ One "step" is one forward+backward pass of one memory layer over one batch of sy
 at the paper shape (B=8 per GPU, L=1024, d=768, 12x64 heads, 4,097 chapters of 64 rows, top-64 routed
 plus one shared chapter, routed scale 2.5, bf16 activations, fp32 router), including router losses,
 projection / router gradients and the gradient of the touched bank rows.  Rank 0 prints one JSON line.
+
+Other modes: ``--kernels`` (the hot kernels alone), ``--token-level`` (the token-level routing variant).  Switches for
+experiments, read from the environment and off by default: MOC_BENCH_SLOTS=n (sets of captured step buffers at N > 1),
+MOC_BENCH_TWO_SLOTS=1 (two sets at N = 1), MOC_BENCH_NO_REDUCER=1 (N > 1 as independent replicas, no exchange),
+MOC_BENCH_FLAT_PRIORITY=1 (compute graph on a default-priority stream), MOC_BENCH_DEBUG=1 (status word after each
+set-up phase), MOC_DQ_ON_SIDE_STREAM=0 (dQ kernel back on the main stream).
 """
 from __future__ import annotations
 

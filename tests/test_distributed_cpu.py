@@ -123,3 +123,13 @@ def test_union_helpers_single_process():
     assert torch.equal(out[3:], rows)
     with pytest.raises(IndexError):
         compact_to_union(torch.tensor([9], dtype=torch.int32), rows[:3], u, 6, 3)
+
+
+def test_reducer_rejects_unknown_options():
+    from memory_b200.distributed import GradReducer
+    for bad in (dict(exchange="rdma"), dict(wire_dtype=torch.float16), dict(merge_dtype=torch.float16),
+                dict(sync="spin")):
+        with pytest.raises(ValueError):
+            GradReducer(8, 4, 16, "cpu", **bad)
+    r = GradReducer(8, 4, 16, "cpu", parities=1)
+    assert r.parities == 2 and r.sync == "collective" and r.merge_dtype == torch.float32
