@@ -134,6 +134,13 @@ def test_token_router_split_weight_projection_on_the_tensor_cores(dev):
     rest = p.clone()
     rest.scatter_(1, gi2, 0.0)
     assert (rest.max(-1).values <= sel[:, -1] * (1 + tau)).all(), "an unselected chapter outranks a selected one"
+    # rows whose top-(k+1) probabilities are more than 64 fp32 ulps apart: there "bit-exact" is meaningful, and the
+    # ids must be the fp64 top-k in order
+    srt, order = torch.sort(p, -1, descending=True)
+    gap = ((srt[:, :k] - srt[:, 1:k + 1]) / srt[:, :k]).min(-1).values
+    clear = gap > 64 * float(np.finfo(np.float32).eps)
+    assert clear.float().mean() > 0.5, "the seed leaves too few gap-checked rows"
+    assert torch.equal(gi2[clear], order[clear][:, :k]), "ids on gap-checked rows must be bit-exact"
     same = (gi.cpu() == idx).all(-1).reshape(-1)
     assert same.float().mean() > 0.999, "ids differ from the fp32 oracle beyond rare ulp-level ties"
     assert rel_err(gw.reshape(-1, k)[same.to(dev)], w.reshape(-1, k)[same]) < 1e-5
