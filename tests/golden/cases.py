@@ -108,5 +108,8 @@ TOKEN_CASES = {
              notes="per-token top-3 of 8 routed chapters of 16 rows plus the shared chapter"),
         Case("token_gqa_rms", 2, 32, 128, 2, 1, 9, 64, 3, norm_type="rms", seed=1251,
              notes="64-row chapters, head_dim 64, grouped KV heads, whole-bank RMS normalisation"),
+        Case("token_multi_tile", 1, 256, 128, 2, 2, 5, 64, 2, seed=1252,
+             notes="256 tokens x top-2 of 4 routed 64-row chapters: chapters with more than 128 (token, slot) pairs, "
+                   "i.e. several tiles per chapter in the tensor-core mixture"),
     ]
 }

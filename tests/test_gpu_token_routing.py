@@ -81,10 +81,11 @@ def test_token_layer_fp32_matches_reference_golden(name, dev):
         assert_close_all_forms(g, torch.from_numpy(gold[k]), FP32_BWD, k)
 
 
-def test_token_layer_bf16_matches_reference_golden(dev):
-    """64-row chapters and head_dim 64: projections and the shared branch on the tensor-core kernels."""
+@pytest.mark.parametrize("name", ["token_gqa_rms", "token_multi_tile"])
+def test_token_layer_bf16_matches_reference_golden(name, dev):
+    """64-row chapters and head_dim 64: projections, the shared branch and the per-token mixture on the tensor-core
+    kernels (``token_multi_tile``: chapters selected by more than 128 (token, slot) pairs)."""
     from memory_b200 import _lib as L
-    name = "token_gqa_rms"
     case, gold = TOKEN_CASES[name], load_gold(name)
     idx, w, losses, out, grads = run_token_layer_gpu(case, torch.bfloat16, dev)
     L.check_device_status(dev)
